@@ -1,0 +1,594 @@
+// C ABI of libfrisk_b200.so: plan creation, kernel choice, TMA descriptor encoding, launches.
+// See include/frisk_b200.h for the contract of every entry point.
+#include "../../include/frisk_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "gemm_simt.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int cuda_fail(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return FRISK_ERR_CUDA;
+}
+#define FRISK_CUDA(call)                                   \
+  do {                                                     \
+    cudaError_t e__ = (call);                              \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call);  \
+  } while (0)
+
+int elem_size(int dt) {
+  switch (dt) {
+    case FRISK_DT_F32: return 4;
+    case FRISK_DT_F16: return 2;
+    case FRISK_DT_BF16: return 2;
+    case FRISK_DT_E4M3: return 1;
+    default: return 0;
+  }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime, so the library links against
+// libcudart only and loads on machines without a driver.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// One GEMM operand as the tcgen05 kernel sees it: `mn` rows of the product dimension, K deep.
+struct OperandView {
+  const void* ptr;
+  int64_t mn, k, ld;  // extents and leading dimension in elements
+  bool mn_major;      // the M/N dimension is contiguous in memory
+};
+
+}  // namespace
+
+struct frisk_gemm_plan {
+  frisk_gemm_desc d;
+  int device = -1;
+  int sm_count = 148;
+  bool have_device = false;
+  frisk_gemm_plan_info info;
+  frisk::GemmParams gp;  // everything but pointers
+  size_t ws_bytes = 0;
+  size_t dyn_smem = 0;
+  // run-time caches
+  CUtensorMap tmap_a, tmap_b;
+  const void* cached_a = nullptr;
+  const void* cached_b = nullptr;
+  const void* clean_ws = nullptr;  // workspace known to hold zeros
+  bool smem_attr_set = false;
+  // device buffers of frisk_b200_gemm_run_host
+  void *hA = nullptr, *hB = nullptr, *hC = nullptr, *hWs = nullptr;
+  float *hSa = nullptr, *hSb = nullptr;
+  int32_t* hStatus = nullptr;
+  cudaStream_t hstream = nullptr;
+};
+
+namespace {
+
+uint64_t make_desc_base(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;  // 128-byte swizzle
+  return d;
+}
+
+// Fills the shared-memory side of one operand for a tile of `tile_mn` rows and 128 bytes of K.
+void fill_operand(frisk::OperandParams& o, bool mn_major, uint32_t tile_mn, uint32_t es,
+                  uint32_t bk_elems) {
+  o.mn_major = mn_major ? 1 : 0;
+  o.stage_bytes = tile_mn * 128u;  // tile_mn x bk_elems elements either way
+  if (mn_major) {
+    // boxes of (128 bytes of M/N) x (bk rows of K); each box is one column of swizzle atoms
+    const uint32_t mn_per_box = 128u / es;
+    o.box_mn = mn_per_box;
+    o.num_boxes = tile_mn / mn_per_box;
+    o.box_bytes = 128u * bk_elems;
+    o.desc_base = make_desc_base(/*LBO: next 128-byte column of M/N*/ o.box_bytes,
+                                 /*SBO: next group of 8 K rows*/ 1024u);
+    o.k_step_bytes = (32u / es) * 128u;  // one UMMA K step = 32 bytes of K = that many rows
+    o.sub_stride_bytes = (128u / mn_per_box) * o.box_bytes;
+  } else {
+    // one box: tile_mn rows x 128 bytes of K (split in two when it exceeds the 256-row box limit)
+    o.num_boxes = tile_mn > 256 ? 2 : 1;
+    o.box_mn = tile_mn / o.num_boxes;
+    o.box_bytes = o.box_mn * 128u;
+    o.desc_base = make_desc_base(/*LBO unused for swizzled K-major*/ 16u,
+                                 /*SBO: next group of 8 rows*/ 1024u);
+    o.k_step_bytes = 32u;
+    o.sub_stride_bytes = 128u * 128u;
+  }
+}
+
+uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t n) {
+  uint32_t fmt = 0;  // kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3
+  if (ab_type == FRISK_DT_BF16) fmt = 1;
+  uint32_t d = 0;
+  d |= 1u << 4;  // fp32 accumulator
+  d |= fmt << 7;
+  d |= fmt << 10;
+  d |= (a_mn_major ? 1u : 0u) << 15;
+  d |= (b_mn_major ? 1u : 0u) << 16;
+  d |= (n >> 3) << 17;
+  d |= (128u >> 4) << 24;
+  return d;
+}
+
+int encode_operand_map(CUtensorMap* map, const OperandView& v, int dtype, uint32_t box_mn,
+                       uint32_t bk_elems) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    g_last_error = "cuTensorMapEncodeTiled not available from the driver";
+    return FRISK_ERR_CUDA;
+  }
+  const uint32_t es = elem_size(dtype);
+  CUtensorMapDataType dt = dtype == FRISK_DT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : dtype == FRISK_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  cuuint64_t dims[2], strides[1];
+  cuuint32_t box[2], estr[2] = {1, 1};
+  if (v.mn_major) {
+    dims[0] = (cuuint64_t)v.mn;
+    dims[1] = (cuuint64_t)v.k;
+    box[0] = box_mn;
+    box[1] = bk_elems;
+  } else {
+    dims[0] = (cuuint64_t)v.k;
+    dims[1] = (cuuint64_t)v.mn;
+    box[0] = bk_elems;
+    box[1] = box_mn;
+  }
+  strides[0] = (cuuint64_t)v.ld * es;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(v.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof buf,
+             "cuTensorMapEncodeTiled failed (%d): dims %llu x %llu, stride %llu, box %u x %u", (int)r,
+             (unsigned long long)dims[0], (unsigned long long)dims[1],
+             (unsigned long long)strides[0], box[0], box[1]);
+    g_last_error = buf;
+    return FRISK_ERR_CUDA;
+  }
+  return FRISK_OK;
+}
+
+uint32_t next_pow2_cols(uint32_t c) {
+  uint32_t v = 32;
+  while (v < c) v <<= 1;
+  return v;
+}
+
+constexpr size_t kMaxDynSmem = 227 * 1024 - 1024;  // leave room for the static barriers
+
+bool tcgen05_eligible(const frisk_gemm_desc& d) {
+  if (d.a_type != FRISK_DT_F16 && d.a_type != FRISK_DT_BF16 && d.a_type != FRISK_DT_E4M3)
+    return false;
+  const int es = elem_size(d.a_type);
+  if ((d.lda * es) % 16 || (d.ldb * es) % 16) return false;
+  if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31)) return false;
+  // 8-bit operands are taken K-major only (A row-major, B column-major)
+  if (d.a_type == FRISK_DT_E4M3 && (d.transA || !d.transB)) return false;
+  return true;
+}
+
+void plan_tcgen05(frisk_gemm_plan* pl, bool swap) {
+  const frisk_gemm_desc& d = pl->d;
+  frisk::GemmParams& g = pl->gp;
+  memset(&g, 0, sizeof g);
+  const uint32_t es = elem_size(d.a_type);
+  const uint32_t bk = 128u / es;
+  bool a_mn, b_mn;  // majors of the kernel's a-role / b-role operands
+  int64_t rows, cols;
+  if (!swap) {
+    a_mn = d.transA != 0;  // A stored K x M
+    b_mn = d.transB == 0;  // B stored K x N
+    rows = d.M;
+    cols = d.N;
+    g.mi = 1;
+    uint32_t tn = d.tile_n ? (uint32_t)d.tile_n : (cols > 128 ? 256u : (cols > 64 ? 128u : 64u));
+    g.tile_n = tn;
+  } else {
+    // D = C^T: rows run over N (the weights), columns over M (the few activations rows)
+    a_mn = d.transB == 0;  // B stored K x N: N contiguous
+    b_mn = false;          // A stored M x K (transA == 0 is a precondition of this plan)
+    rows = d.N;
+    cols = d.M;
+    g.mi = rows > 128 ? 2 : 1;
+    g.tile_n = (uint32_t)((cols + 15) / 16 * 16);
+  }
+  g.bk_elems = bk;
+  g.k_steps = 4;
+  fill_operand(g.a, a_mn, 128u * g.mi, es, bk);
+  fill_operand(g.b, b_mn, g.tile_n, es, bk);
+  g.stage_bytes = g.a.stage_bytes + g.b.stage_bytes;
+  uint32_t stages = (uint32_t)(kMaxDynSmem / g.stage_bytes);
+  stages = std::min<uint32_t>(stages, frisk::kMaxStages);
+  if (d.stages > 0) stages = std::min<uint32_t>(stages, (uint32_t)d.stages);
+  g.stages = std::max<uint32_t>(stages, 1);
+  g.acc_bufs = (2 * g.mi * g.tile_n <= 512) ? 2 : 1;
+  g.tmem_cols = next_pow2_cols(g.acc_bufs * g.mi * g.tile_n);
+  g.idesc = make_idesc(d.a_type, a_mn, b_mn, g.tile_n);
+  g.kind_f8 = d.a_type == FRISK_DT_E4M3;
+  g.rows = (uint32_t)rows;
+  g.cols = (uint32_t)cols;
+  g.tiles_r = (uint32_t)((rows + 128 * g.mi - 1) / (128 * g.mi));
+  g.tiles_c = (uint32_t)((cols + g.tile_n - 1) / g.tile_n);
+  g.num_kb = (uint32_t)((d.K + bk - 1) / bk);
+  g.group_r = 16;
+  g.split_mode = swap ? 1 : 0;
+  g.transposed_out = swap ? 1 : 0;
+  g.clear_accum = d.clear_accum ? 1 : 0;
+  g.c_type = d.c_type;
+  g.ldc = d.ldc;
+  g.ws_ld = d.N;
+
+  const uint64_t tiles = (uint64_t)g.tiles_r * g.tiles_c;
+  const uint64_t units = swap ? tiles * g.num_kb : tiles;
+  uint32_t ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)pl->sm_count);
+  if (d.num_ctas > 0) ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)d.num_ctas);
+  pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024;
+  pl->ws_bytes = swap ? (size_t)d.M * d.N * sizeof(float) : 0;
+
+  frisk_gemm_plan_info& in = pl->info;
+  in.kernel = swap ? FRISK_KERNEL_SKINNY : FRISK_KERNEL_TCGEN05;
+  in.tile_m = swap ? (int)g.tile_n : 128 * (int)g.mi;
+  in.tile_n = swap ? 128 * (int)g.mi : (int)g.tile_n;
+  in.tile_k = (int)bk;
+  in.stages = (int)g.stages;
+  in.num_ctas = (int)ctas;
+  in.swap_ab = swap;
+  in.split_k = swap;
+  in.smem_bytes = (int)pl->dyn_smem;
+  in.launches = swap ? 2 : 1;
+  in.swizzle_a = in.swizzle_b = 128;
+}
+
+template <typename TC>
+int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
+  auto kern = frisk::gemm_tcgen05_kernel<TC>;
+  if (!pl->smem_attr_set) {
+    FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)pl->dyn_smem));
+    pl->smem_attr_set = true;
+  }
+  kern<<<pl->info.num_ctas, frisk::kGemmThreads, pl->dyn_smem, st>>>(pl->tmap_a, pl->tmap_b, g);
+  FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
+template <typename TC>
+int launch_finalize_t(const frisk_gemm_plan* pl, float* ws, void* C, const float* sa,
+                      const float* sb, cudaStream_t st) {
+  const frisk_gemm_desc& d = pl->d;
+  const int64_t work = d.M * ((d.N + 3) / 4);
+  const int threads = 256;
+  const int blocks = (int)std::min<int64_t>((work + threads - 1) / threads, 4 * (int64_t)pl->sm_count);
+  frisk::splitk_finalize_kernel<TC><<<blocks, threads, 0, st>>>(
+      ws, d.N, reinterpret_cast<TC*>(C), d.ldc, d.M, d.N, sa, sb, d.clear_accum);
+  FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
+template <typename TIn>
+int launch_simt_in(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaStream_t st) {
+  dim3 grid((unsigned)((d.N + frisk::kSimtTile - 1) / frisk::kSimtTile),
+            (unsigned)((d.M + frisk::kSimtTile - 1) / frisk::kSimtTile));
+  switch (d.c_type) {
+    case FRISK_DT_F32: frisk::gemm_simt_kernel<TIn, float><<<grid, 256, 0, st>>>(sp); break;
+    case FRISK_DT_F16: frisk::gemm_simt_kernel<TIn, __half><<<grid, 256, 0, st>>>(sp); break;
+    case FRISK_DT_BF16: frisk::gemm_simt_kernel<TIn, __nv_bfloat16><<<grid, 256, 0, st>>>(sp); break;
+    default: return FRISK_ERR_UNSUPPORTED;
+  }
+  FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
+int launch_simt(const frisk_gemm_desc& d, const void* A, const void* B, void* C, const float* sa,
+                const float* sb, cudaStream_t st) {
+  if ((d.M + frisk::kSimtTile - 1) / frisk::kSimtTile > 65535) return FRISK_ERR_UNSUPPORTED;
+  frisk::SimtParams sp;
+  sp.A = A; sp.B = B; sp.C = C;
+  sp.scale_a = d.scale_mode ? sa : nullptr;
+  sp.scale_b = d.scale_mode ? sb : nullptr;
+  sp.M = d.M; sp.N = d.N; sp.K = d.K;
+  sp.lda = d.lda; sp.ldb = d.ldb; sp.ldc = d.ldc;
+  sp.transA = d.transA; sp.transB = d.transB; sp.clear_accum = d.clear_accum;
+  switch (d.a_type) {
+    case FRISK_DT_F32: return launch_simt_in<float>(d, sp, st);
+    case FRISK_DT_F16: return launch_simt_in<__half>(d, sp, st);
+    case FRISK_DT_BF16: return launch_simt_in<__nv_bfloat16>(d, sp, st);
+    case FRISK_DT_E4M3: return launch_simt_in<frisk::e4m3_t>(d, sp, st);
+    default: return FRISK_ERR_UNSUPPORTED;
+  }
+}
+
+size_t a_bytes(const frisk_gemm_desc& d) {
+  return (size_t)(d.transA ? d.K : d.M) * d.lda * elem_size(d.a_type);
+}
+size_t b_bytes(const frisk_gemm_desc& d) {
+  return (size_t)(d.transB ? d.N : d.K) * d.ldb * elem_size(d.b_type);
+}
+size_t c_bytes(const frisk_gemm_desc& d) { return (size_t)d.M * d.ldc * elem_size(d.c_type); }
+
+}  // namespace
+
+extern "C" {
+
+int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** out) {
+  if (!desc || !out) return FRISK_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  frisk_gemm_desc d = *desc;
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return FRISK_ERR_INVALID_ARGUMENT;
+  if (!elem_size(d.a_type) || !elem_size(d.b_type) || !elem_size(d.c_type))
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.c_type == FRISK_DT_E4M3) return FRISK_ERR_UNSUPPORTED;
+  if (d.a_type != d.b_type) return FRISK_ERR_INVALID_ARGUMENT;  // ffi/ir.cpp:357-359
+  if (d.scale_mode != FRISK_SCALE_NONE && d.scale_mode != FRISK_SCALE_ROW_COL)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  d.transA = d.transA != 0;
+  d.transB = d.transB != 0;
+  if (d.lda == 0) d.lda = d.transA ? d.M : d.K;
+  if (d.ldb == 0) d.ldb = d.transB ? d.K : d.N;
+  if (d.ldc == 0) d.ldc = d.N;
+  if (d.lda < (d.transA ? d.M : d.K) || d.ldb < (d.transB ? d.K : d.N) || d.ldc < d.N)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.tile_n != 0 && d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.force_kernel < 0 || d.force_kernel > 3 || d.stages < 0 || d.num_ctas < 0)
+    return FRISK_ERR_INVALID_ARGUMENT;
+
+  frisk_gemm_plan* pl = new (std::nothrow) frisk_gemm_plan();
+  if (!pl) return FRISK_ERR_INVALID_ARGUMENT;
+  pl->d = d;
+  memset(&pl->info, 0, sizeof pl->info);
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) == cudaSuccess) {
+      pl->device = dev;
+      pl->sm_count = prop.multiProcessorCount;
+      pl->have_device = prop.major == 10;
+    }
+  } else {
+    cudaGetLastError();  // plans can be made (and inspected) on a machine without a GPU
+  }
+
+  const bool tc_ok = tcgen05_eligible(d);
+  const bool skinny_ok = tc_ok && d.M <= 64 && d.N >= 256 && !d.transA;
+  int kind;
+  if (d.force_kernel) {
+    kind = d.force_kernel - 1;
+    if ((kind == FRISK_KERNEL_TCGEN05 && !tc_ok) || (kind == FRISK_KERNEL_SKINNY && !skinny_ok)) {
+      delete pl;
+      return tc_ok ? FRISK_ERR_UNSUPPORTED : FRISK_ERR_MISALIGNED;
+    }
+  } else {
+    kind = skinny_ok ? FRISK_KERNEL_SKINNY : (tc_ok ? FRISK_KERNEL_TCGEN05 : FRISK_KERNEL_SIMT);
+  }
+  if (kind == FRISK_KERNEL_SIMT) {
+    pl->info.kernel = FRISK_KERNEL_SIMT;
+    pl->info.tile_m = pl->info.tile_n = frisk::kSimtTile;
+    pl->info.tile_k = frisk::kSimtBK;
+    pl->info.stages = 1;
+    pl->info.num_ctas = (int)(((d.M + 63) / 64) * ((d.N + 63) / 64));
+    pl->info.launches = 1;
+  } else {
+    plan_tcgen05(pl, kind == FRISK_KERNEL_SKINNY);
+  }
+  *out = pl;
+  return FRISK_OK;
+}
+
+void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* pl) {
+  if (!pl) return;
+  cudaFree(pl->hA); cudaFree(pl->hB); cudaFree(pl->hC); cudaFree(pl->hWs);
+  cudaFree(pl->hSa); cudaFree(pl->hSb); cudaFree(pl->hStatus);
+  if (pl->hstream) cudaStreamDestroy(pl->hstream);
+  cudaGetLastError();
+  delete pl;
+}
+
+int frisk_b200_gemm_plan_info(const frisk_gemm_plan* pl, frisk_gemm_plan_info* out) {
+  if (!pl || !out) return FRISK_ERR_INVALID_ARGUMENT;
+  *out = pl->info;
+  return FRISK_OK;
+}
+
+int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* pl, size_t* out) {
+  if (!pl || !out) return FRISK_ERR_INVALID_ARGUMENT;
+  *out = pl->ws_bytes;
+  return FRISK_OK;
+}
+
+int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
+                        const float* scale_a, const float* scale_b, void* workspace,
+                        size_t workspace_bytes, int32_t* device_status, void* stream) {
+  if (!pl || !A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
+  const frisk_gemm_desc& d = pl->d;
+  if (d.scale_mode == FRISK_SCALE_ROW_COL && (!scale_a || !scale_b))
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (!pl->have_device) return FRISK_ERR_NO_DEVICE;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const float* sa = d.scale_mode ? scale_a : nullptr;
+  const float* sb = d.scale_mode ? scale_b : nullptr;
+
+  const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
+  if (pl->info.kernel == FRISK_KERNEL_SIMT || !ptr_aligned)
+    return launch_simt(d, A, B, C, sa, sb, st);  // the CUDA-core kernel has no alignment rule
+
+  const bool swap = pl->info.kernel == FRISK_KERNEL_SKINNY;
+  if (swap) {
+    if (!workspace || workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
+    if ((uintptr_t)workspace % 16) return FRISK_ERR_MISALIGNED;
+  }
+  frisk::GemmParams g = pl->gp;
+  if (A != pl->cached_a || B != pl->cached_b) {
+    OperandView va{A, d.M, d.K, d.lda, d.transA != 0};
+    OperandView vb{B, d.N, d.K, d.ldb, d.transB == 0};
+    const OperandView& ra = swap ? vb : va;  // a-role: the 128-row operand
+    const OperandView& rb = swap ? va : vb;
+    int rc = encode_operand_map(&pl->tmap_a, ra, d.a_type, g.a.box_mn, g.bk_elems);
+    if (rc) return rc;
+    rc = encode_operand_map(&pl->tmap_b, rb, d.a_type, g.b.box_mn, g.bk_elems);
+    if (rc) return rc;
+    pl->cached_a = A;
+    pl->cached_b = B;
+  }
+  g.C = C;
+  g.status = device_status;
+  g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
+  if (swap) {
+    g.ws = reinterpret_cast<float*>(workspace);
+    g.row_scale = nullptr;  // applied by the finalize kernel
+    g.col_scale = nullptr;
+    if (pl->clean_ws != workspace) {
+      FRISK_CUDA(cudaMemsetAsync(workspace, 0, pl->ws_bytes, st));
+      pl->clean_ws = workspace;
+    }
+  } else {
+    g.row_scale = sa;
+    g.col_scale = sb;
+  }
+  int rc;
+  switch (d.c_type) {
+    case FRISK_DT_F32: rc = launch_tcgen05_t<float>(pl, g, st); break;
+    case FRISK_DT_F16: rc = launch_tcgen05_t<__half>(pl, g, st); break;
+    case FRISK_DT_BF16: rc = launch_tcgen05_t<__nv_bfloat16>(pl, g, st); break;
+    default: rc = FRISK_ERR_UNSUPPORTED;
+  }
+  if (rc) { pl->clean_ws = nullptr; return rc; }
+  if (swap) {
+    switch (d.c_type) {
+      case FRISK_DT_F32: rc = launch_finalize_t<float>(pl, g.ws, C, sa, sb, st); break;
+      case FRISK_DT_F16: rc = launch_finalize_t<__half>(pl, g.ws, C, sa, sb, st); break;
+      case FRISK_DT_BF16: rc = launch_finalize_t<__nv_bfloat16>(pl, g.ws, C, sa, sb, st); break;
+      default: rc = FRISK_ERR_UNSUPPORTED;
+    }
+    if (rc) pl->clean_ws = nullptr;
+  }
+  return rc;
+}
+
+int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
+                             const float* scale_a, const float* scale_b) {
+  if (!pl || !A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
+  if (!pl->have_device) return FRISK_ERR_NO_DEVICE;
+  const frisk_gemm_desc& d = pl->d;
+  if (d.scale_mode == FRISK_SCALE_ROW_COL && (!scale_a || !scale_b))
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (!pl->hA) {
+    FRISK_CUDA(cudaStreamCreateWithFlags(&pl->hstream, cudaStreamNonBlocking));
+    FRISK_CUDA(cudaMalloc(&pl->hA, a_bytes(d)));
+    FRISK_CUDA(cudaMalloc(&pl->hB, b_bytes(d)));
+    FRISK_CUDA(cudaMalloc(&pl->hC, c_bytes(d)));
+    FRISK_CUDA(cudaMalloc(&pl->hStatus, sizeof(int32_t)));
+    if (pl->ws_bytes) FRISK_CUDA(cudaMalloc(&pl->hWs, pl->ws_bytes));
+    if (d.scale_mode) {
+      FRISK_CUDA(cudaMalloc(&pl->hSa, d.M * sizeof(float)));
+      FRISK_CUDA(cudaMalloc(&pl->hSb, d.N * sizeof(float)));
+    }
+  }
+  cudaStream_t st = pl->hstream;
+  FRISK_CUDA(cudaMemsetAsync(pl->hStatus, 0, sizeof(int32_t), st));
+  FRISK_CUDA(cudaMemcpyAsync(pl->hA, A, a_bytes(d), cudaMemcpyHostToDevice, st));
+  FRISK_CUDA(cudaMemcpyAsync(pl->hB, B, b_bytes(d), cudaMemcpyHostToDevice, st));
+  if (!d.clear_accum)
+    FRISK_CUDA(cudaMemcpyAsync(pl->hC, C, c_bytes(d), cudaMemcpyHostToDevice, st));
+  if (d.scale_mode) {
+    FRISK_CUDA(cudaMemcpyAsync(pl->hSa, scale_a, d.M * sizeof(float), cudaMemcpyHostToDevice, st));
+    FRISK_CUDA(cudaMemcpyAsync(pl->hSb, scale_b, d.N * sizeof(float), cudaMemcpyHostToDevice, st));
+  }
+  int rc = frisk_b200_gemm_run(pl, pl->hA, pl->hB, pl->hC, pl->hSa, pl->hSb, pl->hWs, pl->ws_bytes,
+                               pl->hStatus, st);
+  if (rc) return rc;
+  FRISK_CUDA(cudaMemcpyAsync(C, pl->hC, c_bytes(d), cudaMemcpyDeviceToHost, st));
+  return frisk_b200_check_status(pl->hStatus, st);
+}
+
+int frisk_b200_check_status(const int32_t* device_status, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int32_t h = 0;
+  if (device_status)
+    FRISK_CUDA(cudaMemcpyAsync(&h, device_status, sizeof h, cudaMemcpyDeviceToHost, st));
+  FRISK_CUDA(cudaStreamSynchronize(st));
+  if (h != 0) {
+    char buf[64];
+    snprintf(buf, sizeof buf, "device status word 0x%x", (unsigned)h);
+    g_last_error = buf;
+    return FRISK_ERR_DEVICE_TIMEOUT;
+  }
+  return FRISK_OK;
+}
+
+const char* frisk_b200_strerror(int code) {
+  switch (code) {
+    case FRISK_OK: return "ok";
+    case FRISK_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case FRISK_ERR_UNSUPPORTED: return "unsupported dtype or layout";
+    case FRISK_ERR_MISALIGNED: return "pointer or leading dimension is not 16-byte aligned";
+    case FRISK_ERR_WORKSPACE: return "workspace missing or too small";
+    case FRISK_ERR_CUDA: return "CUDA call failed";
+    case FRISK_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    case FRISK_ERR_NO_DEVICE: return "no sm_100 device";
+    case FRISK_ERR_SHARD: return "invalid rank or rank count";
+    case FRISK_ERR_TOO_LARGE: return "problem exceeds the capacity of this entry point";
+    default: return "unknown error";
+  }
+}
+
+const char* frisk_b200_last_error(void) { return g_last_error.c_str(); }
+
+int frisk_b200_shard_rows(int64_t M, int nranks, int rank, int64_t* row0, int64_t* rows) {
+  if (!row0 || !rows || M < 0) return FRISK_ERR_INVALID_ARGUMENT;
+  if (nranks <= 0 || rank < 0 || rank >= nranks) return FRISK_ERR_SHARD;
+  const int64_t base = M / nranks, extra = M % nranks;
+  *rows = base + (rank < extra ? 1 : 0);
+  *row0 = rank * base + std::min<int64_t>(rank, extra);
+  return FRISK_OK;
+}
+
+int frisk_b200_device_sm_count(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return FRISK_ERR_NO_DEVICE;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return FRISK_ERR_CUDA;
+  }
+  return n;
+}
+
+const char* frisk_b200_version(void) { return "frisk_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

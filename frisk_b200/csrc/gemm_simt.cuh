@@ -1,0 +1,111 @@
+// CUDA-core GEMM: fp32 FMA on exactly decoded inputs.  Serves the fp32 configuration (single-pass
+// TF32 tensor-core math cannot hold a 1e-4 relative Frobenius error at K = 512) and every shape or
+// layout the TMA path cannot take (leading dimensions that are not 16-byte multiples, ...).
+// 64 x 64 output tile per CTA, 256 threads, 4 x 4 outputs per thread, 16-deep K slices staged in
+// shared memory as fp32.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+#include "gemm_tcgen05.cuh"  // cast_in / cast_out
+
+namespace frisk {
+
+struct SimtParams {
+  const void* A;
+  const void* B;
+  void* C;
+  const float* scale_a;  // [M] or nullptr
+  const float* scale_b;  // [N] or nullptr
+  int64_t M, N, K;
+  int64_t lda, ldb, ldc;
+  int32_t transA, transB, clear_accum;
+};
+
+struct e4m3_t {
+  uint8_t bits;
+};
+template <>
+__device__ __forceinline__ float cast_in<e4m3_t>(e4m3_t v) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(v.bits, __NV_E4M3)));
+}
+
+constexpr int kSimtTile = 64;
+constexpr int kSimtBK = 16;
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const SimtParams p) {
+  __shared__ float As[kSimtBK][kSimtTile + 4];  // [k][m]
+  __shared__ float Bs[kSimtBK][kSimtTile + 4];  // [k][n]
+  const TIn* A = reinterpret_cast<const TIn*>(p.A);
+  const TIn* B = reinterpret_cast<const TIn*>(p.B);
+  TOut* C = reinterpret_cast<TOut*>(p.C);
+  const int64_t m0 = (int64_t)blockIdx.y * kSimtTile;
+  const int64_t n0 = (int64_t)blockIdx.x * kSimtTile;
+  const int tx = threadIdx.x & 15;  // column group
+  const int ty = threadIdx.x >> 4;  // row group
+
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int64_t k0 = 0; k0 < p.K; k0 += kSimtBK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = threadIdx.x + e * 256;
+      // walk the contiguous global dimension with consecutive threads
+      int am, ak, bn, bk;
+      if (p.transA) { am = idx & 63; ak = idx >> 6; } else { ak = idx & 15; am = idx >> 4; }
+      if (p.transB) { bk = idx & 15; bn = idx >> 4; } else { bn = idx & 63; bk = idx >> 6; }
+      float av = 0.f, bv = 0.f;
+      if (m0 + am < p.M && k0 + ak < p.K) {
+        const int64_t off = p.transA ? (k0 + ak) * p.lda + (m0 + am) : (m0 + am) * p.lda + (k0 + ak);
+        av = cast_in<TIn>(A[off]);
+      }
+      if (n0 + bn < p.N && k0 + bk < p.K) {
+        const int64_t off = p.transB ? (n0 + bn) * p.ldb + (k0 + bk) : (k0 + bk) * p.ldb + (n0 + bn);
+        bv = cast_in<TIn>(B[off]);
+      }
+      As[ak][am] = av;
+      Bs[bk][bn] = bv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kSimtBK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= p.M) continue;
+    const float sa = p.scale_a ? p.scale_a[m] : 1.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t n = n0 + tx * 4 + j;
+      if (n >= p.N) continue;
+      float v = acc[i][j] * sa;
+      if (p.scale_b) v *= p.scale_b[n];
+      TOut* dst = C + m * p.ldc + n;
+      if (!p.clear_accum) v += cast_in<TOut>(*dst);
+      *dst = cast_out<TOut>(v);
+    }
+  }
+}
+
+}  // namespace frisk

@@ -1,0 +1,269 @@
+"""ctypes binding of libfrisk_b200.so -- the execution side of ``frisk.gemm``.
+
+The reference's Python surface can only build and print IR (its ``create_gemm_op`` is at
+ffi/ir.cpp:322-366; nothing below it executes).  This module is the part a user calls to run the
+op: ``plan`` turns a GEMM description (or a ``frisk.gemm`` op found in a module) into a
+``GemmPlan``; ``GemmPlan.run`` launches it on device pointers, ``GemmPlan.run_host`` on numpy
+arrays.  There is no CPU fallback: when the shared library is missing every entry point raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import numpy as np
+
+from . import workloads as W
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfrisk_b200.so")
+
+KERNEL_NAMES = {0: "simt", 1: "tcgen05", 2: "skinny"}
+
+
+class FriskError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = code
+        super().__init__(what)
+
+
+class GemmDesc(C.Structure):
+    _fields_ = [
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
+        ("a_type", C.c_int32), ("b_type", C.c_int32), ("c_type", C.c_int32),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+        ("transA", C.c_int32), ("transB", C.c_int32),
+        ("clear_accum", C.c_int32), ("scale_mode", C.c_int32),
+        ("force_kernel", C.c_int32), ("tile_n", C.c_int32), ("stages", C.c_int32),
+        ("num_ctas", C.c_int32),
+    ]
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [
+        ("kernel", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
+        ("stages", C.c_int32), ("num_ctas", C.c_int32), ("swap_ab", C.c_int32),
+        ("split_k", C.c_int32), ("smem_bytes", C.c_int32), ("launches", C.c_int32),
+        ("swizzle_a", C.c_int32), ("swizzle_b", C.c_int32),
+    ]
+
+    def as_dict(self) -> dict:
+        d = {n: int(getattr(self, n)) for n, _ in self._fields_}
+        d["kernel_name"] = KERNEL_NAMES.get(d["kernel"], "?")
+        return d
+
+
+class LayoutDesc(C.Structure):
+    _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("elem_bits", C.c_int32),
+                ("k_inner", C.c_int32)]
+
+
+class TmaParams(C.Structure):
+    _fields_ = [
+        ("swizzle_bytes", C.c_int32), ("box_inner", C.c_int32), ("box_outer", C.c_int32),
+        ("num_boxes", C.c_int32), ("umma_layout_type", C.c_int32), ("umma_major", C.c_int32),
+        ("leading_byte_offset", C.c_int32), ("stride_byte_offset", C.c_int32),
+        ("k_step_bytes", C.c_int32), ("reference_layout", C.c_char * 24),
+    ]
+
+    def as_dict(self) -> dict:
+        d = {n: getattr(self, n) for n, _ in self._fields_}
+        d["reference_layout"] = d["reference_layout"].decode()
+        return d
+
+
+class BankStats(C.Structure):
+    _fields_ = [("avg_max_conflict", C.c_double), ("max_conflict", C.c_int32),
+                ("samples", C.c_int32)]
+
+
+SWIZZLE_128B_ATOM_32B = 1032
+SWIZZLE_128B_ATOM_64B = 1064
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads libfrisk_b200.so (built in-tree by ``python -m frisk_b200.build``)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FriskError(-5, f"{LIB_PATH} is missing: build it with `python -m frisk_b200.build` "
+                             "(there is no fallback path)")
+    L = C.CDLL(LIB_PATH)
+    vp, i32p = C.c_void_p, C.POINTER(C.c_int32)
+    L.frisk_b200_gemm_plan_create.argtypes = [C.POINTER(GemmDesc), C.POINTER(vp)]
+    L.frisk_b200_gemm_plan_create.restype = C.c_int
+    L.frisk_b200_gemm_plan_destroy.argtypes = [vp]
+    L.frisk_b200_gemm_plan_destroy.restype = None
+    L.frisk_b200_gemm_plan_info.argtypes = [vp, C.POINTER(PlanInfo)]
+    L.frisk_b200_gemm_plan_info.restype = C.c_int
+    L.frisk_b200_gemm_workspace_bytes.argtypes = [vp, C.POINTER(C.c_size_t)]
+    L.frisk_b200_gemm_workspace_bytes.restype = C.c_int
+    L.frisk_b200_gemm_run.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp, vp]
+    L.frisk_b200_gemm_run.restype = C.c_int
+    L.frisk_b200_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp]
+    L.frisk_b200_gemm_run_host.restype = C.c_int
+    L.frisk_b200_check_status.argtypes = [vp, vp]
+    L.frisk_b200_check_status.restype = C.c_int
+    L.frisk_b200_strerror.argtypes = [C.c_int]
+    L.frisk_b200_strerror.restype = C.c_char_p
+    L.frisk_b200_last_error.argtypes = []
+    L.frisk_b200_last_error.restype = C.c_char_p
+    L.frisk_b200_shard_rows.argtypes = [C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int64),
+                                        C.POINTER(C.c_int64)]
+    L.frisk_b200_shard_rows.restype = C.c_int
+    L.frisk_b200_layout_to_tma.argtypes = [C.POINTER(LayoutDesc), C.POINTER(TmaParams)]
+    L.frisk_b200_layout_to_tma.restype = C.c_int
+    L.frisk_b200_swizzled_offset.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
+                                             C.c_int32]
+    L.frisk_b200_swizzled_offset.restype = C.c_int64
+    L.frisk_b200_bank_conflicts.argtypes = [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                            C.c_int32, C.POINTER(BankStats)]
+    L.frisk_b200_bank_conflicts.restype = C.c_int
+    L.frisk_b200_device_sm_count.argtypes = []
+    L.frisk_b200_device_sm_count.restype = C.c_int
+    L.frisk_b200_version.argtypes = []
+    L.frisk_b200_version.restype = C.c_char_p
+    _lib = L
+    return L
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        L = lib()
+        msg = L.frisk_b200_strerror(rc).decode()
+        detail = L.frisk_b200_last_error().decode()
+        raise FriskError(rc, f"{what}: {msg}" + (f" ({detail})" if detail and rc in (-5, -6) else ""))
+
+
+def _ptr(x) -> Optional[int]:
+    """Device or host address of a torch tensor / numpy array / int / None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    raise TypeError(f"cannot take the address of {type(x)}")
+
+
+class GemmPlan:
+    """A planned ``frisk.gemm``.  See include/frisk_b200.h for the operand convention."""
+
+    def __init__(self, M: int, N: int, K: int, ab_type: int, c_type: Optional[int] = None, *,
+                 transA: bool = False, transB: bool = False, clear_accum: bool = True,
+                 scales: bool = False, lda: int = 0, ldb: int = 0, ldc: int = 0,
+                 force_kernel: Optional[str] = None, tile_n: int = 0, stages: int = 0,
+                 num_ctas: int = 0):
+        L = lib()
+        d = GemmDesc()
+        d.M, d.N, d.K = M, N, K
+        d.a_type = d.b_type = ab_type
+        d.c_type = ab_type if c_type is None else c_type
+        d.lda, d.ldb, d.ldc = lda, ldb, ldc
+        d.transA, d.transB = int(transA), int(transB)
+        d.clear_accum = int(clear_accum)
+        d.scale_mode = 1 if scales else 0
+        d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2}[force_kernel]
+        d.tile_n, d.stages, d.num_ctas = tile_n, stages, num_ctas
+        self.desc = d
+        self._h = C.c_void_p()
+        _check(L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(self._h)), "plan_create")
+        info = PlanInfo()
+        _check(L.frisk_b200_gemm_plan_info(self._h, C.byref(info)), "plan_info")
+        self.info = info.as_dict()
+        ws = C.c_size_t()
+        _check(L.frisk_b200_gemm_workspace_bytes(self._h, C.byref(ws)), "workspace_bytes")
+        self.workspace_bytes = int(ws.value)
+
+    @classmethod
+    def for_workload(cls, w: W.GemmWorkload, **kw) -> "GemmPlan":
+        return cls(w.M, w.N, w.K, w.ab_type, w.c_type, transA=w.transA, transB=w.transB,
+                   clear_accum=w.clear_accum, scales=w.scale_a is not None, **kw)
+
+    def close(self) -> None:
+        if self._h:
+            lib().frisk_b200_gemm_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def run(self, A, B, Cout, scale_a=None, scale_b=None, workspace=None, status=None,
+            stream: int = 0) -> None:
+        """Asynchronous launch on device buffers (torch CUDA tensors or raw addresses)."""
+        ws_bytes = 0
+        if workspace is not None:
+            ws_bytes = workspace.numel() * workspace.element_size() if hasattr(workspace, "numel") \
+                else self.workspace_bytes
+        rc = lib().frisk_b200_gemm_run(self._h, _ptr(A), _ptr(B), _ptr(Cout), _ptr(scale_a),
+                                       _ptr(scale_b), _ptr(workspace), ws_bytes, _ptr(status),
+                                       stream or None)
+        _check(rc, "gemm_run")
+
+    def run_host(self, A: np.ndarray, B: np.ndarray, Cout: np.ndarray,
+                 scale_a: Optional[np.ndarray] = None, scale_b: Optional[np.ndarray] = None) -> None:
+        """Synchronous GEMM on host arrays (copies in, runs, copies C back)."""
+        rc = lib().frisk_b200_gemm_run_host(self._h, _ptr(A), _ptr(B), _ptr(Cout), _ptr(scale_a),
+                                            _ptr(scale_b))
+        _check(rc, "gemm_run_host")
+
+
+def check_status(status, stream: int = 0) -> None:
+    _check(lib().frisk_b200_check_status(_ptr(status), stream or None), "device status")
+
+
+def gemm_host(w: W.GemmWorkload, **plan_kw) -> np.ndarray:
+    """Runs a workload from host buffers and returns C as raw storage bits."""
+    plan = GemmPlan.for_workload(w, **plan_kw)
+    out = np.zeros((w.M, w.N), dtype=W.storage_numpy_dtype(w.c_type))
+    if not w.clear_accum and w.C0 is not None:
+        out[...] = w.C0
+    try:
+        plan.run_host(np.ascontiguousarray(w.A), np.ascontiguousarray(w.B), out, w.scale_a, w.scale_b)
+    finally:
+        plan.close()
+    return out
+
+
+def shard_rows(M: int, nranks: int, rank: int) -> tuple[int, int]:
+    """Rows [row0, row0 + rows) of A and C that `rank` owns when C = A*B is split by rows."""
+    r0, n = C.c_int64(), C.c_int64()
+    _check(lib().frisk_b200_shard_rows(M, nranks, rank, C.byref(r0), C.byref(n)), "shard_rows")
+    return int(r0.value), int(n.value)
+
+
+def layout_to_tma(rows: int, cols: int, elem_bits: int, k_inner: bool) -> dict:
+    ld = LayoutDesc(rows, cols, elem_bits, int(k_inner))
+    out = TmaParams()
+    _check(lib().frisk_b200_layout_to_tma(C.byref(ld), C.byref(out)), "layout_to_tma")
+    return out.as_dict()
+
+
+def swizzled_offset(row: int, col: int, rows: int, cols: int, elem_bits: int, mode: int) -> int:
+    return int(lib().frisk_b200_swizzled_offset(row, col, rows, cols, elem_bits, mode))
+
+
+def bank_conflicts(rows: int, cols: int, elem_bits: int, mode: int, lane_vector: int,
+                   distinct_words_only: bool = False) -> dict:
+    st = BankStats()
+    _check(lib().frisk_b200_bank_conflicts(rows, cols, elem_bits, mode, lane_vector,
+                                           int(distinct_words_only), C.byref(st)), "bank_conflicts")
+    return {"avg_max_conflict": st.avg_max_conflict, "max_conflict": st.max_conflict,
+            "samples": st.samples}
+
+
+def device_sm_count() -> int:
+    return int(lib().frisk_b200_device_sm_count())
+
+
+def version() -> str:
+    return lib().frisk_b200_version().decode()

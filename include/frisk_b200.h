@@ -1,0 +1,214 @@
+/*
+ * frisk_b200.h -- C ABI of libfrisk_b200.so, the execution back end for `frisk.gemm`.
+ *
+ * The reference (Xiebaokang/frisk) can build a `frisk.gemm` op but has no way to run it:
+ * there is no lowering, kernel or runtime below its pybind11 IR builder.  This library is
+ * what a binding of that builder calls to execute the op on an NVIDIA B200 (sm_100a).
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns 0 or a negative
+ * FRISK_ERR_* code and never throws.  Unless stated otherwise, matrix pointers are DEVICE
+ * pointers owned by the caller.  A plan is bound to the CUDA device that was current when it
+ * was created and may be used from one host thread at a time.
+ *
+ * Operand convention (the one the reference's builder enforces, ffi/ir.cpp:339-359):
+ *   A is a logical [M,K] matrix, B a logical [K,N] matrix, C a logical [M,N] matrix,
+ *   whatever the trans flags say.  The trans flags select the memory order of the buffer
+ *   (lib/Dialect/Frisk/IR/FriskOps.cpp:1359-1360 and 1376-1377 derive "K is the inner
+ *   dimension" as !transA for A and transB for B):
+ *     transA == 0 : A[m,k] at  A + m*lda + k      (K contiguous)
+ *     transA == 1 : A[m,k] at  A + k*lda + m      (M contiguous)
+ *     transB == 0 : B[k,n] at  B + k*ldb + n      (N contiguous)
+ *     transB == 1 : B[k,n] at  B + n*ldb + k      (K contiguous, "column-major B")
+ *   C[m,n] at C + m*ldc + n always.
+ * Semantics (include/Dialect/Frisk/IR/FriskOps.td:248-289):
+ *   C = (clear_accum ? 0 : C) + scale_a[m] * scale_b[n] * sum_k A[m,k] * B[k,n]
+ * with the products and the sum in fp32 and one round-to-nearest-even cast to C's type.
+ * The scales are an addition to the reference op (it has no fp8 GEMM); they are optional.
+ */
+#ifndef FRISK_B200_H_
+#define FRISK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------- */
+enum {
+  FRISK_OK = 0,
+  FRISK_ERR_INVALID_ARGUMENT = -1, /* NULL pointer, non-positive size, bad enum            */
+  FRISK_ERR_UNSUPPORTED = -2,      /* dtype / layout combination no kernel covers          */
+  FRISK_ERR_MISALIGNED = -3,       /* pointer or leading dimension breaks an alignment rule */
+  FRISK_ERR_WORKSPACE = -4,        /* workspace missing or smaller than workspace_bytes     */
+  FRISK_ERR_CUDA = -5,             /* a CUDA runtime/driver call failed (see last_error)    */
+  FRISK_ERR_DEVICE_TIMEOUT = -6,   /* a bounded device-side wait ran out (status word)      */
+  FRISK_ERR_NO_DEVICE = -7,        /* no sm_100 device is visible                           */
+  FRISK_ERR_SHARD = -8,            /* rank/nranks invalid for row sharding                  */
+  FRISK_ERR_TOO_LARGE = -9         /* problem exceeds a fixed capacity of the entry point    */
+};
+
+/* ---- element types: the dtype vocabulary of ffi/ir.cpp:163-175, 240-245, 410-423 ----- */
+typedef enum {
+  FRISK_DT_F32 = 0,
+  FRISK_DT_F16 = 1,
+  FRISK_DT_BF16 = 2,
+  FRISK_DT_E4M3 = 3 /* "e4m3fn": finite-only fp8, max 448, no inf */
+} frisk_dtype;
+
+typedef enum { FRISK_SCALE_NONE = 0, FRISK_SCALE_ROW_COL = 1 } frisk_scale_mode;
+
+/* Which kernel family a plan resolved to (reported by frisk_b200_gemm_plan_info). */
+typedef enum {
+  FRISK_KERNEL_SIMT = 0,    /* CUDA-core fp32-FMA tiles: fp32 inputs and every odd shape   */
+  FRISK_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma, accumulators in TMEM, whole-tile output   */
+  FRISK_KERNEL_SKINNY = 2   /* same pipeline, operands swapped, K split across all SMs      */
+} frisk_kernel_kind;
+
+/*
+ * Description of one `frisk.gemm`.  Mirrors the op's attributes
+ * (include/Dialect/Frisk/IR/FriskOps.td:256-262: transA, transB, M, N, K, clear_accum) plus
+ * what the memref types carry (element types) and what an executor needs (leading dimensions).
+ * lda/ldb/ldc are in ELEMENTS; 0 means "packed" (the natural value for the chosen order).
+ */
+typedef struct frisk_gemm_desc {
+  int64_t M, N, K;
+  int32_t a_type, b_type, c_type; /* frisk_dtype; a_type must equal b_type                  */
+  int64_t lda, ldb, ldc;
+  int32_t transA, transB;
+  int32_t clear_accum; /* 1: C = A*B ; 0: C += A*B                                          */
+  int32_t scale_mode;  /* frisk_scale_mode                                                  */
+  /* Tuning overrides; 0 = let the plan choose.                                             */
+  int32_t force_kernel; /* 1 + frisk_kernel_kind, or 0                                       */
+  int32_t tile_n;       /* tcgen05 tile width along N: 64, 128 or 256                        */
+  int32_t stages;       /* TMA pipeline depth                                                */
+  int32_t num_ctas;     /* persistent grid size                                              */
+} frisk_gemm_desc;
+
+typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */
+
+typedef struct frisk_gemm_plan_info {
+  int32_t kernel;      /* frisk_kernel_kind                                                 */
+  int32_t tile_m, tile_n, tile_k;
+  int32_t stages;
+  int32_t num_ctas;
+  int32_t swap_ab;     /* 1 when the weights feed the 128-row operand (skinny path)          */
+  int32_t split_k;     /* 1 when partial sums go through the fp32 workspace                  */
+  int32_t smem_bytes;  /* dynamic shared memory per CTA                                      */
+  int32_t launches;    /* kernels launched per run                                           */
+  int32_t swizzle_a, swizzle_b; /* TMA/UMMA swizzle width in bytes (0, 32, 64, 128)          */
+} frisk_gemm_plan_info;
+
+/* Replaces: nothing executable in the reference.  The closest reference interface is
+ * builder.create_gemm_op (ffi/ir.cpp:322-366), whose shape and dtype checks are repeated here:
+ * rank-2 static shapes, matching inner dimensions, one element type for A and B.           */
+int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** out);
+void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* plan);
+int frisk_b200_gemm_plan_info(const frisk_gemm_plan* plan, frisk_gemm_plan_info* out);
+
+/* Bytes of device scratch `run` needs (0 for plans that write C directly). */
+int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* plan, size_t* out);
+
+/*
+ * Launch the GEMM on `stream` (a cudaStream_t passed as void*; NULL = the default stream).
+ * Asynchronous and stream-ordered.  scale_a ([M] fp32) and scale_b ([N] fp32) are used only
+ * when desc.scale_mode == FRISK_SCALE_ROW_COL.  `device_status` may be NULL; otherwise it
+ * points to one int32 in device memory that a kernel ORs a non-zero code into when one of its
+ * bounded waits ran out (read it with frisk_b200_check_status after synchronising).
+ * The executor behind the op created by ffi/ir.cpp:362.
+ */
+int frisk_b200_gemm_run(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
+                        const float* scale_a, const float* scale_b, void* workspace,
+                        size_t workspace_bytes, int32_t* device_status, void* stream);
+
+/*
+ * The same GEMM for callers that hold HOST buffers (what a binding of the reference's Python
+ * builder would be handed: numpy arrays).  Copies A, B (and C when clear_accum == 0, and the
+ * scales) to the device, runs, copies C back and synchronises.  Device buffers are cached in
+ * the plan between calls.  Returns FRISK_ERR_DEVICE_TIMEOUT if the status word came back set.
+ */
+int frisk_b200_gemm_run_host(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
+                             const float* scale_a, const float* scale_b);
+
+/* Copies the status word to the host (synchronises `stream`) and maps it to a return code. */
+int frisk_b200_check_status(const int32_t* device_status, void* stream);
+
+const char* frisk_b200_strerror(int code);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* frisk_b200_last_error(void);
+
+/*
+ * Row-block sharding of C = A*B over `nranks` GPUs: rank r owns rows [row0, row0+rows) of A
+ * and C, B is replicated.  Rows are dealt in contiguous blocks; when M is not a multiple of
+ * nranks the first M % nranks ranks get one extra row.  No counterpart in the reference,
+ * which has no multi-device notion (its only "parallel" is the intra-kernel frisk.parallel,
+ * include/Dialect/Frisk/IR/FriskOps.td:81-140).
+ */
+int frisk_b200_shard_rows(int64_t M, int nranks, int rank, int64_t* row0, int64_t* rows);
+
+/* ---- layout mapping ------------------------------------------------------------------- */
+/*
+ * A shared-memory operand layout as the reference's GemmOp::inferLayout chooses it
+ * (lib/Dialect/Frisk/IR/FriskOps.cpp:589-618, buildHopperSharedLayout): a rows x cols tile of
+ * `elem_bits`-wide elements, row-major, with `k_inner` telling whether the contiguous
+ * dimension is the GEMM's K.
+ */
+typedef struct frisk_layout_desc {
+  int64_t rows, cols;  /* tile shape as stored: cols is the contiguous dimension             */
+  int32_t elem_bits;   /* 8, 16 or 32                                                        */
+  int32_t k_inner;     /* 1: cols is K (K-major operand); 0: cols is M or N (MN-major)        */
+} frisk_layout_desc;
+
+/* What the B200 pipeline needs for that tile: TMA box + swizzle, UMMA descriptor fields. */
+typedef struct frisk_tma_params {
+  int32_t swizzle_bytes;     /* 0, 32, 64 or 128: CU_TENSOR_MAP_SWIZZLE_{NONE,32B,64B,128B}   */
+  int32_t box_inner;         /* elements per box row (= swizzle_bytes / element size)         */
+  int32_t box_outer;         /* rows per box                                                  */
+  int32_t num_boxes;         /* boxes that make up the tile                                   */
+  int32_t umma_layout_type;  /* bits 61..63 of the shared-memory descriptor: 0, 6, 4, 2        */
+  int32_t umma_major;        /* 0 = K-major, 1 = MN-major (instruction-descriptor bit)        */
+  int32_t leading_byte_offset; /* LBO in bytes                                                */
+  int32_t stride_byte_offset;  /* SBO in bytes                                                */
+  int32_t k_step_bytes;      /* start-address advance per UMMA K step (32 bytes of K)          */
+  char reference_layout[24]; /* name of the reference swizzle: "full_bank", "half_bank", ...   */
+} frisk_tma_params;
+
+/* The selection rule of FriskOps.cpp:608-617 carried over to TMA / UMMA descriptors. */
+int frisk_b200_layout_to_tma(const frisk_layout_desc* layout, frisk_tma_params* out);
+
+/*
+ * Byte offset inside a swizzled rows x cols tile of element (row, col), as TMA writes it and
+ * UMMA reads it (-1 on a bad argument).  The reference's makeFull/Half/QuarterBankSwizzle
+ * (FriskOps.cpp:500-558) return (column atom tc, row atom ts, offset in atom) and never
+ * linearise them; here the three are laid out as
+ *   tc * (rows * span) + ts * (8 * span) + offset * elem_bytes,   span = swizzle_bytes,
+ * i.e. one TMA box per column atom.
+ */
+int64_t frisk_b200_swizzled_offset(int64_t row, int64_t col, int64_t rows, int64_t cols,
+                                   int32_t elem_bits, int32_t swizzle_bytes);
+
+/*
+ * Shared-memory bank-conflict model of exp/layout/gemm_layout_tool.cpp:135-208 applied to a
+ * swizzle mode: walks the tile in windows of 32*lane_vector row-major elements, maps every
+ * element to its bank (4-byte words, 32 banks) and reports the worst bucket per window.
+ * `mode` is swizzle_bytes (0/32/64/128) or one of the Blackwell-only atoms below.
+ */
+enum { FRISK_SWIZZLE_128B_ATOM_32B = 1032, FRISK_SWIZZLE_128B_ATOM_64B = 1064 };
+typedef struct frisk_bank_stats {
+  double avg_max_conflict;
+  int32_t max_conflict;
+  int32_t samples;
+} frisk_bank_stats;
+int frisk_b200_bank_conflicts(int64_t rows, int64_t cols, int32_t elem_bits, int32_t mode,
+                              int32_t lane_vector, int32_t distinct_words_only,
+                              frisk_bank_stats* out);
+
+/* Library / device facts: returns the SM count of the current device (or a negative code). */
+int frisk_b200_device_sm_count(void);
+const char* frisk_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRISK_B200_H_ */

@@ -7,6 +7,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -464,6 +465,8 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   }
   g.C = C;
   g.status = device_status;
+  if (const char* dbg = getenv("FRISK_B200_DEBUG_MODE")) g.debug_mode = (uint32_t)atoi(dbg);
+  if (const char* tr = getenv("FRISK_B200_TRACE")) g.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
   g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
   if (swap) {
     g.ws = reinterpret_cast<float*>(workspace);

@@ -1,5 +1,7 @@
 // Persistent, warp-specialised GEMM for sm_100a:
-//   warp 0   : TMA producer  (global -> 128B-swizzled shared memory, mbarrier completion)
+//   warps 0,6: TMA producers (global -> 128B-swizzled shared memory, mbarrier completion);
+//              they take alternate k-blocks, because one warp cannot issue a stage's loads as
+//              fast as the tensor pipe consumes a stage
 //   warp 1   : MMA issuer    (tcgen05.mma, fp32 accumulators in tensor memory)
 //   warps 2-5: epilogue      (tcgen05.ld -> registers -> scale / cast -> global)
 // One kernel serves two plans:
@@ -24,8 +26,9 @@
 namespace frisk {
 
 constexpr int kMaxStages = 12;
-constexpr int kGemmThreads = 192;
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait, far above any legitimate wait
+constexpr int kProducerWarps = 2;  // warps 0 and 6 issue the TMA loads of alternate k-blocks
+constexpr int kGemmThreads = 224;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock per wait, far above any legitimate wait
 
 enum : int32_t {
   kStatusProducerTimeout = 1,
@@ -72,26 +75,44 @@ struct GemmParams {
   uint32_t transposed_out; // 1: D[r, c] is C[c, r]
   uint32_t clear_accum;
   uint32_t c_vec_ok;       // C rows allow 16-byte stores
+  uint32_t debug_mode;     // measurement only: bit 0 = issue no loads, bit 1 = issue no MMAs
+  long long* trace;        // measurement only: clock64 samples of CTA 0 (may be nullptr)
   int32_t* status;
 };
 
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
-                                             volatile uint32_t* abort_flag, int32_t* status,
-                                             int32_t code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = ptx::globaltimer_ns();
-  uint32_t spins = 0;
-  while (true) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xFF) == 0) {
-      if (*abort_flag) return false;
-      if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        if (status) atomicOr(status, code);
-        return false;
-      }
+// Slow path of bounded_wait: polls until the phase completes, the CTA aborts or the limit runs
+// out.  Called by whole warps (every lane polls the same barrier, so the outcome is warp-uniform).
+__device__ __noinline__ bool bounded_wait_slow(uint32_t bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, int32_t* status,
+                                               int32_t code, uint32_t backoff_ns) {
+  const long long t0 = clock64();
+  bool done = false;
+  while (!done) {
+#pragma unroll 1
+    for (int i = 0; i < 256 && !done; ++i) {
+      done = ptx::mbar_try_wait(bar, parity) != 0;
+      if (!done && backoff_ns) __nanosleep(backoff_ns);
+    }
+    if (done) break;
+    if (*abort_flag) break;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, code);
+      break;
     }
   }
+  // one answer for the whole warp: the callers go on to warp-collective instructions
+  return __all_sync(0xffffffffu, done);
+}
+
+// Waits for a phase of an mbarrier with a limit.  Returns false when the limit ran out here or in
+// another role of the CTA; the caller then falls through to the kernel's tear-down.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
+                                             volatile uint32_t* abort_flag, int32_t* status,
+                                             int32_t code, uint32_t backoff_ns = 0) {
+  // the vote makes the outcome provably warp-uniform for the compiler (see the role branches)
+  if (__all_sync(0xffffffffu, ptx::mbar_try_wait(bar, parity))) return true;
+  return bounded_wait_slow(bar, parity, abort_flag, status, code, backoff_ns);
 }
 
 // Sequence of (tile, k-block range) work items of one CTA; identical in all three roles.
@@ -103,10 +124,10 @@ struct WorkIter {
   uint64_t u, u_end;
   uint32_t num_kb, split;
 
-  __device__ void init(const GemmParams& p) {
-    num_kb = p.num_kb;
-    split = p.split_mode;
-    num_tiles = p.tiles_r * p.tiles_c;
+  __device__ void init(uint32_t num_kb_, uint32_t split_, uint32_t num_tiles_) {
+    num_kb = num_kb_;
+    split = split_;
+    num_tiles = num_tiles_;
     if (split) {
       const uint64_t total = (uint64_t)num_tiles * num_kb;
       u = total * blockIdx.x / gridDim.x;
@@ -137,12 +158,12 @@ struct WorkIter {
 
 // Tile index -> (tile row, tile column).  Tiles are walked in bands of `group_r` tile rows,
 // down the band first, so that CTAs running at the same time share A rows and B columns in L2.
-__device__ __forceinline__ void tile_coords(const GemmParams& p, uint32_t tile, uint32_t& tr,
-                                            uint32_t& tc) {
-  const uint32_t band_tiles = p.group_r * p.tiles_c;
+__device__ __forceinline__ void tile_coords(uint32_t group_r, uint32_t tiles_r, uint32_t tiles_c,
+                                            uint32_t tile, uint32_t& tr, uint32_t& tc) {
+  const uint32_t band_tiles = group_r * tiles_c;
   const uint32_t band = tile / band_tiles;
-  const uint32_t first_r = band * p.group_r;
-  const uint32_t rows_in_band = min(p.group_r, p.tiles_r - first_r);
+  const uint32_t first_r = band * group_r;
+  const uint32_t rows_in_band = min(group_r, tiles_r - first_r);
   const uint32_t in_band = tile - band * band_tiles;
   tr = first_r + in_band % rows_in_band;
   tc = in_band / rows_in_band;
@@ -169,9 +190,23 @@ __device__ __forceinline__ float cast_in<__nv_bfloat16>(__nv_bfloat16 v) {
   return __bfloat162float(v);
 }
 
+// The epilogue's view of the kernel parameters.  Every role copies what its loop needs out of the
+// __grid_constant__ parameter block into plain locals first: the block is read through its address,
+// and the inline-PTX statements clobber memory, so a field left in the block would be re-fetched
+// with a generic load after every one of them (measured: ~350 cycles per tcgen05.mma issued).
+struct EpiArgs {
+  void* C;
+  float* ws;
+  const float* row_scale;
+  const float* col_scale;
+  int64_t ldc, ws_ld;
+  uint32_t rows, cols;
+  uint32_t split_mode, transposed_out, clear_accum, c_vec_ok;
+};
+
 // Writes NC accumulator values of one D row (columns col0 .. col0+NC-1) held by this thread.
 template <typename TC, int NC>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t row, uint32_t col0,
+__device__ __forceinline__ void epilogue_store(const EpiArgs& p, uint32_t row, uint32_t col0,
                                                const uint32_t (&acc)[NC]) {
   if (row >= p.rows) return;
   const float rs = p.row_scale ? __ldg(p.row_scale + row) : 1.0f;
@@ -249,29 +284,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
 
-  const uint32_t warp = threadIdx.x >> 5;
+  // The broadcast tells the compiler that the warp index is the same in every lane, so the role
+  // branches below are uniform and the code inside them may use the uniform datapath (which the
+  // TMA and tcgen05 instructions take their operands from).
+  const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const uint32_t lane = threadIdx.x & 31;
   volatile uint32_t* abort_flag = &abort_word;
 
   // tiles live in dynamic shared memory, 1024-byte aligned (one swizzle atom)
   const uint32_t tiles_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t full0 = ptx::smem_u32(&bar_full[0]);
+  const uint32_t empty0 = ptx::smem_u32(&bar_empty[0]);
+  const uint32_t acc_full0 = ptx::smem_u32(&bar_acc_full[0]);
+  const uint32_t acc_empty0 = ptx::smem_u32(&bar_acc_empty[0]);
+
+  // fields every role needs, held in registers from here on
+  const uint32_t stages = p.stages;
+  const uint32_t stage_bytes = p.stage_bytes;
+  const uint32_t mi = p.mi;
+  const uint32_t tile_n = p.tile_n;
+  const uint32_t acc_bufs = p.acc_bufs;
+  const uint32_t tmem_cols = p.tmem_cols;
+  const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r;
+  const uint32_t debug_mode = p.debug_mode;
+  int32_t* const status = p.status;
+  long long* const trace = blockIdx.x == 0 ? p.trace : nullptr;
 
   if (threadIdx.x == 0) {
     abort_word = 0;
-    for (uint32_t s = 0; s < p.stages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+    for (uint32_t s = 0; s < stages; ++s) {
+      ptx::mbar_init(full0 + 8 * s, 1);
+      ptx::mbar_init(empty0 + 8 * s, 1);
     }
     for (uint32_t i = 0; i < 2; ++i) {
-      ptx::mbar_init(ptx::smem_u32(&bar_acc_full[i]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bar_acc_empty[i]), 4);  // one arrival per epilogue warp
+      ptx::mbar_init(acc_full0 + 8 * i, 1);
+      ptx::mbar_init(acc_empty0 + 8 * i, 4);  // one arrival per epilogue warp
     }
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), p.tmem_cols);
+    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), tmem_cols);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -280,155 +334,221 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = tmem_base_slot;
 
   WorkIter work;
-  work.init(p);
+  work.init(p.num_kb, p.split_mode, tiles_r * tiles_c);
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0, issued = 0;
+    // The whole warp walks the loop (uniform control flow); one elected lane issues.
+    {
+      const uint32_t a_boxes = p.a.num_boxes, a_box_bytes = p.a.box_bytes, a_box_mn = p.a.box_mn;
+      const uint32_t b_boxes = p.b.num_boxes, b_box_bytes = p.b.box_bytes, b_box_mn = p.b.box_mn;
+      const uint32_t a_mn_major = p.a.mn_major, b_mn_major = p.b.mn_major;
+      const uint32_t a_stage_bytes = p.a.stage_bytes;
+      const uint32_t bk_elems = p.bk_elems;
+      const uint32_t my_turn = warp == 0 ? 0u : 1u;
+      uint32_t stage = 0, phase = 0, issued = 0, turn = 0;
       bool ok = true;
       while (ok && work.next()) {
         uint32_t tr, tc;
-        tile_coords(p, work.tile, tr, tc);
-        const int32_t r0 = (int32_t)(tr * 128u * p.mi);
-        const int32_t c0 = (int32_t)(tc * p.tile_n);
+        tile_coords(group_r, tiles_r, tiles_c, work.tile, tr, tc);
+        const int32_t r0 = (int32_t)(tr * 128u * mi);
+        const int32_t c0 = (int32_t)(tc * tile_n);
         for (uint32_t kb = work.kb0; kb < work.kb1; ++kb) {
-          if (!bounded_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, p.status,
-                            kStatusProducerTimeout)) {
-            ok = false;
-            break;
+          if (turn != my_turn) {  // the other producer warp loads this k-block
+            turn ^= 1u;
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
           }
-          const uint32_t full = ptx::smem_u32(&bar_full[stage]);
-          ptx::mbar_arrive_expect_tx(full, p.stage_bytes);
-          const uint32_t a_dst = tiles_base + stage * p.stage_bytes;
-          const uint32_t b_dst = a_dst + p.a.stage_bytes;
-          const int32_t k0 = (int32_t)(kb * p.bk_elems);
-          for (uint32_t bx = 0; bx < p.a.num_boxes; ++bx) {
-            const int32_t mn = r0 + (int32_t)(bx * p.a.box_mn);
-            if (p.a.mn_major)
-              ptx::tma_load_2d(a_dst + bx * p.a.box_bytes, &tmap_a, full, mn, k0);
-            else
-              ptx::tma_load_2d(a_dst + bx * p.a.box_bytes, &tmap_a, full, k0, mn);
+          turn ^= 1u;
+          ok = bounded_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status,
+                            kStatusProducerTimeout);
+          if (!ok) break;
+          const uint32_t full = full0 + 8 * stage;
+          const bool tr_on = trace && issued < 32 && warp == 0;
+          if (tr_on && ptx::elect_one()) trace[2 * issued] = clock64();
+          if (debug_mode & 1u) {
+            if (ptx::elect_one()) ptx::mbar_arrive(full);
+          } else {
+            if (ptx::elect_one()) ptx::mbar_arrive_expect_tx(full, stage_bytes);
+            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued] = clock64();
+            const uint32_t a_dst = tiles_base + stage * stage_bytes;
+            const uint32_t b_dst = a_dst + a_stage_bytes;
+            const int32_t k0 = (int32_t)(kb * bk_elems);
+            for (uint32_t bx = 0; bx < a_boxes; ++bx) {
+              const int32_t mn = r0 + (int32_t)(bx * a_box_mn);
+              const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
+              if (ptx::elect_one()) ptx::tma_load_2d(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
+            }
+            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued + 1] = clock64();
+            for (uint32_t bx = 0; bx < b_boxes; ++bx) {
+              const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
+              const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
+              if (ptx::elect_one()) ptx::tma_load_2d(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
+            }
           }
-          for (uint32_t bx = 0; bx < p.b.num_boxes; ++bx) {
-            const int32_t mn = c0 + (int32_t)(bx * p.b.box_mn);
-            if (p.b.mn_major)
-              ptx::tma_load_2d(b_dst + bx * p.b.box_bytes, &tmap_b, full, mn, k0);
-            else
-              ptx::tma_load_2d(b_dst + bx * p.b.box_bytes, &tmap_b, full, k0, mn);
-          }
+          if (tr_on && ptx::elect_one()) trace[2 * issued + 1] = clock64();
           ++issued;
-          if (++stage == p.stages) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1;
           }
         }
       }
       if (!ok) {
-        // Give copies that are still in flight a bounded chance to land before the CTA exits.
-        // Stages below `stage` were last armed in the current round (parity `phase`), the others
-        // in the previous one; a stage that was never armed is skipped.
-        for (uint32_t s = 0; s < p.stages; ++s) {
-          if (issued <= s) continue;
-          const uint32_t armed_parity = (s < stage) ? phase : (phase ^ 1u);
-          const uint64_t t0 = ptx::globaltimer_ns();
-          while (!ptx::mbar_try_wait(ptx::smem_u32(&bar_full[s]), armed_parity) &&
-                 ptx::globaltimer_ns() - t0 < 1000000ull) {
-          }
+        // Give copies that are still in flight time to land before the CTA exits (a copy takes
+        // a few microseconds at most; this waits about 50).
+        const long long t0 = clock64();
+        while (clock64() - t0 < 100000ll) {
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    {
+      const uint64_t a_desc_base = p.a.desc_base, b_desc_base = p.b.desc_base;
+      const uint32_t a_k_step = p.a.k_step_bytes, b_k_step = p.b.k_step_bytes;
+      const uint32_t a_sub_stride = p.a.sub_stride_bytes;
+      const uint32_t a_stage_bytes = p.a.stage_bytes;
+      const uint32_t k_steps = p.k_steps;
+      const uint32_t idesc = p.idesc;
+      const uint32_t kind_f8 = p.kind_f8;
       uint32_t stage = 0, phase = 0, item = 0;
       bool ok = true;
       while (ok && work.next()) {
-        const uint32_t acc = item % p.acc_bufs;
-        const uint32_t acc_phase = (item / p.acc_bufs) & 1u;
-        if (!bounded_wait(ptx::smem_u32(&bar_acc_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
-                          kStatusMmaTimeout)) {
-          ok = false;
-          break;
-        }
+        const uint32_t acc = item % acc_bufs;
+        const uint32_t acc_phase = (item / acc_bufs) & 1u;
+        ok = bounded_wait(acc_empty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
+                          kStatusMmaTimeout);
+        if (!ok) break;
         ptx::tc_fence_after();
-        const uint32_t d_base = tmem_base + acc * (p.mi * p.tile_n);
+        const uint32_t d_base = tmem_base + acc * (mi * tile_n);
+        // The tensor pipe queues only a little work, so the time between the last MMA of one
+        // k-block and the first of the next is idle time.  To keep it short the stage of k-block
+        // i is released (tcgen05.commit) only after the first MMA of k-block i+1 has been issued,
+        // and the barrier of k-block i+1 is polled before the last MMA of k-block i.
+        uint32_t prev_stage = 0;
+        bool have_prev = false;
+        uint32_t ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * stage, phase));
         for (uint32_t kb = work.kb0; kb < work.kb1; ++kb) {
-          if (!bounded_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_flag, p.status,
-                            kStatusMmaTimeout)) {
-            ok = false;
-            break;
+          if (!ready) {
+            ok = bounded_wait_slow(full0 + 8 * stage, phase, abort_flag, status, kStatusMmaTimeout,
+                                   0);
+            if (!ok) break;
           }
           ptx::tc_fence_after();
-          const uint32_t a_addr = tiles_base + stage * p.stage_bytes;
-          const uint32_t b_addr = a_addr + p.a.stage_bytes;
-          for (uint32_t ks = 0; ks < p.k_steps; ++ks) {
-            const uint64_t bdesc =
-                p.b.desc_base | (uint64_t)(((b_addr + ks * p.b.k_step_bytes) & 0x3FFFFu) >> 4);
-            for (uint32_t sub = 0; sub < p.mi; ++sub) {
-              const uint64_t adesc =
-                  p.a.desc_base |
-                  (uint64_t)(((a_addr + sub * p.a.sub_stride_bytes + ks * p.a.k_step_bytes) &
-                              0x3FFFFu) >> 4);
-              const uint32_t accumulate = (kb > work.kb0 || ks > 0) ? 1u : 0u;
-              if (p.kind_f8)
-                ptx::mma_f8(d_base + sub * p.tile_n, adesc, bdesc, p.idesc, accumulate);
-              else
-                ptx::mma_f16(d_base + sub * p.tile_n, adesc, bdesc, p.idesc, accumulate);
+          // Everything below is computed by the whole warp (uniform values); only the issuing
+          // instructions themselves sit under the elected lane.
+          const uint32_t a_addr = tiles_base + stage * stage_bytes;
+          const uint32_t b_addr = a_addr + a_stage_bytes;
+          const uint64_t adesc0 = a_desc_base | (uint64_t)((a_addr & 0x3FFFFu) >> 4);
+          const uint64_t bdesc0 = b_desc_base | (uint64_t)((b_addr & 0x3FFFFu) >> 4);
+          const uint32_t first = (kb > work.kb0) ? 1u : 0u;
+          const bool tr_on = trace && item == 0 && (kb - work.kb0) < 32;
+          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0)] = clock64();
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == stages) {
+            next_stage = 0;
+            next_phase ^= 1;
+          }
+          if (debug_mode & 2u) {
+            if (ptx::elect_one()) ptx::mbar_arrive(empty0 + 8 * stage);
+            ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+          } else {
+            // the start-address field advances by whole 16-byte units and never carries out of
+            // its 14 bits (the tiles end below 256 KiB), so the step is added to the low word
+#pragma unroll
+            for (uint32_t ks = 0; ks < 4; ++ks) {
+              const uint64_t bdesc = bdesc0 + (uint64_t)((ks * b_k_step) >> 4);
+              const uint64_t adesc = adesc0 + (uint64_t)((ks * a_k_step) >> 4);
+              const uint32_t accumulate = first | (ks > 0 ? 1u : 0u);
+              if (ks == 3)
+                ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+              if (kind_f8) {
+                if (ptx::elect_one()) ptx::mma_f8(d_base, adesc, bdesc, idesc, accumulate);
+                if (mi > 1 && ptx::elect_one())
+                  ptx::mma_f8(d_base + tile_n, adesc + (a_sub_stride >> 4), bdesc, idesc, accumulate);
+              } else {
+                if (ptx::elect_one()) ptx::mma_f16(d_base, adesc, bdesc, idesc, accumulate);
+                if (mi > 1 && ptx::elect_one())
+                  ptx::mma_f16(d_base + tile_n, adesc + (a_sub_stride >> 4), bdesc, idesc, accumulate);
+              }
+              if (ks == 0 && have_prev && ptx::elect_one()) ptx::tc_commit(empty0 + 8 * prev_stage);
             }
+            if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 1] = clock64();
+            prev_stage = stage;
+            have_prev = true;
           }
-          ptx::tc_commit(ptx::smem_u32(&bar_empty[stage]));  // frees the stage when the MMAs retire
-          if (++stage == p.stages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 2] = clock64();
+          stage = next_stage;
+          phase = next_phase;
         }
         if (!ok) break;
-        ptx::tc_commit(ptx::smem_u32(&bar_acc_full[acc]));
+        // release the last stage of this work item
+        if (have_prev && ptx::elect_one()) ptx::tc_commit(empty0 + 8 * prev_stage);
+        if (!ok) break;
+        if (ptx::elect_one()) ptx::tc_commit(acc_full0 + 8 * acc);
+        __syncwarp();
         ++item;
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------- epilogue
+    EpiArgs ep;
+    ep.C = p.C;
+    ep.ws = p.ws;
+    ep.row_scale = p.row_scale;
+    ep.col_scale = p.col_scale;
+    ep.ldc = p.ldc;
+    ep.ws_ld = p.ws_ld;
+    ep.rows = p.rows;
+    ep.cols = p.cols;
+    ep.split_mode = p.split_mode;
+    ep.transposed_out = p.transposed_out;
+    ep.clear_accum = p.clear_accum;
+    ep.c_vec_ok = p.c_vec_ok;
     const uint32_t quarter = warp & 3u;  // TMEM lanes 32*quarter .. +31 belong to this warp
     uint32_t item = 0;
     bool ok = true;
     while (ok && work.next()) {
-      const uint32_t acc = item % p.acc_bufs;
-      const uint32_t acc_phase = (item / p.acc_bufs) & 1u;
+      const uint32_t acc = item % acc_bufs;
+      const uint32_t acc_phase = (item / acc_bufs) & 1u;
       uint32_t tr, tc;
-      tile_coords(p, work.tile, tr, tc);
+      tile_coords(group_r, tiles_r, tiles_c, work.tile, tr, tc);
       // the tcgen05.ld below is warp-collective: leave the loop only as a whole warp
-      ok = __all_sync(0xffffffffu,
-                      bounded_wait(ptx::smem_u32(&bar_acc_full[acc]), acc_phase, abort_flag,
-                                   p.status, kStatusEpilogueTimeout));
+      ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
+                        (debug_mode & 4u) ? 256u : 0u);
       if (!ok) break;
       ptx::tc_fence_after();
-      for (uint32_t sub = 0; sub < p.mi; ++sub) {
-        const uint32_t row = (tr * p.mi + sub) * 128u + quarter * 32u + lane;
-        const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + acc * (p.mi * p.tile_n) +
-                               sub * p.tile_n;
-        if ((p.tile_n & 31u) == 0) {
-          for (uint32_t cc = 0; cc < p.tile_n; cc += 32) {
+      if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item] = clock64();
+      for (uint32_t sub = 0; sub < mi; ++sub) {
+        const uint32_t row = (tr * mi + sub) * 128u + quarter * 32u + lane;
+        const uint32_t t_row =
+            tmem_base + ((quarter * 32u) << 16) + acc * (mi * tile_n) + sub * tile_n;
+        if ((tile_n & 31u) == 0) {
+          for (uint32_t cc = 0; cc < tile_n; cc += 32) {
             uint32_t v[32];
             ptx::tmem_ld_32x32b_x32(t_row + cc, v);
             ptx::tmem_ld_wait();
-            epilogue_store<TC, 32>(p, row, tc * p.tile_n + cc, v);
+            epilogue_store<TC, 32>(ep, row, tc * tile_n + cc, v);
           }
         } else {
-          for (uint32_t cc = 0; cc < p.tile_n; cc += 16) {
+          for (uint32_t cc = 0; cc < tile_n; cc += 16) {
             uint32_t v[16];
             ptx::tmem_ld_32x32b_x16(t_row + cc, v);
             ptx::tmem_ld_wait();
-            epilogue_store<TC, 16>(p, row, tc * p.tile_n + cc, v);
+            epilogue_store<TC, 16>(ep, row, tc * tile_n + cc, v);
           }
         }
       }
       ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_acc_empty[acc]));
+      if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
+      if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item + 1] = clock64();
       ++item;
     }
     __syncwarp();
@@ -439,7 +559,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, p.tmem_cols);
+    ptx::tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 

@@ -19,6 +19,21 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// Picks one lane of a fully converged warp.  Unlike a test of the lane index, the compiler knows
+// that exactly one thread passes, so code under it can keep TMA / tcgen05 operands in uniform
+// registers; issuing those instructions from an `if (lane == 0)` branch costs hundreds of cycles each.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

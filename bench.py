@@ -1,0 +1,484 @@
+#!/usr/bin/env python
+"""Benchmark of the frisk.gemm hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5] [--impl reference]
+
+One step = one pass of the GEMM over one batch of synthetic input.  The default workload is the
+row-sharded bf16 GEMM (M=65536, N=K=8192): rank r of N computes rows [r*M/N, (r+1)*M/N) of C with
+B replicated, no collective on the data path (strong scaling: the total work is fixed).  Rank 0
+prints ONE JSON line: whole-job TFLOP/s with inputs resident in HBM (`value`), the same metric
+through the host-buffer C-ABI call with the copies inside the timed region (`e2e`), the roofline
+of the dominant kernel, the CPU baseline (the oracle port on the host cores) and, at N=1, the
+other benchmark configurations under `other_configs`.
+
+`--impl reference` times the CPU restatement of the op (the reference has no GEMM implementation
+of its own to run) on a bounded sample of the same workload, with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from frisk_b200 import workloads as W  # noqa: E402
+
+FULL_DIMS = {
+    "cfg1": (512, 512, 512), "cfg2": (4096, 4096, 4096), "cfg3": (16, 8192, 8192),
+    "cfg4": (8192, 8192, 8192), "cfg5": (65536, 8192, 8192), "bf16_8192": (8192, 8192, 8192),
+}
+AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3}
+C_TYPE = {"cfg1": W.F32, "cfg2": W.F16}
+TRANS_B = {"cfg2", "cfg4"}
+BOUND = {"cfg3": "hbm"}  # everything else is judged against the tensor-core peak
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
+# from the ncu captures summarised under profiles/; None where no capture exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(mx)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def device_inputs(torch, name, M, N, K, dev, seed):
+    """Synthetic inputs of the workload's shapes and distributions, drawn on the device."""
+    ab = AB_TYPE.get(name, W.BF16)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    a_shape = (M, K)
+    b_shape = (N, K) if name in TRANS_B else (K, N)
+    sa = sb = None
+    if ab == W.E4M3:
+        A = torch.randn(a_shape, generator=g, device=dev).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        B = torch.randn(b_shape, generator=g, device=dev).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        sa = (torch.rand(M, generator=g, device=dev) * 1.5 + 0.5) / 448.0
+        sb = (torch.rand(N, generator=g, device=dev) * 1.5 + 0.5) / 448.0
+    elif ab == W.F32:
+        A = torch.rand(a_shape, generator=g, device=dev) * 2 - 1
+        B = torch.rand(b_shape, generator=g, device=dev) * 2 - 1
+    else:
+        tdt = torch.float16 if ab == W.F16 else torch.bfloat16
+        a_scale = K ** -0.5 if name == "cfg2" else 1.0
+        b_scale = K ** -0.5 if name == "cfg2" else 0.02
+        A = (torch.randn(a_shape, generator=g, device=dev) * a_scale).to(tdt)
+        B = (torch.randn(b_shape, generator=g, device=dev) * b_scale).to(tdt)
+    return A, B, sa, sb
+
+
+def out_dtype(torch, name):
+    ct = C_TYPE.get(name, W.BF16)
+    return {W.F32: torch.float32, W.F16: torch.float16, W.BF16: torch.bfloat16}[ct]
+
+
+def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, flush_l2=False):
+    """K steps of the plan on device-resident inputs; returns (ms_per_step, plan info)."""
+    A, B, sa, sb = device_inputs(torch, name, M, N, K, dev, seed)
+    C = torch.empty((M, N), device=dev, dtype=out_dtype(torch, name))
+    plan = R.GemmPlan(M, N, K, AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16),
+                      transB=name in TRANS_B, scales=sa is not None)
+    ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev) if flush_l2 else None
+    for _ in range(warmup):
+        plan.run(A, B, C, sa, sb, ws, status, stream)
+    torch.cuda.synchronize()
+    R.check_status(status, stream)
+    if flush_l2:
+        # small inputs: write a buffer larger than L2 between iterations, time each launch alone
+        total = 0.0
+        for _ in range(steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            plan.run(A, B, C, sa, sb, ws, status, stream)
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        ms = total / steps
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            plan.run(A, B, C, sa, sb, ws, status, stream)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+    R.check_status(status, stream)
+    info = plan.info
+    plan.close()
+    return ms, info
+
+
+def roofline_for(name, M, N, K, ms, peaks, sustained):
+    ab, ct = AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16)
+    if BOUND.get(name) == "hbm":
+        alg = M * K * W.ELEM_SIZE[ab] + K * N * W.ELEM_SIZE[ab] + M * N * W.ELEM_SIZE[ct]
+        achieved = alg / (ms * 1e-3) / 1e9
+        peak = peaks["hbm_gbs"]
+        unit = "GB/s"
+    else:
+        achieved = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+        if ab == W.E4M3:
+            peak *= 2.0  # fp8 runs at twice the bf16 rate; only the bf16 peak is measured
+        if ab == W.F32:
+            peak = None  # CUDA-core kernel: no tensor roofline applies
+        unit = "TFLOP/s"
+    return {"bound": BOUND.get(name, "tensor"), "achieved": round(achieved, 2),
+            "peak": None if peak is None else round(peak, 1), "unit": unit,
+            "frac": None if peak is None else round(achieved / peak, 4),
+            "traffic": NCU_TRAFFIC_BYTES.get(name),
+            "peak_source": peaks["source"] + (" (sustained)" if sustained and unit == "TFLOP/s" else " (burst)" if unit == "TFLOP/s" else "")}
+
+
+def cpu_baseline(name, target_s=12.0):
+    """The oracle port (naive fp32 loop, OpenMP over rows) on a bounded sample of the workload."""
+    from oracle import ref
+
+    M, N, K = FULL_DIMS[name]
+    threads = ref.max_threads()
+    rows = min(M, 16)
+    w = W.make_workload(name, rows, N, K)
+    t0 = time.perf_counter()
+    ref.ref_gemm(w)
+    dt = time.perf_counter() - t0
+    # grow the sample towards the target time
+    rows2 = int(min(M, max(rows, rows * target_s / max(dt, 1e-3))))
+    rows2 = max(threads, rows2 // threads * threads)
+    if rows2 > rows:
+        w = W.make_workload(name, rows2, N, K)
+        t0 = time.perf_counter()
+        ref.ref_gemm(w)
+        dt = time.perf_counter() - t0
+        rows = rows2
+    tflops = 2.0 * rows * N * K / dt / 1e12
+    out = {"value": round(tflops, 5), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+           "sample": f"rows [0, {rows}) of {name} ({rows}x{N}x{K}), {dt:.1f} s, per-FLOP rate of the full problem assumed equal"}
+    try:
+        import torch
+
+        torch.set_num_threads(threads)
+        a = torch.from_numpy(w.a_logical().astype(np.float32))
+        b = torch.from_numpy(np.ascontiguousarray(w.b_logical().astype(np.float32)))
+        a @ b
+        t0 = time.perf_counter()
+        for _ in range(3):
+            a @ b
+        dt2 = (time.perf_counter() - t0) / 3
+        out["torch_matmul_cpu_tflops"] = round(2.0 * rows * N * K / dt2 / 1e12, 4)
+    except Exception:  # torch CPU matmul is an extra, never required
+        pass
+    return out
+
+
+def run_reference(args):
+    """`--impl reference`: the CPU restatement timed on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import ref
+
+    name = args.workload
+    M, N, K = FULL_DIMS[name]
+    threads = ref.max_threads()
+    rows = max(threads, min(M, 8 * threads))
+    w = W.make_workload(name, rows, N, K)
+    for _ in range(max(args.warmup, 0)):
+        ref.ref_gemm(w)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ref.ref_gemm(w)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * rows * N * K / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": round(tflops, 5), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": W.DTYPE_NAMES[AB_TYPE.get(name, W.BF16)], "data": "synthetic",
+        "config": {"workload": name, "M": M, "N": N, "K": K,
+                   "note": "the reference has no executable GEMM; this is its op restated as a "
+                           "naive fp32 loop (oracle/frisk_ref_gemm.c) on a row sample"},
+        "cpu_baseline": {"value": round(tflops, 5), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"rows [0, {rows}) of {name} per step"},
+        "e2e": {"value": round(tflops, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg5", choices=sorted(FULL_DIMS))
+    ap.add_argument("--impl", default="frisk_b200", choices=["frisk_b200", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    from frisk_b200 import runtime as R
+
+    R.lib()  # fail loudly when the CUDA library is missing: there is no other path
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (sm_100a); none is visible")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    name = args.workload
+    M, N, K = FULL_DIMS[name]
+    row0, rows = R.shard_rows(M, world, rank)
+    peaks = load_peaks()
+
+    # ---- device-resident timing: K steps, barrier + synchronize on both sides, max over ranks
+    A, B, sa, sb = device_inputs(torch, name, rows, N, K, dev, seed=4 + 1000 * rank)
+    if world > 1:  # B is replicated: every rank holds rank 0's B
+        dist.broadcast(B, 0)
+    C = torch.empty((rows, N), device=dev, dtype=out_dtype(torch, name))
+    plan = R.GemmPlan(rows, N, K, AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16),
+                      transB=name in TRANS_B, scales=sa is not None)
+    ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    small_inputs = (A.numel() * A.element_size() + B.numel() * B.element_size()) < 256 * 2 ** 20
+    flush = torch.empty(192 * 2 ** 20, dtype=torch.uint8, device=dev) if small_inputs else None
+    for _ in range(args.warmup):
+        plan.run(A, B, C, sa, sb, ws, status, stream)
+    torch.cuda.synchronize()
+    R.check_status(status, stream)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if flush is None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            plan.run(A, B, C, sa, sb, ws, status, stream)
+        e1.record()
+        torch.cuda.synchronize()
+        elapsed_ms = e0.elapsed_time(e1)
+    else:
+        elapsed_ms = 0.0
+        for _ in range(args.steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            plan.run(A, B, C, sa, sb, ws, status, stream)
+            e1.record()
+            torch.cuda.synchronize()
+            elapsed_ms += e0.elapsed_time(e1)
+    if dist:
+        dist.barrier()
+    R.check_status(status, stream)
+    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = elapsed_ms / args.steps
+    total_flops = 2.0 * M * N * K
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- optional all-gather of C over NVLink (not on the data path; reported separately)
+    allgather = None
+    if dist and world > 1 and M % world == 0:
+        full = torch.empty((M, N), device=dev, dtype=C.dtype)
+        for _ in range(2):
+            dist.all_gather_into_tensor(full, C)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            dist.all_gather_into_tensor(full, C)
+        e1.record()
+        torch.cuda.synchronize()
+        tg = torch.tensor([e0.elapsed_time(e1) / 5], device=dev, dtype=torch.float64)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        ag_ms = float(tg.item())
+        recv = (world - 1) * rows * N * C.element_size()
+        allgather = {"ms": round(ag_ms, 3), "recv_GBps_per_gpu": round(recv / (ag_ms * 1e-3) / 1e9, 1),
+                     "note": "ncclAllGather of the C shards, after the GEMM, not in `value`"}
+        del full
+
+    # ---- end to end: host buffers through the C-ABI call, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        hA = torch.empty(A.shape, dtype=A.dtype, pin_memory=True).copy_(A)
+        hB = torch.empty(B.shape, dtype=B.dtype, pin_memory=True).copy_(B)
+        hC = torch.empty(C.shape, dtype=C.dtype, pin_memory=True)
+        hsa = None if sa is None else sa.cpu()
+        hsb = None if sb is None else sb.cpu()
+        e2e_steps = max(1, min(args.steps, 5))
+        L = R.lib()
+
+        def host_step():
+            rc = L.frisk_b200_gemm_run_host(plan._h, hA.data_ptr(), hB.data_ptr(), hC.data_ptr(),
+                                            None if hsa is None else hsa.data_ptr(),
+                                            None if hsb is None else hsb.data_ptr())
+            if rc != 0:
+                raise SystemExit(f"frisk_b200_gemm_run_host failed: {rc}")
+
+        host_step()
+        if dist:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            host_step()  # synchronous: returns after C is back in host memory
+        dt = (time.perf_counter() - t0) / e2e_steps
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        if dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        h2d = hA.numel() * hA.element_size() + hB.numel() * hB.element_size()
+        if sa is not None:
+            h2d += 4 * (rows + N)
+        d2h = hC.numel() * hC.element_size()
+        e2e = {"value": round(total_flops / dt / 1e12, 3), "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "ms_per_step": round(dt * 1e3, 3), "steps": e2e_steps,
+               "api": "frisk_b200_gemm_run_host (pinned host buffers, per rank)"}
+        del hA, hB, hC
+    info = plan.info
+    plan.close()
+    del A, B, C
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    sustained = elapsed_ms > 500.0
+    roof = roofline_for(name, rows, N, K, ms_per_step, peaks, sustained)
+    line = {
+        "metric": "gemm_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": W.DTYPE_NAMES[AB_TYPE.get(name, W.BF16)], "data": "synthetic",
+        "config": {"workload": name, "M": M, "N": N, "K": K, "rows_per_gpu": rows,
+                   "sharding": f"rows of A and C over {world} GPU(s), B replicated, no collective",
+                   "accumulate": "fp32", "kernel": info["kernel_name"],
+                   "tile": f"{info['tile_m']}x{info['tile_n']}x{info['tile_k']}",
+                   "stages": info["stages"], "ctas": info["num_ctas"],
+                   "l2": "inputs larger than L2" if flush is None else "192 MiB written between iterations"},
+        "roofline": roof,
+        "clocks": clocks,
+        "gpu_launches": info["launches"] * args.steps,
+        "e2e": e2e,
+    }
+    if allgather:
+        line["allgather"] = allgather
+
+    if world == 1 and not args.no_others:
+        others = {}
+        for other in ("cfg1", "cfg2", "cfg3", "cfg4", "bf16_8192"):
+            if other == name:
+                continue
+            m, n, k = FULL_DIMS[other]
+            small = other in ("cfg1", "cfg2", "cfg3")  # inputs fit in L2: flush between launches
+            ms, oinfo = time_device(torch, R, other, m, n, k, max(args.steps, 10), args.warmup, dev,
+                                    seed=int(other[-1]) if other[-1].isdigit() else 5, flush_l2=small)
+            r = roofline_for(other, m, n, k, ms, peaks, sustained=False)
+            others[other] = {"ms": round(ms, 5), "kernel": oinfo["kernel_name"],
+                             "tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 2),
+                             "launches_per_step": oinfo["launches"], "roofline": r,
+                             "l2": "192 MiB written between iterations" if small else "inputs larger than L2"}
+        line["other_configs"] = others
+
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(name)
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

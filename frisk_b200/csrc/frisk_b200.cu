@@ -14,6 +14,7 @@
 
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 
 namespace {
 
@@ -127,7 +128,7 @@ void fill_operand(frisk::OperandParams& o, bool mn_major, uint32_t tile_mn, uint
   }
 }
 
-uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t n) {
+uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t m, uint32_t n) {
   uint32_t fmt = 0;  // kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3
   if (ab_type == FRISK_DT_BF16) fmt = 1;
   uint32_t d = 0;
@@ -137,7 +138,7 @@ uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t n) {
   d |= (a_mn_major ? 1u : 0u) << 15;
   d |= (b_mn_major ? 1u : 0u) << 16;
   d |= (n >> 3) << 17;
-  d |= (128u >> 4) << 24;
+  d |= (m >> 4) << 24;
   return d;
 }
 
@@ -200,7 +201,7 @@ bool tcgen05_eligible(const frisk_gemm_desc& d) {
   return true;
 }
 
-void plan_tcgen05(frisk_gemm_plan* pl, bool swap) {
+void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   const frisk_gemm_desc& d = pl->d;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
@@ -215,6 +216,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap) {
     cols = d.N;
     g.mi = 1;
     uint32_t tn = d.tile_n ? (uint32_t)d.tile_n : (cols > 128 ? 256u : (cols > 64 ? 128u : 64u));
+    if (pair && tn < 128) tn = 128;
     g.tile_n = tn;
   } else {
     // D = C^T: rows run over N (the weights), columns over M (the few activations rows)
@@ -227,8 +229,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap) {
   }
   g.bk_elems = bk;
   g.k_steps = 4;
+  // a CTA of a pair stages its own 128 rows of A and half of the tile's B columns
   fill_operand(g.a, a_mn, 128u * g.mi, es, bk);
-  fill_operand(g.b, b_mn, g.tile_n, es, bk);
+  fill_operand(g.b, b_mn, pair ? g.tile_n / 2 : g.tile_n, es, bk);
   g.stage_bytes = g.a.stage_bytes + g.b.stage_bytes;
   uint32_t stages = (uint32_t)(kMaxDynSmem / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
@@ -236,11 +239,12 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap) {
   g.stages = std::max<uint32_t>(stages, 1);
   g.acc_bufs = (2 * g.mi * g.tile_n <= 512) ? 2 : 1;
   g.tmem_cols = next_pow2_cols(g.acc_bufs * g.mi * g.tile_n);
-  g.idesc = make_idesc(d.a_type, a_mn, b_mn, g.tile_n);
+  g.idesc = make_idesc(d.a_type, a_mn, b_mn, pair ? 256u : 128u, g.tile_n);
   g.kind_f8 = d.a_type == FRISK_DT_E4M3;
   g.rows = (uint32_t)rows;
   g.cols = (uint32_t)cols;
-  g.tiles_r = (uint32_t)((rows + 128 * g.mi - 1) / (128 * g.mi));
+  const uint32_t tile_rows = pair ? 256u : 128u * g.mi;
+  g.tiles_r = (uint32_t)((rows + tile_rows - 1) / tile_rows);
   g.tiles_c = (uint32_t)((cols + g.tile_n - 1) / g.tile_n);
   g.num_kb = (uint32_t)((d.K + bk - 1) / bk);
   g.group_r = 16;
@@ -255,12 +259,17 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap) {
   const uint64_t units = swap ? tiles * g.num_kb : tiles;
   uint32_t ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)pl->sm_count);
   if (d.num_ctas > 0) ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)d.num_ctas);
+  if (pair) {  // one cluster of two CTAs per tile in flight
+    uint64_t pairs = std::min<uint64_t>(units, (uint64_t)pl->sm_count / 2);
+    if (d.num_ctas > 1) pairs = std::min<uint64_t>(pairs, (uint64_t)d.num_ctas / 2);
+    ctas = (uint32_t)(2 * std::max<uint64_t>(pairs, 1));
+  }
   pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024;
   pl->ws_bytes = swap ? (size_t)d.M * d.N * sizeof(float) : 0;
 
   frisk_gemm_plan_info& in = pl->info;
-  in.kernel = swap ? FRISK_KERNEL_SKINNY : FRISK_KERNEL_TCGEN05;
-  in.tile_m = swap ? (int)g.tile_n : 128 * (int)g.mi;
+  in.kernel = swap ? FRISK_KERNEL_SKINNY : (pair ? FRISK_KERNEL_TCGEN05_PAIR : FRISK_KERNEL_TCGEN05);
+  in.tile_m = swap ? (int)g.tile_n : (int)tile_rows;
   in.tile_n = swap ? 128 * (int)g.mi : (int)g.tile_n;
   in.tile_k = (int)bk;
   in.stages = (int)g.stages;
@@ -282,6 +291,31 @@ int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream
   }
   kern<<<pl->info.num_ctas, frisk::kGemmThreads, pl->dyn_smem, st>>>(pl->tmap_a, pl->tmap_b, g);
   FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
+template <typename TC>
+int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
+  auto kern = frisk::gemm_tcgen05_pair_kernel<TC>;
+  if (!pl->smem_attr_set) {
+    FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)pl->dyn_smem));
+    pl->smem_attr_set = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
+  cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = pl->dyn_smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
   return FRISK_OK;
 }
 
@@ -363,7 +397,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.tile_n != 0 && d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256)
     return FRISK_ERR_INVALID_ARGUMENT;
-  if (d.force_kernel < 0 || d.force_kernel > 3 || d.stages < 0 || d.num_ctas < 0)
+  if (d.force_kernel < 0 || d.force_kernel > 4 || d.stages < 0 || d.num_ctas < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
 
   frisk_gemm_plan* pl = new (std::nothrow) frisk_gemm_plan();
@@ -384,15 +418,24 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
 
   const bool tc_ok = tcgen05_eligible(d);
   const bool skinny_ok = tc_ok && d.M <= 64 && d.N >= 256 && !d.transA;
+  const bool pair_ok = tc_ok && d.M > 128 && d.N > 64 && d.tile_n != 64 && pl->sm_count >= 2;
   int kind;
   if (d.force_kernel) {
     kind = d.force_kernel - 1;
-    if ((kind == FRISK_KERNEL_TCGEN05 && !tc_ok) || (kind == FRISK_KERNEL_SKINNY && !skinny_ok)) {
+    if ((kind == FRISK_KERNEL_TCGEN05 && !tc_ok) || (kind == FRISK_KERNEL_SKINNY && !skinny_ok) ||
+        (kind == FRISK_KERNEL_TCGEN05_PAIR && !pair_ok)) {
       delete pl;
       return tc_ok ? FRISK_ERR_UNSUPPORTED : FRISK_ERR_MISALIGNED;
     }
   } else {
-    kind = skinny_ok ? FRISK_KERNEL_SKINNY : (tc_ok ? FRISK_KERNEL_TCGEN05 : FRISK_KERNEL_SIMT);
+    // The CTA-pair kernel is correct but not yet faster than the one-CTA kernel; it runs only
+    // when asked for (force_kernel or FRISK_B200_PAIR=1).
+    const char* want_pair = getenv("FRISK_B200_PAIR");
+    const bool use_pair = pair_ok && want_pair && want_pair[0] == '1';
+    kind = skinny_ok ? FRISK_KERNEL_SKINNY
+           : use_pair ? FRISK_KERNEL_TCGEN05_PAIR
+           : tc_ok    ? FRISK_KERNEL_TCGEN05
+                      : FRISK_KERNEL_SIMT;
   }
   if (kind == FRISK_KERNEL_SIMT) {
     pl->info.kernel = FRISK_KERNEL_SIMT;
@@ -402,7 +445,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     pl->info.num_ctas = (int)(((d.M + 63) / 64) * ((d.N + 63) / 64));
     pl->info.launches = 1;
   } else {
-    plan_tcgen05(pl, kind == FRISK_KERNEL_SKINNY);
+    plan_tcgen05(pl, kind == FRISK_KERNEL_SKINNY, kind == FRISK_KERNEL_TCGEN05_PAIR);
   }
   *out = pl;
   return FRISK_OK;
@@ -481,11 +524,20 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
     g.col_scale = sb;
   }
   int rc;
-  switch (d.c_type) {
-    case FRISK_DT_F32: rc = launch_tcgen05_t<float>(pl, g, st); break;
-    case FRISK_DT_F16: rc = launch_tcgen05_t<__half>(pl, g, st); break;
-    case FRISK_DT_BF16: rc = launch_tcgen05_t<__nv_bfloat16>(pl, g, st); break;
-    default: rc = FRISK_ERR_UNSUPPORTED;
+  if (pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) {
+    switch (d.c_type) {
+      case FRISK_DT_F32: rc = launch_pair_t<float>(pl, g, st); break;
+      case FRISK_DT_F16: rc = launch_pair_t<__half>(pl, g, st); break;
+      case FRISK_DT_BF16: rc = launch_pair_t<__nv_bfloat16>(pl, g, st); break;
+      default: rc = FRISK_ERR_UNSUPPORTED;
+    }
+  } else {
+    switch (d.c_type) {
+      case FRISK_DT_F32: rc = launch_tcgen05_t<float>(pl, g, st); break;
+      case FRISK_DT_F16: rc = launch_tcgen05_t<__half>(pl, g, st); break;
+      case FRISK_DT_BF16: rc = launch_tcgen05_t<__nv_bfloat16>(pl, g, st); break;
+      default: rc = FRISK_ERR_UNSUPPORTED;
+    }
   }
   if (rc) { pl->clean_ws = nullptr; return rc; }
   if (swap) {

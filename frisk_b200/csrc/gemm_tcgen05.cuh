@@ -26,6 +26,10 @@
 namespace frisk {
 
 constexpr int kMaxStages = 12;
+// Warps that wait for a long time sleep between polls: a tight polling loop takes issue slots
+// from the MMA warp on the same SM sub-partition and nearly halves its issue rate.
+constexpr uint32_t kEpilogueBackoffNs = 128;
+constexpr uint32_t kProducerBackoffNs = 32;
 constexpr int kProducerWarps = 2;  // warps 0 and 6 issue the TMA loads of alternate k-blocks
 constexpr int kGemmThreads = 224;
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock per wait, far above any legitimate wait
@@ -331,7 +335,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
-  const uint32_t tmem_base = tmem_base_slot;
+  // broadcast: a value loaded from shared memory is not warp-uniform for the compiler otherwise
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_slot, 0);
 
   WorkIter work;
   work.init(p.num_kb, p.split_mode, tiles_r * tiles_c);
@@ -364,7 +369,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           turn ^= 1u;
           ok = bounded_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status,
-                            kStatusProducerTimeout);
+                            kStatusProducerTimeout, kProducerBackoffNs);
           if (!ok) break;
           const uint32_t full = full0 + 8 * stage;
           const bool tr_on = trace && issued < 32 && warp == 0;
@@ -521,7 +526,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tile_coords(group_r, tiles_r, tiles_c, work.tile, tr, tc);
       // the tcgen05.ld below is warp-collective: leave the loop only as a whole warp
       ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
-                        (debug_mode & 4u) ? 256u : 0u);
+                        kEpilogueBackoffNs);
       if (!ok) break;
       ptx::tc_fence_after();
       if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item] = clock64();

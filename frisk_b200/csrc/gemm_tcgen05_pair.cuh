@@ -1,0 +1,322 @@
+// The GEMM of gemm_tcgen05.cuh run by PAIRS of CTAs (a cluster of two, one CTA per SM of a TPC)
+// with two-SM MMAs (tcgen05.mma.cta_group::2).  A pair owns a 256 x tile_n output tile: each CTA
+// holds the accumulator of 128 of its rows in its own tensor memory, loads its own 128 rows of A
+// and only HALF of B's tile_n columns; the hardware shares the B halves between the two SMs.
+// Against the one-CTA kernel this cuts, per output element, the bytes each SM pulls from L2 by a
+// third and the shared-memory traffic (TMA writes + operand reads) from about 192 to 128 bytes
+// per clock, which is what the one-CTA kernel is bound by.
+//
+// Roles per CTA (224 threads) as in the one-CTA kernel: warps 0 and 6 produce, warp 1 issues MMAs
+// (in the leader CTA only), warps 2-5 run the epilogue.  Barriers:
+//   full[s]      in the leader: both CTAs' producers arrive (with their byte counts) and both
+//                CTAs' TMA loads report their bytes there;
+//   empty[s]     in each CTA: the leader's MMA warp commits to both;
+//   acc_full[b]  in each CTA: the leader commits to both after the last k-block of a tile;
+//   acc_empty[b] in the leader: the four epilogue warps of both CTAs arrive.
+// No load is shared between the CTAs: each fetches its own boxes with ordinary TMA.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace frisk {
+
+template <typename TC>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ uint32_t abort_word;
+
+  const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
+  const uint32_t lane = threadIdx.x & 31;
+  // values that come out of inline PTX or shared memory are broadcast so that the compiler can
+  // treat them (and the branches on them) as warp-uniform
+  const uint32_t rank = __shfl_sync(0xffffffffu, ptx::cluster_ctarank(), 0);  // 0 = leader
+  const uint32_t pair = blockIdx.x >> 1;
+  const uint32_t num_pairs = gridDim.x >> 1;
+  volatile uint32_t* abort_flag = &abort_word;
+
+  const uint32_t tiles_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t full0 = ptx::smem_u32(&bar_full[0]);
+  const uint32_t empty0 = ptx::smem_u32(&bar_empty[0]);
+  const uint32_t acc_full0 = ptx::smem_u32(&bar_acc_full[0]);
+  const uint32_t acc_empty0 = ptx::smem_u32(&bar_acc_empty[0]);
+  // the same locations in the leader / in the other CTA (cluster-window addresses)
+  const uint32_t leader_full0 = __shfl_sync(0xffffffffu, ptx::mapa(full0, 0), 0);
+  const uint32_t leader_acc_empty0 = __shfl_sync(0xffffffffu, ptx::mapa(acc_empty0, 0), 0);
+  const uint32_t peer_empty0 = __shfl_sync(0xffffffffu, ptx::mapa(empty0, rank ^ 1u), 0);
+  const uint32_t peer_acc_full0 = __shfl_sync(0xffffffffu, ptx::mapa(acc_full0, rank ^ 1u), 0);
+  const uint32_t peer_abort = __shfl_sync(0xffffffffu, ptx::mapa(ptx::smem_u32(&abort_word), rank ^ 1u), 0);
+
+  const uint32_t stages = p.stages;
+  const uint32_t stage_bytes = p.stage_bytes;  // per CTA
+  const uint32_t tile_n = p.tile_n;
+  const uint32_t tmem_cols = p.tmem_cols;
+  const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r;
+  const uint32_t num_tiles = tiles_r * tiles_c;
+  const uint32_t num_kb = p.num_kb;
+  int32_t* const status = p.status;
+  const uint32_t debug_mode = p.debug_mode;
+  long long* const trace = blockIdx.x == 0 ? p.trace : nullptr;
+
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (uint32_t s = 0; s < stages; ++s) {
+      ptx::mbar_init(full0 + 8 * s, 2);  // one producer arrival per CTA
+      ptx::mbar_init(empty0 + 8 * s, 1);
+    }
+    for (uint32_t i = 0; i < 2; ++i) {
+      ptx::mbar_init(acc_full0 + 8 * i, 1);
+      ptx::mbar_init(acc_empty0 + 8 * i, 8);  // four epilogue warps in each CTA
+    }
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_slot), tmem_cols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers must be initialised before either signals the other
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_slot, 0);
+
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------- TMA producers (both CTAs)
+    const uint32_t a_boxes = p.a.num_boxes, a_box_bytes = p.a.box_bytes, a_box_mn = p.a.box_mn;
+    const uint32_t b_boxes = p.b.num_boxes, b_box_bytes = p.b.box_bytes, b_box_mn = p.b.box_mn;
+    const uint32_t a_mn_major = p.a.mn_major, b_mn_major = p.b.mn_major;
+    const uint32_t a_stage_bytes = p.a.stage_bytes;
+    const uint32_t bk_elems = p.bk_elems;
+    const uint32_t my_turn = warp == 0 ? 0u : 1u;
+    uint32_t stage = 0, phase = 0, turn = 0;
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      uint32_t tr, tc;
+      tile_coords(group_r, tiles_r, tiles_c, tile, tr, tc);
+      const int32_t r0 = (int32_t)(tr * 256u + rank * 128u);
+      const int32_t c0 = (int32_t)(tc * tile_n + rank * (tile_n >> 1));
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        if (turn != my_turn) {  // the other producer warp loads this k-block
+          turn ^= 1u;
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+          continue;
+        }
+        turn ^= 1u;
+        ok = bounded_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status,
+                          kStatusProducerTimeout, kProducerBackoffNs);
+        if (!ok) break;
+        const uint32_t full = leader_full0 + 8 * stage;
+        if (debug_mode & 1u) {
+          if (ptx::elect_one()) ptx::mbar_arrive_cluster(full);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1;
+          }
+          continue;
+        }
+        if (ptx::elect_one()) ptx::mbar_arrive_expect_tx_cluster(full, stage_bytes);
+        const uint32_t a_dst = tiles_base + stage * stage_bytes;
+        const uint32_t b_dst = a_dst + a_stage_bytes;
+        const int32_t k0 = (int32_t)(kb * bk_elems);
+        for (uint32_t bx = 0; bx < a_boxes; ++bx) {
+          const int32_t mn = r0 + (int32_t)(bx * a_box_mn);
+          const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
+          if (ptx::elect_one()) ptx::tma_load_2d_pair(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
+        }
+        for (uint32_t bx = 0; bx < b_boxes; ++bx) {
+          const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
+          const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
+          if (ptx::elect_one()) ptx::tma_load_2d_pair(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
+        }
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok) {
+      // tell the other CTA, then give copies in flight time to land (a copy takes a few
+      // microseconds at most; this waits about 50)
+      if (ptx::elect_one()) ptx::st_shared_cluster_u32(peer_abort, 1);
+      const long long t0 = clock64();
+      while (clock64() - t0 < 100000ll) {
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer (leader only)
+    if (rank == 0) {
+      const uint64_t a_desc_base = p.a.desc_base, b_desc_base = p.b.desc_base;
+      const uint32_t a_k_step = p.a.k_step_bytes, b_k_step = p.b.k_step_bytes;
+      const uint32_t a_stage_bytes = p.a.stage_bytes;
+      const uint32_t idesc = p.idesc;
+      const uint32_t kind_f8 = p.kind_f8;
+      uint32_t stage = 0, phase = 0, item = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        const uint32_t acc = item & 1u;
+        const uint32_t acc_phase = (item >> 1) & 1u;
+        ok = bounded_wait(acc_empty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
+                          kStatusMmaTimeout);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t d_base = tmem_base + acc * tile_n;
+        // as in the one-CTA kernel: a stage is released after the first MMA of the next k-block,
+        // and the next barrier is polled before the last MMA of the current one
+        uint32_t prev_stage = 0;
+        bool have_prev = false;
+        uint32_t ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * stage, phase));
+        long long sec_a = 0, sec_b = 0, sec_c = 0, t_prev = clock64();
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          const long long t_top = clock64();
+          sec_c += t_top - t_prev;
+          const bool tr_top = trace && item == 1 && kb < 32;
+          if (tr_top && ptx::elect_one()) {
+            trace[64 + 3 * kb] = clock64();
+            trace[64 + 3 * kb + 1] = ready;
+          }
+          if (!ready) {
+            ok = bounded_wait_slow(full0 + 8 * stage, phase, abort_flag, status, kStatusMmaTimeout,
+                                   0);
+            if (!ok) break;
+          }
+          if (tr_top && ptx::elect_one()) trace[64 + 3 * kb + 2] = clock64();
+          ptx::tc_fence_after();
+          const uint32_t a_addr = tiles_base + stage * stage_bytes;
+          const uint32_t b_addr = a_addr + a_stage_bytes;
+          const uint64_t adesc0 = a_desc_base | (uint64_t)((a_addr & 0x3FFFFu) >> 4);
+          const uint64_t bdesc0 = b_desc_base | (uint64_t)((b_addr & 0x3FFFFu) >> 4);
+          const uint32_t first = kb > 0 ? 1u : 0u;
+          uint32_t next_stage = stage + 1, next_phase = phase;
+          if (next_stage == stages) {
+            next_stage = 0;
+            next_phase ^= 1;
+          }
+          const bool tr_on = false;
+          const long long t_mid = clock64();
+          sec_a += t_mid - t_top;
+          if (debug_mode & 2u) {
+            if (ptx::elect_one()) ptx::mbar_arrive_cluster(empty0 + 8 * stage);
+            if (ptx::elect_one()) ptx::mbar_arrive_cluster(peer_empty0 + 8 * stage);
+            ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+            stage = next_stage;
+            phase = next_phase;
+            continue;
+          }
+#pragma unroll
+          for (uint32_t ks = 0; ks < 4; ++ks) {
+            const uint64_t bdesc = bdesc0 + (uint64_t)((ks * b_k_step) >> 4);
+            const uint64_t adesc = adesc0 + (uint64_t)((ks * a_k_step) >> 4);
+            const uint32_t accumulate = first | (ks > 0 ? 1u : 0u);
+            if (ks == 3)
+              ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+            if (kind_f8) {
+              if (ptx::elect_one()) ptx::mma_f8_pair(d_base, adesc, bdesc, idesc, accumulate);
+            } else {
+              if (ptx::elect_one()) ptx::mma_f16_pair(d_base, adesc, bdesc, idesc, accumulate);
+            }
+            if (tr_on && ptx::elect_one()) trace[128 + 8 * kb + ks] = clock64();
+            if (ks == 0 && have_prev) {
+              if (debug_mode & 8u) {
+                if (ptx::elect_one()) ptx::tc_commit_pair_both(empty0 + 8 * prev_stage, 3u);
+              } else {
+                if (ptx::elect_one()) ptx::tc_commit_pair(empty0 + 8 * prev_stage);
+                if (ptx::elect_one()) ptx::tc_commit_pair(peer_empty0 + 8 * prev_stage);
+              }
+              if (tr_on && ptx::elect_one()) trace[128 + 8 * kb + 4] = clock64();
+            }
+          }
+          t_prev = clock64();
+          sec_b += t_prev - t_mid;
+          prev_stage = stage;
+          have_prev = true;
+          stage = next_stage;
+          phase = next_phase;
+        }
+        if (trace && item == 1 && ptx::elect_one()) {
+          trace[400] = sec_a;
+          trace[401] = sec_b;
+          trace[402] = sec_c;
+        }
+        if (!ok) break;
+        if (have_prev) {
+          if (ptx::elect_one()) ptx::tc_commit_pair(empty0 + 8 * prev_stage);
+          if (ptx::elect_one()) ptx::tc_commit_pair(peer_empty0 + 8 * prev_stage);
+        }
+        if (ptx::elect_one()) ptx::tc_commit_pair(acc_full0 + 8 * acc);
+        if (ptx::elect_one()) ptx::tc_commit_pair(peer_acc_full0 + 8 * acc);
+        ++item;
+      }
+      if (!ok && ptx::elect_one()) ptx::st_shared_cluster_u32(peer_abort, 1);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------- epilogue (both CTAs)
+    EpiArgs ep;
+    ep.C = p.C;
+    ep.ws = p.ws;
+    ep.row_scale = p.row_scale;
+    ep.col_scale = p.col_scale;
+    ep.ldc = p.ldc;
+    ep.ws_ld = p.ws_ld;
+    ep.rows = p.rows;
+    ep.cols = p.cols;
+    ep.split_mode = 0;
+    ep.transposed_out = 0;
+    ep.clear_accum = p.clear_accum;
+    ep.c_vec_ok = p.c_vec_ok;
+    const uint32_t quarter = warp & 3u;
+    uint32_t item = 0;
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      const uint32_t acc = item & 1u;
+      const uint32_t acc_phase = (item >> 1) & 1u;
+      uint32_t tr, tc;
+      tile_coords(group_r, tiles_r, tiles_c, tile, tr, tc);
+      ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
+                        kEpilogueBackoffNs);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const uint32_t row = tr * 256u + rank * 128u + quarter * 32u + lane;
+      const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + acc * tile_n;
+      for (uint32_t cc = 0; cc < tile_n; cc += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(t_row + cc, v);
+        ptx::tmem_ld_wait();
+        epilogue_store<TC, 32>(ep, row, tc * tile_n + cc, v);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(leader_acc_empty0 + 8 * acc);
+      ++item;
+    }
+    if (!ok && lane == 0) ptx::st_shared_cluster_u32(peer_abort, 1);
+    __syncwarp();
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  // Neither CTA may exit (or free tensor memory) while the other can still signal its barriers.
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, tmem_cols);
+  }
+}
+
+}  // namespace frisk

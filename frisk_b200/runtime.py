@@ -19,7 +19,7 @@ from . import workloads as W
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfrisk_b200.so")
 
-KERNEL_NAMES = {0: "simt", 1: "tcgen05", 2: "skinny"}
+KERNEL_NAMES = {0: "simt", 1: "tcgen05", 2: "skinny", 3: "tcgen05_pair"}
 
 
 class FriskError(RuntimeError):
@@ -169,7 +169,7 @@ class GemmPlan:
         d.transA, d.transB = int(transA), int(transB)
         d.clear_accum = int(clear_accum)
         d.scale_mode = 1 if scales else 0
-        d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2}[force_kernel]
+        d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2, "tcgen05_pair": 3}[force_kernel]
         d.tile_n, d.stages, d.num_ctas = tile_n, stages, num_ctas
         self.desc = d
         self._h = C.c_void_p()

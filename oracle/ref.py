@@ -113,3 +113,20 @@ def ref_gemm_f64(w: W.GemmWorkload, rows: Optional[np.ndarray] = None) -> np.nda
         c0 = W.decode(w.C0, w.c_type).astype(np.float64)
         c = c + (c0[rows] if rows is not None else c0)
     return c
+
+
+def abs_dot(w: W.GemmWorkload, rows: Optional[np.ndarray] = None) -> np.ndarray:
+    """sum_k |A[m,k]| |B[k,n]| (times |scales|): the magnitude of the data behind each output,
+    used as the floor of the relative-error metric."""
+    a = np.abs(w.a_logical().astype(np.float64))
+    b = np.abs(w.b_logical().astype(np.float64))
+    if rows is not None:
+        a = a[rows]
+    s = a @ b
+    if w.scale_a is not None:
+        sa = np.abs(w.scale_a.astype(np.float64))
+        s = s * (sa[rows] if rows is not None else sa)[:, None] * np.abs(w.scale_b.astype(np.float64))[None, :]
+    if not w.clear_accum and w.C0 is not None:
+        c0 = np.abs(W.decode(w.C0, w.c_type).astype(np.float64))
+        s = s + (c0[rows] if rows is not None else c0)
+    return s

@@ -1,0 +1,128 @@
+"""Host-side checks of the C ABI that need no GPU: every declared symbol is exported, plans pick
+the expected kernel family, argument errors map to the documented codes, row sharding and the
+layout mapping are right.  No compute call is made here."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from frisk_b200 import runtime as R
+from frisk_b200 import workloads as W
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "frisk_b200.h")).read()
+    return sorted(set(re.findall(r"\b(frisk_b200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = C.CDLL(R.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/frisk_b200.h but not exported"
+
+
+def test_version_and_strerror():
+    assert "sm_100a" in R.version()
+    L = R.lib()
+    assert L.frisk_b200_strerror(0) == b"ok"
+    for code in range(-9, 0):
+        assert L.frisk_b200_strerror(code) not in (b"", b"unknown error")
+    assert L.frisk_b200_strerror(-99) == b"unknown error"
+
+
+@pytest.mark.parametrize("name,kernel", [
+    ("cfg1", "simt"), ("cfg2", "tcgen05"), ("cfg3", "skinny"), ("cfg4", "tcgen05"),
+    ("cfg5", "tcgen05"), ("bf16_8192", "tcgen05"),
+])
+def test_plan_picks_kernel_family_for_the_benchmark_configs(name, kernel):
+    full = {"cfg1": (512, 512, 512), "cfg2": (4096, 4096, 4096), "cfg3": (16, 8192, 8192),
+            "cfg4": (8192, 8192, 8192), "cfg5": (65536, 8192, 8192),
+            "bf16_8192": (8192, 8192, 8192)}[name]
+    ab = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3}.get(name, W.BF16)
+    ct = {"cfg1": W.F32, "cfg2": W.F16}.get(name, W.BF16)
+    plan = R.GemmPlan(*full, ab, ct, transB=name in ("cfg2", "cfg4"), scales=name == "cfg4")
+    assert plan.info["kernel_name"] == kernel
+    if kernel == "skinny":
+        assert plan.info["swap_ab"] == 1 and plan.info["split_k"] == 1
+        assert plan.workspace_bytes == 16 * 8192 * 4
+        assert plan.info["launches"] == 2
+    else:
+        assert plan.workspace_bytes == 0 and plan.info["launches"] == 1
+    if kernel != "simt":
+        assert plan.info["smem_bytes"] <= 227 * 1024
+        assert plan.info["swizzle_a"] == 128 and plan.info["swizzle_b"] == 128
+    plan.close()
+
+
+def test_plan_falls_back_to_simt_for_unaligned_leading_dimensions():
+    p = R.GemmPlan(100, 100, 100, W.BF16, lda=101, ldb=100)  # 202-byte rows: no TMA
+    assert p.info["kernel_name"] == "simt"
+    p.close()
+    p = R.GemmPlan(100, 104, 104, W.BF16)
+    assert p.info["kernel_name"] == "tcgen05"
+    p.close()
+    p = R.GemmPlan(128, 128, 128, W.E4M3, W.BF16, transB=False)  # fp8 MN-major B: CUDA cores
+    assert p.info["kernel_name"] == "simt"
+    p.close()
+
+
+def test_plan_create_rejects_bad_descriptions():
+    for kw in (dict(M=0), dict(K=-1), dict(lda=3), dict(ldc=5)):
+        args = dict(M=8, N=8, K=8)
+        args.update({k: v for k, v in kw.items() if k in args})
+        extra = {k: v for k, v in kw.items() if k not in args}
+        with pytest.raises(R.FriskError) as e:
+            R.GemmPlan(args["M"], args["N"], args["K"], W.F32, **extra)
+        assert e.value.code == -1
+    L = R.lib()
+    d = R.GemmDesc()
+    d.M = d.N = d.K = 8
+    d.a_type, d.b_type, d.c_type = W.F16, W.BF16, W.F16  # ffi/ir.cpp:357-359: one element type
+    h = C.c_void_p()
+    assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -1
+    assert L.frisk_b200_gemm_plan_create(None, C.byref(h)) == -1
+    d.b_type = W.F16
+    d.c_type = W.E4M3
+    assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -2
+    with pytest.raises(R.FriskError) as e:
+        R.GemmPlan(100, 100, 100, W.BF16, lda=101, force_kernel="tcgen05")
+    assert e.value.code == -3
+
+
+def test_run_without_device_reports_no_device_or_runs():
+    import torch
+
+    plan = R.GemmPlan(8, 8, 8, W.F32)
+    a = np.zeros((8, 8), np.float32)
+    if not torch.cuda.is_available():
+        with pytest.raises(R.FriskError) as e:
+            plan.run_host(a, a, a.copy())
+        assert e.value.code == -7
+    L = R.lib()
+    assert L.frisk_b200_gemm_run(None, None, None, None, None, None, None, 0, None, None) == -1
+    plan.close()
+
+
+@pytest.mark.parametrize("M,P", [(65536, 1), (65536, 2), (65536, 4), (65536, 8), (10, 3), (7, 8), (0, 4)])
+def test_shard_rows_partitions_every_row_once(M, P):
+    covered = []
+    for r in range(P):
+        row0, rows = R.shard_rows(M, P, r)
+        covered.extend(range(row0, row0 + rows))
+        assert rows in (M // P, M // P + 1)
+    assert covered == list(range(M))
+    if M % P == 0 and M:
+        assert R.shard_rows(M, P, P - 1) == (M - M // P, M // P)
+
+
+def test_shard_rows_errors():
+    for bad in ((8, 0, 0), (8, 4, 4), (8, 4, -1)):
+        with pytest.raises(R.FriskError) as e:
+            R.shard_rows(*bad)
+        assert e.value.code == -8

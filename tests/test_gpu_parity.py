@@ -1,0 +1,307 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  Tolerances (written where they are applied, frisk_b200/workloads.py::check):
+fp32 -> relative Frobenius error <= 1e-4; fp16/bf16 -> max relative error <= 1e-2;
+e4m3 (after scaling) -> max relative error <= 2e-2.  Full-size configurations are checked on
+sampled rows plus size-independent properties (exact scaling by two, row-permutation equivariance,
+zero-padding of K, run-to-run bit equality for the kernels that do not use atomics)."""
+import numpy as np
+import pytest
+
+from frisk_b200 import runtime as R
+from frisk_b200 import workloads as W
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+
+
+def sub_rows(w, rows):
+    """The workload restricted to some rows of A (and of C): what the oracle is run on when the
+    full problem is too large for a CPU loop."""
+    s = W.GemmWorkload(w.name, len(rows), w.N, w.K, w.ab_type, w.c_type, transA=w.transA,
+                       transB=w.transB, clear_accum=w.clear_accum, seed=w.seed, B=w.B,
+                       scale_b=w.scale_b)
+    s.A = np.ascontiguousarray(w.A[:, rows] if w.transA else w.A[rows])
+    s.scale_a = None if w.scale_a is None else w.scale_a[rows]
+    s.C0 = None if w.C0 is None else w.C0[rows]
+    return s
+
+
+def run_and_check(w, rows=None, **plan_kw):
+    plan = R.GemmPlan.for_workload(w, **plan_kw)
+    info = plan.info
+    plan.close()
+    out = R.gemm_host(w, **plan_kw)
+    got = W.decode(out, w.c_type)
+    wo = w
+    if rows is not None:
+        got = got[rows]
+        wo = sub_rows(w, rows)
+    want64 = ref.ref_gemm_f64(wo)
+    floor = ref.abs_dot(wo)
+    oracle = W.decode(ref.ref_gemm(wo), wo.c_type)
+    ok, err, metric = W.check(got, want64, w.ab_type, absdot=floor)
+    assert ok, f"{w.name} {w.M}x{w.N}x{w.K} via {info['kernel_name']}: {metric} = {err:.3e} vs float64"
+    ok, err, metric = W.check(got, oracle, w.ab_type, absdot=floor)
+    assert ok, f"{w.name} via {info['kernel_name']}: {metric} = {err:.3e} vs the fp32 oracle"
+    return out, info
+
+
+# ----------------------------------------------------------------------------- small cases
+SMALL = [
+    # (workload, (M, N, K), expected kernel)
+    ("cfg1", (512, 512, 512), "simt"),
+    ("cfg1", (70, 50, 33), "simt"),
+    ("cfg1", (1, 1, 1), "simt"),
+    ("cfg2", (128, 256, 64), "tcgen05"),
+    ("cfg2", (128, 64, 128), "tcgen05"),
+    ("cfg2", (256, 512, 512), "tcgen05"),
+    ("cfg2", (200, 300, 136), "tcgen05"),
+    ("cfg2", (1, 8, 8), "tcgen05"),
+    ("cfg5", (128, 256, 64), "tcgen05"),
+    ("cfg5", (520, 392, 264), "tcgen05"),
+    ("cfg5", (130, 264, 72), "tcgen05"),
+    ("cfg4", (128, 256, 128), "tcgen05"),
+    ("cfg4", (200, 300, 400), "tcgen05"),
+    ("cfg3", (16, 256, 64), "skinny"),
+    ("cfg3", (16, 1024, 4096), "skinny"),
+    ("cfg3", (5, 1000, 520), "skinny"),
+    ("cfg3", (48, 2048, 1024), "skinny"),
+    ("cfg3", (64, 512, 256), "skinny"),
+]
+
+
+@pytest.mark.parametrize("name,dims,kernel", SMALL)
+def test_small_cases_match_oracle(name, dims, kernel):
+    w = W.make_workload(name, *dims)
+    _, info = run_and_check(w)
+    assert info["kernel_name"] == kernel
+
+
+@pytest.mark.parametrize("force", ["simt", "tcgen05", "tcgen05_pair"])
+@pytest.mark.parametrize("name,dims", [("cfg2", (300, 200, 136)), ("cfg5", (520, 392, 264)),
+                                       ("cfg4", (256, 256, 256))])
+def test_every_kernel_family_agrees(name, dims, force):
+    w = W.make_workload(name, *dims)
+    _, info = run_and_check(w, force_kernel=force)
+    assert info["kernel_name"] == force
+
+
+def test_tile_width_and_stage_overrides():
+    w = W.make_workload("cfg2", 384, 640, 320)
+    for tile_n in (64, 128, 256):
+        for stages in (1, 2, 0):
+            _, info = run_and_check(w, tile_n=tile_n, stages=stages, force_kernel="tcgen05")
+            assert info["tile_n"] == tile_n
+    _, info = run_and_check(w, num_ctas=3, force_kernel="tcgen05")
+    assert info["num_ctas"] == 3
+    w = W.make_workload("cfg3", 16, 2048, 2048)
+    for ctas in (1, 7, 0):
+        run_and_check(w, num_ctas=ctas)
+
+
+@pytest.mark.parametrize("ab", [W.F32, W.F16, W.BF16])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_all_storage_orders(ab, ta, tb):
+    rng = np.random.default_rng(11)
+    M, N, K = 136, 264, 200
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * 0.1).astype(np.float32)
+    w = W.GemmWorkload("orders", M, N, K, ab, ab, transA=ta, transB=tb,
+                       A=np.ascontiguousarray(W.encode(a, ab).T if ta else W.encode(a, ab)),
+                       B=np.ascontiguousarray(W.encode(b, ab).T if tb else W.encode(b, ab)))
+    _, info = run_and_check(w)
+    assert info["kernel_name"] == ("simt" if ab == W.F32 else "tcgen05")
+
+
+@pytest.mark.parametrize("name,dims", [("cfg1", (96, 80, 64)), ("cfg2", (256, 256, 128)),
+                                       ("cfg3", (16, 512, 512)), ("cfg4", (128, 256, 256))])
+def test_accumulate_into_c(name, dims):
+    w = W.make_workload(name, *dims)
+    rng = np.random.default_rng(5)
+    w.clear_accum = False
+    w.C0 = W.encode(rng.standard_normal((w.M, w.N)).astype(np.float32), w.c_type)
+    run_and_check(w)
+
+
+def test_mixed_output_types_and_padded_leading_dimensions():
+    rng = np.random.default_rng(9)
+    M, N, K = 130, 200, 96
+    for ct in (W.F32, W.F16, W.BF16):
+        w = W.make_workload("cfg5", M, N, K)
+        w.c_type = ct
+        run_and_check(w)
+    # leading dimensions larger than the rows: lda = K + 8, ldb = N + 16, ldc = N + 24
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    A = np.zeros((M, K + 8), np.uint16)
+    B = np.zeros((K, N + 16), np.uint16)
+    A[:, :K] = W.bf16_encode(a)
+    B[:, :N] = W.bf16_encode(b)
+    Cbuf = np.full((M, N + 24), 0x7FC0, np.uint16)  # NaN canaries in the padding
+    plan = R.GemmPlan(M, N, K, W.BF16, lda=K + 8, ldb=N + 16, ldc=N + 24)
+    assert plan.info["kernel_name"] == "tcgen05"
+    plan.run_host(A, B, Cbuf)
+    plan.close()
+    assert (Cbuf[:, N:] == 0x7FC0).all(), "the kernel wrote outside its columns"
+    w = W.GemmWorkload("ld", M, N, K, W.BF16, W.BF16, A=W.bf16_encode(a), B=W.bf16_encode(b))
+    ok, err, _ = W.check(W.bf16_decode(Cbuf[:, :N]), ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
+    assert ok, err
+
+
+def test_guard_bands_around_c_and_workspace_stay_untouched():
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    for name, dims in (("cfg2", (200, 300, 136)), ("cfg3", (16, 1000, 520)), ("cfg1", (70, 50, 33))):
+        w = W.make_workload(name, *dims)
+        plan = R.GemmPlan.for_workload(w)
+        cs = W.ELEM_SIZE[w.c_type]
+        guard = 4096
+        cbuf = torch.full((guard * 2 + w.M * w.N * cs,), 0xAB, dtype=torch.uint8, device=dev)
+        wsbuf = torch.full((guard * 2 + max(plan.workspace_bytes, 16),), 0xCD, dtype=torch.uint8, device=dev)
+        A = torch.from_numpy(np.ascontiguousarray(w.A).view(np.uint8).reshape(-1)).to(dev)
+        B = torch.from_numpy(np.ascontiguousarray(w.B).view(np.uint8).reshape(-1)).to(dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ws_ptr = wsbuf.data_ptr() + guard
+        rc = R.lib().frisk_b200_gemm_run(plan._h, A.data_ptr(), B.data_ptr(), cbuf.data_ptr() + guard,
+                                         None, None, ws_ptr, plan.workspace_bytes, status.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        R.check_status(status)
+        assert (cbuf[:guard] == 0xAB).all() and (cbuf[-guard:] == 0xAB).all()
+        assert (wsbuf[:guard] == 0xCD).all() and (wsbuf[guard + plan.workspace_bytes:] == 0xCD).all()
+        got = cbuf[guard:guard + w.M * w.N * cs].cpu().numpy().view(W.storage_numpy_dtype(w.c_type))
+        ok, err, _ = W.check(W.decode(got.reshape(w.M, w.N), w.c_type), ref.ref_gemm_f64(w), w.ab_type,
+                             absdot=ref.abs_dot(w))
+        assert ok, err
+        plan.close()
+
+
+def test_run_argument_errors_on_device():
+    torch = pytest.importorskip("torch")
+    w = W.make_workload("cfg3", 16, 512, 512)
+    plan = R.GemmPlan.for_workload(w)
+    dev = torch.device("cuda:0")
+    buf = torch.zeros(16 * 512 * 512, dtype=torch.uint8, device=dev)
+    L = R.lib()
+    # split plan without a workspace / with a short one
+    assert L.frisk_b200_gemm_run(plan._h, buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), None, None,
+                                 None, 0, None, None) == -4
+    assert L.frisk_b200_gemm_run(plan._h, buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), None, None,
+                                 buf.data_ptr(), 16, None, None) == -4
+    plan.close()
+    w = W.make_workload("cfg4", 128, 128, 128)
+    plan = R.GemmPlan.for_workload(w)
+    assert L.frisk_b200_gemm_run(plan._h, buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), None, None,
+                                 None, 0, None, None) == -1  # scales requested but missing
+    plan.close()
+
+
+def test_misaligned_pointers_take_the_cuda_core_kernel():
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    w = W.make_workload("cfg5", 128, 128, 128)
+    plan = R.GemmPlan.for_workload(w)
+    assert plan.info["kernel_name"] == "tcgen05"
+    A = torch.zeros(w.A.size * 2 + 64, dtype=torch.uint8, device=dev)
+    A[2:2 + w.A.size * 2] = torch.from_numpy(w.A.view(np.uint8).reshape(-1)).to(dev)  # 2-byte offset
+    B = torch.from_numpy(w.B.view(np.uint8).reshape(-1)).to(dev)
+    Cd = torch.zeros(w.M * w.N * 2, dtype=torch.uint8, device=dev)
+    plan.run(A.data_ptr() + 2, B, Cd)
+    torch.cuda.synchronize()
+    got = W.bf16_decode(Cd.cpu().numpy().view(np.uint16).reshape(w.M, w.N))
+    ok, err, _ = W.check(got, ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
+    assert ok, err
+    plan.close()
+
+
+# ----------------------------------------------------------------------------- exact properties
+@pytest.mark.parametrize("name,dims", [("cfg2", (512, 768, 1024)), ("cfg5", (512, 768, 1024)),
+                                       ("cfg4", (512, 512, 1024)), ("cfg1", (200, 136, 300))])
+def test_exact_properties(name, dims):
+    w = W.make_workload(name, *dims)
+    base = R.gemm_host(w)
+    # bit-identical on a second run (no atomics in these kernels)
+    assert np.array_equal(base, R.gemm_host(w))
+    # permuting the rows of A permutes the rows of C bit-exactly
+    perm = np.random.default_rng(1).permutation(w.M)
+    w2 = W.make_workload(name, *dims)
+    w2.A = np.ascontiguousarray(w.A[perm])
+    if w2.scale_a is not None:
+        w2.scale_a = w.scale_a[perm]
+    assert np.array_equal(R.gemm_host(w2), base[perm])
+    # doubling A doubles C exactly (power-of-two scaling commutes with rounding)
+    if name != "cfg4":
+        w3 = W.make_workload(name, *dims)
+        w3.A = W.encode(W.decode(w.A, w.ab_type) * 2.0, w.ab_type)
+        got = W.decode(R.gemm_host(w3), w.c_type)
+        assert np.array_equal(got, 2.0 * W.decode(base, w.c_type))
+    # appending zero columns to K changes nothing
+    pad = 64
+    w4 = W.make_workload(name, *dims)
+    w4.K = w.K + pad
+    za = np.zeros((w.M, pad), w.A.dtype)
+    w4.A = np.ascontiguousarray(np.concatenate([w.A, za], axis=1))
+    if w.transB:
+        w4.B = np.ascontiguousarray(np.concatenate([w.B, np.zeros((w.N, pad), w.B.dtype)], axis=1))
+    else:
+        w4.B = np.ascontiguousarray(np.concatenate([w.B, np.zeros((pad, w.N), w.B.dtype)], axis=0))
+    assert np.array_equal(R.gemm_host(w4), base)
+
+
+# ----------------------------------------------------------------------------- full configurations
+def sampled_rows(M, n=48, seed=7):
+    n = min(n, M)
+    return np.sort(np.random.default_rng(seed).choice(M, n, replace=False))
+
+
+def test_cfg1_full_fp32_512():
+    w = W.make_workload("cfg1")
+    out, info = run_and_check(w)
+    assert info["kernel_name"] == "simt"
+    assert W.rel_frobenius(out, ref.ref_gemm(w)) <= 1e-4
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3"])
+def test_full_size_configs_on_sampled_rows(name):
+    w = W.make_workload(name)
+    run_and_check(w, rows=sampled_rows(w.M))
+
+
+def test_cfg4_full_size_fp8_on_sampled_rows():
+    w = W.make_workload("cfg4", 2048, 8192, 8192)  # full N and K, a quarter of the rows
+    run_and_check(w, rows=sampled_rows(w.M))
+
+
+def test_cfg5_shard_and_bf16_8192_on_sampled_rows():
+    # one rank's share of cfg5 at 8 GPUs (8192 rows) is the bf16 8192^3 problem with cfg5's data
+    w = W.make_workload("cfg5", 8192, 8192, 8192)
+    out, _ = run_and_check(w, rows=sampled_rows(w.M))
+    # the shards of a row-split product are exactly the rows of the unsplit product
+    row0, rows = R.shard_rows(w.M, 8, 3)
+    ws = W.make_workload("cfg5", 8192, 8192, 8192)
+    ws.M = rows
+    ws.A = np.ascontiguousarray(w.A[row0:row0 + rows])
+    assert np.array_equal(R.gemm_host(ws), out[row0:row0 + rows])
+
+
+def test_cfg5_full_m_on_device_generated_data():
+    """All 65536 rows once (A 1 GiB, C 1 GiB): inputs drawn on the device, rows sampled back."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    M, N, K = 65536, 8192, 8192
+    g = torch.Generator(device=dev).manual_seed(4)
+    A = torch.randn(M, K, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    B = (torch.randn(K, N, generator=g, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    Cd = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    plan = R.GemmPlan(M, N, K, W.BF16)
+    plan.run(A, B, Cd, status=status)
+    R.check_status(status)
+    rows = sampled_rows(M, 32)
+    idx = torch.from_numpy(rows).to(dev)
+    w = W.GemmWorkload("cfg5-dev", len(rows), N, K, W.BF16, W.BF16,
+                       A=A[idx].view(torch.uint16).cpu().numpy(), B=B.view(torch.uint16).cpu().numpy())
+    got = W.bf16_decode(Cd[idx].view(torch.uint16).cpu().numpy())
+    ok, err, metric = W.check(got, ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
+    assert ok, f"{metric} = {err}"
+    plan.close()

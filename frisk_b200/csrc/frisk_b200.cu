@@ -236,7 +236,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   uint32_t stages = (uint32_t)(kMaxDynSmem / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
   if (d.stages > 0) stages = std::min<uint32_t>(stages, (uint32_t)d.stages);
-  g.stages = std::max<uint32_t>(stages, 1);
+  // at least two: a stage is released only after the first MMA of the NEXT k-block was issued,
+  // so with a single stage the producer and the MMA warp would wait for each other
+  g.stages = std::max<uint32_t>(stages, 2);
   g.acc_bufs = (2 * g.mi * g.tile_n <= 512) ? 2 : 1;
   g.tmem_cols = next_pow2_cols(g.acc_bufs * g.mi * g.tile_n);
   g.idesc = make_idesc(d.a_type, a_mn, b_mn, pair ? 256u : 128u, g.tile_n);
@@ -584,7 +586,10 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, 
   int rc = frisk_b200_gemm_run(pl, pl->hA, pl->hB, pl->hC, pl->hSa, pl->hSb, pl->hWs, pl->ws_bytes,
                                pl->hStatus, st);
   if (rc) return rc;
-  FRISK_CUDA(cudaMemcpyAsync(C, pl->hC, c_bytes(d), cudaMemcpyDeviceToHost, st));
+  // only the N columns of each row come back: padding beyond them in the caller's C stays as it was
+  const size_t c_pitch = (size_t)d.ldc * elem_size(d.c_type);
+  FRISK_CUDA(cudaMemcpy2DAsync(C, c_pitch, pl->hC, c_pitch, (size_t)d.N * elem_size(d.c_type),
+                               (size_t)d.M, cudaMemcpyDeviceToHost, st));
   return frisk_b200_check_status(pl->hStatus, st);
 }
 

@@ -32,7 +32,9 @@ constexpr uint32_t kEpilogueBackoffNs = 128;
 constexpr uint32_t kProducerBackoffNs = 32;
 constexpr int kProducerWarps = 2;  // warps 0 and 6 issue the TMA loads of alternate k-blocks
 constexpr int kGemmThreads = 224;
-constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock per wait, far above any legitimate wait
+// ~0.3 s of SM clock per wait: far above any legitimate wait (a whole GEMM takes milliseconds),
+// short enough that a stuck kernel is gone well before a shared GPU's context-switch timeout
+constexpr long long kWaitLimitCycles = 1ll << 29;
 
 enum : int32_t {
   kStatusProducerTimeout = 1,

@@ -89,9 +89,9 @@ def test_every_kernel_family_agrees(name, dims, force):
 def test_tile_width_and_stage_overrides():
     w = W.make_workload("cfg2", 384, 640, 320)
     for tile_n in (64, 128, 256):
-        for stages in (1, 2, 0):
+        for stages in (1, 2, 3, 0):  # 1 is raised to 2: the pipeline needs two stages
             _, info = run_and_check(w, tile_n=tile_n, stages=stages, force_kernel="tcgen05")
-            assert info["tile_n"] == tile_n
+            assert info["tile_n"] == tile_n and info["stages"] >= 2
     _, info = run_and_check(w, num_ctas=3, force_kernel="tcgen05")
     assert info["num_ctas"] == 3
     w = W.make_workload("cfg3", 16, 2048, 2048)
@@ -229,8 +229,9 @@ def test_exact_properties(name, dims):
     if w2.scale_a is not None:
         w2.scale_a = w.scale_a[perm]
     assert np.array_equal(R.gemm_host(w2), base[perm])
-    # doubling A doubles C exactly (power-of-two scaling commutes with rounding)
-    if name != "cfg4":
+    # doubling A doubles C exactly (power-of-two scaling commutes with rounding; not for fp16
+    # outputs, whose subnormal results round on a fixed grid, nor for the saturating e4m3 inputs)
+    if name in ("cfg1", "cfg5"):
         w3 = W.make_workload(name, *dims)
         w3.A = W.encode(W.decode(w.A, w.ab_type) * 2.0, w.ab_type)
         got = W.decode(R.gemm_host(w3), w.c_type)
@@ -278,9 +279,8 @@ def test_cfg5_shard_and_bf16_8192_on_sampled_rows():
     out, _ = run_and_check(w, rows=sampled_rows(w.M))
     # the shards of a row-split product are exactly the rows of the unsplit product
     row0, rows = R.shard_rows(w.M, 8, 3)
-    ws = W.make_workload("cfg5", 8192, 8192, 8192)
-    ws.M = rows
-    ws.A = np.ascontiguousarray(w.A[row0:row0 + rows])
+    ws = W.GemmWorkload("cfg5-shard", rows, w.N, w.K, W.BF16, W.BF16, B=w.B,
+                        A=np.ascontiguousarray(w.A[row0:row0 + rows]))
     assert np.array_equal(R.gemm_host(ws), out[row0:row0 + rows])
 
 

@@ -41,7 +41,12 @@ TRANS_B = {"cfg2", "cfg4"}
 BOUND = {"cfg3": "hbm"}  # everything else is judged against the tensor-core peak
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/; None where no capture exists.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "bf16_8192": 1097518336,   # profiles/gemm_tcgen05_bf16_8192.md: 969.0 MB read + 128.5 MB written
+    "cfg5": 8 * 1097518336,    # scaled from the 8192-row capture: cfg5 is eight such row slabs of the
+                               # same B, walked band by band, so the traffic grows with the rows
+    "cfg3": 139361280,         # profiles/gemm_skinny_cfg3.md: 135.1 MB read + 4.3 MB written
+}
 
 
 def load_peaks() -> dict:
@@ -291,6 +296,7 @@ def main():
 
     import torch
     from frisk_b200 import runtime as R
+    from frisk_b200 import sharding as S
 
     R.lib()  # fail loudly when the CUDA library is missing: there is no other path
     if not torch.cuda.is_available():
@@ -310,7 +316,7 @@ def main():
 
     name = args.workload
     M, N, K = FULL_DIMS[name]
-    row0, rows = R.shard_rows(M, world, rank)
+    row0, rows = S.local_rows(M, world, rank)
     peaks = load_peaks()
 
     # ---- device-resident timing: K steps, barrier + synchronize on both sides, max over ranks
@@ -357,10 +363,7 @@ def main():
     if dist:
         dist.barrier()
     R.check_status(status, stream)
-    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-    if dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
+    elapsed_ms = S.max_over_ranks(dist, elapsed_ms, dev)
     clocks = sampler.stop() if sampler else None
     ms_per_step = elapsed_ms / args.steps
     total_flops = 2.0 * M * N * K
@@ -369,19 +372,16 @@ def main():
     # ---- optional all-gather of C over NVLink (not on the data path; reported separately)
     allgather = None
     if dist and world > 1 and M % world == 0:
-        full = torch.empty((M, N), device=dev, dtype=C.dtype)
         for _ in range(2):
-            dist.all_gather_into_tensor(full, C)
+            full = S.allgather_rows(dist, C, M, world, rank)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(5):
-            dist.all_gather_into_tensor(full, C)
+            full = S.allgather_rows(dist, C, M, world, rank)
         e1.record()
         torch.cuda.synchronize()
-        tg = torch.tensor([e0.elapsed_time(e1) / 5], device=dev, dtype=torch.float64)
-        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
-        ag_ms = float(tg.item())
+        ag_ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / 5, dev)
         recv = (world - 1) * rows * N * C.element_size()
         allgather = {"ms": round(ag_ms, 3), "recv_GBps_per_gpu": round(recv / (ag_ms * 1e-3) / 1e9, 1),
                      "note": "ncclAllGather of the C shards, after the GEMM, not in `value`"}
@@ -412,10 +412,7 @@ def main():
         for _ in range(e2e_steps):
             host_step()  # synchronous: returns after C is back in host memory
         dt = (time.perf_counter() - t0) / e2e_steps
-        t = torch.tensor([dt], device=dev, dtype=torch.float64)
-        if dist:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt = float(t.item())
+        dt = S.max_over_ranks(dist, dt, dev)
         h2d = hA.numel() * hA.element_size() + hB.numel() * hB.element_size()
         if sa is not None:
             h2d += 4 * (rows + N)

@@ -69,10 +69,12 @@ def build_ffi(force: bool = False) -> str:
     deps = srcs + _csrc_files((".h",), "ir")
     if not force and _newer(out, deps):
         return out
+    # the system compiler first: some toolchain wrappers link shared objects without libstdc++
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++")
     cmd = [
-        os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-shared", "-fPIC",
-        "-fvisibility=hidden", "-I", pybind11.get_include(),
-        "-I", sysconfig.get_paths()["include"], *srcs, "-o", out,
+        cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+        "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], *srcs, "-o", out,
+        "-lstdc++",
     ]
     _run(cmd)
     return out

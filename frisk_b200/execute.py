@@ -1,0 +1,95 @@
+"""Running the ``frisk.gemm`` ops of a module: the step the reference stops short of.
+
+``find_gemms`` walks a kernel for ``frisk.gemm`` ops whose operands are kernel arguments in the
+GLOBAL memory space (what the reference's flagship script emits: test/python/bind_test.py:53,
+captured in tmp/log_11_18:12) and turns each into a GEMM description; ``run`` plans and launches
+them through libfrisk_b200 with the buffers bound to the kernel arguments.  Ops around the gemm
+(alloc_buffer, copy, fill, for, block, parallel) describe a tiling the B200 back end chooses for
+itself and are not executed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import runtime as R
+from . import workloads as W
+from .frisk_ffi import ir
+
+
+@dataclass
+class GemmCall:
+    M: int
+    N: int
+    K: int
+    ab_type: int
+    c_type: int
+    transA: bool
+    transB: bool
+    clear_accum: bool
+    arg_a: int  # kernel argument indices of A, B, C
+    arg_b: int
+    arg_c: int
+
+
+def _dtype_of(ty) -> int:
+    s = str(ty)
+    table = {"f32": W.F32, "f16": W.F16, "bf16": W.BF16, "f8E4M3FN": W.E4M3}
+    if s not in table:
+        raise R.FriskError(-2, f"element type {s} has no GEMM kernel")
+    return table[s]
+
+
+def find_gemms(module, kernel_name: str) -> List[GemmCall]:
+    kernel = module.get_kernel(kernel_name)
+    if kernel is None:
+        raise KeyError(f"no frisk.kernel named {kernel_name!r} in the module")
+    args = {kernel.arg(i).id(): i for i in range(kernel.get_num_arguments())}
+    calls: List[GemmCall] = []
+
+    def visit(op):
+        g = op.to_gemm_op()
+        if g is None:
+            return
+        vals = [g.get_matrix_A(), g.get_matrix_B(), g.get_matrix_C()]
+        idx = []
+        for name, v in zip("ABC", vals):
+            if v.id() not in args:
+                raise R.FriskError(-2, f"frisk.gemm operand {name} is not a kernel argument: only "
+                                       "whole-problem GEMMs on global buffers are executed")
+            space = v.get_type().get_memory_space()
+            if space != ir.MemorySpace.GLOBAL:
+                raise R.FriskError(-2, f"frisk.gemm operand {name} must live in GLOBAL memory")
+            idx.append(args[v.id()])
+        a = g.get_attrs()
+        ta, tc = vals[0].get_type(), vals[2].get_type()
+        calls.append(GemmCall(a["M"], a["N"], a["K"], _dtype_of(ta.get_element_ty()),
+                              _dtype_of(tc.get_element_ty()), a["transA"], a["transB"],
+                              a["clear_accum"], *idx))
+
+    kernel.get_region(0).front().walk(visit)
+    return calls
+
+
+def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Optional[np.ndarray] = None,
+        scale_b: Optional[np.ndarray] = None, plan_options: Optional[Dict] = None) -> None:
+    """Executes every ``frisk.gemm`` of the kernel on host buffers (one per kernel argument, raw
+    storage bits in the memory order the op's trans flags state).  C buffers are updated in
+    place.  Raises when the CUDA library or a device is missing: there is no CPU path."""
+    if not module.verify():
+        raise R.FriskError(-1, "module does not verify: " + module.verify_message())
+    for call in find_gemms(module, kernel_name):
+        plan = R.GemmPlan(call.M, call.N, call.K, call.ab_type, call.c_type, transA=call.transA,
+                          transB=call.transB, clear_accum=call.clear_accum,
+                          scales=scale_a is not None, **(plan_options or {}))
+        try:
+            a = np.ascontiguousarray(buffers[call.arg_a])
+            b = np.ascontiguousarray(buffers[call.arg_b])
+            c = buffers[call.arg_c]
+            if not c.flags["C_CONTIGUOUS"]:
+                raise ValueError("the C buffer must be C-contiguous (it is written in place)")
+            plan.run_host(a, b, c, scale_a, scale_b)
+        finally:
+            plan.close()

@@ -1,0 +1,137 @@
+"""Layout mapping and cost model against the reference's pinned outputs: the shared-memory maps
+GemmOp::inferLayout printed for five cases (tmp/log_12_18, evaluated point-wise as functions), the
+swizzle selection rule of FriskOps.cpp:589-618, and the bank statistics of
+exp/layout/result/log_12_23."""
+import json
+import os
+
+import pytest
+
+import frisk as F
+from frisk_b200 import runtime as R
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def eval_map(text, d0, d1):
+    """Evaluates the results of a printed affine map '(d0, d1) -> (e0, e1, ...)' at a point."""
+    body = text.split("->", 1)[1].strip()
+    assert body[0] == "(" and body[-1] == ")"
+    py = body[1:-1].replace("floordiv", "//").replace("mod", "%")
+    return list(eval("(" + py + ",)", {"d0": d0, "d1": d1}))
+
+
+def golden_cases():
+    gold = json.load(open(os.path.join(GOLDEN, "layouts.json")))
+    out = []
+    for case in gold["cases"]:
+        for operand, lay in case["layouts"].items():
+            if lay["kind"] == "Layout":  # shared-memory operands (fragments are register layouts)
+                out.append((case["name"], case["target"], operand, lay))
+    return out
+
+
+@pytest.mark.parametrize("name,target,operand,lay", golden_cases(),
+                         ids=[f"{c[0]}-{c[2]}" for c in golden_cases()])
+def test_shared_layout_maps_equal_reference_pointwise(name, target, operand, lay):
+    rows, cols = lay["shape"]
+    h = F.create_session()
+    f16 = h.builder.get_f16_ty()
+    tys = [h.memref_type((128, 64), f16, space=F.MemorySpace.SHARED),
+           h.memref_type((64, 128), f16, space=F.MemorySpace.SHARED),
+           h.memref_type((128, 128), f16, space=F.MemorySpace.LOCAL)]
+    _, entry = h.new_kernel(name, tys)
+    g = h.create_gemm(*[entry.get_argument(i) for i in range(3)])
+    attr = g.infer_shared_layout(operand, hopper=target == "sm_90")
+    amap = F.frisk.layout_index_map(attr)
+    assert amap.get_num_results() == 3
+    tma = R.layout_to_tma(rows, cols, 16, k_inner=(operand == "A"))
+    assert tma["swizzle_bytes"] == 128 and tma["reference_layout"] == "full_bank"
+    span = tma["swizzle_bytes"]
+    for i in range(rows):
+        for j in range(0, cols, 3):
+            want = eval_map(lay["index"], i, j)
+            assert amap.evaluate([i, j]) == want
+            tc, ts, index = want
+            # the same element where TMA puts it: one box per column atom, 8-row atoms inside
+            off = R.swizzled_offset(i, j, rows, cols, 16, span)
+            assert off == tc * rows * span + ts * 8 * span + index * 2
+
+
+@pytest.mark.parametrize("bits", [8, 16, 32])
+def test_swizzle_selection_rule_and_descriptor_fields(bits):
+    vec = 128 // bits
+    es = bits // 8
+    for cont, sw, name, ltype in ((vec * 8, 128, "full_bank", 2), (vec * 16, 128, "full_bank", 2),
+                                  (vec * 4, 64, "half_bank", 4), (vec * 12, 64, "half_bank", 4),
+                                  (vec * 2, 32, "quarter_bank", 6), (vec * 3, 0, "linear", 0)):
+        for k_inner in (True, False):
+            p = R.layout_to_tma(64, cont, bits, k_inner)
+            assert (p["swizzle_bytes"], p["reference_layout"], p["umma_layout_type"]) == (sw, name, ltype)
+            assert p["umma_major"] == (0 if k_inner else 1)
+            span = sw or 16
+            assert p["box_inner"] * es == span and p["box_outer"] == 64
+            assert p["num_boxes"] * span == cont * es
+            assert p["stride_byte_offset"] == 8 * span
+            if k_inner:
+                assert p["k_step_bytes"] == 32
+            else:
+                assert p["k_step_bytes"] == (32 // es) * span and p["leading_byte_offset"] == 64 * span
+    with pytest.raises(R.FriskError) as e:
+        R.layout_to_tma(64, vec + 1, bits, True)  # the reference returns no layout either
+    assert e.value.code == -3
+    with pytest.raises(R.FriskError):
+        R.layout_to_tma(64, 64, 64, True)  # f64 has no tcgen05 operand type
+    with pytest.raises(R.FriskError):
+        R.layout_to_tma(512, 64, 16, True)  # more rows than a TMA box holds
+
+
+def test_kernel_operand_layouts_are_the_mapped_ones():
+    """The tiles the tcgen05 kernel stages are what layout_to_tma yields for them."""
+    a = R.layout_to_tma(128, 64, 16, True)    # A tile 128 x 64 bf16, K-major
+    assert (a["swizzle_bytes"], a["num_boxes"], a["box_inner"], a["box_outer"]) == (128, 1, 64, 128)
+    assert (a["stride_byte_offset"], a["k_step_bytes"]) == (1024, 32)
+    b = R.layout_to_tma(64, 256, 16, False)   # B tile 64 (K) x 256 (N) bf16, N contiguous
+    assert (b["num_boxes"], b["box_inner"], b["box_outer"]) == (4, 64, 64)
+    assert (b["leading_byte_offset"], b["stride_byte_offset"], b["k_step_bytes"]) == (8192, 1024, 2048)
+    f8 = R.layout_to_tma(256, 128, 8, True)   # e4m3 B tile 256 x 128, K-major
+    assert (f8["swizzle_bytes"], f8["box_inner"], f8["k_step_bytes"]) == (128, 128, 32)
+
+
+def test_swizzled_offsets_are_a_permutation_of_the_tile():
+    for mode in (0, 32, 64, 128, R.SWIZZLE_128B_ATOM_32B, R.SWIZZLE_128B_ATOM_64B):
+        rows, cols, bits = 16, 128, 16
+        offs = {R.swizzled_offset(i, j, rows, cols, bits, mode) for i in range(rows) for j in range(cols)}
+        assert offs == set(range(0, rows * cols * 2, 2))
+    assert R.swizzled_offset(0, 128, 16, 128, 16, 128) == -1
+    assert R.swizzled_offset(0, 0, 16, 100, 16, 128) == -1  # row not a multiple of the span
+
+
+def test_bank_model_reproduces_reference_statistics():
+    gold = json.load(open(os.path.join(GOLDEN, "bank_stats.json")))
+    lv = gold["config"]["lane_vector"]
+    checked = 0
+    for lay in gold["layouts"]:
+        if "bank_stats" not in lay or lay["operand"] == "C":
+            continue
+        rows, cols = lay["shape"]
+        ours = R.bank_conflicts(rows, cols, lay["element_bits"], 128, lv)
+        base = R.bank_conflicts(rows, cols, lay["element_bits"], 0, lv)
+        for got, want in ((ours, lay["bank_stats"]), (base, lay["baseline_row_major"])):
+            assert got["samples"] == want["samples"]
+            assert got["max_conflict"] == want["max_conflict"]
+            assert got["avg_max_conflict"] == pytest.approx(want["avg_max_conflict"])
+        checked += 1
+    assert checked == 2
+
+
+def test_bank_model_blackwell_modes_and_distinct_word_counting():
+    # counting distinct 4-byte words per bank (what the hardware serialises on): a 512-byte warp
+    # request over a swizzled or a linear 128-byte-row tile needs 4 wavefronts, the minimum
+    for mode in (0, 32, 64, 128, R.SWIZZLE_128B_ATOM_32B, R.SWIZZLE_128B_ATOM_64B):
+        st = R.bank_conflicts(128, 64, 16, mode, 8, distinct_words_only=True)
+        assert st["samples"] == 32 and st["max_conflict"] == 4
+    # column walk (one 16-byte chunk per lane, 8 rows x 4 chunk columns): what ldmatrix and the
+    # tensor-core operand fetch do.  Unswizzled 128-byte rows hit 8-way conflicts on words.
+    with pytest.raises(R.FriskError):
+        R.bank_conflicts(128, 60, 16, 128, 8)

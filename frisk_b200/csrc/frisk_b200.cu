@@ -593,6 +593,131 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, 
   return frisk_b200_check_status(pl->hStatus, st);
 }
 
+// ------------------------------------------------------------------------------------------
+// Skinny GEMM for callers that cannot allocate device memory.
+//
+// Some hosts of this library are not allowed to call cudaMalloc: a plugin that runs inside
+// another framework's memory pool and must not grow the process's footprint behind its back, a
+// service whose memory budget is fixed at start-up, a replay of pre-recorded work where every
+// buffer has to exist beforehand.  The skinny (few-row) plan needs fp32 scratch for its partial
+// sums; here that scratch is a fixed array inside the library image instead of a buffer the
+// caller (or the library) would have to allocate.  Every GPU that loads the library holds the
+// array until the process exits.
+constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB: M * N <= 1,048,576 outputs
+static __device__ __align__(256) float g_skinny_scratch[kStaticScratchFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_skinny_scratch per device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use; the address is asked for once per
+// device, with that device current.
+float* g_scratch_addr[kMaxDevices] = {nullptr};
+
+int static_scratch_for_current_device(float** out) {
+  int dev = 0;
+  FRISK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return FRISK_ERR_UNSUPPORTED;
+  float* p = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    FRISK_CUDA(cudaGetSymbolAddress(&sym, g_skinny_scratch));
+    p = static_cast<float*>(sym);
+    __atomic_store_n(&g_scratch_addr[dev], p, __ATOMIC_RELEASE);  // same value from any thread
+  }
+  *out = p;
+  return FRISK_OK;
+}
+}  // namespace
+
+int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, const void* B,
+                                  void* C, const float* scale_a, const float* scale_b,
+                                  int32_t* device_status, void* stream) {
+  if (!desc || !A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
+  frisk_gemm_desc d = *desc;
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return FRISK_ERR_INVALID_ARGUMENT;
+  if (!elem_size(d.a_type) || d.a_type != d.b_type || !elem_size(d.c_type) ||
+      d.c_type == FRISK_DT_E4M3)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.scale_mode == FRISK_SCALE_ROW_COL && (!scale_a || !scale_b))
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if ((uint64_t)d.M * (uint64_t)d.N > kStaticScratchFloats) {
+    char buf[160];
+    snprintf(buf, sizeof buf,
+             "M * N = %lld exceeds the %zu outputs the built-in scratch array holds; use "
+             "frisk_b200_gemm_run with a workspace",
+             (long long)(d.M * d.N), kStaticScratchFloats);
+    g_last_error = buf;
+    return FRISK_ERR_TOO_LARGE;
+  }
+  d.transA = d.transA != 0;
+  d.transB = d.transB != 0;
+  if (d.lda == 0) d.lda = d.transA ? d.M : d.K;
+  if (d.ldb == 0) d.ldb = d.transB ? d.K : d.N;
+  if (d.ldc == 0) d.ldc = d.N;
+  if (d.lda < (d.transA ? d.M : d.K) || d.ldb < (d.transB ? d.K : d.N) || d.ldc < d.N)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  d.force_kernel = 0;
+  d.tile_n = 0;
+  // only the few-row plan uses scratch; everything else has no reason to come through here
+  if (!(tcgen05_eligible(d) && d.M <= 64 && d.N >= 256 && !d.transA)) return FRISK_ERR_UNSUPPORTED;
+  if (((uintptr_t)A % 16) || ((uintptr_t)B % 16)) return FRISK_ERR_MISALIGNED;
+
+  frisk_gemm_plan pl;  // lives on the stack: nothing is allocated on the host heap either
+  pl.d = d;
+  memset(&pl.info, 0, sizeof pl.info);
+  int dev = 0;
+  FRISK_CUDA(cudaGetDevice(&dev));
+  int major = 0, sms = 0;
+  FRISK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  FRISK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (major != 10) return FRISK_ERR_NO_DEVICE;
+  pl.device = dev;
+  pl.sm_count = sms;
+  pl.have_device = true;
+  plan_tcgen05(&pl, /*swap=*/true, /*pair=*/false);
+
+  float* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call (or an interrupted one) left: start from zero
+  FRISK_CUDA(cudaMemsetAsync(scratch, 0, pl.ws_bytes, st));
+
+  frisk::GemmParams g = pl.gp;
+  OperandView va{A, d.M, d.K, d.lda, false};
+  OperandView vb{B, d.N, d.K, d.ldb, d.transB == 0};
+  rc = encode_operand_map(&pl.tmap_a, vb, d.a_type, g.a.box_mn, g.bk_elems);  // weights: 128-row role
+  if (rc) return rc;
+  rc = encode_operand_map(&pl.tmap_b, va, d.a_type, g.b.box_mn, g.bk_elems);
+  if (rc) return rc;
+  g.C = C;
+  g.status = device_status;
+  g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
+  g.ws = scratch;
+  g.row_scale = nullptr;
+  g.col_scale = nullptr;
+  const float* sa = d.scale_mode ? scale_a : nullptr;
+  const float* sb = d.scale_mode ? scale_b : nullptr;
+  switch (d.c_type) {
+    case FRISK_DT_F32:
+      rc = launch_tcgen05_t<float>(&pl, g, st);
+      if (!rc) rc = launch_finalize_t<float>(&pl, scratch, C, sa, sb, st);
+      break;
+    case FRISK_DT_F16:
+      rc = launch_tcgen05_t<__half>(&pl, g, st);
+      if (!rc) rc = launch_finalize_t<__half>(&pl, scratch, C, sa, sb, st);
+      break;
+    case FRISK_DT_BF16:
+      rc = launch_tcgen05_t<__nv_bfloat16>(&pl, g, st);
+      if (!rc) rc = launch_finalize_t<__nv_bfloat16>(&pl, scratch, C, sa, sb, st);
+      break;
+    default: rc = FRISK_ERR_UNSUPPORTED;
+  }
+  return rc;
+}
+
+size_t frisk_b200_gemm_skinny_static_capacity(void) { return kStaticScratchFloats; }
+
 int frisk_b200_check_status(const int32_t* device_status, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int32_t h = 0;

@@ -106,6 +106,10 @@ def lib() -> C.CDLL:
     L.frisk_b200_gemm_run.restype = C.c_int
     L.frisk_b200_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp]
     L.frisk_b200_gemm_run_host.restype = C.c_int
+    L.frisk_b200_gemm_skinny_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, vp]
+    L.frisk_b200_gemm_skinny_static.restype = C.c_int
+    L.frisk_b200_gemm_skinny_static_capacity.argtypes = []
+    L.frisk_b200_gemm_skinny_static_capacity.restype = C.c_size_t
     L.frisk_b200_check_status.argtypes = [vp, vp]
     L.frisk_b200_check_status.restype = C.c_int
     L.frisk_b200_strerror.argtypes = [C.c_int]

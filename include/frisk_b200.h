@@ -132,6 +132,30 @@ int frisk_b200_gemm_run(frisk_gemm_plan* plan, const void* A, const void* B, voi
 int frisk_b200_gemm_run_host(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
                              const float* scale_a, const float* scale_b);
 
+/*
+ * No counterpart in the reference.  The few-row ("skinny") GEMM for callers that may not
+ * allocate device memory: code running inside someone else's memory pool, services with a
+ * memory budget fixed at start-up, replays of pre-recorded work.  The fp32 scratch that
+ * frisk_b200_gemm_run takes as `workspace` is here a fixed 4 MiB array inside the library
+ * image (held by every GPU that loads the library until the process exits), so the call
+ * allocates nothing on the device or the host.
+ *   - Accepts what the skinny plan accepts: fp16 / bf16 / e4m3 inputs, M <= 64, N >= 256,
+ *     transA == 0, 16-byte aligned A and B with 16-byte row pitches; anything else returns
+ *     FRISK_ERR_UNSUPPORTED or FRISK_ERR_MISALIGNED.
+ *   - M * N must not exceed frisk_b200_gemm_skinny_static_capacity() (1,048,576 outputs);
+ *     larger problems return FRISK_ERR_TOO_LARGE (text in frisk_b200_last_error()).
+ *   - The first call on a device looks up the array's device address (the device must be
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array and each clears the part it uses first, so calls that
+ *     overlap on the GPU (different streams, different threads) race: serialise them.
+ * A, B, C, the scales and device_status are the caller's device buffers, as for
+ * frisk_b200_gemm_run; the call is asynchronous on `stream`.
+ */
+int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, const void* B,
+                                  void* C, const float* scale_a, const float* scale_b,
+                                  int32_t* device_status, void* stream);
+size_t frisk_b200_gemm_skinny_static_capacity(void);
+
 /* Copies the status word to the host (synchronises `stream`) and maps it to a return code. */
 int frisk_b200_check_status(const int32_t* device_status, void* stream);
 

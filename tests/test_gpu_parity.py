@@ -305,3 +305,29 @@ def test_cfg5_full_m_on_device_generated_data():
     ok, err, metric = W.check(got, ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
     assert ok, f"{metric} = {err}"
     plan.close()
+
+
+def test_module_built_with_the_ir_builder_executes():
+    """The reference's flow end to end: build frisk.gemm through the builder, then run it."""
+    import frisk as F
+
+    w = W.make_workload("cfg2", 256, 384, 192)
+    h = F.create_session()
+    f16 = h.builder.get_f16_ty()
+    tys = [h.memref_type((w.M, w.K), f16), h.memref_type((w.K, w.N), f16), h.memref_type((w.M, w.N), f16)]
+    _, entry = h.new_kernel("k", tys)
+    h.create_gemm(*[entry.get_argument(i) for i in range(3)], trans_b=True, clear_accum=True)
+    calls = F.find_gemms(h.module, "k")
+    assert len(calls) == 1 and (calls[0].M, calls[0].N, calls[0].K, calls[0].transB) == (256, 384, 192, True)
+    out = np.zeros((w.M, w.N), np.float16)
+    F.run(h.module, "k", [w.A, w.B, out])
+    ok, err, _ = W.check(out.astype(np.float32), ref.ref_gemm_f64(w), W.F16, absdot=ref.abs_dot(w))
+    assert ok, err
+    # operands that are not GLOBAL kernel arguments are refused, not silently skipped
+    h2 = F.create_session()
+    _, e2 = h2.new_kernel("k", [h2.memref_type((128, 64), f16, space=F.MemorySpace.SHARED),
+                                h2.memref_type((64, 128), f16, space=F.MemorySpace.SHARED),
+                                h2.memref_type((128, 128), f16, space=F.MemorySpace.LOCAL)])
+    h2.create_gemm(*[e2.get_argument(i) for i in range(3)])
+    with pytest.raises(R.FriskError):
+        F.find_gemms(h2.module, "k")

@@ -76,6 +76,7 @@ struct frisk_gemm_plan {
   frisk_gemm_plan_info info;
   frisk::GemmParams gp;  // everything but pointers
   size_t ws_bytes = 0;
+  size_t slot_bytes = 0;  // split mode 2: bytes of partial-tile slots before the counters
   size_t dyn_smem = 0;
   // run-time caches
   CUtensorMap tmap_a, tmap_b;
@@ -267,7 +268,17 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
     ctas = (uint32_t)(2 * std::max<uint64_t>(pairs, 1));
   }
   pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024;
-  pl->ws_bytes = swap ? (size_t)d.M * d.N * sizeof(float) : 0;
+  pl->ws_bytes = 0;
+  if (swap) {
+    // Split mode 2: every CTA writes the partial tiles of its unit range into private slots; the
+    // workspace is [ctas * max_items slots of tile_rows x tile_n fp32][one arrival counter per tile].
+    g.split_mode = 2;
+    const uint64_t per_cta = (units + ctas - 1) / ctas;
+    g.max_items = (uint32_t)((per_cta + g.num_kb - 1) / g.num_kb + 1);
+    const size_t tile_elems = (size_t)128 * g.mi * g.tile_n;
+    pl->slot_bytes = (size_t)ctas * g.max_items * tile_elems * sizeof(float);
+    pl->ws_bytes = pl->slot_bytes + (size_t)tiles * sizeof(uint32_t);
+  }
 
   frisk_gemm_plan_info& in = pl->info;
   in.kernel = swap ? FRISK_KERNEL_SKINNY : (pair ? FRISK_KERNEL_TCGEN05_PAIR : FRISK_KERNEL_TCGEN05);
@@ -279,7 +290,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   in.swap_ab = swap;
   in.split_k = swap;
   in.smem_bytes = (int)pl->dyn_smem;
-  in.launches = swap ? 2 : 1;
+  in.launches = 1;
   in.swizzle_a = in.swizzle_b = 128;
 }
 
@@ -514,11 +525,13 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   if (const char* tr = getenv("FRISK_B200_TRACE")) g.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
   g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
   if (swap) {
+    // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)
     g.ws = reinterpret_cast<float*>(workspace);
-    g.row_scale = nullptr;  // applied by the finalize kernel
-    g.col_scale = nullptr;
-    if (pl->clean_ws != workspace) {
-      FRISK_CUDA(cudaMemsetAsync(workspace, 0, pl->ws_bytes, st));
+    g.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->slot_bytes);
+    g.row_scale = sb;
+    g.col_scale = sa;
+    if (pl->clean_ws != workspace) {  // the counters must start at zero; the kernel re-zeroes them
+      FRISK_CUDA(cudaMemsetAsync(g.counters, 0, pl->ws_bytes - pl->slot_bytes, st));
       pl->clean_ws = workspace;
     }
   } else {
@@ -541,16 +554,7 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
       default: rc = FRISK_ERR_UNSUPPORTED;
     }
   }
-  if (rc) { pl->clean_ws = nullptr; return rc; }
-  if (swap) {
-    switch (d.c_type) {
-      case FRISK_DT_F32: rc = launch_finalize_t<float>(pl, g.ws, C, sa, sb, st); break;
-      case FRISK_DT_F16: rc = launch_finalize_t<__half>(pl, g.ws, C, sa, sb, st); break;
-      case FRISK_DT_BF16: rc = launch_finalize_t<__nv_bfloat16>(pl, g.ws, C, sa, sb, st); break;
-      default: rc = FRISK_ERR_UNSUPPORTED;
-    }
-    if (rc) pl->clean_ws = nullptr;
-  }
+  if (rc) pl->clean_ws = nullptr;
   return rc;
 }
 
@@ -675,6 +679,10 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   pl.sm_count = sms;
   pl.have_device = true;
   plan_tcgen05(&pl, /*swap=*/true, /*pair=*/false);
+  // this entry point keeps the atomic split (mode 1): its scratch is M x N fp32, independent of
+  // the grid, which is what lets a fixed array serve it
+  pl.gp.split_mode = 1;
+  pl.ws_bytes = (size_t)d.M * d.N * sizeof(float);
 
   float* scratch = nullptr;
   int rc = static_scratch_for_current_device(&scratch);

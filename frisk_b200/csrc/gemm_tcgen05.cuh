@@ -69,7 +69,10 @@ struct GemmParams {
   uint32_t rows, cols; // extent of D
   uint32_t tiles_r, tiles_c, num_kb;
   uint32_t group_r;    // tile rasterisation: rows of tiles walked together
-  uint32_t split_mode;
+  uint32_t split_mode;  // 0: whole tiles; 1: stream-K, atomics into ws + finalize kernel;
+                        // 2: stream-K, private partial slots, the last CTA of a tile reduces
+  uint32_t max_items;   // split mode 2: most tiles one CTA's unit range can touch
+  uint32_t* counters;   // split mode 2: k-blocks arrived per tile (zero between launches)
   // epilogue
   void* C;
   float* ws;               // fp32 partial sums, C orientation, leading dimension ws_ld
@@ -277,6 +280,59 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs& p, uint32_t row, u
   }
 }
 
+// ---- split mode 2: partial tiles in private slots, reduced by the last CTA to arrive -----------
+// A slot holds one partial tile as [column][row] fp32 (rows fastest, so a warp's 32 rows of one
+// column are one 128-byte store).  Slot of CTA c for tile t: c * max_items + (t - first tile of c).
+__device__ __forceinline__ uint64_t unit_begin(uint64_t total_units, uint32_t cta, uint32_t grid) {
+  return total_units * cta / grid;
+}
+
+// Rendezvous of the 128 epilogue threads on an mbarrier (count 128), bounded like every other
+// wait of the kernel: a named hardware barrier could not give up if one warp had left the loop.
+__device__ __forceinline__ bool epilogue_rendezvous(uint32_t bar, uint32_t& phase,
+                                                    volatile uint32_t* abort_flag, int32_t* status) {
+  ptx::mbar_arrive(bar);
+  const bool ok = bounded_wait(bar, phase, abort_flag, status, kStatusEpilogueTimeout);
+  phase ^= 1u;
+  return ok;
+}
+
+template <int NC>
+__device__ __forceinline__ void slot_store(float* slot, uint32_t tile_rows, uint32_t r_local,
+                                           uint32_t c0, const uint32_t (&acc)[NC]) {
+#pragma unroll
+  for (int j = 0; j < NC; ++j)
+    slot[(size_t)(c0 + j) * tile_rows + r_local] = __uint_as_float(acc[j]);
+}
+
+// Sums, in CTA order (so the result does not depend on who arrives last), every partial of
+// `tile` for 16 columns of one row.
+__device__ __forceinline__ void reduce_slots_x16(const float* ws, uint32_t tile, uint32_t num_kb,
+                                                 uint64_t total_units, uint32_t grid,
+                                                 uint32_t max_items, uint32_t tile_rows,
+                                                 uint32_t tile_elems, uint32_t r_local, uint32_t c0,
+                                                 uint32_t (&acc)[16]) {
+  float sum[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) sum[j] = 0.f;
+  const uint64_t u_lo = (uint64_t)tile * num_kb, u_hi = u_lo + num_kb;
+  uint32_t c = (uint32_t)(u_lo * grid / total_units);
+  while (c + 1 < grid && unit_begin(total_units, c + 1, grid) <= u_lo) ++c;
+  while (c > 0 && unit_begin(total_units, c, grid) > u_lo) --c;
+  for (; c < grid; ++c) {
+    const uint64_t b = unit_begin(total_units, c, grid);
+    if (b >= u_hi) break;
+    const uint64_t e = unit_begin(total_units, c + 1, grid);
+    if (e <= u_lo) continue;
+    const uint32_t first_tile = (uint32_t)(b / num_kb);
+    const float* slot = ws + (size_t)(c * max_items + (tile - first_tile)) * tile_elems;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sum[j] += __ldcg(slot + (size_t)(c0 + j) * tile_rows + r_local);
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(sum[j]);
+}
+
 template <typename TC>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -289,6 +345,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
+  __shared__ uint32_t last_flag;
+  __shared__ __align__(8) uint64_t bar_epilogue;
 
   // The broadcast tells the compiler that the warp index is the same in every lane, so the role
   // branches below are uniform and the code inside them may use the uniform datapath (which the
@@ -326,6 +384,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::mbar_init(acc_full0 + 8 * i, 1);
       ptx::mbar_init(acc_empty0 + 8 * i, 4);  // one arrival per epilogue warp
     }
+    ptx::mbar_init(ptx::smem_u32(&bar_epilogue), 128);
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
@@ -519,6 +578,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ep.clear_accum = p.clear_accum;
     ep.c_vec_ok = p.c_vec_ok;
     const uint32_t quarter = warp & 3u;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    const uint32_t split_mode = p.split_mode, max_items = p.max_items, num_kb_all = p.num_kb;
+    const uint32_t tile_rows = 128u * mi, tile_elems = tile_rows * tile_n;
+    const uint64_t total_units = (uint64_t)tiles_r * tiles_c * num_kb_all;
+    const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
+    uint32_t epi_phase = 0;
     uint32_t item = 0;
     bool ok = true;
     while (ok && work.next()) {
@@ -532,8 +596,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) break;
       ptx::tc_fence_after();
       if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item] = clock64();
+      // split mode 2: a work item that covers all of K is written straight to C; a partial one goes
+      // to this CTA's private slot and the last CTA to arrive for the tile sums the slots
+      const bool whole = work.kb0 == 0 && work.kb1 == num_kb_all;
+      const bool to_slot = split_mode == 2 && !whole;
+      EpiArgs ep_item = ep;
+      if (split_mode == 2) ep_item.split_mode = 0;
+      float* slot = nullptr;
+      if (to_slot) {
+        const uint32_t first_tile =
+            (uint32_t)(unit_begin(total_units, blockIdx.x, gridDim.x) / num_kb_all);
+        slot = ep.ws + (size_t)(blockIdx.x * max_items + (work.tile - first_tile)) * tile_elems;
+      }
       for (uint32_t sub = 0; sub < mi; ++sub) {
-        const uint32_t row = (tr * mi + sub) * 128u + quarter * 32u + lane;
+        const uint32_t r_local = sub * 128u + quarter * 32u + lane;
+        const uint32_t row = tr * tile_rows + r_local;
         const uint32_t t_row =
             tmem_base + ((quarter * 32u) << 16) + acc * (mi * tile_n) + sub * tile_n;
         if ((tile_n & 31u) == 0) {
@@ -541,20 +618,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t v[32];
             ptx::tmem_ld_32x32b_x32(t_row + cc, v);
             ptx::tmem_ld_wait();
-            epilogue_store<TC, 32>(ep, row, tc * tile_n + cc, v);
+            if (to_slot) slot_store<32>(slot, tile_rows, r_local, cc, v);
+            else epilogue_store<TC, 32>(ep_item, row, tc * tile_n + cc, v);
           }
         } else {
           for (uint32_t cc = 0; cc < tile_n; cc += 16) {
             uint32_t v[16];
             ptx::tmem_ld_32x32b_x16(t_row + cc, v);
             ptx::tmem_ld_wait();
-            epilogue_store<TC, 16>(ep, row, tc * tile_n + cc, v);
+            if (to_slot) slot_store<16>(slot, tile_rows, r_local, cc, v);
+            else epilogue_store<TC, 16>(ep_item, row, tc * tile_n + cc, v);
           }
         }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
+      if (to_slot) {
+        __threadfence();      // this thread's partial is visible device-wide ...
+        // ... and so is every epilogue thread's, before the count goes up
+        ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
+        if (!ok) break;
+        if (threadIdx.x == 64) {
+          const uint32_t mine = work.kb1 - work.kb0;
+          const uint32_t before = atomicAdd(p.counters + work.tile, mine);
+          last_flag = (before + mine == num_kb_all) ? 1u : 0u;
+        }
+        ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
+        if (!ok) break;
+        if (last_flag) {
+          __threadfence();
+          for (uint32_t sub = 0; sub < mi; ++sub) {
+            const uint32_t r_local = sub * 128u + quarter * 32u + lane;
+            const uint32_t row = tr * tile_rows + r_local;
+            for (uint32_t cc = 0; cc < tile_n; cc += 16) {
+              uint32_t v[16];
+              reduce_slots_x16(ep.ws, work.tile, num_kb_all, total_units, gridDim.x, max_items,
+                               tile_rows, tile_elems, r_local, cc, v);
+              epilogue_store<TC, 16>(ep_item, row, tc * tile_n + cc, v);
+            }
+          }
+          if (threadIdx.x == 64) p.counters[work.tile] = 0;  // ready for the next launch
+        }
+        // last_flag is rewritten by the next item
+        ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
+        if (!ok) break;
+      }
       if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item + 1] = clock64();
       ++item;
     }

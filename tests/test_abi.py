@@ -50,8 +50,9 @@ def test_plan_picks_kernel_family_for_the_benchmark_configs(name, kernel):
     assert plan.info["kernel_name"] == kernel
     if kernel == "skinny":
         assert plan.info["swap_ab"] == 1 and plan.info["split_k"] == 1
-        assert plan.workspace_bytes == 16 * 8192 * 4
-        assert plan.info["launches"] == 2
+        # 148 CTAs x 2 partial-tile slots of 256 x 16 fp32, plus one arrival counter per tile
+        assert plan.workspace_bytes == 148 * 2 * 256 * 16 * 4 + 32 * 4
+        assert plan.info["launches"] == 1
     else:
         assert plan.workspace_bytes == 0 and plan.info["launches"] == 1
     if kernel != "simt":

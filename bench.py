@@ -76,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -203,16 +203,24 @@ def roofline_for(name, M, N, K, ms, peaks, sustained):
             "peak_source": peaks["source"] + (" (sustained)" if sustained and unit == "TFLOP/s" else " (burst)" if unit == "TFLOP/s" else "")}
 
 
+def host_threads() -> int:
+    """All cores this process may use (torchrun sets OMP_NUM_THREADS=1; the CPU legs ignore that)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(name, target_s=12.0):
     """The oracle port (naive fp32 loop, OpenMP over rows) on a bounded sample of the workload."""
     from oracle import ref
 
     M, N, K = FULL_DIMS[name]
-    threads = ref.max_threads()
+    threads = host_threads()
     rows = min(M, 16)
     w = W.make_workload(name, rows, N, K)
     t0 = time.perf_counter()
-    ref.ref_gemm(w)
+    ref.ref_gemm(w, num_threads=threads)
     dt = time.perf_counter() - t0
     # grow the sample towards the target time
     rows2 = int(min(M, max(rows, rows * target_s / max(dt, 1e-3))))
@@ -220,7 +228,7 @@ def cpu_baseline(name, target_s=12.0):
     if rows2 > rows:
         w = W.make_workload(name, rows2, N, K)
         t0 = time.perf_counter()
-        ref.ref_gemm(w)
+        ref.ref_gemm(w, num_threads=threads)
         dt = time.perf_counter() - t0
         rows = rows2
     tflops = 2.0 * rows * N * K / dt / 1e12
@@ -252,14 +260,14 @@ def run_reference(args):
 
     name = args.workload
     M, N, K = FULL_DIMS[name]
-    threads = ref.max_threads()
+    threads = host_threads()
     rows = max(threads, min(M, 8 * threads))
     w = W.make_workload(name, rows, N, K)
     for _ in range(max(args.warmup, 0)):
-        ref.ref_gemm(w)
+        ref.ref_gemm(w, num_threads=threads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        ref.ref_gemm(w)
+        ref.ref_gemm(w, num_threads=threads)
     dt = (time.perf_counter() - t0) / args.steps
     tflops = 2.0 * rows * N * K / dt / 1e12
     line = {

@@ -202,6 +202,15 @@ bool tcgen05_eligible(const frisk_gemm_desc& d) {
   return true;
 }
 
+// Few rows of A against a wide B: the shape the swapped, K-split plan is for.  The kernel counts
+// (tile, k-block) units in 32 bits and multiplies the count by the grid size, so the product has
+// to stay below 2^32 (conservatively: the smallest tile and k-block the plan could pick).
+bool skinny_shape(const frisk_gemm_desc& d, int sm_count) {
+  if (!(d.M <= 64 && d.N >= 256 && !d.transA)) return false;
+  const uint64_t units = (uint64_t)((d.N + 127) / 128) * (uint64_t)((d.K + 31) / 32);
+  return units * (uint64_t)(sm_count + 1) < (1ull << 32);
+}
+
 void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   const frisk_gemm_desc& d = pl->d;
   frisk::GemmParams& g = pl->gp;
@@ -227,6 +236,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
     cols = d.M;
     g.mi = rows > 128 ? 2 : 1;
     g.tile_n = (uint32_t)((cols + 15) / 16 * 16);
+    if (const char* e = getenv("FRISK_B200_SKINNY_MI")) g.mi = atoi(e) > 1 && rows > 128 ? 2 : 1;
   }
   g.bk_elems = bk;
   g.k_steps = 4;
@@ -252,6 +262,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   g.num_kb = (uint32_t)((d.K + bk - 1) / bk);
   g.group_r = 16;
   g.split_mode = swap ? 1 : 0;
+  // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
+  // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
+  g.epilogue_backoff_ns = swap ? 0u : frisk::kEpilogueBackoffNs;
+  if (const char* e = getenv("FRISK_B200_EPI_BACKOFF")) g.epilogue_backoff_ns = (uint32_t)atoi(e);
   g.transposed_out = swap ? 1 : 0;
   g.clear_accum = d.clear_accum ? 1 : 0;
   g.c_type = d.c_type;
@@ -294,9 +308,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   in.swizzle_a = in.swizzle_b = 128;
 }
 
-template <typename TC>
-int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_kernel<TC>;
+template <typename TC, bool kSplit>
+int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
+  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit>;
   if (!pl->smem_attr_set) {
     FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)pl->dyn_smem));
@@ -305,6 +319,12 @@ int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream
   kern<<<pl->info.num_ctas, frisk::kGemmThreads, pl->dyn_smem, st>>>(pl->tmap_a, pl->tmap_b, g);
   FRISK_CUDA(cudaGetLastError());
   return FRISK_OK;
+}
+
+template <typename TC>
+int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
+  return g.split_mode ? launch_tcgen05_ts<TC, true>(pl, g, st)
+                      : launch_tcgen05_ts<TC, false>(pl, g, st);
 }
 
 template <typename TC>
@@ -430,7 +450,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   }
 
   const bool tc_ok = tcgen05_eligible(d);
-  const bool skinny_ok = tc_ok && d.M <= 64 && d.N >= 256 && !d.transA;
+  const bool skinny_ok = tc_ok && skinny_shape(d, pl->sm_count);
   const bool pair_ok = tc_ok && d.M > 128 && d.N > 64 && d.tile_n != 64 && pl->sm_count >= 2;
   int kind;
   if (d.force_kernel) {
@@ -663,7 +683,7 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   d.force_kernel = 0;
   d.tile_n = 0;
   // only the few-row plan uses scratch; everything else has no reason to come through here
-  if (!(tcgen05_eligible(d) && d.M <= 64 && d.N >= 256 && !d.transA)) return FRISK_ERR_UNSUPPORTED;
+  if (!(tcgen05_eligible(d) && skinny_shape(d, 1024))) return FRISK_ERR_UNSUPPORTED;
   if (((uintptr_t)A % 16) || ((uintptr_t)B % 16)) return FRISK_ERR_MISALIGNED;
 
   frisk_gemm_plan pl;  // lives on the stack: nothing is allocated on the host heap either

@@ -84,6 +84,7 @@ struct GemmParams {
   uint32_t transposed_out; // 1: D[r, c] is C[c, r]
   uint32_t clear_accum;
   uint32_t c_vec_ok;       // C rows allow 16-byte stores
+  uint32_t epilogue_backoff_ns;  // sleep between polls of the accumulator-ready barrier
   uint32_t debug_mode;     // measurement only: bit 0 = issue no loads, bit 1 = issue no MMAs
   long long* trace;        // measurement only: clock64 samples of CTA 0 (may be nullptr)
   int32_t* status;
@@ -130,7 +131,7 @@ struct WorkIter {
   // whole-tile mode
   uint32_t next_tile, tile_step, num_tiles;
   // split mode
-  uint64_t u, u_end;
+  uint32_t u, u_end;   // total units x grid size stays below 2^32 (checked when planning)
   uint32_t num_kb, split;
 
   __device__ void init(uint32_t num_kb_, uint32_t split_, uint32_t num_tiles_) {
@@ -138,7 +139,7 @@ struct WorkIter {
     split = split_;
     num_tiles = num_tiles_;
     if (split) {
-      const uint64_t total = (uint64_t)num_tiles * num_kb;
+      const uint32_t total = num_tiles * num_kb;
       u = total * blockIdx.x / gridDim.x;
       u_end = total * (blockIdx.x + 1) / gridDim.x;
     } else {
@@ -149,10 +150,10 @@ struct WorkIter {
   __device__ bool next() {
     if (split) {
       if (u >= u_end) return false;
-      tile = (uint32_t)(u / num_kb);
-      kb0 = (uint32_t)(u - (uint64_t)tile * num_kb);
-      const uint64_t left = u_end - u;
-      kb1 = (left < (uint64_t)(num_kb - kb0)) ? kb0 + (uint32_t)left : num_kb;
+      tile = u / num_kb;
+      kb0 = u - tile * num_kb;
+      const uint32_t left = u_end - u;
+      kb1 = (left < num_kb - kb0) ? kb0 + left : num_kb;
       u += kb1 - kb0;
       return true;
     }
@@ -283,7 +284,7 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs& p, uint32_t row, u
 // ---- split mode 2: partial tiles in private slots, reduced by the last CTA to arrive -----------
 // A slot holds one partial tile as [column][row] fp32 (rows fastest, so a warp's 32 rows of one
 // column are one 128-byte store).  Slot of CTA c for tile t: c * max_items + (t - first tile of c).
-__device__ __forceinline__ uint64_t unit_begin(uint64_t total_units, uint32_t cta, uint32_t grid) {
+__device__ __forceinline__ uint32_t unit_begin(uint32_t total_units, uint32_t cta, uint32_t grid) {
   return total_units * cta / grid;
 }
 
@@ -308,23 +309,23 @@ __device__ __forceinline__ void slot_store(float* slot, uint32_t tile_rows, uint
 // Sums, in CTA order (so the result does not depend on who arrives last), every partial of
 // `tile` for 16 columns of one row.
 __device__ __forceinline__ void reduce_slots_x16(const float* ws, uint32_t tile, uint32_t num_kb,
-                                                 uint64_t total_units, uint32_t grid,
+                                                 uint32_t total_units, uint32_t grid,
                                                  uint32_t max_items, uint32_t tile_rows,
                                                  uint32_t tile_elems, uint32_t r_local, uint32_t c0,
                                                  uint32_t (&acc)[16]) {
   float sum[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) sum[j] = 0.f;
-  const uint64_t u_lo = (uint64_t)tile * num_kb, u_hi = u_lo + num_kb;
-  uint32_t c = (uint32_t)(u_lo * grid / total_units);
+  const uint32_t u_lo = tile * num_kb, u_hi = u_lo + num_kb;
+  uint32_t c = u_lo * grid / total_units;
   while (c + 1 < grid && unit_begin(total_units, c + 1, grid) <= u_lo) ++c;
   while (c > 0 && unit_begin(total_units, c, grid) > u_lo) --c;
   for (; c < grid; ++c) {
-    const uint64_t b = unit_begin(total_units, c, grid);
+    const uint32_t b = unit_begin(total_units, c, grid);
     if (b >= u_hi) break;
-    const uint64_t e = unit_begin(total_units, c + 1, grid);
+    const uint32_t e = unit_begin(total_units, c + 1, grid);
     if (e <= u_lo) continue;
-    const uint32_t first_tile = (uint32_t)(b / num_kb);
+    const uint32_t first_tile = b / num_kb;
     const float* slot = ws + (size_t)(c * max_items + (tile - first_tile)) * tile_elems;
 #pragma unroll
     for (int j = 0; j < 16; ++j) sum[j] += __ldcg(slot + (size_t)(c0 + j) * tile_rows + r_local);
@@ -333,7 +334,118 @@ __device__ __forceinline__ void reduce_slots_x16(const float* ws, uint32_t tile,
   for (int j = 0; j < 16; ++j) acc[j] = __float_as_uint(sum[j]);
 }
 
+// Most partials of one tile the vector reduction handles; a tile with more (a grid much larger
+// than the tile count) takes the row-wise reduce_slots_x16 instead.
+constexpr uint32_t kMaxContrib = 16;
+constexpr int kReduceBatch = 8;  // slots summed per round of loads by reduce_tile
+
+// Lists, in CTA order, the slots that hold a partial of `tile`; returns how many there are (only
+// the first `cap` are stored).  One thread calls this while the tile's MMAs are still running.
+__device__ __noinline__ uint32_t list_contributors(uint32_t tile, uint32_t num_kb,
+                                                   uint32_t total_units, uint32_t grid,
+                                                   uint32_t max_items, uint32_t* out,
+                                                   uint32_t cap) {
+  const uint32_t u_lo = tile * num_kb, u_hi = u_lo + num_kb;
+  uint32_t c = u_lo * grid / total_units;
+  while (c + 1 < grid && unit_begin(total_units, c + 1, grid) <= u_lo) ++c;
+  while (c > 0 && unit_begin(total_units, c, grid) > u_lo) --c;
+  uint32_t n = 0;
+  uint32_t b = unit_begin(total_units, c, grid);
+  for (; c < grid && b < u_hi; ++c) {
+    const uint32_t e = unit_begin(total_units, c + 1, grid);
+    if (e > u_lo) {
+      if (n < cap) out[n] = c * max_items + (tile - b / num_kb);
+      ++n;
+    }
+    b = e;
+  }
+  return n;
+}
+
+// Four consecutive D rows of one column: scale, accumulate into C if asked, cast and store.
 template <typename TC>
+__device__ __forceinline__ void store_rows4(const EpiArgs& p, uint32_t row, uint32_t col,
+                                            float4 s) {
+  if (col >= p.cols || row >= p.rows) return;
+  const float v[4] = {s.x, s.y, s.z, s.w};
+  TC* C = reinterpret_cast<TC*>(p.C);
+  struct alignas(4 * sizeof(TC)) Pack {
+    TC e[4];
+  };
+  if (p.transposed_out && p.clear_accum && p.c_vec_ok && row + 3 < p.rows) {
+    // C[col, row .. row+3] is contiguous and, with row a multiple of 4, aligned for one store
+    Pack pack;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float o = v[j] * (p.row_scale ? __ldg(p.row_scale + row + j) : 1.0f);
+      if (p.col_scale) o *= __ldg(p.col_scale + col);
+      pack.e[j] = cast_out<TC>(o);
+    }
+    *reinterpret_cast<Pack*>(C + (int64_t)col * p.ldc + row) = pack;
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t r = row + j;
+    if (r < p.rows) {
+      float o = v[j] * (p.row_scale ? __ldg(p.row_scale + r) : 1.0f);
+      if (p.col_scale) o *= __ldg(p.col_scale + col);
+      TC* dst = p.transposed_out ? C + (int64_t)col * p.ldc + r : C + (int64_t)r * p.ldc + col;
+      if (!p.clear_accum) o += cast_in<TC>(*dst);
+      *dst = cast_out<TC>(o);
+    }
+  }
+}
+
+// Sums the listed slots, in list order (so the result does not depend on who arrives last), and
+// writes the tile to C.  Called by the 128 epilogue threads (tid 0 .. 127); each handles float4
+// pieces tid, tid + 128, ... of the [column][row] slot image, 4 pieces x 8 slots in flight.
+template <typename TC>
+__device__ __forceinline__ void reduce_tile(const EpiArgs& p, const uint32_t* slots, uint32_t n,
+                                            uint32_t tile_rows, uint32_t tile_elems,
+                                            uint32_t row0, uint32_t col0, uint32_t tid) {
+  const uint32_t n_vec = tile_elems >> 2;            // a multiple of 512
+  const uint32_t row_shift = (tile_rows == 256u) ? 8u : 7u;
+  for (uint32_t v0 = tid; v0 < n_vec; v0 += 512u) {
+    float4 sum[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t k0 = 0; k0 < n; k0 += kReduceBatch) {
+      float4 x[kReduceBatch][4];
+#pragma unroll
+      for (int kk = 0; kk < kReduceBatch; ++kk) {
+        if (k0 + kk < n) {
+          const float4* s =
+              reinterpret_cast<const float4*>(p.ws + (size_t)slots[k0 + kk] * tile_elems) + v0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[kk][i] = __ldcg(s + i * 128);
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < kReduceBatch; ++kk) {
+        if (k0 + kk < n) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            sum[i].x += x[kk][i].x;
+            sum[i].y += x[kk][i].y;
+            sum[i].z += x[kk][i].z;
+            sum[i].w += x[kk][i].w;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t e = (v0 + i * 128u) << 2;
+      store_rows4<TC>(p, row0 + (e & (tile_rows - 1u)), col0 + (e >> row_shift), sum[i]);
+    }
+  }
+}
+
+// kSplit selects the K-split (stream-K) code at compile time.  The whole-tile instantiation carries
+// none of it: with the slot reduction inlined the kernel needs 200+ registers and measurably slows
+// the whole-tile main loop (8192^3 bf16: 0.98 ms against 0.83 ms), so the two are kept apart.
+template <typename TC, bool kSplit>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
@@ -346,6 +458,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
   __shared__ uint32_t last_flag;
+  __shared__ uint32_t contrib_n;
+  __shared__ uint32_t contrib_slots[kMaxContrib];
   __shared__ __align__(8) uint64_t bar_epilogue;
 
   // The broadcast tells the compiler that the warp index is the same in every lane, so the role
@@ -374,6 +488,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   int32_t* const status = p.status;
   long long* const trace = blockIdx.x == 0 ? p.trace : nullptr;
 
+  // every stamp is relative to the stamping thread's own clock at kernel entry
+  const long long t_entry = trace ? clock64() : 0;
+  if (trace && threadIdx.x == 64) {
+    trace[320] = 0;
+    trace[324] = (long long)ptx::globaltimer_ns();
+  }
   if (threadIdx.x == 0) {
     abort_word = 0;
     for (uint32_t s = 0; s < stages; ++s) {
@@ -398,9 +518,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::tc_fence_after();
   // broadcast: a value loaded from shared memory is not warp-uniform for the compiler otherwise
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_slot, 0);
+  if (trace && threadIdx.x == 64) trace[321] = clock64() - t_entry;
 
   WorkIter work;
-  work.init(p.num_kb, p.split_mode, tiles_r * tiles_c);
+  work.init(p.num_kb, kSplit ? p.split_mode : 0u, tiles_r * tiles_c);
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------- TMA producer
@@ -434,12 +555,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (!ok) break;
           const uint32_t full = full0 + 8 * stage;
           const bool tr_on = trace && issued < 32 && warp == 0;
-          if (tr_on && ptx::elect_one()) trace[2 * issued] = clock64();
+          if (tr_on && ptx::elect_one()) trace[2 * issued] = clock64() - t_entry;
           if (debug_mode & 1u) {
             if (ptx::elect_one()) ptx::mbar_arrive(full);
           } else {
             if (ptx::elect_one()) ptx::mbar_arrive_expect_tx(full, stage_bytes);
-            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued] = clock64();
+            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued] = clock64() - t_entry;
             const uint32_t a_dst = tiles_base + stage * stage_bytes;
             const uint32_t b_dst = a_dst + a_stage_bytes;
             const int32_t k0 = (int32_t)(kb * bk_elems);
@@ -448,14 +569,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
               if (ptx::elect_one()) ptx::tma_load_2d(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
             }
-            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued + 1] = clock64();
+            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued + 1] = clock64() - t_entry;
             for (uint32_t bx = 0; bx < b_boxes; ++bx) {
               const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
               const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
               if (ptx::elect_one()) ptx::tma_load_2d(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
             }
           }
-          if (tr_on && ptx::elect_one()) trace[2 * issued + 1] = clock64();
+          if (tr_on && ptx::elect_one()) trace[2 * issued + 1] = clock64() - t_entry;
           ++issued;
           if (++stage == stages) {
             stage = 0;
@@ -514,7 +635,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t bdesc0 = b_desc_base | (uint64_t)((b_addr & 0x3FFFFu) >> 4);
           const uint32_t first = (kb > work.kb0) ? 1u : 0u;
           const bool tr_on = trace && item == 0 && (kb - work.kb0) < 32;
-          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0)] = clock64();
+          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0)] = clock64() - t_entry;
           uint32_t next_stage = stage + 1, next_phase = phase;
           if (next_stage == stages) {
             next_stage = 0;
@@ -522,7 +643,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if (debug_mode & 2u) {
             if (ptx::elect_one()) ptx::mbar_arrive(empty0 + 8 * stage);
-            ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+            ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8 * next_stage, next_phase));
           } else {
             // the start-address field advances by whole 16-byte units and never carries out of
             // its 14 bits (the tiles end below 256 KiB), so the step is added to the low word
@@ -531,8 +652,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const uint64_t bdesc = bdesc0 + (uint64_t)((ks * b_k_step) >> 4);
               const uint64_t adesc = adesc0 + (uint64_t)((ks * a_k_step) >> 4);
               const uint32_t accumulate = first | (ks > 0 ? 1u : 0u);
+              // (test_wait, not try_wait: try_wait suspends the warp for microseconds when the
+              // phase is not complete, and after the CTA's last k-block it never completes)
               if (ks == 3)
-                ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+                ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8 * next_stage, next_phase));
               if (kind_f8) {
                 if (ptx::elect_one()) ptx::mma_f8(d_base, adesc, bdesc, idesc, accumulate);
                 if (mi > 1 && ptx::elect_one())
@@ -544,11 +667,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
               if (ks == 0 && have_prev && ptx::elect_one()) ptx::tc_commit(empty0 + 8 * prev_stage);
             }
-            if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 1] = clock64();
+            if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 1] = clock64() - t_entry;
             prev_stage = stage;
             have_prev = true;
           }
-          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 2] = clock64();
+          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 2] = clock64() - t_entry;
           stage = next_stage;
           phase = next_phase;
         }
@@ -557,6 +680,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (have_prev && ptx::elect_one()) ptx::tc_commit(empty0 + 8 * prev_stage);
         if (!ok) break;
         if (ptx::elect_one()) ptx::tc_commit(acc_full0 + 8 * acc);
+        if (trace && item == 0 && ptx::elect_one()) trace[323] = clock64() - t_entry;
         __syncwarp();
         ++item;
       }
@@ -573,15 +697,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ep.ws_ld = p.ws_ld;
     ep.rows = p.rows;
     ep.cols = p.cols;
-    ep.split_mode = p.split_mode;
+    ep.split_mode = kSplit ? p.split_mode : 0u;
     ep.transposed_out = p.transposed_out;
     ep.clear_accum = p.clear_accum;
     ep.c_vec_ok = p.c_vec_ok;
     const uint32_t quarter = warp & 3u;  // TMEM lanes 32*quarter .. +31 belong to this warp
-    const uint32_t split_mode = p.split_mode, max_items = p.max_items, num_kb_all = p.num_kb;
+    const uint32_t split_mode = kSplit ? p.split_mode : 0u, max_items = p.max_items, num_kb_all = p.num_kb;
     const uint32_t tile_rows = 128u * mi, tile_elems = tile_rows * tile_n;
-    const uint64_t total_units = (uint64_t)tiles_r * tiles_c * num_kb_all;
+    const uint32_t total_units = tiles_r * tiles_c * num_kb_all;
     const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
+    const uint32_t epi_backoff = p.epilogue_backoff_ns;
     uint32_t epi_phase = 0;
     uint32_t item = 0;
     bool ok = true;
@@ -590,12 +715,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc_phase = (item / acc_bufs) & 1u;
       uint32_t tr, tc;
       tile_coords(group_r, tiles_r, tiles_c, work.tile, tr, tc);
-      // the tcgen05.ld below is warp-collective: leave the loop only as a whole warp
-      ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
-                        kEpilogueBackoffNs);
-      if (!ok) break;
-      ptx::tc_fence_after();
-      if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item] = clock64();
       // split mode 2: a work item that covers all of K is written straight to C; a partial one goes
       // to this CTA's private slot and the last CTA to arrive for the tile sums the slots
       const bool whole = work.kb0 == 0 && work.kb1 == num_kb_all;
@@ -604,10 +723,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (split_mode == 2) ep_item.split_mode = 0;
       float* slot = nullptr;
       if (to_slot) {
+        // worked out while the item's MMAs still run: where the partial goes, and (one thread) who
+        // else holds a partial of this tile, in case this CTA turns out to be the last to arrive
         const uint32_t first_tile =
-            (uint32_t)(unit_begin(total_units, blockIdx.x, gridDim.x) / num_kb_all);
+            unit_begin(total_units, blockIdx.x, gridDim.x) / num_kb_all;
         slot = ep.ws + (size_t)(blockIdx.x * max_items + (work.tile - first_tile)) * tile_elems;
+        if (threadIdx.x == 64)
+          contrib_n = list_contributors(work.tile, num_kb_all, total_units, gridDim.x, max_items,
+                                        contrib_slots, kMaxContrib);
       }
+      // the tcgen05.ld below is warp-collective: leave the loop only as a whole warp
+      ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
+                        epi_backoff);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item] = clock64() - t_entry;
       for (uint32_t sub = 0; sub < mi; ++sub) {
         const uint32_t r_local = sub * 128u + quarter * 32u + lane;
         const uint32_t row = tr * tile_rows + r_local;
@@ -634,6 +764,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
+      if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 1] = clock64() - t_entry;
       if (to_slot) {
         __threadfence();      // this thread's partial is visible device-wide ...
         // ... and so is every epilogue thread's, before the count goes up
@@ -646,25 +777,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
         if (!ok) break;
+        if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 2] = clock64() - t_entry;
         if (last_flag) {
           __threadfence();
-          for (uint32_t sub = 0; sub < mi; ++sub) {
-            const uint32_t r_local = sub * 128u + quarter * 32u + lane;
-            const uint32_t row = tr * tile_rows + r_local;
-            for (uint32_t cc = 0; cc < tile_n; cc += 16) {
-              uint32_t v[16];
-              reduce_slots_x16(ep.ws, work.tile, num_kb_all, total_units, gridDim.x, max_items,
-                               tile_rows, tile_elems, r_local, cc, v);
-              epilogue_store<TC, 16>(ep_item, row, tc * tile_n + cc, v);
+          if (contrib_n <= kMaxContrib) {
+            reduce_tile<TC>(ep_item, contrib_slots, contrib_n, tile_rows, tile_elems,
+                            tr * tile_rows, tc * tile_n, threadIdx.x - 64u);
+          } else {
+            for (uint32_t sub = 0; sub < mi; ++sub) {
+              const uint32_t r_local = sub * 128u + quarter * 32u + lane;
+              const uint32_t row = tr * tile_rows + r_local;
+              for (uint32_t cc = 0; cc < tile_n; cc += 16) {
+                uint32_t v[16];
+                reduce_slots_x16(ep.ws, work.tile, num_kb_all, total_units, gridDim.x, max_items,
+                                 tile_rows, tile_elems, r_local, cc, v);
+                epilogue_store<TC, 16>(ep_item, row, tc * tile_n + cc, v);
+              }
             }
           }
           if (threadIdx.x == 64) p.counters[work.tile] = 0;  // ready for the next launch
+          if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 3] = clock64() - t_entry;
         }
         // last_flag is rewritten by the next item
         ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
         if (!ok) break;
       }
-      if (trace && warp == 2 && lane == 0 && item < 8) trace[192 + 2 * item + 1] = clock64();
+      if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 5] = clock64() - t_entry;
       ++item;
     }
     __syncwarp();
@@ -673,6 +811,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ---------------------------------------------------------------- tear-down
   ptx::tc_fence_before();
   __syncthreads();
+  if (trace && threadIdx.x == 64) {
+    trace[322] = clock64() - t_entry;
+    trace[325] = (long long)ptx::globaltimer_ns();
+  }
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, tmem_cols);

@@ -211,7 +211,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (debug_mode & 2u) {
             if (ptx::elect_one()) ptx::mbar_arrive_cluster(empty0 + 8 * stage);
             if (ptx::elect_one()) ptx::mbar_arrive_cluster(peer_empty0 + 8 * stage);
-            ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+            ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8 * next_stage, next_phase));
             stage = next_stage;
             phase = next_phase;
             continue;
@@ -222,7 +222,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint64_t adesc = adesc0 + (uint64_t)((ks * a_k_step) >> 4);
             const uint32_t accumulate = first | (ks > 0 ? 1u : 0u);
             if (ks == 3)
-              ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * next_stage, next_phase));
+              ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8 * next_stage, next_phase));
             if (kind_f8) {
               if (ptx::elect_one()) ptx::mma_f8_pair(d_base, adesc, bdesc, idesc, accumulate);
             } else {

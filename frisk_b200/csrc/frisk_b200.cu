@@ -236,7 +236,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
     cols = d.M;
     g.mi = rows > 128 ? 2 : 1;
     g.tile_n = (uint32_t)((cols + 15) / 16 * 16);
+#ifdef FRISK_B200_MEASURE
     if (const char* e = getenv("FRISK_B200_SKINNY_MI")) g.mi = atoi(e) > 1 && rows > 128 ? 2 : 1;
+#endif
   }
   g.bk_elems = bk;
   g.k_steps = 4;
@@ -265,7 +267,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
   g.epilogue_backoff_ns = swap ? 0u : frisk::kEpilogueBackoffNs;
+#ifdef FRISK_B200_MEASURE
   if (const char* e = getenv("FRISK_B200_EPI_BACKOFF")) g.epilogue_backoff_ns = (uint32_t)atoi(e);
+#endif
   g.transposed_out = swap ? 1 : 0;
   g.clear_accum = d.clear_accum ? 1 : 0;
   g.c_type = d.c_type;
@@ -461,10 +465,21 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       return tc_ok ? FRISK_ERR_UNSUPPORTED : FRISK_ERR_MISALIGNED;
     }
   } else {
-    // The CTA-pair kernel is correct but not yet faster than the one-CTA kernel; it runs only
-    // when asked for (force_kernel or FRISK_B200_PAIR=1).
-    const char* want_pair = getenv("FRISK_B200_PAIR");
-    const bool use_pair = pair_ok && want_pair && want_pair[0] == '1';
+    // Two SMs on one 256-row tile (each stages half of B) run about 1.12x faster per tile than
+    // two one-CTA tiles, so the pair kernel is taken unless its coarser tiles lose more than that
+    // to the last, partly filled wave.  FRISK_B200_PAIR=0 / =1 overrides the estimate.
+    bool use_pair = false;
+    if (pair_ok) {
+      const uint64_t tn = d.tile_n ? (uint64_t)d.tile_n : (d.N > 128 ? 256u : 128u);
+      const uint64_t cols_t = ((uint64_t)d.N + tn - 1) / tn;
+      const uint64_t one_tiles = (((uint64_t)d.M + 127) / 128) * cols_t;
+      const uint64_t two_tiles = (((uint64_t)d.M + 255) / 256) * cols_t;
+      const uint64_t sms = (uint64_t)pl->sm_count, pairs = sms / 2;
+      const double one_cost = (double)((one_tiles + sms - 1) / sms);
+      const double two_cost = (double)((two_tiles + pairs - 1) / pairs) / 1.12;
+      use_pair = two_cost < one_cost;
+      if (const char* want_pair = getenv("FRISK_B200_PAIR")) use_pair = want_pair[0] == '1';
+    }
     kind = skinny_ok ? FRISK_KERNEL_SKINNY
            : use_pair ? FRISK_KERNEL_TCGEN05_PAIR
            : tc_ok    ? FRISK_KERNEL_TCGEN05
@@ -541,8 +556,10 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   }
   g.C = C;
   g.status = device_status;
+#ifdef FRISK_B200_MEASURE
   if (const char* dbg = getenv("FRISK_B200_DEBUG_MODE")) g.debug_mode = (uint32_t)atoi(dbg);
   if (const char* tr = getenv("FRISK_B200_TRACE")) g.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
+#endif
   g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
   if (swap) {
     // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)

@@ -26,6 +26,13 @@
 namespace frisk {
 
 constexpr int kMaxStages = 12;
+// Measurement builds (-DFRISK_B200_MEASURE) keep the debug modes and the clock stamps of CTA 0;
+// the normal build compiles them out of the kernels.
+#ifdef FRISK_B200_MEASURE
+constexpr bool kMeasureBuild = true;
+#else
+constexpr bool kMeasureBuild = false;
+#endif
 // Warps that wait for a long time sleep between polls: a tight polling loop takes issue slots
 // from the MMA warp on the same SM sub-partition and nearly halves its issue rate.
 constexpr uint32_t kEpilogueBackoffNs = 128;
@@ -484,12 +491,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t acc_bufs = p.acc_bufs;
   const uint32_t tmem_cols = p.tmem_cols;
   const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r;
-  const uint32_t debug_mode = p.debug_mode;
+  const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
   int32_t* const status = p.status;
-  long long* const trace = blockIdx.x == 0 ? p.trace : nullptr;
+  long long* const trace = (kMeasureBuild && blockIdx.x == 0) ? p.trace : nullptr;
 
   // every stamp is relative to the stamping thread's own clock at kernel entry
   const long long t_entry = trace ? clock64() : 0;
+  // (measurement builds) wall-clock entry and exit of every CTA at [1024 + 2 * CTA]
+  if (kMeasureBuild && p.trace && threadIdx.x == 64)
+    p.trace[1024 + 2 * blockIdx.x] = (long long)ptx::globaltimer_ns();
   if (trace && threadIdx.x == 64) {
     trace[320] = 0;
     trace[324] = (long long)ptx::globaltimer_ns();
@@ -577,6 +587,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
           if (tr_on && ptx::elect_one()) trace[2 * issued + 1] = clock64() - t_entry;
+          // Reconverge here: without it the warp stays split after the elected-lane issues above
+          // and walks the next wait that way (measured: 8192^3 bf16 0.89 ms without, 0.82 ms with).
+          __syncwarp();
           ++issued;
           if (++stage == stages) {
             stage = 0;
@@ -811,6 +824,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ---------------------------------------------------------------- tear-down
   ptx::tc_fence_before();
   __syncthreads();
+  if (kMeasureBuild && p.trace && threadIdx.x == 64)
+    p.trace[1024 + 2 * blockIdx.x + 1] = (long long)ptx::globaltimer_ns();
   if (trace && threadIdx.x == 64) {
     trace[322] = clock64() - t_entry;
     trace[325] = (long long)ptx::globaltimer_ns();

@@ -61,8 +61,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t num_tiles = tiles_r * tiles_c;
   const uint32_t num_kb = p.num_kb;
   int32_t* const status = p.status;
-  const uint32_t debug_mode = p.debug_mode;
-  long long* const trace = blockIdx.x == 0 ? p.trace : nullptr;
+  const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
+  long long* const trace = (kMeasureBuild && blockIdx.x == 0) ? p.trace : nullptr;
 
   if (threadIdx.x == 0) {
     abort_word = 0;
@@ -141,6 +141,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
           if (ptx::elect_one()) ptx::tma_load_2d_pair(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
         }
+        __syncwarp();  // reconverge after the elected-lane issues (see the one-CTA kernel)
         if (++stage == stages) {
           stage = 0;
           phase ^= 1;

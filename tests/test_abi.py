@@ -37,8 +37,8 @@ def test_version_and_strerror():
 
 
 @pytest.mark.parametrize("name,kernel", [
-    ("cfg1", "simt"), ("cfg2", "tcgen05"), ("cfg3", "skinny"), ("cfg4", "tcgen05"),
-    ("cfg5", "tcgen05"), ("bf16_8192", "tcgen05"),
+    ("cfg1", "simt"), ("cfg2", "tcgen05_pair"), ("cfg3", "skinny"), ("cfg4", "tcgen05_pair"),
+    ("cfg5", "tcgen05_pair"), ("bf16_8192", "tcgen05_pair"),
 ])
 def test_plan_picks_kernel_family_for_the_benchmark_configs(name, kernel):
     full = {"cfg1": (512, 512, 512), "cfg2": (4096, 4096, 4096), "cfg3": (16, 8192, 8192),

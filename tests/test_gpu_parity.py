@@ -54,14 +54,14 @@ SMALL = [
     ("cfg1", (1, 1, 1), "simt"),
     ("cfg2", (128, 256, 64), "tcgen05"),
     ("cfg2", (128, 64, 128), "tcgen05"),
-    ("cfg2", (256, 512, 512), "tcgen05"),
-    ("cfg2", (200, 300, 136), "tcgen05"),
+    ("cfg2", (256, 512, 512), "tcgen05_pair"),
+    ("cfg2", (200, 300, 136), "tcgen05_pair"),
     ("cfg2", (1, 8, 8), "tcgen05"),
     ("cfg5", (128, 256, 64), "tcgen05"),
-    ("cfg5", (520, 392, 264), "tcgen05"),
-    ("cfg5", (130, 264, 72), "tcgen05"),
+    ("cfg5", (520, 392, 264), "tcgen05_pair"),
+    ("cfg5", (130, 264, 72), "tcgen05_pair"),
     ("cfg4", (128, 256, 128), "tcgen05"),
-    ("cfg4", (200, 300, 400), "tcgen05"),
+    ("cfg4", (200, 300, 400), "tcgen05_pair"),
     ("cfg3", (16, 256, 64), "skinny"),
     ("cfg3", (16, 1024, 4096), "skinny"),
     ("cfg3", (5, 1000, 520), "skinny"),
@@ -110,7 +110,7 @@ def test_all_storage_orders(ab, ta, tb):
                        A=np.ascontiguousarray(W.encode(a, ab).T if ta else W.encode(a, ab)),
                        B=np.ascontiguousarray(W.encode(b, ab).T if tb else W.encode(b, ab)))
     _, info = run_and_check(w)
-    assert info["kernel_name"] == ("simt" if ab == W.F32 else "tcgen05")
+    assert info["kernel_name"] == ("simt" if ab == W.F32 else "tcgen05_pair")  # M = 136 > 128
 
 
 @pytest.mark.parametrize("name,dims", [("cfg1", (96, 80, 64)), ("cfg2", (256, 256, 128)),
@@ -139,7 +139,7 @@ def test_mixed_output_types_and_padded_leading_dimensions():
     B[:, :N] = W.bf16_encode(b)
     Cbuf = np.full((M, N + 24), 0x7FC0, np.uint16)  # NaN canaries in the padding
     plan = R.GemmPlan(M, N, K, W.BF16, lda=K + 8, ldb=N + 16, ldc=N + 24)
-    assert plan.info["kernel_name"] == "tcgen05"
+    assert plan.info["kernel_name"] == "tcgen05_pair"  # M = 130 > 128
     plan.run_host(A, B, Cbuf)
     plan.close()
     assert (Cbuf[:, N:] == 0x7FC0).all(), "the kernel wrote outside its columns"

@@ -320,8 +320,20 @@ int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStrea
                                     (int)pl->dyn_smem));
     pl->smem_attr_set = true;
   }
-  kern<<<pl->info.num_ctas, frisk::kGemmThreads, pl->dyn_smem, st>>>(pl->tmap_a, pl->tmap_b, g);
-  FRISK_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
+  cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = pl->dyn_smem;
+  cfg.stream = st;
+  // the kernel's set-up may start while the previous kernel of the stream drains; it waits
+  // (griddepcontrol.wait) before it touches global memory
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
   return FRISK_OK;
 }
 
@@ -345,13 +357,15 @@ int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t 
   cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = pl->dyn_smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = 2;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
   FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
   return FRISK_OK;
 }

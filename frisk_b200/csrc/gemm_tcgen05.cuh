@@ -528,6 +528,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::tc_fence_after();
   // broadcast: a value loaded from shared memory is not warp-uniform for the compiler otherwise
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_slot, 0);
+  // Everything above touched only this CTA's shared and tensor memory, so it may overlap the tail
+  // of the previous kernel in the stream; global memory (operands a previous GEMM may have
+  // written, the workspace a previous launch of this plan still uses) is touched only from here.
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   if (trace && threadIdx.x == 64) trace[321] = clock64() - t_entry;
 
   WorkIter work;

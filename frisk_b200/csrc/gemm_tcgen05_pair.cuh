@@ -89,6 +89,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   ptx::cluster_wait();
   ptx::tc_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, tmem_base_slot, 0);
+  // the set-up above may overlap the tail of the previous kernel in the stream; global memory is
+  // touched only after that kernel has completed
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------- TMA producers (both CTAs)

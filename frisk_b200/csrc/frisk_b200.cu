@@ -211,13 +211,18 @@ bool skinny_shape(const frisk_gemm_desc& d, int sm_count) {
   return units * (uint64_t)(sm_count + 1) < (1ull << 32);
 }
 
-void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
+bool skinny_clusters_fit(frisk_gemm_plan* pl);
+
+// cluster_try: which cluster candidate of a skinny plan to take (-1: none, plan stream-K).
+void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0) {
   const frisk_gemm_desc& d = pl->d;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
   const uint32_t es = elem_size(d.a_type);
   const uint32_t bk = 128u / es;
   bool a_mn, b_mn;  // majors of the kernel's a-role / b-role operands
+  uint32_t cluster_mi = 1, cluster_k = 1;
+  bool use_cluster = false;
   int64_t rows, cols;
   if (!swap) {
     a_mn = d.transA != 0;  // A stored K x M
@@ -236,9 +241,48 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
     cols = d.M;
     g.mi = rows > 128 ? 2 : 1;
     g.tile_n = (uint32_t)((cols + 15) / 16 * 16);
+    // Split mode 3 (a cluster per tile, a K slice per CTA, partials summed through distributed
+    // shared memory) needs tiles x cluster size CTAs to cover most of the SMs; otherwise the
+    // stream-K plan (mode 2) spreads the work evenly over all of them.
+    // Candidates: 256- or 128-row tiles with the largest power-of-two cluster that keeps the grid
+    // within the SMs, most CTAs first, then the larger tile (fewer, larger TMA boxes).  `cluster_try` skips the candidates the device could not place.
+    const uint32_t kbs = (uint32_t)((d.K + bk - 1) / bk);
+    // percent of the SMs a cluster plan has to use: measured, 64 CTAs in clusters still beat
+    // stream-K over all SMs (16x2048x2048: 10.4 against 15.5 us; 32x2048x8192: 18.7 against 25.7)
+    uint32_t min_cover = 40;
 #ifdef FRISK_B200_MEASURE
-    if (const char* e = getenv("FRISK_B200_SKINNY_MI")) g.mi = atoi(e) > 1 && rows > 128 ? 2 : 1;
+    if (const char* e = getenv("FRISK_B200_MIN_COVER")) min_cover = (uint32_t)atoi(e);
 #endif
+    struct Cand {
+      uint32_t ctas, mi, s;
+    } cand[8];
+    int n_cand = 0;
+    for (uint32_t mi = (rows > 128 ? 2u : 1u); mi >= 1; --mi) {
+      const uint32_t t = (uint32_t)((rows + 128 * mi - 1) / (128 * mi));
+      for (uint32_t s = 8; s >= 2; s >>= 1) {
+        if (s > kbs || (uint64_t)t * s > (uint64_t)pl->sm_count) continue;
+        if (t * s * 100u >= (uint32_t)pl->sm_count * min_cover) cand[n_cand++] = Cand{t * s, mi, s};
+      }
+    }
+    std::sort(cand, cand + n_cand, [](const Cand& x, const Cand& y) {
+      return x.ctas != y.ctas ? x.ctas > y.ctas : x.mi > y.mi;
+    });
+    use_cluster = cluster_try >= 0 && cluster_try < n_cand && d.num_ctas == 0;
+    if (use_cluster) {
+      cluster_mi = cand[cluster_try].mi;
+      cluster_k = cand[cluster_try].s;
+    }
+#ifdef FRISK_B200_MEASURE
+    if (const char* e = getenv("FRISK_B200_SKINNY_CLUSTER")) {
+      const int t = cluster_try + atoi(e);   // skip that many more candidates; negative: none
+      use_cluster = atoi(e) >= 0 && t < n_cand && d.num_ctas == 0;
+      if (use_cluster) {
+        cluster_mi = cand[t].mi;
+        cluster_k = cand[t].s;
+      }
+    }
+#endif
+    if (use_cluster) g.mi = cluster_mi;
   }
   g.bk_elems = bk;
   g.k_steps = 4;
@@ -246,7 +290,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   fill_operand(g.a, a_mn, 128u * g.mi, es, bk);
   fill_operand(g.b, b_mn, pair ? g.tile_n / 2 : g.tile_n, es, bk);
   g.stage_bytes = g.a.stage_bytes + g.b.stage_bytes;
-  uint32_t stages = (uint32_t)(kMaxDynSmem / g.stage_bytes);
+  // split mode 3 keeps one fp32 tile behind the stage buffers: the region the cluster's partials
+  // are pushed into
+  const size_t red_bytes = (swap && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
+  uint32_t stages = (uint32_t)((kMaxDynSmem - red_bytes - (red_bytes ? 1024 : 0)) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
   if (d.stages > 0) stages = std::min<uint32_t>(stages, (uint32_t)d.stages);
   // at least two: a stage is released only after the first MMA of the NEXT k-block was issued,
@@ -285,12 +332,20 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
     if (d.num_ctas > 1) pairs = std::min<uint64_t>(pairs, (uint64_t)d.num_ctas / 2);
     ctas = (uint32_t)(2 * std::max<uint64_t>(pairs, 1));
   }
-  pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024;
+  pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes;
   pl->ws_bytes = 0;
-  if (swap) {
+  if (swap && use_cluster) {
+    g.split_mode = 3;
+    g.cluster_k = cluster_k;
+    ctas = (uint32_t)tiles * cluster_k;
+  } else if (swap) {
     // Split mode 2: every CTA writes the partial tiles of its unit range into private slots; the
     // workspace is [ctas * max_items slots of tile_rows x tile_n fp32][one arrival counter per tile].
     g.split_mode = 2;
+    // the vector reduction sums at most kMaxContrib partials per tile: a tile's k-blocks spread
+    // over ctas / tiles CTAs plus one at each end
+    if (d.num_ctas == 0 && tiles * (frisk::kMaxContrib - 2) < ctas)
+      ctas = (uint32_t)(tiles * (frisk::kMaxContrib - 2));
     const uint64_t per_cta = (units + ctas - 1) / ctas;
     g.max_items = (uint32_t)((per_cta + g.num_kb - 1) / g.num_kb + 1);
     const size_t tile_elems = (size_t)128 * g.mi * g.tile_n;
@@ -310,6 +365,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair) {
   in.smem_bytes = (int)pl->dyn_smem;
   in.launches = 1;
   in.swizzle_a = in.swizzle_b = 128;
+  // the clusters must all be resident at once for the plan to make sense; if this device cannot
+  // place them, plan again without
+  if (swap && use_cluster && pl->have_device && !skinny_clusters_fit(pl))
+    plan_tcgen05(pl, swap, pair, cluster_try + 1);
 }
 
 template <typename TC, bool kSplit>
@@ -328,13 +387,57 @@ int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStrea
   cfg.stream = st;
   // the kernel's set-up may start while the previous kernel of the stream drains; it waits
   // (griddepcontrol.wait) before it touches global memory
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (kSplit && g.split_mode == 3 && g.cluster_k > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = g.cluster_k;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
   return FRISK_OK;
+}
+
+// How many clusters of the plan's size the device can hold at once, for one C type.
+template <typename TC>
+int max_active_clusters_t(frisk_gemm_plan* pl, int* out) {
+  auto kern = frisk::gemm_tcgen05_kernel<TC, true>;
+  FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)pl->dyn_smem));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
+  cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = pl->dyn_smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = pl->gp.cluster_k;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FRISK_CUDA(cudaOccupancyMaxActiveClusters(out, kern, &cfg));
+  return FRISK_OK;
+}
+
+bool skinny_clusters_fit(frisk_gemm_plan* pl) {
+  int n = 0, rc;
+  switch (pl->d.c_type) {
+    case FRISK_DT_F32: rc = max_active_clusters_t<float>(pl, &n); break;
+    case FRISK_DT_F16: rc = max_active_clusters_t<__half>(pl, &n); break;
+    case FRISK_DT_BF16: rc = max_active_clusters_t<__nv_bfloat16>(pl, &n); break;
+    default: return false;
+  }
+  if (rc != FRISK_OK) {
+    cudaGetLastError();
+    return false;
+  }
+  return (uint32_t)n * pl->gp.cluster_k >= (uint32_t)pl->info.num_ctas;
 }
 
 template <typename TC>
@@ -551,7 +654,7 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
     return launch_simt(d, A, B, C, sa, sb, st);  // the CUDA-core kernel has no alignment rule
 
   const bool swap = pl->info.kernel == FRISK_KERNEL_SKINNY;
-  if (swap) {
+  if (swap && pl->ws_bytes) {
     if (!workspace || workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
     if ((uintptr_t)workspace % 16) return FRISK_ERR_MISALIGNED;
   }
@@ -577,11 +680,13 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
   if (swap) {
     // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)
-    g.ws = reinterpret_cast<float*>(workspace);
-    g.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->slot_bytes);
     g.row_scale = sb;
     g.col_scale = sa;
-    if (pl->clean_ws != workspace) {  // the counters must start at zero; the kernel re-zeroes them
+    if (pl->ws_bytes) {
+      g.ws = reinterpret_cast<float*>(workspace);
+      g.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->slot_bytes);
+    }
+    if (pl->ws_bytes && pl->clean_ws != workspace) {  // the counters must start at zero; the kernel re-zeroes them
       FRISK_CUDA(cudaMemsetAsync(g.counters, 0, pl->ws_bytes - pl->slot_bytes, st));
       pl->clean_ws = workspace;
     }
@@ -729,7 +834,7 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   pl.device = dev;
   pl.sm_count = sms;
   pl.have_device = true;
-  plan_tcgen05(&pl, /*swap=*/true, /*pair=*/false);
+  plan_tcgen05(&pl, /*swap=*/true, /*pair=*/false, /*cluster_try=*/-1);
   // this entry point keeps the atomic split (mode 1): its scratch is M x N fp32, independent of
   // the grid, which is what lets a fixed array serve it
   pl.gp.split_mode = 1;

@@ -78,7 +78,10 @@ struct GemmParams {
   uint32_t group_r;    // tile rasterisation: rows of tiles walked together
   uint32_t split_mode;  // 0: whole tiles; 1: stream-K, atomics into ws + finalize kernel;
                         // 2: stream-K, private partial slots, the last CTA of a tile reduces
+                        // 3: one cluster per tile, each CTA a K slice, partials summed
+                        //    through distributed shared memory (no workspace)
   uint32_t max_items;   // split mode 2: most tiles one CTA's unit range can touch
+  uint32_t cluster_k;   // split mode 3: CTAs per cluster = K slices per tile
   uint32_t* counters;   // split mode 2: k-blocks arrived per tile (zero between launches)
   // epilogue
   void* C;
@@ -141,11 +144,17 @@ struct WorkIter {
   uint32_t u, u_end;   // total units x grid size stays below 2^32 (checked when planning)
   uint32_t num_kb, split;
 
-  __device__ void init(uint32_t num_kb_, uint32_t split_, uint32_t num_tiles_) {
+  __device__ void init(uint32_t num_kb_, uint32_t split_, uint32_t num_tiles_,
+                       uint32_t cluster_k = 1) {
     num_kb = num_kb_;
     split = split_;
     num_tiles = num_tiles_;
-    if (split) {
+    if (split == 3) {
+      // cluster c owns tile c; the CTA of rank r in it owns k-blocks [num_kb r / S, num_kb (r+1) / S)
+      const uint32_t t = blockIdx.x / cluster_k, r = blockIdx.x - t * cluster_k;
+      u = t * num_kb + num_kb * r / cluster_k;
+      u_end = t * num_kb + num_kb * (r + 1) / cluster_k;
+    } else if (split) {
       const uint32_t total = num_tiles * num_kb;
       u = total * blockIdx.x / gridDim.x;
       u_end = total * (blockIdx.x + 1) / gridDim.x;
@@ -449,6 +458,46 @@ __device__ __forceinline__ void reduce_tile(const EpiArgs& p, const uint32_t* sl
   }
 }
 
+// Split mode 3.  Rank r of a cluster owns rows [r R, (r + 1) R) of the tile, R = tile_rows /
+// cluster size.  Every CTA pushes each part of its partial tile into the owner's shared memory
+// (remote stores, no waiting), at [source rank][column][row in share] fp32; after one cluster
+// barrier each owner sums what arrived, reading only its own shared memory, so a CTA may leave as
+// soon as it has passed the barrier.  The sum runs over source ranks 0, 1, ... in that order.
+template <int NC>
+__device__ __forceinline__ void cluster_push(uint32_t dst, uint32_t col_stride_bytes, uint32_t c0,
+                                             const uint32_t (&acc)[NC]) {
+#pragma unroll
+  for (int j = 0; j < NC; ++j) ptx::st_shared_cluster_u32(dst + (c0 + j) * col_stride_bytes, acc[j]);
+}
+
+template <typename TC>
+__device__ __forceinline__ void reduce_share(const EpiArgs& p, uint32_t buf, uint32_t cluster_k,
+                                             uint32_t rank, uint32_t share, uint32_t tile_n,
+                                             uint32_t row0, uint32_t col0, uint32_t tid) {
+  const uint32_t q_per_col = share >> 2;          // float4 pieces per column (share: 16 .. 128)
+  const uint32_t pieces = tile_n * q_per_col;
+  const uint32_t src_stride = tile_n * share * 4u;  // bytes between two sources' images
+  for (uint32_t i = tid; i < pieces; i += 128u) {
+    const uint32_t col = i / q_per_col, q = i - col * q_per_col;
+    const uint32_t at = buf + (col * share + 4u * q) * 4u;
+    float4 x[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (k < (int)cluster_k) x[k] = ptx::ld_shared_f32x4(at + k * src_stride);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k < (int)cluster_k) {
+        sum.x += x[k].x;
+        sum.y += x[k].y;
+        sum.z += x[k].z;
+        sum.w += x[k].w;
+      }
+    }
+    store_rows4<TC>(p, row0 + rank * share + 4u * q, col0 + col, sum);
+  }
+}
+
 // kSplit selects the K-split (stream-K) code at compile time.  The whole-tile instantiation carries
 // none of it: with the slot reduction inlined the kernel needs 200+ registers and measurably slows
 // the whole-tile main loop (8192^3 bf16: 0.98 ms against 0.83 ms), so the two are kept apart.
@@ -536,7 +585,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (trace && threadIdx.x == 64) trace[321] = clock64() - t_entry;
 
   WorkIter work;
-  work.init(p.num_kb, kSplit ? p.split_mode : 0u, tiles_r * tiles_c);
+  work.init(p.num_kb, kSplit ? p.split_mode : 0u, tiles_r * tiles_c, kSplit ? p.cluster_k : 1u);
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------- TMA producer
@@ -725,6 +774,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t total_units = tiles_r * tiles_c * num_kb_all;
     const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
     const uint32_t epi_backoff = p.epilogue_backoff_ns;
+    const uint32_t cluster_k = kSplit ? p.cluster_k : 1u;
+    const uint32_t my_rank = blockIdx.x % cluster_k, share = tile_rows / cluster_k;
+    const uint32_t red_base = tiles_base + stages * stage_bytes;
     uint32_t epi_phase = 0;
     uint32_t item = 0;
     bool ok = true;
@@ -738,8 +790,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const bool whole = work.kb0 == 0 && work.kb1 == num_kb_all;
       const bool to_slot = split_mode == 2 && !whole;
       EpiArgs ep_item = ep;
-      if (split_mode == 2) ep_item.split_mode = 0;
+      if (split_mode >= 2) ep_item.split_mode = 0;
       float* slot = nullptr;
+      // split mode 3: the partial is pushed into the shared memory of the tile's owners, into a
+      // region behind the stage buffers that nothing else uses (an owner may still be streaming)
+      const bool to_smem = split_mode == 3 && !whole;
       if (to_slot) {
         // worked out while the item's MMAs still run: where the partial goes, and (one thread) who
         // else holds a partial of this tile, in case this CTA turns out to be the last to arrive
@@ -761,12 +816,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t row = tr * tile_rows + r_local;
         const uint32_t t_row =
             tmem_base + ((quarter * 32u) << 16) + acc * (mi * tile_n) + sub * tile_n;
+        uint32_t push_dst = 0;
+        if (to_smem) {
+          const uint32_t owner = r_local / share, rr = r_local - owner * share;
+          push_dst = ptx::mapa(red_base + ((my_rank * tile_n) * share + rr) * 4u, owner);
+        }
         if ((tile_n & 31u) == 0) {
           for (uint32_t cc = 0; cc < tile_n; cc += 32) {
             uint32_t v[32];
             ptx::tmem_ld_32x32b_x32(t_row + cc, v);
             ptx::tmem_ld_wait();
-            if (to_slot) slot_store<32>(slot, tile_rows, r_local, cc, v);
+            if (to_smem) cluster_push<32>(push_dst, share * 4u, cc, v);
+            else if (to_slot) slot_store<32>(slot, tile_rows, r_local, cc, v);
             else epilogue_store<TC, 32>(ep_item, row, tc * tile_n + cc, v);
           }
         } else {
@@ -774,7 +835,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t v[16];
             ptx::tmem_ld_32x32b_x16(t_row + cc, v);
             ptx::tmem_ld_wait();
-            if (to_slot) slot_store<16>(slot, tile_rows, r_local, cc, v);
+            if (to_smem) cluster_push<16>(push_dst, share * 4u, cc, v);
+            else if (to_slot) slot_store<16>(slot, tile_rows, r_local, cc, v);
             else epilogue_store<TC, 16>(ep_item, row, tc * tile_n + cc, v);
           }
         }
@@ -824,6 +886,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ++item;
     }
     __syncwarp();
+  }
+
+  if (kSplit && p.split_mode == 3 && p.cluster_k > 1) {
+    // Every thread of the cluster passes this barrier, whatever happened in its role (all waits
+    // above are bounded), so a CTA that gave up cannot strand its peers here.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();   // every partial has been pushed to its owner
+    if (trace && threadIdx.x == 64) trace[326] = clock64() - t_entry;
+    if (warp >= 2 && warp <= 5 && !*abort_flag) {
+      EpiArgs ep;
+      ep.C = p.C;
+      ep.ws = nullptr;
+      ep.row_scale = p.row_scale;
+      ep.col_scale = p.col_scale;
+      ep.ldc = p.ldc;
+      ep.ws_ld = 0;
+      ep.rows = p.rows;
+      ep.cols = p.cols;
+      ep.split_mode = 0;
+      ep.transposed_out = p.transposed_out;
+      ep.clear_accum = p.clear_accum;
+      ep.c_vec_ok = p.c_vec_ok;
+      const uint32_t cluster_k = p.cluster_k;
+      const uint32_t tile = blockIdx.x / cluster_k, rank = blockIdx.x - tile * cluster_k;
+      uint32_t tr, tc;
+      tile_coords(group_r, tiles_r, tiles_c, tile, tr, tc);
+      reduce_share<TC>(ep, tiles_base + stages * stage_bytes, cluster_k, rank,
+                       128u * mi / cluster_k, tile_n, tr * 128u * mi, tc * tile_n,
+                       threadIdx.x - 64u);
+    }
+    if (trace && threadIdx.x == 64) trace[327] = clock64() - t_entry;
+    // after the barrier nobody touches another CTA's shared memory, so each CTA leaves on its own
   }
 
   // ---------------------------------------------------------------- tear-down

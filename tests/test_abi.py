@@ -50,9 +50,17 @@ def test_plan_picks_kernel_family_for_the_benchmark_configs(name, kernel):
     assert plan.info["kernel_name"] == kernel
     if kernel == "skinny":
         assert plan.info["swap_ab"] == 1 and plan.info["split_k"] == 1
-        # 148 CTAs x 2 partial-tile slots of 256 x 16 fp32, plus one arrival counter per tile
-        assert plan.workspace_bytes == 148 * 2 * 256 * 16 * 4 + 32 * 4
+        # 32 tiles of 256 columns of B, each owned by a cluster of four CTAs (a K slice each) that
+        # sum their partials through distributed shared memory: no workspace
+        assert plan.workspace_bytes == 0 and plan.info["num_ctas"] == 128
         assert plan.info["launches"] == 1
+        # too few tiles for clusters to cover enough SMs: stream-K, at most 14 CTAs per tile (the
+        # reduction sums up to 16 partials), 28 x 2 partial-tile slots of 256 x 16 fp32 and one
+        # arrival counter per tile
+        sk = R.GemmPlan(16, 512, 4096, ab, ct)
+        assert sk.info["kernel_name"] == "skinny" and sk.info["num_ctas"] == 28
+        assert sk.workspace_bytes == 28 * 2 * 256 * 16 * 4 + 2 * 4
+        sk.close()
     else:
         assert plan.workspace_bytes == 0 and plan.info["launches"] == 1
     if kernel != "simt":

@@ -150,10 +150,15 @@ struct WorkIter {
     split = split_;
     num_tiles = num_tiles_;
     if (split == 3) {
-      // cluster c owns tile c; the CTA of rank r in it owns k-blocks [num_kb r / S, num_kb (r+1) / S)
-      const uint32_t t = blockIdx.x / cluster_k, r = blockIdx.x - t * cluster_k;
-      u = t * num_kb + num_kb * r / cluster_k;
-      u_end = t * num_kb + num_kb * (r + 1) / cluster_k;
+      // cluster c owns tile c; the CTA of rank r in it owns k-blocks [num_kb r / S, num_kb (r+1) / S).
+      // S is a power of two: shifts, because a division costs this short kernel ~100 cycles a time
+      const uint32_t sh = 31u - __clz(cluster_k);
+      const uint32_t t = blockIdx.x >> sh, r = blockIdx.x & (cluster_k - 1u);
+      tile = t;
+      kb0 = (num_kb * r) >> sh;
+      kb1 = (num_kb * (r + 1)) >> sh;
+      u = 0;
+      u_end = 1;   // one work item
     } else if (split) {
       const uint32_t total = num_tiles * num_kb;
       u = total * blockIdx.x / gridDim.x;
@@ -164,6 +169,11 @@ struct WorkIter {
     }
   }
   __device__ bool next() {
+    if (split == 3) {
+      if (u >= u_end) return false;
+      u = u_end;
+      return true;
+    }
     if (split) {
       if (u >= u_end) return false;
       tile = u / num_kb;
@@ -186,6 +196,11 @@ struct WorkIter {
 // down the band first, so that CTAs running at the same time share A rows and B columns in L2.
 __device__ __forceinline__ void tile_coords(uint32_t group_r, uint32_t tiles_r, uint32_t tiles_c,
                                             uint32_t tile, uint32_t& tr, uint32_t& tc) {
+  if (tiles_c == 1) {  // one column of tiles (every split plan): nothing to divide
+    tr = tile;
+    tc = 0;
+    return;
+  }
   const uint32_t band_tiles = group_r * tiles_c;
   const uint32_t band = tile / band_tiles;
   const uint32_t first_r = band * group_r;
@@ -475,10 +490,11 @@ __device__ __forceinline__ void reduce_share(const EpiArgs& p, uint32_t buf, uin
                                              uint32_t rank, uint32_t share, uint32_t tile_n,
                                              uint32_t row0, uint32_t col0, uint32_t tid) {
   const uint32_t q_per_col = share >> 2;          // float4 pieces per column (share: 16 .. 128)
+  const uint32_t q_sh = 31u - __clz(q_per_col);
   const uint32_t pieces = tile_n * q_per_col;
   const uint32_t src_stride = tile_n * share * 4u;  // bytes between two sources' images
   for (uint32_t i = tid; i < pieces; i += 128u) {
-    const uint32_t col = i / q_per_col, q = i - col * q_per_col;
+    const uint32_t col = i >> q_sh, q = i & (q_per_col - 1u);   // share is a power of two
     const uint32_t at = buf + (col * share + 4u * q) * 4u;
     float4 x[8];
 #pragma unroll
@@ -542,6 +558,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r;
   const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
   int32_t* const status = p.status;
+  const bool cluster_sync = kSplit && p.split_mode == 3 && p.cluster_k > 1;
   long long* const trace = (kMeasureBuild && blockIdx.x == 0) ? p.trace : nullptr;
 
   // every stamp is relative to the stamping thread's own clock at kernel entry
@@ -660,6 +677,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     __syncwarp();
+    if (cluster_sync) {  // see the epilogue role
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+    }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
     {
@@ -753,6 +774,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     __syncwarp();
+    if (cluster_sync) {  // see the epilogue role
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+    }
   } else {
     // ------------------------------------------------------------- epilogue
     EpiArgs ep;
@@ -775,7 +800,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
     const uint32_t epi_backoff = p.epilogue_backoff_ns;
     const uint32_t cluster_k = kSplit ? p.cluster_k : 1u;
-    const uint32_t my_rank = blockIdx.x % cluster_k, share = tile_rows / cluster_k;
+    // (the cluster size is a power of two)
+    const uint32_t cluster_sh = 31u - __clz(cluster_k);
+    const uint32_t my_rank = blockIdx.x & (cluster_k - 1u), share = tile_rows >> cluster_sh;
+    const uint32_t share_sh = 31u - __clz(share);
     const uint32_t red_base = tiles_base + stages * stage_bytes;
     uint32_t epi_phase = 0;
     uint32_t item = 0;
@@ -818,7 +846,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tmem_base + ((quarter * 32u) << 16) + acc * (mi * tile_n) + sub * tile_n;
         uint32_t push_dst = 0;
         if (to_smem) {
-          const uint32_t owner = r_local / share, rr = r_local - owner * share;
+          const uint32_t owner = r_local >> share_sh, rr = r_local - owner * share;
           push_dst = ptx::mapa(red_base + ((my_rank * tile_n) * share + rr) * 4u, owner);
         }
         if ((tile_n & 31u) == 0) {
@@ -886,38 +914,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ++item;
     }
     __syncwarp();
-  }
-
-  if (kSplit && p.split_mode == 3 && p.cluster_k > 1) {
-    // Every thread of the cluster passes this barrier, whatever happened in its role (all waits
-    // above are bounded), so a CTA that gave up cannot strand its peers here.
-    ptx::cluster_arrive();
-    ptx::cluster_wait();   // every partial has been pushed to its owner
-    if (trace && threadIdx.x == 64) trace[326] = clock64() - t_entry;
-    if (warp >= 2 && warp <= 5 && !*abort_flag) {
-      EpiArgs ep;
-      ep.C = p.C;
-      ep.ws = nullptr;
-      ep.row_scale = p.row_scale;
-      ep.col_scale = p.col_scale;
-      ep.ldc = p.ldc;
-      ep.ws_ld = 0;
-      ep.rows = p.rows;
-      ep.cols = p.cols;
-      ep.split_mode = 0;
-      ep.transposed_out = p.transposed_out;
-      ep.clear_accum = p.clear_accum;
-      ep.c_vec_ok = p.c_vec_ok;
-      const uint32_t cluster_k = p.cluster_k;
-      const uint32_t tile = blockIdx.x / cluster_k, rank = blockIdx.x - tile * cluster_k;
-      uint32_t tr, tc;
-      tile_coords(group_r, tiles_r, tiles_c, tile, tr, tc);
-      reduce_share<TC>(ep, tiles_base + stages * stage_bytes, cluster_k, rank,
-                       128u * mi / cluster_k, tile_n, tr * 128u * mi, tc * tile_n,
-                       threadIdx.x - 64u);
+    if (cluster_sync) {
+      // Split mode 3.  Every warp of every CTA of the cluster passes this barrier exactly once,
+      // whatever happened in its role (all waits above are bounded), so a CTA that gave up cannot
+      // strand its peers.  After it every partial has reached its owner, and nobody touches
+      // another CTA's shared memory again, so each CTA leaves on its own.
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+      if (trace && threadIdx.x == 64) trace[326] = clock64() - t_entry;
+      if (!*abort_flag) {
+        uint32_t tr, tc;
+        tile_coords(group_r, tiles_r, tiles_c, blockIdx.x >> cluster_sh, tr, tc);
+        EpiArgs ep_out = ep;
+        ep_out.split_mode = 0;
+        reduce_share<TC>(ep_out, red_base, cluster_k, my_rank, share, tile_n, tr * tile_rows,
+                         tc * tile_n, threadIdx.x - 64u);
+      }
+      if (trace && threadIdx.x == 64) trace[327] = clock64() - t_entry;
     }
-    if (trace && threadIdx.x == 64) trace[327] = clock64() - t_entry;
-    // after the barrier nobody touches another CTA's shared memory, so each CTA leaves on its own
   }
 
   // ---------------------------------------------------------------- tear-down

@@ -42,10 +42,13 @@ BOUND = {"cfg3": "hbm"}  # everything else is judged against the tensor-core pea
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/; None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    "bf16_8192": 1097518336,   # profiles/gemm_tcgen05_bf16_8192.md: 969.0 MB read + 128.5 MB written
-    "cfg5": 8 * 1097518336,    # scaled from the 8192-row capture: cfg5 is eight such row slabs of the
-                               # same B, walked band by band, so the traffic grows with the rows
-    "cfg3": 139361280,         # profiles/gemm_skinny_cfg3.md: 135.1 MB read + 4.3 MB written
+    # profiles/gemm_tcgen05_pair_bf16_8192.md: 1222.5 MB read + 128.9 MB written
+    "bf16_8192": 1351333824,
+    # scaled from the 8192-row capture: cfg5 is eight such row slabs of the same B, walked band by
+    # band, so the traffic grows with the rows
+    "cfg5": 8 * 1351333824,
+    # profiles/gemm_skinny_cluster_cfg3.md: 134.57 MB read + 4.01 MB written
+    "cfg3": 138584832,
 }
 
 

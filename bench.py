@@ -44,9 +44,8 @@ BOUND = {"cfg3": "hbm"}  # everything else is judged against the tensor-core pea
 NCU_TRAFFIC_BYTES = {
     # profiles/gemm_tcgen05_pair_bf16_8192.md: 1222.5 MB read + 128.9 MB written
     "bf16_8192": 1351333824,
-    # scaled from the 8192-row capture: cfg5 is eight such row slabs of the same B, walked band by
-    # band, so the traffic grows with the rows
-    "cfg5": 8 * 1351333824,
+    # cfg5 is scaled from the 8192-row capture by the rows a rank holds: it is that many row slabs
+    # against the same B, walked band by band, so the traffic grows with the rows (roofline_for)
     # profiles/gemm_skinny_cluster_cfg3.md: 134.57 MB read + 4.01 MB written
     "cfg3": 138584832,
 }
@@ -205,7 +204,8 @@ def roofline_for(name, M, N, K, ms, peaks, sustained):
     return {"bound": BOUND.get(name, "tensor"), "achieved": round(achieved, 2),
             "peak": None if peak is None else round(peak, 1), "unit": unit,
             "frac": None if peak is None else round(achieved / peak, 4),
-            "traffic": NCU_TRAFFIC_BYTES.get(name),
+            "traffic": (NCU_TRAFFIC_BYTES["bf16_8192"] * M // 8192 if name == "cfg5"
+                        else NCU_TRAFFIC_BYTES.get(name)),
             "peak_source": peaks["source"] + (" (sustained)" if sustained and unit == "TFLOP/s" else " (burst)" if unit == "TFLOP/s" else "")}
 
 

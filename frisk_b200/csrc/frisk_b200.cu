@@ -89,6 +89,14 @@ struct frisk_gemm_plan {
   float *hSa = nullptr, *hSb = nullptr;
   int32_t* hStatus = nullptr;
   cudaStream_t hstream = nullptr;
+  // pipelined form of frisk_b200_gemm_run_host: row chunks on three streams
+  static constexpr int kMaxChunks = 16;
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[kMaxChunks] = {}, ev_done[kMaxChunks] = {}, ev_start = nullptr;
+  frisk_gemm_plan* chunk_plan = nullptr;  // the same GEMM over chunk_rows rows
+  frisk_gemm_plan* tail_plan = nullptr;   // ... over the rows left after the last full chunk
+  int64_t chunk_rows = 0;
+  int n_chunks = 0;                       // 0: not decided yet; 1: no pipelining
 };
 
 namespace {
@@ -310,6 +318,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.tiles_c = (uint32_t)((cols + g.tile_n - 1) / g.tile_n);
   g.num_kb = (uint32_t)((d.K + bk - 1) / bk);
   g.group_r = 16;
+#if defined(FRISK_B200_MEASURE) || defined(FRISK_B200_TUNE)
+  if (const char* e = getenv("FRISK_B200_GROUP_R")) g.group_r = (uint32_t)std::max(1, atoi(e));
+#endif
   g.split_mode = swap ? 1 : 0;
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
@@ -621,6 +632,15 @@ void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* pl) {
   cudaFree(pl->hA); cudaFree(pl->hB); cudaFree(pl->hC); cudaFree(pl->hWs);
   cudaFree(pl->hSa); cudaFree(pl->hSb); cudaFree(pl->hStatus);
   if (pl->hstream) cudaStreamDestroy(pl->hstream);
+  if (pl->s_in) cudaStreamDestroy(pl->s_in);
+  if (pl->s_out) cudaStreamDestroy(pl->s_out);
+  if (pl->ev_start) cudaEventDestroy(pl->ev_start);
+  for (int i = 0; i < frisk_gemm_plan::kMaxChunks; ++i) {
+    if (pl->ev_in[i]) cudaEventDestroy(pl->ev_in[i]);
+    if (pl->ev_done[i]) cudaEventDestroy(pl->ev_done[i]);
+  }
+  frisk_b200_gemm_plan_destroy(pl->chunk_plan);
+  frisk_b200_gemm_plan_destroy(pl->tail_plan);
   cudaGetLastError();
   delete pl;
 }
@@ -714,6 +734,93 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   return rc;
 }
 
+namespace {
+
+// Decides once per plan whether frisk_b200_gemm_run_host runs as a pipeline of row chunks.  With
+// the operands in host memory the call is bound by the PCIe copies (cfg5: 1.2 GB up, 1 GB down
+// against 6 ms of GEMM), and the two directions are independent links: while chunk i is computed
+// chunk i+1 is on its way up and chunk i-1 on its way down.  Needs A stored row-major (a row chunk
+// is then one contiguous block) and enough rows for at least two chunks of 2048.
+int plan_host_pipeline(frisk_gemm_plan* pl) {
+  const frisk_gemm_desc& d = pl->d;
+  pl->n_chunks = 1;
+  if (d.transA || d.M < 4096) return FRISK_OK;
+  int n = (int)std::min<int64_t>(frisk_gemm_plan::kMaxChunks, d.M / 2048);
+  int64_t rows = ((d.M + n - 1) / n + 255) / 256 * 256;
+  n = (int)((d.M + rows - 1) / rows);
+  if (n < 2) return FRISK_OK;
+  frisk_gemm_desc dc = d;
+  dc.M = rows;
+  int rc = frisk_b200_gemm_plan_create(&dc, &pl->chunk_plan);
+  if (rc) return rc;
+  const int64_t tail = d.M - (int64_t)(n - 1) * rows;
+  if (tail != rows) {
+    dc.M = tail;
+    rc = frisk_b200_gemm_plan_create(&dc, &pl->tail_plan);
+    if (rc) return rc;
+  }
+  // the chunk plans must not need a workspace of their own (they are never few-row plans)
+  if (pl->chunk_plan->ws_bytes || (pl->tail_plan && pl->tail_plan->ws_bytes)) return FRISK_OK;
+  FRISK_CUDA(cudaStreamCreateWithFlags(&pl->s_in, cudaStreamNonBlocking));
+  FRISK_CUDA(cudaStreamCreateWithFlags(&pl->s_out, cudaStreamNonBlocking));
+  FRISK_CUDA(cudaEventCreateWithFlags(&pl->ev_start, cudaEventDisableTiming));
+  for (int i = 0; i < n; ++i) {
+    FRISK_CUDA(cudaEventCreateWithFlags(&pl->ev_in[i], cudaEventDisableTiming));
+    FRISK_CUDA(cudaEventCreateWithFlags(&pl->ev_done[i], cudaEventDisableTiming));
+  }
+  pl->chunk_rows = rows;
+  pl->n_chunks = n;
+  return FRISK_OK;
+}
+
+int run_host_pipelined(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
+                       const float* scale_a, const float* scale_b) {
+  const frisk_gemm_desc& d = pl->d;
+  const size_t a_pitch = (size_t)d.lda * elem_size(d.a_type);
+  const size_t c_pitch = (size_t)d.ldc * elem_size(d.c_type);
+  const size_t c_row = (size_t)d.N * elem_size(d.c_type);
+  cudaStream_t s_in = pl->s_in, s_cmp = pl->hstream, s_out = pl->s_out;
+  // up: status word, B, scales, then the chunks of A (and of C when the GEMM accumulates into it)
+  FRISK_CUDA(cudaMemsetAsync(pl->hStatus, 0, sizeof(int32_t), s_in));
+  FRISK_CUDA(cudaMemcpyAsync(pl->hB, B, b_bytes(d), cudaMemcpyHostToDevice, s_in));
+  if (d.scale_mode) {
+    FRISK_CUDA(cudaMemcpyAsync(pl->hSa, scale_a, d.M * sizeof(float), cudaMemcpyHostToDevice, s_in));
+    FRISK_CUDA(cudaMemcpyAsync(pl->hSb, scale_b, d.N * sizeof(float), cudaMemcpyHostToDevice, s_in));
+  }
+  for (int i = 0; i < pl->n_chunks; ++i) {
+    const int64_t r0 = (int64_t)i * pl->chunk_rows;
+    const int64_t rows = std::min<int64_t>(pl->chunk_rows, d.M - r0);
+    frisk_gemm_plan* sub = (rows == pl->chunk_rows) ? pl->chunk_plan : pl->tail_plan;
+    const char* a_src = static_cast<const char*>(A) + r0 * a_pitch;
+    char* a_dst = static_cast<char*>(pl->hA) + r0 * a_pitch;
+    char* c_host = static_cast<char*>(C) + r0 * c_pitch;
+    char* c_dev = static_cast<char*>(pl->hC) + r0 * c_pitch;
+    FRISK_CUDA(cudaMemcpyAsync(a_dst, a_src, (size_t)rows * a_pitch, cudaMemcpyHostToDevice, s_in));
+    if (!d.clear_accum)
+      FRISK_CUDA(cudaMemcpyAsync(c_dev, c_host, (size_t)rows * c_pitch, cudaMemcpyHostToDevice, s_in));
+    FRISK_CUDA(cudaEventRecord(pl->ev_in[i], s_in));
+    // compute
+    FRISK_CUDA(cudaStreamWaitEvent(s_cmp, pl->ev_in[i], 0));
+    int rc = frisk_b200_gemm_run(sub, a_dst, pl->hB, c_dev, pl->hSa ? pl->hSa + r0 : nullptr,
+                                 pl->hSb, nullptr, 0, pl->hStatus, s_cmp);
+    if (rc) {
+      cudaDeviceSynchronize();  // nothing of this call may still be in flight when it returns
+      return rc;
+    }
+    FRISK_CUDA(cudaEventRecord(pl->ev_done[i], s_cmp));
+    // down: only the N columns of each row, the caller's padding stays as it was
+    FRISK_CUDA(cudaStreamWaitEvent(s_out, pl->ev_done[i], 0));
+    FRISK_CUDA(cudaMemcpy2DAsync(c_host, c_pitch, c_dev, c_pitch, c_row, (size_t)rows,
+                                 cudaMemcpyDeviceToHost, s_out));
+  }
+  // the next call reuses the device buffers: its first copy must not overtake this call's last
+  // GEMM or copy-back, so everything drains here (the call is synchronous anyway)
+  FRISK_CUDA(cudaStreamSynchronize(s_cmp));
+  return frisk_b200_check_status(pl->hStatus, s_out);
+}
+
+}  // namespace
+
 int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
                              const float* scale_a, const float* scale_b) {
   if (!pl || !A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
@@ -734,6 +841,11 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, 
     }
   }
   cudaStream_t st = pl->hstream;
+  if (pl->n_chunks == 0) {
+    int rc = plan_host_pipeline(pl);
+    if (rc) return rc;
+  }
+  if (pl->n_chunks > 1) return run_host_pipelined(pl, A, B, C, scale_a, scale_b);
   FRISK_CUDA(cudaMemsetAsync(pl->hStatus, 0, sizeof(int32_t), st));
   FRISK_CUDA(cudaMemcpyAsync(pl->hA, A, a_bytes(d), cudaMemcpyHostToDevice, st));
   FRISK_CUDA(cudaMemcpyAsync(pl->hB, B, b_bytes(d), cudaMemcpyHostToDevice, st));

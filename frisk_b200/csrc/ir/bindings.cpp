@@ -826,7 +826,8 @@ void initBuilder(py::module_& m) {
         return AffineMap::get(map.numDims, map.numSymbols, r);
       })
       // frisk ops
-      .def("create_gemm_op", [](PyBuilder& s, PyValue& A, PyValue& B, PyValue& C, bool transA, bool transB, bool clearAccum) {
+      .def("create_gemm_op", [](PyBuilder& s, PyValue& A, PyValue& B, PyValue& C, bool transA, bool transB, bool clearAccum,
+                                std::optional<PyValue> scaleA, std::optional<PyValue> scaleB) {
         const TypeStorage* a = requireMemRef(A.v, "A");
         const TypeStorage* b = requireMemRef(B.v, "B");
         const TypeStorage* c = requireMemRef(C.v, "C");
@@ -847,10 +848,28 @@ void initBuilder(py::module_& m) {
         // inputs, which it cannot express at all, may pair with a wider C
         if (!typeEqual(a->element, b->element) || (!typeEqual(a->element, c->element) && !fp8))
           throw std::invalid_argument("create_gemm_op expects operands to have matching element types");
+        // addition: per-row scales of A and per-column scales of B (fp32 vectors of M and N
+        // entries) for 8-bit float inputs; the reference's op has three operands only
+        if (scaleA.has_value() != scaleB.has_value())
+          throw std::invalid_argument("create_gemm_op expects scale_a and scale_b together");
+        if (scaleA) {
+          if (!fp8) throw std::invalid_argument("create_gemm_op takes scales only with 8-bit float operands");
+          auto vec = [](Value v, int64_t n, const char* what) {
+            const TypeStorage* t = requireMemRef(v, what);
+            if (t->shape.size() != 1 || t->shape[0] != n || t->element->kind != TypeKind::F32)
+              throw std::invalid_argument(std::string("create_gemm_op expects ") + what + " to be a rank-1 f32 memref of matching length");
+          };
+          vec(scaleA->v, mm, "scale_a");
+          vec(scaleB->v, n, "scale_b");
+        }
         Operation* op = s.b.create("frisk.gemm");
         op->addOperand(A.v);
         op->addOperand(B.v);
         op->addOperand(C.v);
+        if (scaleA) {
+          op->addOperand(scaleA->v);
+          op->addOperand(scaleB->v);
+        }
         op->attrs["transA"] = IntAttr{transA, 1};
         op->attrs["transB"] = IntAttr{transB, 1};
         op->attrs["M"] = IntAttr{mm, 64};
@@ -859,7 +878,8 @@ void initBuilder(py::module_& m) {
         op->attrs["policy"] = EnumAttr{"gemm_warp_policy", "Square"};
         op->attrs["clear_accum"] = IntAttr{clearAccum, 1};
         return wrapOp<PyGemm>(op);
-      }, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("transA") = false, py::arg("transB") = false, py::arg("clear_accum") = false)
+      }, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("transA") = false, py::arg("transB") = false, py::arg("clear_accum") = false,
+         py::arg("scale_a") = py::none(), py::arg("scale_b") = py::none())
       .def("create_kernel_op", [](PyBuilder& s, PyModule& mod, const std::string& name, PyType& ty) {
         if (Operation* k = lookupSymbol(mod.op, name, "frisk.kernel")) return wrapOp<PyKernel>(k);
         if (!ty.t || ty.t->kind != TypeKind::Function) throw std::invalid_argument("invalid kernel function type");
@@ -964,6 +984,25 @@ void initBuilder(py::module_& m) {
 
 void initFrisk(py::module_ m) {
   m.def("load_dialects", [](Context& c) { c.friskLoaded = true; });
+  // addition: the tiled matrix product around a frisk.gemm (tmp/ir.mlir:1-17) lifted to one
+  // whole-problem GEMM; raises ValueError with the reason when the kernel is anything else
+  m.def("lift_tiled_gemm", [](PyKernel& k) {
+    TiledGemm t = liftTiledGemm(k.op);
+    if (!t.ok) throw std::invalid_argument("not a tiled matrix product: " + t.why);
+    py::dict d;
+    d["M"] = t.M;
+    d["N"] = t.N;
+    d["K"] = t.K;
+    d["arg_a"] = t.argA;
+    d["arg_b"] = t.argB;
+    d["arg_c"] = t.argC;
+    d["clear_accum"] = t.clearAccum;
+    d["ab_type"] = castType(t.elemAB);
+    d["c_type"] = castType(t.elemC);
+    d["tile"] = t.tile;
+    d["grid"] = t.grid;
+    return d;
+  });
 
   py::class_<PyGemm, PyOpState>(m, "GemmOp", py::module_local())
       .def_static("from_operation", [](PyOperation& o) -> py::object {
@@ -975,8 +1014,15 @@ void initFrisk(py::module_ m) {
       .def("get_matrix_C", [](PyGemm& g) { return castValue(g.op->operands[2]); })
       .def("get_all_matrix", [](PyGemm& g) {
         PyValueRange r;
-        for (Value v : g.op->operands) r.vals.push_back(PyValue{v, g.keep});
+        for (size_t i = 0; i < 3; ++i) r.vals.push_back(PyValue{g.op->operands[i], g.keep});
         return r;
+      })
+      // additions: the scale vectors of an 8-bit float gemm (None when the op has none)
+      .def("get_scale_A", [](PyGemm& g) -> py::object {
+        return g.op->operands.size() == 5 ? castValue(g.op->operands[3]) : py::object(py::none());
+      })
+      .def("get_scale_B", [](PyGemm& g) -> py::object {
+        return g.op->operands.size() == 5 ? castValue(g.op->operands[4]) : py::object(py::none());
       })
       // additions: the op's attributes, and the shared-memory layout the reference infers for an
       // operand tile together with its Blackwell mapping inputs

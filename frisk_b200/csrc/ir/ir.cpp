@@ -441,11 +441,14 @@ void printOp(std::ostream& os, Operation* op, int indent, const Names& n) {
     printAttrDict(os, op, {"srcMap", "dstMap", "srcExtents", "dstExtents"}, /*leadingSpace=*/false);
     os << " : " << printType(op->operands[0]->type) << ", " << printType(op->operands[1]->type);
   } else if (nm == "frisk.gemm") {
-    os << nm << "(" << nameOf(n, op->operands[0]) << ", " << nameOf(n, op->operands[1]) << ", "
-       << nameOf(n, op->operands[2]) << ")";
+    // three operands as in the reference; five when the (additional) scale vectors are present
+    os << nm << "(";
+    for (size_t i = 0; i < op->operands.size(); ++i) os << (i ? ", " : "") << nameOf(n, op->operands[i]);
+    os << ")";
     printAttrDict(os, op, {});
-    os << " : " << printType(op->operands[0]->type) << ", " << printType(op->operands[1]->type)
-       << ", " << printType(op->operands[2]->type);
+    os << " : ";
+    for (size_t i = 0; i < op->operands.size(); ++i)
+      os << (i ? ", " : "") << printType(op->operands[i]->type);
   } else if (nm == "frisk.fill" || nm == "frisk.reduce") {
     os << nm << " ";
     for (size_t i = 0; i < op->operands.size(); ++i) os << (i ? ", " : "") << nameOf(n, op->operands[i]);

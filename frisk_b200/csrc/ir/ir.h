@@ -203,4 +203,20 @@ struct Builder {
 std::optional<LayoutAttrData> sharedLayoutForOperand(const std::vector<int64_t>& shape,
                                                      unsigned elemBits, bool kInner, bool hopper);
 
+// The tiled matrix product of the reference's sketch (tmp/ir.mlir:1-17: parallel grid, tiles in
+// shared / local buffers, a k loop of two copies and a gemm, a copy of the result) recognised and
+// lifted to one whole-problem GEMM C = A x B over kernel arguments; `ok` is false, with the
+// reason in `why`, for anything else.
+struct TiledGemm {
+  bool ok = false;
+  std::string why;
+  int64_t M = 0, N = 0, K = 0;
+  int argA = -1, argB = -1, argC = -1;  // kernel argument positions
+  bool clearAccum = true;               // false: the C tile is loaded from C before the loop
+  Type elemAB, elemC;
+  std::vector<int64_t> tile;            // TM, TN, TK of the program (a hint; not used to execute)
+  std::vector<int64_t> grid;            // GY, GX
+};
+TiledGemm liftTiledGemm(Operation* kernel);
+
 }  // namespace fir

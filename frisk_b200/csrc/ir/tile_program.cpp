@@ -1,0 +1,273 @@
+// Recognises the tiled matrix product written with the ops around frisk.gemm and lifts it to one
+// whole-problem GEMM.
+//
+// The reference's sketch of the intended program (tmp/ir.mlir:1-17) is
+//
+//   frisk.kernel @matmul(%A, %B, %C)
+//     frisk.parallel %by, %bx : ((GY, GX), threads)
+//       %a = alloc_buffer [TM, TK] shared      %b = alloc_buffer [TK, TN] shared
+//       %c = alloc_buffer [TM, TN] local       frisk.fill %c, 0.0
+//       frisk.for %k = lb to ub step st
+//         frisk.copy A[by*TM, k*..] -> %a      frisk.copy B[k*.., bx*TN] -> %b
+//         frisk.gemm(%a, %b, %c)
+//       frisk.copy %c -> C[by*TM, bx*TN]
+//
+// built from FriskOps.td:81-228 (parallel, for, alloc_buffer), 348-410 (copy, fill) and 248-289
+// (gemm).  On a B200 the tile sizes, the staging through shared memory and the grid are the back
+// end's own choice, so the program is not interpreted op by op: it is checked to be exactly this
+// product (every tile of C written once, every k-slice visited once, plain sub-block copies) and
+// then handed to the GEMM planner as C = A x B over the kernel's arguments.  Anything that does not
+// match is refused with the reason; nothing is guessed.
+#include "ir.h"
+
+#include <array>
+#include <stdexcept>
+#include <string>
+
+namespace fir {
+
+namespace {
+
+struct Fail {
+  std::string why;
+};
+
+[[noreturn]] void fail(const std::string& why) { throw Fail{why}; }
+
+bool isTerminatorOrNothing(const Operation* op) { return op->isTerminator(); }
+
+const std::vector<int64_t>& dense(const Operation* op, const char* name) {
+  const Attribute* a = op->attr(name);
+  if (!a || !std::holds_alternative<DenseI64>(*a)) fail(op->name + ": missing attribute " + name);
+  return std::get<DenseI64>(*a).values;
+}
+
+const AffineMap& mapAttr(const Operation* op, const char* name) {
+  const Attribute* a = op->attr(name);
+  if (!a || !std::holds_alternative<AffineMap>(*a)) fail(op->name + ": missing attribute " + name);
+  return std::get<AffineMap>(*a);
+}
+
+// The three loop variables an index may be: the two block indices and the k-loop variable.
+struct Ivs {
+  Value by = nullptr, bx = nullptr, k = nullptr;
+};
+
+// origin[r] = coef[r][0]*by + coef[r][1]*bx + coef[r][2]*k + coef[r][3], for both coordinates.
+struct Origin {
+  std::array<std::array<int64_t, 4>, 2> coef{};
+};
+
+// Evaluates the copy's map at probe points to read the origin off as a linear form of
+// (by, bx, k), and checks with a mixed point that it is linear at all.
+Origin originOf(const Operation* copy, bool srcSide, const Ivs& ivs) {
+  const AffineMap& map = mapAttr(copy, srcSide ? "srcMap" : "dstMap");
+  if (map.results.size() != 2) fail("frisk.copy: only rank-2 buffers are lifted");
+  const int first = srcSide ? 2 : 2 + copy->segmentSizes[2];
+  const int count = srcSide ? copy->segmentSizes[2] : copy->segmentSizes[3];
+  if ((int)(map.numDims + map.numSymbols) != count) fail("frisk.copy: map inputs and indices differ");
+  std::vector<int> which(count);
+  for (int i = 0; i < count; ++i) {
+    Value v = copy->operands[first + i];
+    which[i] = v == ivs.by ? 0 : v == ivs.bx ? 1 : v == ivs.k ? 2 : -1;
+    if (which[i] < 0) fail("frisk.copy: an index is neither a block index nor the loop variable");
+  }
+  auto at = [&](std::array<int64_t, 3> p, int r) {
+    std::vector<int64_t> dims(map.numDims), syms(map.numSymbols);
+    for (int i = 0; i < count; ++i) {
+      const int64_t val = p[which[i]];
+      if (i < (int)map.numDims) dims[i] = val;
+      else syms[i - map.numDims] = val;
+    }
+    return evaluate(map.results[r], dims, syms);
+  };
+  Origin o;
+  for (int r = 0; r < 2; ++r) {
+    const int64_t c = at({0, 0, 0}, r);
+    o.coef[r] = {at({1, 0, 0}, r) - c, at({0, 1, 0}, r) - c, at({0, 0, 1}, r) - c, c};
+    const int64_t want = 3 * o.coef[r][0] + 5 * o.coef[r][1] + 7 * o.coef[r][2] + c;
+    if (at({3, 5, 7}, r) != want) fail("frisk.copy: the origin is not linear in the loop variables");
+  }
+  return o;
+}
+
+bool isZeroOrigin(const Origin& o) {
+  for (auto& row : o.coef)
+    for (int64_t v : row)
+      if (v != 0) return false;
+  return true;
+}
+
+int argIndex(const Block* entry, Value v) {
+  if (!v || v->block != entry) return -1;
+  return (int)v->index;
+}
+
+const TypeStorage* memref2d(Value v, const char* what) {
+  if (!v || !v->type || v->type->kind != TypeKind::MemRef || v->type->shape.size() != 2)
+    fail(std::string(what) + " is not a rank-2 memref");
+  return v->type.get();
+}
+
+}  // namespace
+
+TiledGemm liftTiledGemm(Operation* kernel) {
+  TiledGemm out;
+  try {
+    if (!kernel || kernel->name != "frisk.kernel" || kernel->regions.empty() ||
+        kernel->regions[0]->blocks.empty())
+      fail("not a frisk.kernel with a body");
+    const Block* entry = kernel->regions[0]->blocks[0];
+
+    // ---- the kernel body: one parallel op
+    const Operation* par = nullptr;
+    for (const Operation* op : entry->ops) {
+      if (isTerminatorOrNothing(op)) continue;
+      if (op->name != "frisk.parallel" || par) fail("the kernel body must be one frisk.parallel");
+      par = op;
+    }
+    if (!par || par->regions.empty() || par->regions[0]->blocks.empty())
+      fail("the kernel body must be one frisk.parallel");
+    const std::vector<int64_t>& grid = dense(par, "ranges");
+    const Block* pbody = par->regions[0]->blocks[0];
+    if (grid.size() != 2 || pbody->args.size() != 2) fail("the grid must have two dimensions");
+    Ivs ivs;
+    ivs.by = pbody->args[0];
+    ivs.bx = pbody->args[1];
+
+    // ---- the block body: allocs, at most one fill / one load of the accumulator, one for, one store
+    const Operation *loop = nullptr, *fill = nullptr, *store = nullptr, *preload = nullptr;
+    for (const Operation* op : pbody->ops) {
+      if (isTerminatorOrNothing(op) || op->name == "frisk.alloc_buffer") continue;
+      if (op->name == "frisk.fill" && !loop && !fill) fill = op;
+      else if (op->name == "frisk.for" && !loop) loop = op;
+      else if (op->name == "frisk.copy" && !loop && !preload) preload = op;
+      else if (op->name == "frisk.copy" && loop && !store) store = op;
+      else fail("unexpected " + op->name + " in the block body");
+    }
+    if (!loop || !store) fail("the block body needs a frisk.for and a frisk.copy of the result after it");
+    const Block* lbody = loop->regions.at(0)->blocks.at(0);
+    ivs.k = lbody->args.at(0);
+    const int64_t lb = loop->intAttr("lower"), ub = loop->intAttr("upper"), st = loop->intAttr("step");
+    if (st <= 0 || ub <= lb) fail("the k loop must run forwards at least once");
+    const int64_t trips = (ub - lb + st - 1) / st;
+
+    // ---- the loop body: two copies into tiles and the gemm on them
+    const Operation* gemm = nullptr;
+    std::vector<const Operation*> loads;
+    for (const Operation* op : lbody->ops) {
+      if (isTerminatorOrNothing(op)) continue;
+      if (op->name == "frisk.gemm" && !gemm) gemm = op;
+      else if (op->name == "frisk.copy" && !gemm) loads.push_back(op);
+      else fail("unexpected " + op->name + " in the k loop");
+    }
+    if (!gemm || loads.size() != 2) fail("the k loop must be two frisk.copy and one frisk.gemm");
+    Value ta = gemm->operands.at(0), tb = gemm->operands.at(1), tc = gemm->operands.at(2);
+    for (Value t : {ta, tb, tc})
+      if (!t->defOp || t->defOp->name != "frisk.alloc_buffer" || t->defOp->parent != pbody)
+        fail("the gemm operands must be buffers allocated in the block body");
+    if (ta == tb || ta == tc || tb == tc) fail("the gemm operands must be three different buffers");
+    const TypeStorage *tat = memref2d(ta, "the A tile"), *tbt = memref2d(tb, "the B tile"),
+                      *tct = memref2d(tc, "the C tile");
+    const int64_t TM = tat->shape[0], TK = tat->shape[1], TN = tbt->shape[1];
+    if (tbt->shape[0] != TK || tct->shape[0] != TM || tct->shape[1] != TN || TM <= 0 || TN <= 0 || TK <= 0)
+      fail("tile shapes must be [TM,TK], [TK,TN], [TM,TN]");
+
+    auto loadOf = [&](Value tile, const char* what) -> const Operation* {
+      const Operation* found = nullptr;
+      for (const Operation* c : loads)
+        if (c->operands.at(1) == tile) {
+          if (found) fail(std::string("two copies write ") + what);
+          found = c;
+        }
+      if (!found) fail(std::string("no copy writes ") + what);
+      return found;
+    };
+    const Operation *la = loadOf(ta, "the A tile"), *lbop = loadOf(tb, "the B tile");
+
+    // a load: global argument -> whole tile
+    auto checkLoad = [&](const Operation* c, int64_t rows, int64_t cols, const char* what) {
+      const int arg = argIndex(entry, c->operands.at(0));
+      if (arg < 0) fail(std::string(what) + " is not loaded from a kernel argument");
+      const TypeStorage* g = memref2d(c->operands.at(0), what);
+      if (g->memorySpace != 1) fail(std::string(what) + " must be loaded from GLOBAL memory");
+      const auto &se = dense(c, "srcExtents"), &de = dense(c, "dstExtents");
+      if (se != std::vector<int64_t>{rows, cols} || de != se)
+        fail(std::string(what) + ": the copy must cover exactly the tile");
+      if (!isZeroOrigin(originOf(c, false, ivs))) fail(std::string(what) + ": the tile must be filled from its origin");
+      return arg;
+    };
+    out.argA = checkLoad(la, TM, TK, "A");
+    out.argB = checkLoad(lbop, TK, TN, "B");
+    const Origin oa = originOf(la, true, ivs), ob = originOf(lbop, true, ivs);
+
+    // rows of A follow by, columns of A follow k; rows of B follow k, columns of B follow bx
+    const std::array<int64_t, 4> rowsA{TM, 0, 0, 0}, colsB{0, TN, 0, 0};
+    if (oa.coef[0] != rowsA) fail("A tile rows must start at by * TM");
+    if (ob.coef[1] != colsB) fail("B tile columns must start at bx * TN");
+    if (oa.coef[1] != ob.coef[0]) fail("A and B must walk K the same way");
+    const auto& kc = oa.coef[1];
+    if (kc[0] != 0 || kc[1] != 0) fail("the K offset may depend on the loop variable only");
+    // k = lb, lb+st, ...: offsets kc[2]*k + kc[3] must be 0, TK, 2 TK, ...
+    if (kc[2] * lb + kc[3] != 0 || kc[2] * st != TK) fail("the k loop must visit consecutive slices of TK");
+
+    // ---- the result: accumulator tile -> global argument at (by*TM, bx*TN)
+    if (store->operands.at(0) != tc) fail("the copy after the loop must read the C tile");
+    out.argC = argIndex(entry, store->operands.at(1));
+    if (out.argC < 0) fail("C is not stored to a kernel argument");
+    const TypeStorage* gc = memref2d(store->operands.at(1), "C");
+    if (gc->memorySpace != 1) fail("C must be stored to GLOBAL memory");
+    if (dense(store, "srcExtents") != std::vector<int64_t>{TM, TN} ||
+        dense(store, "dstExtents") != std::vector<int64_t>{TM, TN})
+      fail("C: the copy must cover exactly the tile");
+    if (!isZeroOrigin(originOf(store, true, ivs))) fail("C: the tile must be read from its origin");
+    const Origin oc = originOf(store, false, ivs);
+    const std::array<int64_t, 4> colsC{0, TN, 0, 0};
+    if (oc.coef[0] != rowsA || oc.coef[1] != colsC) fail("C tiles must land at (by * TM, bx * TN)");
+
+    // ---- how the accumulator starts
+    if (fill) {
+      if (fill->operands.at(0) != tc) fail("the fill before the loop must clear the C tile");
+      const Attribute* v = fill->attr("value");
+      if (!v || !std::holds_alternative<FloatAttr>(*v) || std::get<FloatAttr>(*v).value != 0.0)
+        fail("the C tile must be filled with zero");
+      if (preload) fail("the C tile is both filled and loaded");
+      out.clearAccum = true;
+    } else if (preload) {
+      if (preload->operands.at(1) != tc || preload->operands.at(0) != store->operands.at(1))
+        fail("the copy before the loop must load the C tile from C");
+      const Origin op0 = originOf(preload, true, ivs);
+      if (op0.coef[0] != rowsA || op0.coef[1] != colsC || !isZeroOrigin(originOf(preload, false, ivs)))
+        fail("the C tile must be loaded from (by * TM, bx * TN)");
+      out.clearAccum = false;
+    } else {
+      fail("the C tile is neither cleared nor loaded before the loop");
+    }
+    if (gemm->intAttr("clear_accum")) fail("the gemm in the loop must accumulate (clear_accum = false)");
+
+    // ---- the whole problem
+    out.M = grid[0] * TM;
+    out.N = grid[1] * TN;
+    out.K = trips * TK;
+    const TypeStorage *ga = la->operands[0]->type.get(), *gb = lbop->operands[0]->type.get();
+    if (ga->shape != std::vector<int64_t>{out.M, out.K}) fail("the grid and the loop must cover A exactly");
+    if (gb->shape != std::vector<int64_t>{out.K, out.N}) fail("the grid and the loop must cover B exactly");
+    if (gc->shape != std::vector<int64_t>{out.M, out.N}) fail("the grid must cover C exactly");
+    if (out.argA == out.argC || out.argB == out.argC) fail("C must not alias A or B");
+    out.elemAB = ga->element;
+    out.elemC = gc->element;
+    if (!typeEqual(ga->element, gb->element)) fail("A and B must have one element type");
+    out.tile = {TM, TN, TK};
+    out.grid = {grid[0], grid[1]};
+    out.ok = true;
+  } catch (const Fail& f) {
+    out.ok = false;
+    out.why = f.why;
+  } catch (const std::out_of_range&) {
+    out.ok = false;
+    out.why = "malformed operation (missing operand or region)";
+  }
+  return out;
+}
+
+}  // namespace fir

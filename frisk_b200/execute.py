@@ -1,11 +1,18 @@
 """Running the ``frisk.gemm`` ops of a module: the step the reference stops short of.
 
-``find_gemms`` walks a kernel for ``frisk.gemm`` ops whose operands are kernel arguments in the
-GLOBAL memory space (what the reference's flagship script emits: test/python/bind_test.py:53,
-captured in tmp/log_11_18:12) and turns each into a GEMM description; ``run`` plans and launches
-them through libfrisk_b200 with the buffers bound to the kernel arguments.  Ops around the gemm
-(alloc_buffer, copy, fill, for, block, parallel) describe a tiling the B200 back end chooses for
-itself and are not executed.
+Two forms are executed, both through libfrisk_b200 on the buffers bound to the kernel arguments:
+
+* a ``frisk.gemm`` whose operands are kernel arguments in the GLOBAL memory space (what the
+  reference's flagship script emits: test/python/bind_test.py:53, captured in tmp/log_11_18:12):
+  one whole-problem GEMM per op;
+* the tiled matrix product the reference sketches in tmp/ir.mlir:1-17 -- a ``frisk.parallel`` grid
+  whose body allocates tiles, clears (or loads) the accumulator tile, runs a ``frisk.for`` over K of
+  two ``frisk.copy`` and a ``frisk.gemm`` on the tiles, and copies the accumulator out.  The
+  program is checked to be exactly that product (``frisk_ffi.ir.frisk.lift_tiled_gemm``) and run as
+  ONE GEMM over the kernel's arguments: tile sizes, staging and grid are the B200 back end's own
+  choice, so the copy / fill / for / parallel ops are recognised, not interpreted one by one.
+
+Anything else around a gemm is refused with the reason; there is no CPU path.
 """
 from __future__ import annotations
 
@@ -32,6 +39,8 @@ class GemmCall:
     arg_a: int  # kernel argument indices of A, B, C
     arg_b: int
     arg_c: int
+    arg_scale_a: Optional[int] = None  # ... and of the scale vectors of an 8-bit float gemm
+    arg_scale_b: Optional[int] = None
 
 
 def _dtype_of(ty) -> int:
@@ -63,13 +72,29 @@ def find_gemms(module, kernel_name: str) -> List[GemmCall]:
             if space != ir.MemorySpace.GLOBAL:
                 raise R.FriskError(-2, f"frisk.gemm operand {name} must live in GLOBAL memory")
             idx.append(args[v.id()])
+        for name, v in (("scale_a", g.get_scale_A()), ("scale_b", g.get_scale_B())):
+            if v is None:
+                idx.append(None)
+            elif v.id() not in args:
+                raise R.FriskError(-2, f"frisk.gemm operand {name} is not a kernel argument")
+            else:
+                idx.append(args[v.id()])
         a = g.get_attrs()
         ta, tc = vals[0].get_type(), vals[2].get_type()
         calls.append(GemmCall(a["M"], a["N"], a["K"], _dtype_of(ta.get_element_ty()),
                               _dtype_of(tc.get_element_ty()), a["transA"], a["transB"],
                               a["clear_accum"], *idx))
 
-    kernel.get_region(0).front().walk(visit)
+    try:
+        kernel.get_region(0).front().walk(visit)
+    except R.FriskError as whole_problem_error:
+        # not whole-problem gemms on kernel arguments: the kernel has to be the tiled product
+        try:
+            t = ir.frisk.lift_tiled_gemm(kernel)
+        except ValueError as e:
+            raise R.FriskError(-2, f"{whole_problem_error}; and the kernel is {e}") from None
+        return [GemmCall(t["M"], t["N"], t["K"], _dtype_of(t["ab_type"]), _dtype_of(t["c_type"]),
+                         False, False, t["clear_accum"], t["arg_a"], t["arg_b"], t["arg_c"])]
     return calls
 
 
@@ -81,15 +106,19 @@ def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Opt
     if not module.verify():
         raise R.FriskError(-1, "module does not verify: " + module.verify_message())
     for call in find_gemms(module, kernel_name):
+        sa, sb = scale_a, scale_b
+        if sa is None and call.arg_scale_a is not None:  # scale vectors bound as kernel arguments
+            sa = np.ascontiguousarray(buffers[call.arg_scale_a], dtype=np.float32)
+            sb = np.ascontiguousarray(buffers[call.arg_scale_b], dtype=np.float32)
         plan = R.GemmPlan(call.M, call.N, call.K, call.ab_type, call.c_type, transA=call.transA,
                           transB=call.transB, clear_accum=call.clear_accum,
-                          scales=scale_a is not None, **(plan_options or {}))
+                          scales=sa is not None, **(plan_options or {}))
         try:
             a = np.ascontiguousarray(buffers[call.arg_a])
             b = np.ascontiguousarray(buffers[call.arg_b])
             c = buffers[call.arg_c]
             if not c.flags["C_CONTIGUOUS"]:
                 raise ValueError("the C buffer must be C-contiguous (it is written in place)")
-            plan.run_host(a, b, c, scale_a, scale_b)
+            plan.run_host(a, b, c, sa, sb)
         finally:
             plan.close()

@@ -271,3 +271,12 @@ def device_sm_count() -> int:
 
 def version() -> str:
     return lib().frisk_b200_version().decode()
+
+
+# Names the reference-facing ``frisk.runtime`` module is asked for: ``plan`` makes a plan for one
+# GEMM, ``workspace_size`` tells what ``run`` needs beside the operands.
+plan = GemmPlan
+
+
+def workspace_size(p: "GemmPlan") -> int:
+    return p.workspace_bytes

@@ -331,3 +331,25 @@ def test_module_built_with_the_ir_builder_executes():
     h2.create_gemm(*[e2.get_argument(i) for i in range(3)])
     with pytest.raises(R.FriskError):
         F.find_gemms(h2.module, "k")
+
+
+def test_fp8_gemm_with_scale_operands_built_through_the_ir_builder_executes():
+    """cfg4's form written as IR: e4m3 A and B (both K-inner), bf16 C, the two fp32 scale vectors
+    as the additional fourth and fifth operands of frisk.gemm, bound as kernel arguments."""
+    import frisk as F
+
+    w = W.make_workload("cfg4", 256, 384, 512)
+    h = F.create_session()
+    f32 = h.builder.get_f32_ty()
+    tys = [h.memref_type((w.M, w.K), "e4m3fn"), h.memref_type((w.K, w.N), "e4m3fn"),
+           h.memref_type((w.M, w.N), "bf16"), h.memref_type((w.M,), f32), h.memref_type((w.N,), f32)]
+    _, entry = h.new_kernel("k", tys)
+    a = [entry.get_argument(i) for i in range(5)]
+    h.builder.create_gemm_op(a[0], a[1], a[2], False, True, True, a[3], a[4])
+    (call,) = F.find_gemms(h.module, "k")
+    assert (call.arg_scale_a, call.arg_scale_b, call.ab_type, call.c_type) == (3, 4, W.E4M3, W.BF16)
+    out = np.zeros((w.M, w.N), np.uint16)
+    F.run(h.module, "k", [w.A, w.B, out, w.scale_a, w.scale_b])
+    assert np.array_equal(out, R.gemm_host(w))
+    ok, err, _ = W.check(W.bf16_decode(out), ref.ref_gemm_f64(w), W.E4M3, absdot=ref.abs_dot(w))
+    assert ok, err

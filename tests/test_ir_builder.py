@@ -237,6 +237,33 @@ def test_create_gemm_op_error_conventions():
     assert g.get_attrs()["transB"] is True and h.module.verify()
 
 
+def test_gemm_scale_operands_extension():
+    """Additive: an 8-bit float gemm may carry per-row / per-column fp32 scale vectors as a fourth
+    and fifth operand; the reference's three-operand form prints exactly as before."""
+    def tys(h):
+        f32 = h.builder.get_f32_ty()
+        return [h.memref_type((8, 4), "e4m3fn"), h.memref_type((4, 16), "e4m3fn"),
+                h.memref_type((8, 16), "bf16"), h.memref_type((8,), f32), h.memref_type((16,), f32),
+                h.memref_type((9,), f32), h.memref_type((8, 4), h.builder.get_f16_ty()),
+                h.memref_type((4, 16), h.builder.get_f16_ty()), h.memref_type((8, 16), h.builder.get_f16_ty())]
+    h, a = _kernel_with_args(tys)
+    g = h.builder.create_gemm_op(a[0], a[1], a[2], False, True, True, a[3], a[4])
+    assert g.get_scale_A().id() == a[3].id() and g.get_scale_B().id() == a[4].id()
+    assert len(list(g.get_all_matrix())) == 3
+    assert h.module.verify(), h.module.verify_message()
+    text = str(h.module)
+    assert "frisk.gemm(%arg0, %arg1, %arg2, %arg3, %arg4) {" in text
+    assert text.rstrip().count("memref<8xf32, 1>, memref<16xf32, 1>") >= 1
+    plain = h.builder.create_gemm_op(a[0], a[1], a[2])
+    assert plain.get_scale_A() is None and plain.get_scale_B() is None
+    with pytest.raises(ValueError, match="together"):
+        h.builder.create_gemm_op(a[0], a[1], a[2], False, False, False, a[3])
+    with pytest.raises(ValueError, match="matching length"):
+        h.builder.create_gemm_op(a[0], a[1], a[2], False, False, False, a[5], a[4])
+    with pytest.raises(ValueError, match="8-bit float"):
+        h.builder.create_gemm_op(a[6], a[7], a[8], False, False, False, a[3], a[4])
+
+
 def test_other_builder_errors():
     ctx = F.context()
     b = F.builder(ctx)

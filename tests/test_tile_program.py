@@ -1,0 +1,92 @@
+"""The tiled matrix product around frisk.gemm (tmp/ir.mlir:1-17 of the reference) is recognised
+and lifted to one whole-problem GEMM; everything that is not exactly that product is refused."""
+import numpy as np
+import pytest
+
+import frisk as F
+from frisk_b200 import runtime as R, workloads as W
+from tile_programs import build_tiled_matmul
+
+
+def test_sketch_program_prints_like_the_reference_and_lifts():
+    m = build_tiled_matmul(1024, 1024, 1024, 128, 128, 32)  # the sizes of the reference's sketch
+    assert m.verify(), m.verify_message()
+    text = str(m)
+    assert "frisk.parallel (%arg3, %arg4) = (8, 8), threads = 128" in text
+    assert "frisk.copy %arg0[%arg3 * 128, %arg5 * 32], %0[0, 0]" in text
+    assert "frisk.copy %2[0, 0], %arg2[%arg3 * 128, %arg4 * 128]" in text
+    t = F.ir.frisk.lift_tiled_gemm(m.get_kernel("matmul"))
+    assert (t["M"], t["N"], t["K"]) == (1024, 1024, 1024)
+    assert (t["arg_a"], t["arg_b"], t["arg_c"]) == (0, 1, 2)
+    assert t["clear_accum"] is True and t["tile"] == [128, 128, 32] and t["grid"] == [8, 8]
+    assert str(t["ab_type"]) == "f16" and str(t["c_type"]) == "f16"
+    (call,) = F.find_gemms(m, "matmul")
+    assert (call.M, call.N, call.K, call.ab_type, call.c_type) == (1024, 1024, 1024, W.F16, W.F16)
+    assert not call.transA and not call.transB and call.clear_accum
+
+
+@pytest.mark.parametrize("dims,tile,dtype,acc,kstep", [
+    ((512, 768, 256), (64, 128, 32), "bf16", True, 4),    # C tile loaded first: C += A x B
+    ((256, 256, 512), (256, 64, 64), "fp32", False, 1),
+    ((128, 384, 96), (128, 128, 32), "fp16", False, 32),  # loop variable counts elements of K
+])
+def test_variants_lift(dims, tile, dtype, acc, kstep):
+    m = build_tiled_matmul(*dims, *tile, dtype=dtype, accumulate=acc, kstep=kstep)
+    assert m.verify(), m.verify_message()
+    (call,) = F.find_gemms(m, "matmul")
+    assert (call.M, call.N, call.K) == dims and call.clear_accum == (not acc)
+    assert call.ab_type == {"fp16": W.F16, "bf16": W.BF16, "fp32": W.F32}[dtype]
+
+
+@pytest.mark.parametrize("tweak,reason", [
+    ("fill_one", "filled with zero"),
+    ("no_init", "neither cleared nor loaded"),
+    ("no_store", "copy of the result"),
+    ("a_rows_follow_bx", "A tile rows must start at by"),
+    ("k_gap", "consecutive slices"),
+    ("c_swapped", "C tiles must land"),
+    ("grid_short", "cover A exactly"),
+    ("extra_fill", "unexpected frisk.fill in the k loop"),
+    ("gemm_clears", "must accumulate"),
+])
+def test_everything_else_is_refused_with_the_reason(tweak, reason):
+    m = build_tiled_matmul(512, 512, 256, 128, 128, 32, tweak=tweak)
+    with pytest.raises(ValueError, match=reason):
+        F.ir.frisk.lift_tiled_gemm(m.get_kernel("matmul"))
+    with pytest.raises(R.FriskError, match="not a tiled matrix product"):
+        F.find_gemms(m, "matmul")
+
+
+def test_reference_flagship_module_is_still_a_whole_problem_gemm():
+    # bind_test.py's module (gemm on the kernel arguments inside for / block) is not a tile program
+    from test_ir_builder import build_bind_test_module  # the reference script's program
+    m = build_bind_test_module()[0]
+    (call,) = F.find_gemms(m, "test_gemm")
+    assert (call.M, call.N, call.K) == (4096, 4096, 4096)
+    with pytest.raises(ValueError, match="not a tiled matrix product"):
+        F.ir.frisk.lift_tiled_gemm(m.get_kernel("test_gemm"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dims,tile,dtype,acc", [
+    ((1024, 1024, 1024), (128, 128, 32), "fp16", False),
+    ((512, 768, 256), (64, 128, 32), "bf16", True),
+])
+def test_lifted_program_runs_and_matches_the_oracle(dims, tile, dtype, acc):
+    from oracle import ref
+    M, N, K = dims
+    ab = {"fp16": W.F16, "bf16": W.BF16}[dtype]
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((M, K)).astype(np.float32) * K ** -0.5
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    c0 = rng.standard_normal((M, N)).astype(np.float32)
+    A, B, C = W.encode(a, ab), W.encode(b, ab), W.encode(c0, ab)
+    m = build_tiled_matmul(M, N, K, *tile, dtype=dtype, accumulate=acc)
+    w = W.GemmWorkload("tiled", M, N, K, ab, ab, A=A, B=B, C0=C.copy() if acc else None,
+                       clear_accum=not acc)
+    F.run(m, "matmul", [A, B, C])
+    got = W.decode(C, ab)
+    ok, err, metric = W.check(got, ref.ref_gemm_f64(w), ab, absdot=ref.abs_dot(w))
+    assert ok, f"{metric} = {err}"
+    # one GEMM over the arguments: the same bits as planning that GEMM directly
+    assert np.array_equal(C, R.gemm_host(w))

@@ -1,0 +1,55 @@
+"""Builds, through the reference's builder API, the tiled matrix product its authors sketch in
+tmp/ir.mlir:1-17 (parallel grid, tiles in shared / local buffers, a k loop of two copies and a
+gemm, a copy of the accumulator tile to C).  `tweak` lets a test break one aspect at a time."""
+import frisk as F
+
+
+def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kstep=1, tweak=None):
+    ctx = F.context()
+    F.frisk.load_dialects(ctx)
+    b = F.builder(ctx)
+    module = b.create_module()
+    module.context = ctx
+    ty = {"fp16": b.get_f16_ty, "bf16": b.get_bf16_ty, "fp32": b.get_f32_ty}[dtype]()
+    mk = lambda shape: b.get_memref_ty(ty, shape, F.AffineMap(), F.MemorySpace.GLOBAL)
+    kernel = b.create_kernel_op(module, "matmul", b.get_kernel_ty([mk([M, K]), mk([K, N]), mk([M, N])]))
+    module.push_back(kernel)
+    entry = kernel.add_entry_block()
+    b.set_insertion_point_to_start(entry)
+    A, B, C = (entry.get_argument(i) for i in range(3))
+    grid = [M // TM, N // TN]
+    if tweak == "grid_short":
+        grid[0] -= 1
+    par = b.create_parallel_op(grid, 128)
+    body = par.add_entry_block()
+    b.set_insertion_point_to_start(body)
+    by, bx = body.get_argument(0), body.get_argument(1)
+    sA = b.create_alloc_buffer_op([TM, TK], dtype, F.MemorySpace.SHARED, 1024).get_result(0)
+    sB = b.create_alloc_buffer_op([TK, TN], dtype, F.MemorySpace.SHARED, 1024).get_result(0)
+    acc = b.create_alloc_buffer_op([TM, TN], dtype, F.MemorySpace.LOCAL).get_result(0)
+    d0, d1 = b.get_affine_dim_expr(0), b.get_affine_dim_expr(1)
+    c = b.get_affine_constant_expr
+    zero = F.AffineMap.get(0, 0, [c(0), c(0)], ctx)
+    map_c = F.AffineMap.get(2, 0, [d0 * c(TM), d1 * c(TN)], ctx)
+    if accumulate:
+        b.create_copy_op(C, acc, [by, bx], [], map_c, zero, [TM, TN], [TM, TN])
+    elif tweak != "no_init":
+        b.create_fill_op(acc, 1.0 if tweak == "fill_one" else 0.0, dtype)
+
+    def loop(_, k):
+        # k runs over 0, kstep, 2 kstep, ...: slice k / kstep starts at K offset (k / kstep) * TK
+        per_k = TK // kstep if tweak != "k_gap" else 2 * TK // kstep
+        map_a = F.AffineMap.get(2, 0, [d0 * c(TM), d1 * c(per_k)], ctx)
+        map_b = F.AffineMap.get(2, 0, [d0 * c(per_k), d1 * c(TN)], ctx)
+        row_iv = bx if tweak == "a_rows_follow_bx" else by
+        b.create_copy_op(A, sA, [row_iv, k], [], map_a, zero, [TM, TK], [TM, TK])
+        b.create_copy_op(B, sB, [k, bx], [], map_b, zero, [TK, TN], [TK, TN])
+        if tweak == "extra_fill":
+            b.create_fill_op(sA, 0.0, dtype)
+        b.create_gemm_op(sA, sB, acc, False, False, tweak == "gemm_clears")
+
+    b.create_for_op(0, (K // TK) * kstep, kstep, loop)
+    if tweak != "no_store":
+        out_map = F.AffineMap.get(2, 0, [d1 * c(TM), d0 * c(TN)], ctx) if tweak == "c_swapped" else map_c
+        b.create_copy_op(acc, C, [], [by, bx], zero, out_map, [TM, TN], [TM, TN])
+    return module

@@ -63,7 +63,7 @@ typedef enum { FRISK_SCALE_NONE = 0, FRISK_SCALE_ROW_COL = 1 } frisk_scale_mode;
 typedef enum {
   FRISK_KERNEL_SIMT = 0,    /* CUDA-core fp32-FMA tiles: fp32 inputs and every odd shape   */
   FRISK_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma, accumulators in TMEM, whole-tile output   */
-  FRISK_KERNEL_SKINNY = 2,  /* same pipeline, operands swapped, K split across all SMs      */
+  FRISK_KERNEL_SKINNY = 2,  /* same pipeline, operands swapped, K split over a cluster / SMs */
   FRISK_KERNEL_TCGEN05_PAIR = 3 /* CTA pairs with two-SM MMAs on 256 x tile_n output tiles   */
 } frisk_kernel_kind;
 
@@ -95,7 +95,7 @@ typedef struct frisk_gemm_plan_info {
   int32_t stages;
   int32_t num_ctas;
   int32_t swap_ab;     /* 1 when the weights feed the 128-row operand (skinny path)          */
-  int32_t split_k;     /* 1 when partial sums go through the fp32 workspace                  */
+  int32_t split_k;     /* 1 when several CTAs share a tile's K range (skinny path)           */
   int32_t smem_bytes;  /* dynamic shared memory per CTA                                      */
   int32_t launches;    /* kernels launched per run                                           */
   int32_t swizzle_a, swizzle_b; /* TMA/UMMA swizzle width in bytes (0, 32, 64, 128)          */
@@ -108,7 +108,9 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
 void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* plan);
 int frisk_b200_gemm_plan_info(const frisk_gemm_plan* plan, frisk_gemm_plan_info* out);
 
-/* Bytes of device scratch `run` needs (0 for plans that write C directly). */
+/* Bytes of device scratch `run` needs.  0 for every plan but the stream-K form of the few-row
+ * plan (few-row shapes whose tiles cannot be covered by thread-block clusters); `run` then takes
+ * a NULL workspace. */
 int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* plan, size_t* out);
 
 /*
@@ -126,8 +128,10 @@ int frisk_b200_gemm_run(frisk_gemm_plan* plan, const void* A, const void* B, voi
 /*
  * The same GEMM for callers that hold HOST buffers (what a binding of the reference's Python
  * builder would be handed: numpy arrays).  Copies A, B (and C when clear_accum == 0, and the
- * scales) to the device, runs, copies C back and synchronises.  Device buffers are cached in
- * the plan between calls.  Returns FRISK_ERR_DEVICE_TIMEOUT if the status word came back set.
+ * scales) to the device, runs, copies C back and synchronises.  With 4096 or more rows of a
+ * row-major A the rows go through in up to 16 chunks on three streams, so the upload of one chunk,
+ * the GEMM of the previous and the download of the one before overlap.  Device buffers are
+ * cached in the plan between calls.  Returns FRISK_ERR_DEVICE_TIMEOUT if the status word came back set.
  */
 int frisk_b200_gemm_run_host(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
                              const float* scale_a, const float* scale_b);
@@ -135,10 +139,10 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* plan, const void* A, const void* B
 /*
  * No counterpart in the reference.  The few-row ("skinny") GEMM for callers that may not
  * allocate device memory: code running inside someone else's memory pool, services with a
- * memory budget fixed at start-up, replays of pre-recorded work.  The fp32 scratch that
- * frisk_b200_gemm_run takes as `workspace` is here a fixed 4 MiB array inside the library
- * image (held by every GPU that loads the library until the process exits), so the call
- * allocates nothing on the device or the host.
+ * memory budget fixed at start-up, replays of pre-recorded work.  It always uses the K-split
+ * form that adds partial sums into an M x N fp32 scratch, and that scratch is a fixed 4 MiB array
+ * inside the library image (held by every GPU that loads the library until the process exits),
+ * so the call allocates nothing on the device or the host.
  *   - Accepts what the skinny plan accepts: fp16 / bf16 / e4m3 inputs, M <= 64, N >= 256,
  *     transA == 0, 16-byte aligned A and B with 16-byte row pitches; anything else returns
  *     FRISK_ERR_UNSUPPORTED or FRISK_ERR_MISALIGNED.

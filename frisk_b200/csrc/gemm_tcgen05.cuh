@@ -688,7 +688,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t a_k_step = p.a.k_step_bytes, b_k_step = p.b.k_step_bytes;
       const uint32_t a_sub_stride = p.a.sub_stride_bytes;
       const uint32_t a_stage_bytes = p.a.stage_bytes;
-      const uint32_t k_steps = p.k_steps;
       const uint32_t idesc = p.idesc;
       const uint32_t kind_f8 = p.kind_f8;
       uint32_t stage = 0, phase = 0, item = 0;

@@ -62,7 +62,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t num_kb = p.num_kb;
   int32_t* const status = p.status;
   const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
-  long long* const trace = (kMeasureBuild && blockIdx.x == 0) ? p.trace : nullptr;
 
   if (threadIdx.x == 0) {
     abort_word = 0;
@@ -184,21 +183,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t prev_stage = 0;
         bool have_prev = false;
         uint32_t ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * stage, phase));
-        long long sec_a = 0, sec_b = 0, sec_c = 0, t_prev = clock64();
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-          const long long t_top = clock64();
-          sec_c += t_top - t_prev;
-          const bool tr_top = trace && item == 1 && kb < 32;
-          if (tr_top && ptx::elect_one()) {
-            trace[64 + 3 * kb] = clock64();
-            trace[64 + 3 * kb + 1] = ready;
-          }
           if (!ready) {
             ok = bounded_wait_slow(full0 + 8 * stage, phase, abort_flag, status, kStatusMmaTimeout,
                                    0);
             if (!ok) break;
           }
-          if (tr_top && ptx::elect_one()) trace[64 + 3 * kb + 2] = clock64();
           ptx::tc_fence_after();
           const uint32_t a_addr = tiles_base + stage * stage_bytes;
           const uint32_t b_addr = a_addr + a_stage_bytes;
@@ -210,9 +200,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             next_stage = 0;
             next_phase ^= 1;
           }
-          const bool tr_on = false;
-          const long long t_mid = clock64();
-          sec_a += t_mid - t_top;
           if (debug_mode & 2u) {
             if (ptx::elect_one()) ptx::mbar_arrive_cluster(empty0 + 8 * stage);
             if (ptx::elect_one()) ptx::mbar_arrive_cluster(peer_empty0 + 8 * stage);
@@ -233,28 +220,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             } else {
               if (ptx::elect_one()) ptx::mma_f16_pair(d_base, adesc, bdesc, idesc, accumulate);
             }
-            if (tr_on && ptx::elect_one()) trace[128 + 8 * kb + ks] = clock64();
             if (ks == 0 && have_prev) {
-              if (debug_mode & 8u) {
-                if (ptx::elect_one()) ptx::tc_commit_pair_both(empty0 + 8 * prev_stage, 3u);
-              } else {
-                if (ptx::elect_one()) ptx::tc_commit_pair(empty0 + 8 * prev_stage);
-                if (ptx::elect_one()) ptx::tc_commit_pair(peer_empty0 + 8 * prev_stage);
-              }
-              if (tr_on && ptx::elect_one()) trace[128 + 8 * kb + 4] = clock64();
+              if (ptx::elect_one()) ptx::tc_commit_pair(empty0 + 8 * prev_stage);
+              if (ptx::elect_one()) ptx::tc_commit_pair(peer_empty0 + 8 * prev_stage);
             }
           }
-          t_prev = clock64();
-          sec_b += t_prev - t_mid;
           prev_stage = stage;
           have_prev = true;
           stage = next_stage;
           phase = next_phase;
-        }
-        if (trace && item == 1 && ptx::elect_one()) {
-          trace[400] = sec_a;
-          trace[401] = sec_b;
-          trace[402] = sec_c;
         }
         if (!ok) break;
         if (have_prev) {

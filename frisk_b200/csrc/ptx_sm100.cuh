@@ -275,18 +275,6 @@ __device__ __forceinline__ void mma_f8_pair(uint32_t d_tmem, uint64_t adesc, uin
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Arrives on the barrier at this shared-memory offset in every CTA of `cta_mask` once the pair's
-// MMAs issued so far retire (a signal fan-out; no data is copied).
-__device__ __forceinline__ void tc_commit_pair_both(uint32_t bar, uint32_t cta_mask) {
-  asm volatile(
-      "{\n\t"
-      ".reg .b16 lo, hi;\n\t"
-      "mov.b32 {lo, hi}, %1;\n\t"
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], lo;\n\t"
-      "}" ::"r"(bar),
-      "r"(cta_mask)
-      : "memory");
-}
 // Arrives on `cluster_bar` (in either CTA of the pair) once the pair's MMAs issued so far retire.
 __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(

@@ -353,3 +353,69 @@ def test_fp8_gemm_with_scale_operands_built_through_the_ir_builder_executes():
     assert np.array_equal(out, R.gemm_host(w))
     ok, err, _ = W.check(W.bf16_decode(out), ref.ref_gemm_f64(w), W.E4M3, absdot=ref.abs_dot(w))
     assert ok, err
+
+
+# ----------------------------------------------------------------------------- few-row plans
+# Shapes chosen so that every form of the few-row plan runs: clusters of 8, 4 and 2 on 256- and
+# 128-row tiles, the stream-K fallback (too few tiles, or a forced grid), ragged N and K, every
+# input type, K-inner and N-inner weights, C += and scales.
+FEW_ROWS = [
+    # (M, N, K, ab, transB, clear_accum, plan options)
+    (16, 4096, 2048, W.BF16, False, True, {}),
+    (16, 2048, 2048, W.F16, False, True, {}),
+    (33, 8192, 512, W.BF16, False, True, {}),
+    (64, 8192, 256, W.F16, True, True, {}),       # weights stored [N, K]
+    (1, 1000, 520, W.BF16, False, True, {}),      # ragged N and K
+    (7, 2304, 1096, W.F16, False, False, {}),     # C += A x B
+    (48, 4096, 1024, W.E4M3, True, True, {}),     # scales
+    (16, 512, 4096, W.BF16, False, True, {}),     # stream-K: two tiles
+    (16, 4096, 2048, W.BF16, False, True, {"num_ctas": 37}),  # stream-K: forced grid
+    (24, 4096, 2048, W.F16, False, False, {"num_ctas": 148}),
+]
+
+
+@pytest.mark.parametrize("M,N,K,ab,tb,clear,opts", FEW_ROWS)
+def test_few_row_plans_match_oracle(M, N, K, ab, tb, clear, opts):
+    rng = np.random.default_rng(M * 131 + N + K)
+    a = (rng.standard_normal((M, K)) * (1.0 if ab != W.E4M3 else 4.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (0.05 if ab != W.E4M3 else 4.0)).astype(np.float32)
+    ct = W.BF16 if ab == W.E4M3 else ab
+    sa = sb = None
+    if ab == W.E4M3:
+        sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32)
+        sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32)
+    Bq = W.encode(b, ab)
+    w = W.GemmWorkload("few-rows", M, N, K, ab, ct, transB=tb, clear_accum=clear,
+                       A=W.encode(a, ab), B=np.ascontiguousarray(Bq.T) if tb else Bq,
+                       scale_a=sa, scale_b=sb,
+                       C0=None if clear else W.encode(rng.standard_normal((M, N)).astype(np.float32), ct))
+    out, info = run_and_check(w, **opts)
+    assert info["kernel_name"] == "skinny"
+    # summation order is fixed by the plan, not by which CTA finishes first
+    assert np.array_equal(out, R.gemm_host(w, **opts))
+
+
+@pytest.mark.parametrize("M,N,K,ab,ct,ta,tb,clear", [
+    (300, 104, 200, W.BF16, W.BF16, False, False, True),    # 128-column tiles
+    (260, 520, 136, W.F16, W.F32, False, True, False),      # fp32 C, C += A x B
+    (512, 768, 640, W.E4M3, W.BF16, False, True, True),     # scales
+    (384, 1024, 2048, W.BF16, W.F16, True, False, True),    # A stored [K, M]
+    (1000, 1000, 1000, W.F16, W.F16, False, False, False),  # ragged everywhere
+])
+def test_cta_pair_kernel_variants_match_oracle(M, N, K, ab, ct, ta, tb, clear):
+    rng = np.random.default_rng(M + 7 * N + 13 * K)
+    big = ab == W.E4M3
+    a = (rng.standard_normal((M, K)) * (4.0 if big else 1.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (4.0 if big else K ** -0.5)).astype(np.float32)
+    sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if big else None
+    sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32) if big else None
+    Aq, Bq = W.encode(a, ab), W.encode(b, ab)
+    w = W.GemmWorkload("pair", M, N, K, ab, ct, transA=ta, transB=tb, clear_accum=clear,
+                       A=np.ascontiguousarray(Aq.T) if ta else Aq,
+                       B=np.ascontiguousarray(Bq.T) if tb else Bq, scale_a=sa, scale_b=sb,
+                       C0=None if clear else W.encode(rng.standard_normal((M, N)).astype(np.float32), ct))
+    out, info = run_and_check(w)
+    assert info["kernel_name"] == "tcgen05_pair"
+    out1, info1 = run_and_check(w, force_kernel="tcgen05")
+    assert info1["kernel_name"] == "tcgen05"
+    assert np.array_equal(out, out1)  # same k order, same fp32 accumulation: same bits

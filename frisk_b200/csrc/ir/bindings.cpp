@@ -984,6 +984,14 @@ void initBuilder(py::module_& m) {
 
 void initFrisk(py::module_ m) {
   m.def("load_dialects", [](Context& c) { c.friskLoaded = true; });
+  // addition: the inverse of str(module) -- reads the custom assembly back, the reference's own
+  // printed modules included; raises ValueError("line L, column C: ...") on text it cannot read
+  m.def("parse_module", [](const std::string& text, CtxPtr ctx) {
+    std::string err;
+    Operation* op = parseModule(text, ctx, &err);
+    if (!op) throw std::invalid_argument("cannot parse module: " + err);
+    return wrapOp<PyModule>(op);
+  });
   // addition: the tiled matrix product around a frisk.gemm (tmp/ir.mlir:1-17) lifted to one
   // whole-problem GEMM; raises ValueError with the reason when the kernel is anything else
   m.def("lift_tiled_gemm", [](PyKernel& k) {

@@ -219,4 +219,9 @@ struct TiledGemm {
 };
 TiledGemm liftTiledGemm(Operation* kernel);
 
+// Reads a module from its textual form (the custom assembly the printers above and the reference's
+// own printers emit).  Returns nullptr and sets *error ("line L, column C: what") on anything it
+// cannot read.  The module's objects belong to `ctx`.
+Operation* parseModule(const std::string& text, std::shared_ptr<Context> ctx, std::string* error);
+
 }  // namespace fir

@@ -98,11 +98,24 @@ def find_gemms(module, kernel_name: str) -> List[GemmCall]:
     return calls
 
 
+def parse_module(text: str):
+    """Reads a module from its textual form (``str(module)``, a ``.mlir`` file written by this
+    package or printed by the reference) into a fresh context; ``ValueError`` names line and
+    column of what cannot be read."""
+    ctx = ir.context()
+    ir.frisk.load_dialects(ctx)
+    module = ir.frisk.parse_module(text, ctx)
+    module.context = ctx
+    return module
+
+
 def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Optional[np.ndarray] = None,
         scale_b: Optional[np.ndarray] = None, plan_options: Optional[Dict] = None) -> None:
-    """Executes every ``frisk.gemm`` of the kernel on host buffers (one per kernel argument, raw
+    """Executes every ``frisk.gemm`` of the kernel (a module, or its text) on host buffers (one per kernel argument, raw
     storage bits in the memory order the op's trans flags state).  C buffers are updated in
     place.  Raises when the CUDA library or a device is missing: there is no CPU path."""
+    if isinstance(module, str):  # the textual form
+        module = parse_module(module)
     if not module.verify():
         raise R.FriskError(-1, "module does not verify: " + module.verify_message())
     for call in find_gemms(module, kernel_name):

@@ -221,6 +221,12 @@ bool skinny_shape(const frisk_gemm_desc& d, int sm_count) {
 
 bool skinny_clusters_fit(frisk_gemm_plan* pl);
 
+// Whether the pair kernel cuts the tiles of its last wave in two (see plan_tcgen05).
+bool pair_tail_split(uint64_t tile_n, uint64_t tiles, uint64_t pairs) {
+  const uint64_t rest = tiles % pairs;
+  return tile_n == 256 && rest > 0 && 2 * rest <= pairs;
+}
+
 // cluster_try: which cluster candidate of a skinny plan to take (-1: none, plan stream-K).
 void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0) {
   const frisk_gemm_desc& d = pl->d;
@@ -297,6 +303,13 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // a CTA of a pair stages its own 128 rows of A and half of the tile's B columns
   fill_operand(g.a, a_mn, 128u * g.mi, es, bk);
   fill_operand(g.b, b_mn, pair ? g.tile_n / 2 : g.tile_n, es, bk);
+  if (pair && !b_mn && g.b.num_boxes == 1 && g.tile_n == 256) {
+    // two boxes of 64 rows instead of one of 128 (same bytes in shared memory): a half-width item
+    // of the last wave loads just the first
+    g.b.num_boxes = 2;
+    g.b.box_mn /= 2;
+    g.b.box_bytes /= 2;
+  }
   g.stage_bytes = g.a.stage_bytes + g.b.stage_bytes;
   // split mode 3 keeps one fp32 tile behind the stage buffers: the region the cluster's partials
   // are pushed into
@@ -338,10 +351,21 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   const uint64_t units = swap ? tiles * g.num_kb : tiles;
   uint32_t ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)pl->sm_count);
   if (d.num_ctas > 0) ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)d.num_ctas);
+  g.n_items = g.narrow_from = (uint32_t)tiles;
   if (pair) {  // one cluster of two CTAs per tile in flight
-    uint64_t pairs = std::min<uint64_t>(units, (uint64_t)pl->sm_count / 2);
-    if (d.num_ctas > 1) pairs = std::min<uint64_t>(pairs, (uint64_t)d.num_ctas / 2);
-    ctas = (uint32_t)(2 * std::max<uint64_t>(pairs, 1));
+    uint64_t slots = (uint64_t)pl->sm_count / 2;
+    if (d.num_ctas > 1) slots = std::min<uint64_t>(slots, (uint64_t)d.num_ctas / 2);
+    slots = std::max<uint64_t>(slots, 1);
+    // Tiles that fill the last wave of pairs at most half are cut into two half-width items each:
+    // the wave then takes about 0.56 of a whole-tile wave instead of a full one.
+    const uint64_t rest = tiles % slots;
+    if (pair_tail_split(g.tile_n, tiles, slots)) {
+      g.narrow_from = (uint32_t)(tiles - rest);
+      g.n_items = (uint32_t)(tiles + rest);
+      g.idesc_narrow = make_idesc(d.a_type, a_mn, b_mn, 256u, g.tile_n / 2);
+    }
+    const uint64_t pairs = std::min<uint64_t>((uint64_t)g.n_items, slots);
+    ctas = (uint32_t)(2 * pairs);
   }
   pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes;
   pl->ws_bytes = 0;
@@ -604,7 +628,9 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       const uint64_t two_tiles = (((uint64_t)d.M + 255) / 256) * cols_t;
       const uint64_t sms = (uint64_t)pl->sm_count, pairs = sms / 2;
       const double one_cost = (double)((one_tiles + sms - 1) / sms);
-      const double two_cost = (double)((two_tiles + pairs - 1) / pairs) / 1.12;
+      double two_waves = (double)((two_tiles + pairs - 1) / pairs);
+      if (pair_tail_split(tn, two_tiles, pairs)) two_waves -= 0.44;  // a wave of half-width items
+      const double two_cost = two_waves / 1.12;
       use_pair = two_cost < one_cost;
       if (const char* want_pair = getenv("FRISK_B200_PAIR")) use_pair = want_pair[0] == '1';
     }

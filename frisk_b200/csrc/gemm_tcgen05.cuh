@@ -82,6 +82,8 @@ struct GemmParams {
                         //    through distributed shared memory (no workspace)
   uint32_t max_items;   // split mode 2: most tiles one CTA's unit range can touch
   uint32_t cluster_k;   // split mode 3: CTAs per cluster = K slices per tile
+  // CTA-pair kernel: work items (whole tiles, then half-width items of the last wave's tiles)
+  uint32_t n_items, narrow_from, idesc_narrow;
   uint32_t* counters;   // split mode 2: k-blocks arrived per tile (zero between launches)
   // epilogue
   void* C;

@@ -19,6 +19,22 @@
 
 namespace frisk {
 
+// Work items of the pair kernel.  Items [0, narrow_from) are whole 256 x tile_n tiles.  When the
+// tiles do not fill the last wave of pairs at least half, each tile of that wave is cut into two
+// 256 x tile_n/2 items instead, so that the wave takes about half as long: items narrow_from,
+// narrow_from + 1, ... are the left and right halves of tiles narrow_from, narrow_from + 1, ...
+struct PairItem {
+  uint32_t tile, narrow, half;
+};
+__device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t narrow_from) {
+  PairItem it;
+  const uint32_t j = i - narrow_from;   // meaningful when i >= narrow_from
+  it.narrow = i >= narrow_from ? 1u : 0u;
+  it.tile = it.narrow ? narrow_from + (j >> 1) : i;
+  it.half = it.narrow ? (j & 1u) : 0u;
+  return it;
+}
+
 template <typename TC>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -58,7 +74,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tile_n = p.tile_n;
   const uint32_t tmem_cols = p.tmem_cols;
   const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r;
-  const uint32_t num_tiles = tiles_r * tiles_c;
+  const uint32_t n_items = p.n_items, narrow_from = p.narrow_from;
   const uint32_t num_kb = p.num_kb;
   int32_t* const status = p.status;
   const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
@@ -103,11 +119,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t my_turn = warp == 0 ? 0u : 1u;
     uint32_t stage = 0, phase = 0, turn = 0;
     bool ok = true;
-    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+    for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
+      const PairItem it = pair_item(i, narrow_from);
       uint32_t tr, tc;
-      tile_coords(group_r, tiles_r, tiles_c, tile, tr, tc);
+      tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc);
       const int32_t r0 = (int32_t)(tr * 256u + rank * 128u);
-      const int32_t c0 = (int32_t)(tc * tile_n + rank * (tile_n >> 1));
+      // a narrow item covers columns [half * tile_n/2, +tile_n/2) of the tile; each CTA stages half
+      const uint32_t cols_item = it.narrow ? (tile_n >> 1) : tile_n;
+      const int32_t c0 = (int32_t)(tc * tile_n + it.half * (tile_n >> 1) + rank * (cols_item >> 1));
+      const uint32_t b_boxes_item = it.narrow ? (b_boxes >> 1) : b_boxes;
+      const uint32_t bytes_item = it.narrow ? a_stage_bytes + ((stage_bytes - a_stage_bytes) >> 1) : stage_bytes;
       for (uint32_t kb = 0; kb < num_kb; ++kb) {
         if (turn != my_turn) {  // the other producer warp loads this k-block
           turn ^= 1u;
@@ -130,7 +151,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           continue;
         }
-        if (ptx::elect_one()) ptx::mbar_arrive_expect_tx_cluster(full, stage_bytes);
+        if (ptx::elect_one()) ptx::mbar_arrive_expect_tx_cluster(full, bytes_item);
         const uint32_t a_dst = tiles_base + stage * stage_bytes;
         const uint32_t b_dst = a_dst + a_stage_bytes;
         const int32_t k0 = (int32_t)(kb * bk_elems);
@@ -139,7 +160,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
           if (ptx::elect_one()) ptx::tma_load_2d_pair(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
         }
-        for (uint32_t bx = 0; bx < b_boxes; ++bx) {
+        for (uint32_t bx = 0; bx < b_boxes_item; ++bx) {
           const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
           const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
           if (ptx::elect_one()) ptx::tma_load_2d_pair(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
@@ -166,11 +187,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint64_t a_desc_base = p.a.desc_base, b_desc_base = p.b.desc_base;
       const uint32_t a_k_step = p.a.k_step_bytes, b_k_step = p.b.k_step_bytes;
       const uint32_t a_stage_bytes = p.a.stage_bytes;
-      const uint32_t idesc = p.idesc;
+      const uint32_t idesc_wide = p.idesc, idesc_narrow = p.idesc_narrow;
       const uint32_t kind_f8 = p.kind_f8;
       uint32_t stage = 0, phase = 0, item = 0;
       bool ok = true;
-      for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+      for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
+        const uint32_t idesc = i >= narrow_from ? idesc_narrow : idesc_wide;
         const uint32_t acc = item & 1u;
         const uint32_t acc_phase = (item >> 1) & 1u;
         ok = bounded_wait(acc_empty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
@@ -260,22 +282,25 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t quarter = warp & 3u;
     uint32_t item = 0;
     bool ok = true;
-    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+    for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
+      const PairItem it = pair_item(i, narrow_from);
       const uint32_t acc = item & 1u;
       const uint32_t acc_phase = (item >> 1) & 1u;
       uint32_t tr, tc;
-      tile_coords(group_r, tiles_r, tiles_c, tile, tr, tc);
+      tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc);
+      const uint32_t cols_item = it.narrow ? (tile_n >> 1) : tile_n;
+      const uint32_t col0 = tc * tile_n + it.half * (tile_n >> 1);
       ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
                         kEpilogueBackoffNs);
       if (!ok) break;
       ptx::tc_fence_after();
       const uint32_t row = tr * 256u + rank * 128u + quarter * 32u + lane;
       const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + acc * tile_n;
-      for (uint32_t cc = 0; cc < tile_n; cc += 32) {
+      for (uint32_t cc = 0; cc < cols_item; cc += 32) {
         uint32_t v[32];
         ptx::tmem_ld_32x32b_x32(t_row + cc, v);
         ptx::tmem_ld_wait();
-        epilogue_store<TC, 32>(ep, row, tc * tile_n + cc, v);
+        epilogue_store<TC, 32>(ep, row, col0 + cc, v);
       }
       ptx::tc_fence_before();
       __syncwarp();

@@ -303,6 +303,8 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
+    ap.add_argument("--band", type=int, default=0,
+                    help="tile rows the rasterisation walks together (0: the plan's choice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -339,7 +341,7 @@ def main():
         dist.broadcast(B, 0)
     C = torch.empty((rows, N), device=dev, dtype=out_dtype(torch, name))
     plan = R.GemmPlan(rows, N, K, AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16),
-                      transB=name in TRANS_B, scales=sa is not None)
+                      transB=name in TRANS_B, scales=sa is not None, band_tiles=args.band)
     ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream

@@ -333,10 +333,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // tile rows walked together: 2048 rows of A either way.  Measured on bf16 8192^3 with the pair
   // kernel (DRAM bytes read per launch): bands of 4 / 6 / 8 / 10 / 12 / 16 tile rows give
   // 1.58 / 1.26 / 1.07 / 1.15 / 1.11 / 1.21 GB
-  g.group_r = pair ? 8 : 16;
-#if defined(FRISK_B200_MEASURE) || defined(FRISK_B200_TUNE)
-  if (const char* e = getenv("FRISK_B200_GROUP_R")) g.group_r = (uint32_t)std::max(1, atoi(e));
-#endif
+  g.group_r = d.band_tiles > 0 ? (uint32_t)d.band_tiles : (pair ? 8u : 16u);
   g.split_mode = swap ? 1 : 0;
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
@@ -589,7 +586,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.tile_n != 0 && d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256)
     return FRISK_ERR_INVALID_ARGUMENT;
-  if (d.force_kernel < 0 || d.force_kernel > 4 || d.stages < 0 || d.num_ctas < 0)
+  if (d.force_kernel < 0 || d.force_kernel > 4 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
 
   frisk_gemm_plan* pl = new (std::nothrow) frisk_gemm_plan();
@@ -959,6 +956,7 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
     return FRISK_ERR_INVALID_ARGUMENT;
   d.force_kernel = 0;
   d.tile_n = 0;
+  d.band_tiles = 0;
   // only the few-row plan uses scratch; everything else has no reason to come through here
   if (!(tcgen05_eligible(d) && skinny_shape(d, 1024))) return FRISK_ERR_UNSUPPORTED;
   if (((uintptr_t)A % 16) || ((uintptr_t)B % 16)) return FRISK_ERR_MISALIGNED;

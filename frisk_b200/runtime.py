@@ -36,7 +36,7 @@ class GemmDesc(C.Structure):
         ("transA", C.c_int32), ("transB", C.c_int32),
         ("clear_accum", C.c_int32), ("scale_mode", C.c_int32),
         ("force_kernel", C.c_int32), ("tile_n", C.c_int32), ("stages", C.c_int32),
-        ("num_ctas", C.c_int32),
+        ("num_ctas", C.c_int32), ("band_tiles", C.c_int32),
     ]
 
 
@@ -163,7 +163,7 @@ class GemmPlan:
                  transA: bool = False, transB: bool = False, clear_accum: bool = True,
                  scales: bool = False, lda: int = 0, ldb: int = 0, ldc: int = 0,
                  force_kernel: Optional[str] = None, tile_n: int = 0, stages: int = 0,
-                 num_ctas: int = 0):
+                 num_ctas: int = 0, band_tiles: int = 0):
         L = lib()
         d = GemmDesc()
         d.M, d.N, d.K = M, N, K
@@ -174,7 +174,7 @@ class GemmPlan:
         d.clear_accum = int(clear_accum)
         d.scale_mode = 1 if scales else 0
         d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2, "tcgen05_pair": 3}[force_kernel]
-        d.tile_n, d.stages, d.num_ctas = tile_n, stages, num_ctas
+        d.tile_n, d.stages, d.num_ctas, d.band_tiles = tile_n, stages, num_ctas, band_tiles
         self.desc = d
         self._h = C.c_void_p()
         _check(L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(self._h)), "plan_create")

@@ -85,6 +85,7 @@ typedef struct frisk_gemm_desc {
   int32_t tile_n;       /* tcgen05 tile width along N: 64, 128 or 256                        */
   int32_t stages;       /* TMA pipeline depth                                                */
   int32_t num_ctas;     /* persistent grid size                                              */
+  int32_t band_tiles;   /* tile rows walked together by the rasterisation (L2 reuse)         */
 } frisk_gemm_desc;
 
 typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */

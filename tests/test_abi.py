@@ -76,13 +76,16 @@ def test_plan_falls_back_to_simt_for_unaligned_leading_dimensions():
     p = R.GemmPlan(100, 104, 104, W.BF16)
     assert p.info["kernel_name"] == "tcgen05"
     p.close()
+    p = R.GemmPlan(4096, 4096, 4096, W.BF16, band_tiles=4, stages=3)  # tuning overrides are accepted
+    assert p.info["kernel_name"] == "tcgen05_pair" and p.info["stages"] == 3
+    p.close()
     p = R.GemmPlan(128, 128, 128, W.E4M3, W.BF16, transB=False)  # fp8 MN-major B: CUDA cores
     assert p.info["kernel_name"] == "simt"
     p.close()
 
 
 def test_plan_create_rejects_bad_descriptions():
-    for kw in (dict(M=0), dict(K=-1), dict(lda=3), dict(ldc=5)):
+    for kw in (dict(M=0), dict(K=-1), dict(lda=3), dict(ldc=5), dict(stages=-1), dict(band_tiles=-2)):
         args = dict(M=8, N=8, K=8)
         args.update({k: v for k, v in kw.items() if k in args})
         extra = {k: v for k, v in kw.items() if k not in args}

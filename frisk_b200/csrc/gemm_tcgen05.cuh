@@ -4,13 +4,16 @@
 //              fast as the tensor pipe consumes a stage
 //   warp 1   : MMA issuer    (tcgen05.mma, fp32 accumulators in tensor memory)
 //   warps 2-5: epilogue      (tcgen05.ld -> registers -> scale / cast -> global)
-// One kernel serves two plans:
-//   * whole-tile mode: every CTA walks output tiles (128*mi x tile_n) round-robin and writes C;
-//   * split mode     : the (tile, k-block) units are dealt in contiguous ranges to all CTAs
-//                      ("stream-K"); partial sums are added into an fp32 workspace and a
-//                      small finalize kernel casts them to C.  With the operands swapped on the
-//                      host (weights feed the 128-row operand) this is the skinny / decode path:
-//                      the weight matrix is streamed once from HBM by all SMs.
+// Two instantiations of one template:
+//   * whole tiles (kSplit = false): every CTA walks output tiles (128 x tile_n) round-robin and
+//     writes C;
+//   * K-split (kSplit = true), the few-row ("skinny" / decode) plans: the operands are swapped
+//     on the host (the weights feed the 128-row operand) and several CTAs share a tile's K range,
+//     so the weight matrix is streamed once from HBM by many SMs.  Split mode 3: one cluster per
+//     tile, a K slice per CTA, partial tiles pushed through distributed shared memory and summed
+//     by their owners.  Split mode 2: (tile, k-block) units dealt in contiguous ranges to the
+//     CTAs ("stream-K"), partials in private workspace slots, summed by the last CTA to arrive.
+//     Split mode 1: partials added to an fp32 workspace with atomics, cast by a second kernel.
 // The kernel computes D[r, c] = sum_k Arole[r, k] * Brole[c, k]; the host decides whether D is C
 // or C transposed (`transposed_out`).
 //

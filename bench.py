@@ -42,8 +42,8 @@ BOUND = {"cfg3": "hbm"}  # everything else is judged against the tensor-core pea
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/; None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    # profiles/gemm_tcgen05_pair_bf16_8192.md (bands of 8 tile rows): 1069.8 MB read + 126.1 MB written
-    "bf16_8192": 1195878912,
+    # profiles/gemm_tcgen05_pair_bf16_8192.md (bands of 8 tile rows): 1089.2 MB read + 126.2 MB written
+    "bf16_8192": 1215415552,
     # cfg5 is scaled from the 8192-row capture by the rows a rank holds: it is that many row slabs
     # against the same B, walked band by band, so the traffic grows with the rows (roofline_for)
     # profiles/gemm_skinny_cluster_cfg3.md: 134.57 MB read + 4.01 MB written

@@ -138,3 +138,43 @@ def test_shard_rows_errors():
         with pytest.raises(R.FriskError) as e:
             R.shard_rows(*bad)
         assert e.value.code == -8
+
+
+def test_planner_invariants_over_random_shapes():
+    """Whatever the shape, a plan names a kernel the library has, fits the SM (shared memory,
+    pipeline depth, grid) and states its workspace; few-row plans either need no workspace
+    (clusters) or the stream-K one."""
+    import random
+    rnd = random.Random(5)
+    seen = set()
+    for _ in range(400):
+        ab = rnd.choice([W.F32, W.F16, W.BF16, W.E4M3])
+        ct = ab if ab != W.E4M3 else W.BF16
+        M = rnd.choice([1, 7, 16, 33, 64, 65, 128, 200, 256, 1000, 4096, 8192])
+        N = rnd.choice([8, 64, 104, 256, 512, 1000, 2048, 4096, 8192, 28672])
+        K = rnd.choice([8, 64, 72, 520, 1024, 4096, 8192])
+        ta, tb = rnd.random() < 0.2, rnd.random() < 0.5
+        if ab == W.E4M3 and (ta or not tb):
+            ta, tb = False, True  # 8-bit inputs run on tensor cores only K-inner
+        p = R.GemmPlan(M, N, K, ab, ct, transA=ta, transB=tb, scales=ab == W.E4M3)
+        i = p.info
+        seen.add(i["kernel_name"])
+        assert i["kernel_name"] in ("simt", "tcgen05", "tcgen05_pair", "skinny")
+        assert i["launches"] == 1 and i["num_ctas"] >= 1
+        if i["kernel_name"] != "simt":
+            assert 2 <= i["stages"] <= 12 and i["smem_bytes"] <= 227 * 1024
+            assert i["num_ctas"] <= 148 and i["tile_k"] * W.ELEM_SIZE[ab] == 128
+        if i["kernel_name"] == "tcgen05_pair":
+            assert i["num_ctas"] % 2 == 0 and i["tile_m"] == 256 and M > 128
+        if i["kernel_name"] == "skinny":
+            assert M <= 64 and N >= 256 and not ta and i["swap_ab"] == 1
+            assert i["tile_m"] == (M + 15) // 16 * 16 and i["tile_n"] in (128, 256)
+            if p.workspace_bytes == 0:   # clusters: tiles x a power-of-two cluster size
+                tiles = -(-N // i["tile_n"])
+                assert i["num_ctas"] % tiles == 0 and i["num_ctas"] // tiles in (2, 4, 8)
+            else:                        # stream-K: slots + one counter per tile
+                assert p.workspace_bytes % 4 == 0 and i["num_ctas"] <= 14 * -(-N // i["tile_n"])
+        else:
+            assert p.workspace_bytes == 0
+        p.close()
+    assert seen == {"simt", "tcgen05", "tcgen05_pair", "skinny"}

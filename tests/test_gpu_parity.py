@@ -419,3 +419,64 @@ def test_cta_pair_kernel_variants_match_oracle(M, N, K, ab, ct, ta, tb, clear):
     out1, info1 = run_and_check(w, force_kernel="tcgen05")
     assert info1["kernel_name"] == "tcgen05"
     assert np.array_equal(out, out1)  # same k order, same fp32 accumulation: same bits
+
+
+def test_back_to_back_dependent_launches_see_each_others_results():
+    """The tensor-core kernels are launched with programmatic stream serialization (their set-up may
+    overlap the previous kernel's tail).  A chain in which every GEMM reads what the one before
+    wrote, launched without any synchronisation, must give the bits of the same chain run one
+    step at a time: CTA-pair kernel -> one-CTA kernel -> cluster few-row plan -> stream-K few-row
+    plan -> CUDA-core kernel."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(11)
+    bf = torch.bfloat16
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(bf)
+    K = 512
+    x0 = rnd(512, K)
+    w = [rnd(K, K, scale=K ** -0.5) for _ in range(3)]
+    w_wide = rnd(K, 4096, scale=K ** -0.5)
+    w_narrow = rnd(4096, 512, scale=4096 ** -0.5)
+    w_f32 = torch.randn(512, 96, generator=g, device=dev) * 512 ** -0.5
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    steps = []  # (plan, A, B, C)
+    def add(M, N, Kd, a, b, ab=W.BF16, ct=W.BF16, **kw):
+        plan = R.GemmPlan(M, N, Kd, ab, ct, **kw)
+        out = torch.empty(M, N, device=dev, dtype={W.BF16: bf, W.F32: torch.float32}[ct])
+        ws = torch.zeros(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
+        steps.append((plan, a, b, out, ws))
+        return out
+    y1 = add(512, K, K, x0, w[0])                              # CTA-pair kernel
+    y2 = add(512, K, K, y1, w[1], force_kernel="tcgen05")      # one-CTA kernel
+    y3 = add(512, K, K, y2, w[2])
+    y4 = add(16, 4096, K, y3[:16], w_wide)                     # few rows: clusters
+    y5 = add(16, 512, 4096, y4, w_narrow)                      # few rows: stream-K (two tiles)
+    y5f = torch.empty(16, 512, device=dev, dtype=torch.float32)
+    kinds = [s[0].info["kernel_name"] for s in steps]
+    assert kinds == ["tcgen05_pair", "tcgen05", "tcgen05_pair", "skinny", "skinny"], kinds
+    f32_plan = R.GemmPlan(16, 96, 512, W.F32, W.F32)           # CUDA-core kernel on the chain's end
+    y6 = torch.empty(16, 96, device=dev, dtype=torch.float32)
+
+    def run_chain(sync):
+        for plan, a, b, out, ws in steps:
+            plan.run(a, b, out, None, None, ws, status)
+            if sync:
+                torch.cuda.synchronize()
+        y5f.copy_(y5)  # a torch kernel in between, then the fp32 GEMM
+        f32_plan.run(y5f, w_f32, y6, None, None, None, status)
+        torch.cuda.synchronize()
+        R.check_status(status)
+        return [t.clone() for t in (y1, y2, y3, y4, y5, y6)]
+
+    want = run_chain(sync=True)
+    for t in (y1, y2, y3, y4, y5, y6):
+        t.zero_()
+    for _ in range(3):
+        got = run_chain(sync=False)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    assert float(want[5].abs().max()) > 0
+    for plan, *_ in steps:
+        plan.close()
+    f32_plan.close()

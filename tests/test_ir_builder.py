@@ -13,7 +13,8 @@ import frisk as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLDEN = os.path.join(HERE, "golden")
-REFERENCE = "/root/reference"
+# a checkout of the reference beside this repository, when there is one (else those tests skip)
+REFERENCE = os.environ.get("FRISK_REFERENCE_ROOT", os.path.normpath(os.path.join(HERE, "..", "..", "reference")))
 
 
 def build_bind_test_module():

@@ -197,7 +197,9 @@ uint32_t next_pow2_cols(uint32_t c) {
   return v;
 }
 
-constexpr size_t kMaxDynSmem = 227 * 1024 - 1024;  // leave room for the static barriers
+// Most dynamic shared memory a plan may use, and the opt-in value every kernel function is set
+// to: the 227 KiB of an SM less room for the kernels' static barriers and flags.
+constexpr size_t kMaxDynSmem = 227 * 1024 - 1024;
 
 bool tcgen05_eligible(const frisk_gemm_desc& d) {
   if (d.a_type != FRISK_DT_F16 && d.a_type != FRISK_DT_BF16 && d.a_type != FRISK_DT_E4M3)
@@ -314,7 +316,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // split mode 3 keeps one fp32 tile behind the stage buffers: the region the cluster's partials
   // are pushed into
   const size_t red_bytes = (swap && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
-  uint32_t stages = (uint32_t)((kMaxDynSmem - red_bytes - (red_bytes ? 1024 : 0)) / g.stage_bytes);
+  // stages * stage_bytes + 1024 (alignment slack) + red_bytes stays within kMaxDynSmem
+  uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
   if (d.stages > 0) stages = std::min<uint32_t>(stages, (uint32_t)d.stages);
   // at least two: a stage is released only after the first MMA of the NEXT k-block was issued,
@@ -410,8 +413,11 @@ template <typename TC, bool kSplit>
 int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
   auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit>;
   if (!pl->smem_attr_set) {
+    // The opt-in limit belongs to the kernel function, not to the plan: every plan asks for the
+    // same value (the most any plan uses), so plans with different pipeline depths do not lower
+    // it under one another.
     FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)pl->dyn_smem));
+                                    (int)kMaxDynSmem));
     pl->smem_attr_set = true;
   }
   cudaLaunchConfig_t cfg;
@@ -443,7 +449,7 @@ template <typename TC>
 int max_active_clusters_t(frisk_gemm_plan* pl, int* out) {
   auto kern = frisk::gemm_tcgen05_kernel<TC, true>;
   FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)pl->dyn_smem));
+                                  (int)kMaxDynSmem));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -485,8 +491,11 @@ template <typename TC>
 int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
   auto kern = frisk::gemm_tcgen05_pair_kernel<TC>;
   if (!pl->smem_attr_set) {
+    // The opt-in limit belongs to the kernel function, not to the plan: every plan asks for the
+    // same value (the most any plan uses), so plans with different pipeline depths do not lower
+    // it under one another.
     FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)pl->dyn_smem));
+                                    (int)kMaxDynSmem));
     pl->smem_attr_set = true;
   }
   cudaLaunchConfig_t cfg;

@@ -1048,7 +1048,25 @@ void initFrisk(py::module_ m) {
         auto l = sharedLayoutForOperand(t->shape, bitWidth(t->element), kInner, hopper);
         if (!l) return py::none();
         return py::cast(PyAttribute{*l});
-      }, py::arg("operand"), py::arg("hopper") = true);
+      }, py::arg("operand"), py::arg("hopper") = true)
+      // addition: where the accumulator of a 128-row tile lives on sm_100a.  The reference's
+      // GemmOp::inferLayout gives C a register fragment (FriskOps.cpp:304-347, per-thread ownership
+      // for mma.sync / wgmma); with tcgen05 the accumulator is in tensor memory, row r of the tile
+      // in lane r, column c in column c, and `tcgen05.ld.32x32b` hands thread t of the warp that
+      // owns lanes 32q .. 32q+31 (warp index mod 4 == q) row 32q + t with consecutive columns as
+      // consecutive registers.  As a layout: index (d0, d1) -> (d1), thread (d0, d1) -> (d0).
+      .def("infer_accumulator_layout_sm100", [](PyGemm& g, int64_t tileRows, int64_t tileCols) {
+        if (tileRows != 128) throw std::invalid_argument("a tcgen05 accumulator tile has 128 rows per CTA");
+        if (tileCols < 8 || tileCols > 256 || tileCols % 8 != 0)
+          throw std::invalid_argument("accumulator columns must be a multiple of 8 up to 256");
+        (void)g;
+        LayoutAttrData l;
+        l.inputShape = {tileRows, tileCols};
+        l.forwardIndex = AffineMap::get(2, 0, {affineDim(1)});
+        l.forwardThread = AffineMap::get(2, 0, {affineDim(0)});
+        l.replicate = 1;
+        return PyAttribute{l};
+      }, py::arg("tile_rows") = 128, py::arg("tile_cols") = 256);
 
   py::class_<PyKernel, PyOpState>(m, "KernelOp", py::module_local())
       .def("arg", [](PyKernel& k, unsigned i) {

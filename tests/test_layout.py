@@ -135,3 +135,26 @@ def test_bank_model_blackwell_modes_and_distinct_word_counting():
     # tensor-core operand fetch do.  Unswizzled 128-byte rows hit 8-way conflicts on words.
     with pytest.raises(R.FriskError):
         R.bank_conflicts(128, 60, 16, 128, 8)
+
+
+def test_accumulator_layout_on_sm100_is_the_tensor_memory_map():
+    """Addition: where the reference gives C a register fragment (mma.sync / wgmma ownership,
+    FriskOps.cpp:304-347), tcgen05 keeps the accumulator in tensor memory: tile row r in lane r,
+    column c in column c; tcgen05.ld.32x32b gives thread r its row, columns as registers."""
+    h = F.create_session()
+    f16 = h.builder.get_f16_ty()
+    tys = [h.memref_type((128, 64), f16, space=F.MemorySpace.SHARED),
+           h.memref_type((64, 256), f16, space=F.MemorySpace.SHARED),
+           h.memref_type((128, 256), f16, space=F.MemorySpace.LOCAL)]
+    _, entry = h.new_kernel("acc", tys)
+    g = h.create_gemm(*[entry.get_argument(i) for i in range(3)])
+    attr = g.infer_accumulator_layout_sm100(128, 256)
+    assert str(attr) == ("#frisk.layout<[128, 256], affine_map<(d0, d1) -> (d1)>, "
+                         "affine_map<(d0, d1) -> (d0)>, 1>")
+    index = F.frisk.layout_index_map(attr)
+    for r, c in ((0, 0), (5, 17), (127, 255)):
+        assert index.evaluate([r, c]) == [c]   # register j of thread r holds column j
+    with pytest.raises(ValueError):
+        g.infer_accumulator_layout_sm100(64, 256)
+    with pytest.raises(ValueError):
+        g.infer_accumulator_layout_sm100(128, 260)

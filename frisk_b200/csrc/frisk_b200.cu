@@ -200,6 +200,10 @@ uint32_t next_pow2_cols(uint32_t c) {
 // Most dynamic shared memory a plan may use, and the opt-in value every kernel function is set
 // to: the 227 KiB of an SM less room for the kernels' static barriers and flags.
 constexpr size_t kMaxDynSmem = 227 * 1024 - 1024;
+// Every tensor-core launch asks for all of it, whatever the plan's pipeline depth needs: that
+// keeps the kernels at one CTA per SM, so a CTA never waits in tcgen05.alloc for tensor memory
+// another CTA on its SM holds (with CTA pairs such a wait could close a cycle across two SMs).
+constexpr size_t kLaunchDynSmem = kMaxDynSmem;
 
 bool tcgen05_eligible(const frisk_gemm_desc& d) {
   if (d.a_type != FRISK_DT_F16 && d.a_type != FRISK_DT_BF16 && d.a_type != FRISK_DT_E4M3)
@@ -424,7 +428,7 @@ int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStrea
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
   cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = pl->dyn_smem;
+  cfg.dynamicSmemBytes = kLaunchDynSmem;
   cfg.stream = st;
   // the kernel's set-up may start while the previous kernel of the stream drains; it waits
   // (griddepcontrol.wait) before it touches global memory
@@ -454,7 +458,7 @@ int max_active_clusters_t(frisk_gemm_plan* pl, int* out) {
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
   cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = pl->dyn_smem;
+  cfg.dynamicSmemBytes = kLaunchDynSmem;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = pl->gp.cluster_k;
@@ -502,7 +506,7 @@ int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t 
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
   cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = pl->dyn_smem;
+  cfg.dynamicSmemBytes = kLaunchDynSmem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -54,7 +54,10 @@ gemm_simt_kernel(const SimtParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  for (int64_t k0 = 0; k0 < p.K; k0 += kSimtBK) {
+  // The K slice after the one being multiplied is fetched into registers while the FMAs run, so
+  // the global-memory latency of a slice is paid once, not once per slice.
+  float av[4], bv[4];
+  auto fetch = [&](int64_t k0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int idx = threadIdx.x + e * 256;
@@ -62,19 +65,31 @@ gemm_simt_kernel(const SimtParams p) {
       int am, ak, bn, bk;
       if (p.transA) { am = idx & 63; ak = idx >> 6; } else { ak = idx & 15; am = idx >> 4; }
       if (p.transB) { bk = idx & 15; bn = idx >> 4; } else { bn = idx & 63; bk = idx >> 6; }
-      float av = 0.f, bv = 0.f;
+      av[e] = 0.f;
+      bv[e] = 0.f;
       if (m0 + am < p.M && k0 + ak < p.K) {
         const int64_t off = p.transA ? (k0 + ak) * p.lda + (m0 + am) : (m0 + am) * p.lda + (k0 + ak);
-        av = cast_in<TIn>(A[off]);
+        av[e] = cast_in<TIn>(A[off]);
       }
       if (n0 + bn < p.N && k0 + bk < p.K) {
         const int64_t off = p.transB ? (n0 + bn) * p.ldb + (k0 + bk) : (k0 + bk) * p.ldb + (n0 + bn);
-        bv = cast_in<TIn>(B[off]);
+        bv[e] = cast_in<TIn>(B[off]);
       }
-      As[ak][am] = av;
-      Bs[bk][bn] = bv;
+    }
+  };
+  fetch(0);
+  for (int64_t k0 = 0; k0 < p.K; k0 += kSimtBK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = threadIdx.x + e * 256;
+      int am, ak, bn, bk;
+      if (p.transA) { am = idx & 63; ak = idx >> 6; } else { ak = idx & 15; am = idx >> 4; }
+      if (p.transB) { bk = idx & 15; bn = idx >> 4; } else { bn = idx & 63; bk = idx >> 6; }
+      As[ak][am] = av[e];
+      Bs[bk][bn] = bv[e];
     }
     __syncthreads();
+    if (k0 + kSimtBK < p.K) fetch(k0 + kSimtBK);
 #pragma unroll
     for (int kk = 0; kk < kSimtBK; ++kk) {
       float a[4], b[4];

@@ -220,7 +220,7 @@ bool tcgen05_eligible(const frisk_gemm_desc& d) {
 // (tile, k-block) units in 32 bits and multiplies the count by the grid size, so the product has
 // to stay below 2^32 (conservatively: the smallest tile and k-block the plan could pick).
 bool skinny_shape(const frisk_gemm_desc& d, int sm_count) {
-  if (!(d.M <= 64 && d.N >= 256 && !d.transA)) return false;
+  if (!(d.M <= 128 && d.N >= 256 && !d.transA)) return false;
   const uint64_t units = (uint64_t)((d.N + 127) / 128) * (uint64_t)((d.K + 31) / 32);
   return units * (uint64_t)(sm_count + 1) < (1ull << 32);
 }
@@ -279,6 +279,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     int n_cand = 0;
     for (uint32_t mi = (rows > 128 ? 2u : 1u); mi >= 1; --mi) {
       const uint32_t t = (uint32_t)((rows + 128 * mi - 1) / (128 * mi));
+      // the pushed-partials region and at least four pipeline stages have to fit beside each other
+      const size_t stage = (size_t)(128 * mi + g.tile_n) * 128u;
+      const size_t red = (size_t)128 * mi * g.tile_n * sizeof(float);
+      if (red + 1024 + 4 * stage > kMaxDynSmem) continue;
       for (uint32_t s = 8; s >= 2; s >>= 1) {
         if (s > kbs || (uint64_t)t * s > (uint64_t)pl->sm_count) continue;
         if (t * s * 100u >= (uint32_t)pl->sm_count * min_cover) cand[n_cand++] = Cand{t * s, mi, s};
@@ -661,6 +665,11 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     pl->info.launches = 1;
   } else {
     plan_tcgen05(pl, kind == FRISK_KERNEL_SKINNY, kind == FRISK_KERNEL_TCGEN05_PAIR);
+    // Between 65 and 128 rows the few-row plan pays only in its cluster form (128 x 8192 x 8192:
+    // 35 us against 59 us for whole tiles on 32 SMs); where clusters do not apply (few tiles, or
+    // more tiles than SMs) whole tiles are as good or better (128 x 28672 x 4096: 45 against 79 us).
+    if (kind == FRISK_KERNEL_SKINNY && d.M > 64 && !d.force_kernel && pl->gp.split_mode != 3)
+      plan_tcgen05(pl, /*swap=*/false, /*pair=*/false);
   }
   *out = pl;
   return FRISK_OK;
@@ -971,7 +980,8 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   d.tile_n = 0;
   d.band_tiles = 0;
   // only the few-row plan uses scratch; everything else has no reason to come through here
-  if (!(tcgen05_eligible(d) && skinny_shape(d, 1024))) return FRISK_ERR_UNSUPPORTED;
+  // (this entry point keeps the 64-row limit the few-row plan had when it was written)
+  if (!(tcgen05_eligible(d) && d.M <= 64 && skinny_shape(d, 1024))) return FRISK_ERR_UNSUPPORTED;
   if (((uintptr_t)A % 16) || ((uintptr_t)B % 16)) return FRISK_ERR_MISALIGNED;
 
   frisk_gemm_plan pl;  // lives on the stack: nothing is allocated on the host heap either

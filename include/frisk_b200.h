@@ -63,7 +63,7 @@ typedef enum { FRISK_SCALE_NONE = 0, FRISK_SCALE_ROW_COL = 1 } frisk_scale_mode;
 typedef enum {
   FRISK_KERNEL_SIMT = 0,    /* CUDA-core fp32-FMA tiles: fp32 inputs and every odd shape   */
   FRISK_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma, accumulators in TMEM, whole-tile output   */
-  FRISK_KERNEL_SKINNY = 2,  /* same pipeline, operands swapped, K split over a cluster / SMs */
+  FRISK_KERNEL_SKINNY = 2,  /* few rows (M <= 128): operands swapped, K split over a cluster / SMs */
   FRISK_KERNEL_TCGEN05_PAIR = 3 /* CTA pairs with two-SM MMAs on 256 x tile_n output tiles   */
 } frisk_kernel_kind;
 

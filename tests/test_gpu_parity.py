@@ -371,6 +371,10 @@ FEW_ROWS = [
     (16, 512, 4096, W.BF16, False, True, {}),     # stream-K: two tiles
     (16, 4096, 2048, W.BF16, False, True, {"num_ctas": 37}),  # stream-K: forced grid
     (24, 4096, 2048, W.F16, False, False, {"num_ctas": 148}),
+    (100, 4096, 1024, W.BF16, False, True, {}),   # more than 64 rows: 128-column tiles of B
+    (128, 8192, 512, W.F16, True, False, {}),
+    (96, 512, 2048, W.BF16, False, True, {"force_kernel": "skinny"}),  # ... and their stream-K form
+    (128, 2048, 1024, W.E4M3, True, True, {}),
 ]
 
 

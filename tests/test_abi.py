@@ -178,3 +178,16 @@ def test_planner_invariants_over_random_shapes():
             assert p.workspace_bytes == 0
         p.close()
     assert seen == {"simt", "tcgen05", "tcgen05_pair", "skinny"}
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    """No CPU fallback: without libfrisk_b200.so every entry point raises, nothing computes."""
+    monkeypatch.setattr(R, "LIB_PATH", str(tmp_path / "libfrisk_b200.so"))
+    monkeypatch.setattr(R, "_lib", None)
+    try:
+        with pytest.raises(R.FriskError, match="missing"):
+            R.GemmPlan(8, 8, 8, W.F32)
+        with pytest.raises(R.FriskError, match="missing"):
+            R.gemm_host(W.make_workload("cfg1", 8, 8, 8))
+    finally:
+        monkeypatch.undo()

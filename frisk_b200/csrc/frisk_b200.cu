@@ -538,23 +538,30 @@ int launch_finalize_t(const frisk_gemm_plan* pl, float* ws, void* C, const float
   return FRISK_OK;
 }
 
-template <typename TIn>
-int launch_simt_in(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaStream_t st) {
-  dim3 grid((unsigned)((d.N + frisk::kSimtTile - 1) / frisk::kSimtTile),
-            (unsigned)((d.M + frisk::kSimtTile - 1) / frisk::kSimtTile));
+template <typename TIn, int TM>
+int launch_simt_tm(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaStream_t st) {
+  dim3 grid((unsigned)((d.N + frisk::kSimtTile - 1) / frisk::kSimtTile), (unsigned)((d.M + TM - 1) / TM));
   switch (d.c_type) {
-    case FRISK_DT_F32: frisk::gemm_simt_kernel<TIn, float><<<grid, 256, 0, st>>>(sp); break;
-    case FRISK_DT_F16: frisk::gemm_simt_kernel<TIn, __half><<<grid, 256, 0, st>>>(sp); break;
-    case FRISK_DT_BF16: frisk::gemm_simt_kernel<TIn, __nv_bfloat16><<<grid, 256, 0, st>>>(sp); break;
+    case FRISK_DT_F32: frisk::gemm_simt_kernel<TIn, float, TM><<<grid, TM * 4, 0, st>>>(sp); break;
+    case FRISK_DT_F16: frisk::gemm_simt_kernel<TIn, __half, TM><<<grid, TM * 4, 0, st>>>(sp); break;
+    case FRISK_DT_BF16: frisk::gemm_simt_kernel<TIn, __nv_bfloat16, TM><<<grid, TM * 4, 0, st>>>(sp); break;
     default: return FRISK_ERR_UNSUPPORTED;
   }
   FRISK_CUDA(cudaGetLastError());
   return FRISK_OK;
 }
 
+template <typename TIn>
+int launch_simt_in(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaStream_t st) {
+  // 32-row tiles when 64-row tiles would leave SMs idle (fp32 512^3: 64 CTAs for 148 SMs)
+  const int64_t ctas64 = ((d.N + 63) / 64) * ((d.M + 63) / 64);
+  if (d.M > 32 && ctas64 < 148) return launch_simt_tm<TIn, 32>(d, sp, st);
+  return launch_simt_tm<TIn, 64>(d, sp, st);
+}
+
 int launch_simt(const frisk_gemm_desc& d, const void* A, const void* B, void* C, const float* sa,
                 const float* sb, cudaStream_t st) {
-  if ((d.M + frisk::kSimtTile - 1) / frisk::kSimtTile > 65535) return FRISK_ERR_UNSUPPORTED;
+  if ((d.M + 31) / 32 > 65535) return FRISK_ERR_UNSUPPORTED;  // grid.y limit
   frisk::SimtParams sp;
   sp.A = A; sp.B = B; sp.C = C;
   sp.scale_a = d.scale_mode ? sa : nullptr;

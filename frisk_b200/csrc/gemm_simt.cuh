@@ -1,8 +1,8 @@
 // CUDA-core GEMM: fp32 FMA on exactly decoded inputs.  Serves the fp32 configuration (single-pass
 // TF32 tensor-core math cannot hold a 1e-4 relative Frobenius error at K = 512) and every shape or
 // layout the TMA path cannot take (leading dimensions that are not 16-byte multiples, ...).
-// 64 x 64 output tile per CTA, 256 threads, 4 x 4 outputs per thread, 16-deep K slices staged in
-// shared memory as fp32.
+// 64 x 64 (or 32 x 64) output tile per CTA, 4 x 4 outputs per thread, 16-deep K slices staged in
+// shared memory as fp32, the next slice fetched into registers during the FMAs.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -35,15 +35,19 @@ __device__ __forceinline__ float cast_in<e4m3_t>(e4m3_t v) {
 constexpr int kSimtTile = 64;
 constexpr int kSimtBK = 16;
 
-template <typename TIn, typename TOut>
-__global__ void __launch_bounds__(256)
+// TM = rows of the CTA tile (64, or 32 for problems that would not fill the SMs with 64-row
+// tiles); the tile is always 64 columns wide and every thread owns 4 x 4 outputs, so a CTA has
+// TM * 4 threads.
+template <typename TIn, typename TOut, int TM>
+__global__ void __launch_bounds__(TM * 4)
 gemm_simt_kernel(const SimtParams p) {
-  __shared__ float As[kSimtBK][kSimtTile + 4];  // [k][m]
+  constexpr int kThreads = TM * 4;
+  __shared__ float As[kSimtBK][TM + 4];         // [k][m]
   __shared__ float Bs[kSimtBK][kSimtTile + 4];  // [k][n]
   const TIn* A = reinterpret_cast<const TIn*>(p.A);
   const TIn* B = reinterpret_cast<const TIn*>(p.B);
   TOut* C = reinterpret_cast<TOut*>(p.C);
-  const int64_t m0 = (int64_t)blockIdx.y * kSimtTile;
+  const int64_t m0 = (int64_t)blockIdx.y * TM;
   const int64_t n0 = (int64_t)blockIdx.x * kSimtTile;
   const int tx = threadIdx.x & 15;  // column group
   const int ty = threadIdx.x >> 4;  // row group
@@ -56,21 +60,32 @@ gemm_simt_kernel(const SimtParams p) {
 
   // The K slice after the one being multiplied is fetched into registers while the FMAs run, so
   // the global-memory latency of a slice is paid once, not once per slice.
-  float av[4], bv[4];
+  constexpr int kAPer = TM * kSimtBK / kThreads;         // 4 elements of the A slice per thread
+  constexpr int kBPer = kSimtTile * kSimtBK / kThreads;  // 4 or 8 of the B slice
+  float av[kAPer], bv[kBPer];
+  // walk the contiguous global dimension with consecutive threads
+  auto a_pos = [&](int idx, int& am, int& ak) {
+    if (p.transA) { am = idx & (TM - 1); ak = idx / TM; } else { ak = idx & 15; am = idx >> 4; }
+  };
+  auto b_pos = [&](int idx, int& bn, int& bk) {
+    if (p.transB) { bk = idx & 15; bn = idx >> 4; } else { bn = idx & 63; bk = idx >> 6; }
+  };
   auto fetch = [&](int64_t k0) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int idx = threadIdx.x + e * 256;
-      // walk the contiguous global dimension with consecutive threads
-      int am, ak, bn, bk;
-      if (p.transA) { am = idx & 63; ak = idx >> 6; } else { ak = idx & 15; am = idx >> 4; }
-      if (p.transB) { bk = idx & 15; bn = idx >> 4; } else { bn = idx & 63; bk = idx >> 6; }
+    for (int e = 0; e < kAPer; ++e) {
+      int am, ak;
+      a_pos(threadIdx.x + e * kThreads, am, ak);
       av[e] = 0.f;
-      bv[e] = 0.f;
       if (m0 + am < p.M && k0 + ak < p.K) {
         const int64_t off = p.transA ? (k0 + ak) * p.lda + (m0 + am) : (m0 + am) * p.lda + (k0 + ak);
         av[e] = cast_in<TIn>(A[off]);
       }
+    }
+#pragma unroll
+    for (int e = 0; e < kBPer; ++e) {
+      int bn, bk;
+      b_pos(threadIdx.x + e * kThreads, bn, bk);
+      bv[e] = 0.f;
       if (n0 + bn < p.N && k0 + bk < p.K) {
         const int64_t off = p.transB ? (n0 + bn) * p.ldb + (k0 + bk) : (k0 + bk) * p.ldb + (n0 + bn);
         bv[e] = cast_in<TIn>(B[off]);
@@ -80,12 +95,15 @@ gemm_simt_kernel(const SimtParams p) {
   fetch(0);
   for (int64_t k0 = 0; k0 < p.K; k0 += kSimtBK) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int idx = threadIdx.x + e * 256;
-      int am, ak, bn, bk;
-      if (p.transA) { am = idx & 63; ak = idx >> 6; } else { ak = idx & 15; am = idx >> 4; }
-      if (p.transB) { bk = idx & 15; bn = idx >> 4; } else { bn = idx & 63; bk = idx >> 6; }
+    for (int e = 0; e < kAPer; ++e) {
+      int am, ak;
+      a_pos(threadIdx.x + e * kThreads, am, ak);
       As[ak][am] = av[e];
+    }
+#pragma unroll
+    for (int e = 0; e < kBPer; ++e) {
+      int bn, bk;
+      b_pos(threadIdx.x + e * kThreads, bn, bk);
       Bs[bk][bn] = bv[e];
     }
     __syncthreads();

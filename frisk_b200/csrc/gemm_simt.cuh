@@ -42,8 +42,10 @@ template <typename TIn, typename TOut, int TM>
 __global__ void __launch_bounds__(TM * 4)
 gemm_simt_kernel(const SimtParams p) {
   constexpr int kThreads = TM * 4;
-  __shared__ float As[kSimtBK][TM + 4];         // [k][m]
-  __shared__ float Bs[kSimtBK][kSimtTile + 4];  // [k][n]
+  // rows are 16-byte multiples apart and every thread reads its four values at a 16-byte offset,
+  // so the inner loop reads each operand with one 128-bit load
+  __shared__ __align__(16) float As[kSimtBK][TM + 4];         // [k][m]
+  __shared__ __align__(16) float Bs[kSimtBK][kSimtTile + 4];  // [k][n]
   const TIn* A = reinterpret_cast<const TIn*>(p.A);
   const TIn* B = reinterpret_cast<const TIn*>(p.B);
   TOut* C = reinterpret_cast<TOut*>(p.C);
@@ -110,11 +112,9 @@ gemm_simt_kernel(const SimtParams p) {
     if (k0 + kSimtBK < p.K) fetch(k0 + kSimtBK);
 #pragma unroll
     for (int kk = 0; kk < kSimtBK; ++kk) {
-      float a[4], b[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 b4 = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll

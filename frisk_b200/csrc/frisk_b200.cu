@@ -665,10 +665,14 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   }
   if (kind == FRISK_KERNEL_SIMT) {
     pl->info.kernel = FRISK_KERNEL_SIMT;
-    pl->info.tile_m = pl->info.tile_n = frisk::kSimtTile;
+    // the same choice launch_simt_in makes: 32-row tiles when 64-row tiles would not fill the SMs
+    const int64_t ctas64 = ((d.N + 63) / 64) * ((d.M + 63) / 64);
+    const int tm = (d.M > 32 && ctas64 < 148) ? 32 : frisk::kSimtTile;
+    pl->info.tile_m = tm;
+    pl->info.tile_n = frisk::kSimtTile;
     pl->info.tile_k = frisk::kSimtBK;
     pl->info.stages = 1;
-    pl->info.num_ctas = (int)(((d.M + 63) / 64) * ((d.N + 63) / 64));
+    pl->info.num_ctas = (int)(((d.M + tm - 1) / tm) * ((d.N + 63) / 64));
     pl->info.launches = 1;
   } else {
     plan_tcgen05(pl, kind == FRISK_KERNEL_SKINNY, kind == FRISK_KERNEL_TCGEN05_PAIR);

@@ -1049,6 +1049,21 @@ void initFrisk(py::module_ m) {
         if (!l) return py::none();
         return py::cast(PyAttribute{*l});
       }, py::arg("operand"), py::arg("hopper") = true)
+      // addition: GemmOp::inferLayout (FriskOps.cpp:1285-1407), which the reference reaches only
+      // from C++ (test_pass/attr_test.cpp:155-232): {"A", "B", "C"} -> #frisk.layout attribute,
+      // plus the warp split and the instruction family it implies.  ValueError with the
+      // reference's message when inference fails.
+      .def("infer_layout", [](PyGemm& g) {
+        GemmLayouts l = inferGemmLayouts(g.op);
+        if (!l.ok) throw std::invalid_argument("'frisk.gemm' op " + l.why);
+        py::dict d;
+        d["A"] = PyAttribute{l.a};
+        d["B"] = PyAttribute{l.b};
+        d["C"] = PyAttribute{l.c};
+        d["warps"] = py::make_tuple(l.warpsM, l.warpsN);
+        d["instruction"] = l.instruction;
+        return d;
+      })
       // addition: where the accumulator of a 128-row tile lives on sm_100a.  The reference's
       // GemmOp::inferLayout gives C a register fragment (FriskOps.cpp:304-347, per-thread ownership
       // for mma.sync / wgmma); with tcgen05 the accumulator is in tensor memory, row r of the tile
@@ -1157,7 +1172,21 @@ void initFrisk(py::module_ m) {
   py::class_<PyReduce, PyOpState>(m, "ReduceOp", py::module_local())
       .def("get_src_memref", [](PyReduce& r) { return castValue(r.op->operands[0]); })
       .def("get_dst_memref", [](PyReduce& r) { return castValue(r.op->operands[1]); })
-      .def("get_reduce_dim", [](PyReduce& r) { return r.op->intAttr("dim"); });
+      .def("get_reduce_dim", [](PyReduce& r) { return r.op->intAttr("dim"); })
+      // addition: ReduceOp::inferLayout (FriskOps_Reduce.cpp:214-357).  Returns the destination's
+      // #frisk.layout, or None when there is nothing to infer; ValueError on a conflict.
+      .def("infer_layout", [](PyReduce& r, py::object src, py::object existing) -> py::object {
+        auto data = [](py::object o) -> const LayoutAttrData* {
+          if (o.is_none()) return nullptr;
+          auto* l = std::get_if<LayoutAttrData>(&o.cast<PyAttribute&>().a);
+          if (!l) throw std::invalid_argument("'frisk.reduce' op source layout entry must be a frisk.layout attribute");
+          return l;
+        };
+        ReduceLayout l = inferReduceLayout(r.op, data(src), data(existing));
+        if (!l.ok) throw std::invalid_argument("'frisk.reduce' op " + l.why);
+        if (!l.inferred && existing.is_none()) return py::none();
+        return py::cast(PyAttribute{l.layout});
+      }, py::arg("src_layout"), py::arg("existing") = py::none());
 
   // addition: LayoutAttr as an object (the reference constructs it only from C++)
   m.def("layout_attr", [](std::vector<int64_t> shape, AffineMap index, AffineMap thread, py::object replicate) {
@@ -1171,6 +1200,28 @@ void initFrisk(py::module_ m) {
   m.def("layout_index_map", [](PyAttribute& a) -> py::object {
     if (auto* l = std::get_if<LayoutAttrData>(&a.a)) return py::cast(l->forwardIndex);
     return py::none();
+  });
+  m.def("layout_thread_map", [](PyAttribute& a) -> py::object {
+    auto* l = std::get_if<LayoutAttrData>(&a.a);
+    if (l && l->forwardThread.valid) return py::cast(l->forwardThread);
+    return py::none();
+  });
+  m.def("layout_replicate", [](PyAttribute& a) -> py::object {
+    auto* l = std::get_if<LayoutAttrData>(&a.a);
+    if (l && l->replicate) return py::int_(*l->replicate);
+    return py::none();
+  });
+  m.def("layout_shape", [](PyAttribute& a) -> py::object {
+    if (auto* l = std::get_if<LayoutAttrData>(&a.a)) return py::cast(l->inputShape);
+    return py::none();
+  });
+  m.def("layout_debug_string", [](PyAttribute& a) -> std::string {
+    if (auto* l = std::get_if<LayoutAttrData>(&a.a)) return layoutDebugString(*l);
+    return "<null layout>";
+  });
+  m.def("used_extent_of_dim", [](const AffineMap& map, unsigned dim, int64_t extent) -> py::object {
+    auto v = usedExtentOfDim(map, dim, extent);
+    return v ? py::object(py::int_(*v)) : py::object(py::none());
   });
   m.def("enum_attr", [](const std::string& mnemonic, const std::string& value) {
     return PyAttribute{EnumAttr{mnemonic, value}};

@@ -203,6 +203,41 @@ struct Builder {
 std::optional<LayoutAttrData> sharedLayoutForOperand(const std::vector<int64_t>& shape,
                                                      unsigned elemBits, bool kInner, bool hopper);
 
+// Layout inference of frisk.gemm (FriskOps.cpp:1285-1407): a shared-memory layout for an operand
+// in shared memory, a register fragment (thread map + register index map + replicate count) for an
+// operand in local memory and for the accumulator.  Needs a 'frisk.target' string on an enclosing
+// op and a thread count ('frisk.threads' on an enclosing op, or an enclosing frisk.parallel).
+// Targets sm_80..89 (mma.sync fragments), sm_90..99 (wgmma accumulator when it applies) and, as
+// an addition, sm_100 and later: operands in shared memory, accumulator in tensor memory.
+struct GemmLayouts {
+  bool ok = false;
+  std::string why;           // the refusal, in the reference's words where it has them
+  LayoutAttrData a, b, c;
+  int64_t warpsM = 1, warpsN = 1;
+  std::string instruction;   // "mma", "wgmma" or "tcgen05"
+};
+GemmLayouts inferGemmLayouts(const Operation* gemm);
+
+// Layout inference of frisk.reduce (FriskOps_Reduce.cpp:214-357): the destination's fragment
+// derived from the source's.  ok && !inferred: nothing to infer (an operand outside local memory,
+// or a source without a thread map), or `existing` was given and agrees (it is returned).
+struct ReduceLayout {
+  bool ok = false;
+  bool inferred = false;
+  std::string why;
+  LayoutAttrData layout;
+};
+ReduceLayout inferReduceLayout(const Operation* reduce, const LayoutAttrData* src,
+                               const LayoutAttrData* existing = nullptr);
+
+// Number of distinct values of the thread map that one coordinate selects, the factor by which a
+// reduce over that coordinate grows the replicate count (LayoutUtils.cpp:181-218).
+std::optional<int64_t> usedExtentOfDim(const AffineMap& map, unsigned dim, int64_t extent);
+std::optional<int64_t> threadBlockSize(const Operation* op);
+// "Fragment(shape=[..], index=affine_map<..>, thread=affine_map<..>, replicate=N)" or
+// "Layout(shape=[..], index=affine_map<..>)" (FriskAttributes.cpp:38-64).
+std::string layoutDebugString(const LayoutAttrData& l);
+
 // The tiled matrix product of the reference's sketch (tmp/ir.mlir:1-17: parallel grid, tiles in
 // shared / local buffers, a k loop of two copies and a gemm, a copy of the result) recognised and
 // lifted to one whole-problem GEMM C = A x B over kernel arguments; `ok` is false, with the

@@ -44,7 +44,8 @@ def build_runtime(force: bool = False, verbose_ptxas: bool = False) -> str:
     if not force and _newer(LIB, deps):
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    srcs = [os.path.join(CSRC, "frisk_b200.cu"), os.path.join(CSRC, "layout_map.cpp")]
+    srcs = [os.path.join(CSRC, "frisk_b200.cu"), os.path.join(CSRC, "reduce.cu"),
+            os.path.join(CSRC, "layout_map.cpp")]
     cmd = [nvcc, *NVCC_FLAGS, "-shared", "-o", LIB, *srcs, "-lcudart"]
     if verbose_ptxas:
         cmd[1:1] = ["-Xptxas", "-v"]

@@ -12,6 +12,7 @@
 #include <new>
 #include <string>
 
+#include "abi_internal.h"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
@@ -19,6 +20,12 @@
 namespace {
 
 thread_local std::string g_last_error;
+
+}  // namespace
+
+void frisk_internal_set_error(const char* text) { g_last_error = text ? text : ""; }
+
+namespace {
 
 int cuda_fail(cudaError_t e, const char* what) {
   g_last_error = std::string(what) + ": " + cudaGetErrorString(e);

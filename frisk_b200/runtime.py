@@ -54,6 +54,22 @@ class PlanInfo(C.Structure):
         return d
 
 
+class ReduceDesc(C.Structure):
+    _fields_ = [("outer", C.c_int64), ("extent", C.c_int64), ("inner", C.c_int64), ("dtype", C.c_int32),
+                ("kind", C.c_int32), ("clear", C.c_int32), ("device", C.c_int32)]
+
+
+class ReduceInfo(C.Structure):
+    _fields_ = [("lines", C.c_int32), ("vector", C.c_int32), ("chunks", C.c_int32), ("launches", C.c_int32),
+                ("chunk_len", C.c_int64), ("ctas", C.c_int64), ("workspace_bytes", C.c_size_t)]
+
+    def as_dict(self) -> dict:
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+REDUCE_KINDS = {"add": 0, "mul": 1, "min": 2, "max": 3}
+
+
 class LayoutDesc(C.Structure):
     _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("elem_bits", C.c_int32),
                 ("k_inner", C.c_int32)]
@@ -127,6 +143,14 @@ def lib() -> C.CDLL:
     L.frisk_b200_bank_conflicts.argtypes = [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_int32, C.POINTER(BankStats)]
     L.frisk_b200_bank_conflicts.restype = C.c_int
+    L.frisk_b200_reduce_info.argtypes = [C.POINTER(ReduceDesc), C.c_int, C.POINTER(ReduceInfo)]
+    L.frisk_b200_reduce_info.restype = C.c_int
+    L.frisk_b200_reduce_workspace_bytes.argtypes = [C.POINTER(ReduceDesc), C.POINTER(C.c_size_t)]
+    L.frisk_b200_reduce_workspace_bytes.restype = C.c_int
+    L.frisk_b200_reduce_run.argtypes = [C.POINTER(ReduceDesc), vp, vp, vp, C.c_size_t, vp]
+    L.frisk_b200_reduce_run.restype = C.c_int
+    L.frisk_b200_reduce_run_host.argtypes = [C.POINTER(ReduceDesc), vp, vp]
+    L.frisk_b200_reduce_run_host.restype = C.c_int
     L.frisk_b200_device_sm_count.argtypes = []
     L.frisk_b200_device_sm_count.restype = C.c_int
     L.frisk_b200_version.argtypes = []
@@ -236,6 +260,51 @@ def gemm_host(w: W.GemmWorkload, **plan_kw) -> np.ndarray:
     finally:
         plan.close()
     return out
+
+
+def reduce_desc(shape, dim: int, dtype: int, kind: str, clear: bool = True, device: int = -1) -> ReduceDesc:
+    """``frisk.reduce`` of a row-major buffer of `shape` over dimension `dim` as the C ABI sees it:
+    [outer, extent, inner] around the reduced dimension."""
+    shape = [int(d) for d in shape]
+    if not 0 <= dim < len(shape):
+        raise ValueError(f"dimension {dim} is out of range for source of rank {len(shape)}")
+    if kind not in REDUCE_KINDS:
+        raise ValueError(f"unsupported reduce kind: {kind}. Supported: add, mul, min, max")
+    outer = int(np.prod(shape[:dim], dtype=np.int64))
+    inner = int(np.prod(shape[dim + 1:], dtype=np.int64))
+    return ReduceDesc(outer, shape[dim], inner, dtype, REDUCE_KINDS[kind], int(bool(clear)), device)
+
+
+def reduce_info(desc: ReduceDesc, src_aligned: bool = True) -> dict:
+    info = ReduceInfo()
+    _check(lib().frisk_b200_reduce_info(C.byref(desc), int(src_aligned), C.byref(info)), "reduce_info")
+    return info.as_dict()
+
+
+def reduce_workspace_bytes(desc: ReduceDesc) -> int:
+    n = C.c_size_t()
+    _check(lib().frisk_b200_reduce_workspace_bytes(C.byref(desc), C.byref(n)), "reduce_workspace_bytes")
+    return int(n.value)
+
+
+def reduce_run(desc: ReduceDesc, src, dst, workspace=None, stream: int = 0) -> None:
+    """Asynchronous launch on device buffers (torch CUDA tensors or raw addresses)."""
+    ws_bytes = 0
+    if workspace is not None and hasattr(workspace, "numel"):
+        ws_bytes = workspace.numel() * workspace.element_size()
+    rc = lib().frisk_b200_reduce_run(C.byref(desc), _ptr(src), _ptr(dst), _ptr(workspace), ws_bytes,
+                                     stream or None)
+    _check(rc, "reduce_run")
+
+
+def reduce_host(src: np.ndarray, dst: np.ndarray, dim: int, dtype: int, kind: str, clear: bool = True) -> None:
+    """Synchronous ``frisk.reduce`` on host arrays of raw storage (copies in, runs, copies dst back)."""
+    desc = reduce_desc(src.shape, dim, dtype, kind, clear)
+    if not (src.flags.c_contiguous and dst.flags.c_contiguous):
+        raise ValueError("reduce_host wants C-contiguous arrays")
+    if dst.size != desc.outer * desc.inner or src.dtype != dst.dtype:
+        raise ValueError("destination must have the source's shape without the reduced dimension and its type")
+    _check(lib().frisk_b200_reduce_run_host(C.byref(desc), _ptr(src), _ptr(dst)), "reduce_run_host")
 
 
 def shard_rows(M: int, nranks: int, rank: int) -> tuple[int, int]:

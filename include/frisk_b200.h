@@ -177,6 +177,59 @@ const char* frisk_b200_last_error(void);
  */
 int frisk_b200_shard_rows(int64_t M, int nranks, int rank, int64_t* row0, int64_t* rows);
 
+/* ---- frisk.reduce on whole buffers ------------------------------------------------------ */
+/*
+ * frisk.reduce (include/Dialect/Frisk/IR/FriskOps.td:413-443; builder ffi/ir.cpp:469-471):
+ * `dst = (clear ? identity : dst) (op) reduce_op over dimension `dim` of src`, kind "add", "mul",
+ * "min" or "max" (verifier, lib/Dialect/Frisk/IR/FriskOps.cpp:1734-1767: the destination has the
+ * source's shape without `dim` and the same element type).  The reference has no lowering for
+ * it; the sketches it is written for are row maxima and row sums of an online softmax
+ * (tmp/ir.mlir:21-78).  A row-major source of any rank is [outer, extent, inner] around the
+ * reduced dimension, the destination [outer, inner].  Arithmetic: elements decoded to fp32, fp32
+ * accumulation (a fixed order: the same result on every run), one round-to-nearest-even cast at
+ * the end; min and max are exact and skip NaN operands (fminf / fmaxf from the identity: a line
+ * of nothing but NaN, like an empty one, gives +inf for min and -inf for max).
+ */
+typedef enum {
+  FRISK_REDUCE_ADD = 0,
+  FRISK_REDUCE_MUL = 1,
+  FRISK_REDUCE_MIN = 2,
+  FRISK_REDUCE_MAX = 3
+} frisk_reduce_kind;
+
+typedef struct frisk_reduce_desc {
+  int64_t outer, extent, inner; /* product of the dimensions before / at / after `dim`       */
+  int32_t dtype;                /* FRISK_DT_F32, _F16 or _BF16, for src and dst              */
+  int32_t kind;                 /* frisk_reduce_kind                                         */
+  int32_t clear;                /* 1: dst is overwritten; 0: dst is folded into the result   */
+  int32_t device;               /* CUDA ordinal, -1 = current                                */
+} frisk_reduce_desc;
+
+typedef struct frisk_reduce_info {
+  int32_t lines;       /* 1: the reduced dimension is the innermost one (a warp per line)    */
+  int32_t vector;      /* elements per 16-byte load along the contiguous dimension, or 1     */
+  int32_t chunks;      /* pieces the reduced dimension is cut into (> 1: two launches)       */
+  int32_t launches;
+  int64_t chunk_len;
+  int64_t ctas;        /* grid of the first launch                                           */
+  size_t workspace_bytes;
+} frisk_reduce_info;
+
+/* How the library would run `desc` for operands at addresses with the given alignment
+ * (`src_align16` = 1 when src is 16-byte aligned).  Pure host arithmetic. */
+int frisk_b200_reduce_info(const frisk_reduce_desc* desc, int src_align16, frisk_reduce_info* out);
+/* Bytes of device workspace frisk_b200_reduce_run needs (0 for most shapes). */
+int frisk_b200_reduce_workspace_bytes(const frisk_reduce_desc* desc, size_t* out);
+/*
+ * Stream-ordered, asynchronous.  src, dst, workspace are device pointers aligned to the element
+ * size (16-byte alignment enables vector loads; any extent and inner size is accepted).
+ * Returns FRISK_ERR_WORKSPACE if ws_bytes is below frisk_b200_reduce_workspace_bytes.
+ */
+int frisk_b200_reduce_run(const frisk_reduce_desc* desc, const void* src, void* dst, void* workspace,
+                          size_t ws_bytes, void* stream);
+/* The same on HOST buffers: allocates, copies in, runs, copies dst back, synchronises. */
+int frisk_b200_reduce_run_host(const frisk_reduce_desc* desc, const void* src, void* dst);
+
 /* ---- layout mapping ------------------------------------------------------------------- */
 /*
  * A shared-memory operand layout as the reference's GemmOp::inferLayout chooses it

@@ -130,3 +130,24 @@ def abs_dot(w: W.GemmWorkload, rows: Optional[np.ndarray] = None) -> np.ndarray:
         c0 = np.abs(W.decode(w.C0, w.c_type).astype(np.float64))
         s = s + (c0[rows] if rows is not None else c0)
     return s
+
+
+def ref_reduce(src: np.ndarray, dim: int, dtype: int, kind: str, clear: bool = True,
+               dst0: Optional[np.ndarray] = None) -> tuple[np.ndarray, np.ndarray]:
+    """``frisk.reduce`` restated (op: include/Dialect/Frisk/IR/FriskOps.td:413-443; shape and kind
+    rules: lib/Dialect/Frisk/IR/FriskOps.cpp:1734-1767): dst = (clear ? identity : dst) (op) the
+    fold of `src` (raw storage bits) over `dim`, computed in float64 on the exactly decoded
+    elements.  Returns (result as float64 without the final cast, sum of magnitudes folded --
+    the scale an error of a sum is measured against).  min / max skip NaN like fminf / fmaxf
+    folded from the identity.
+    PARITY UNPINNED: the reference never executes this op and holds no expected values for it."""
+    x = W.decode(np.asarray(src), dtype).astype(np.float64)
+    fold = {"add": np.add, "mul": np.multiply, "min": np.fmin, "max": np.fmax}[kind]
+    ident = {"add": 0.0, "mul": 1.0, "min": np.inf, "max": -np.inf}[kind]
+    out = fold.reduce(x, axis=dim, initial=ident)
+    mag = np.abs(x).sum(axis=dim) if kind == "add" else np.abs(out)
+    if not clear:
+        d0 = W.decode(np.asarray(dst0), dtype).astype(np.float64).reshape(out.shape)
+        out = fold(d0, out)
+        mag = mag + np.abs(d0) if kind == "add" else np.abs(out)
+    return out, mag

@@ -191,3 +191,46 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
             R.gemm_host(W.make_workload("cfg1", 8, 8, 8))
     finally:
         monkeypatch.undo()
+
+
+def test_reduce_plans_cover_the_reduced_dimension_exactly_once():
+    """frisk_b200_reduce_info is host arithmetic (it assumes 148 SMs when no device is visible):
+    the pieces tile the reduced dimension, the workspace holds one fp32 per piece and output
+    element, and the workspace query covers both alignments of the source."""
+    rng = np.random.default_rng(0)
+    shapes = [((8192, 8192), 1), ((8192, 8192), 0), ((1, 1 << 26), 1), ((4, 8, 16), 1), ((0, 8), 1),
+              ((5, 0), 1), ((3, 7, 0), 1)]
+    for _ in range(200):
+        rank = int(rng.integers(1, 4))
+        shape = tuple(int(rng.choice([1, 2, 3, 5, 8, 16, 33, 100, 1000, 4096, 70001])) for _ in range(rank))
+        if np.prod(shape, dtype=np.int64) > 1 << 34:
+            continue
+        shapes.append((shape, int(rng.integers(0, rank))))
+    for shape, dim in shapes:
+        for dtype in (W.F32, W.F16, W.BF16):
+            d = R.reduce_desc(shape, dim, dtype, "max")
+            need = R.reduce_workspace_bytes(d)
+            for aligned in (True, False):
+                info = R.reduce_info(d, aligned)
+                empty = d.outer == 0 or d.inner == 0
+                assert info["launches"] == (0 if empty else 2 if info["chunks"] > 1 else 1)
+                assert info["lines"] == int(d.inner == 1)
+                assert info["chunks"] >= 1 and info["chunk_len"] >= 1
+                if not empty:
+                    assert info["chunks"] * info["chunk_len"] >= d.extent
+                    assert (info["chunks"] - 1) * info["chunk_len"] < max(d.extent, 1)
+                    assert info["ctas"] >= 1
+                want_ws = d.outer * info["chunks"] * d.inner * 4 if info["chunks"] > 1 else 0
+                assert info["workspace_bytes"] == want_ws <= need
+                if not aligned and d.inner != 1:
+                    assert info["vector"] == 1
+    assert R.reduce_info(R.reduce_desc((8192, 8192), 1, W.F16, "max")) == dict(
+        lines=1, vector=8, chunks=1, launches=1, chunk_len=8192, ctas=1024, workspace_bytes=0)
+    with pytest.raises(R.FriskError) as e:
+        R.reduce_info(R.reduce_desc((4, 4), 1, W.E4M3, "add"))
+    assert e.value.code == -2
+    bad = R.reduce_desc((4, 4), 1, W.F32, "add")
+    bad.kind = 9
+    with pytest.raises(R.FriskError) as e:
+        R.reduce_info(bad)
+    assert e.value.code == -1

@@ -209,6 +209,64 @@ def roofline_for(name, M, N, K, ms, peaks, sustained):
             "peak_source": peaks["source"] + (" (sustained)" if sustained and unit == "TFLOP/s" else " (burst)" if unit == "TFLOP/s" else "")}
 
 
+REDUCE_CASES = (
+    # name, shape, dim, element type, kind: the two reduces of the reference's online-softmax sketch
+    # (tmp/ir.mlir:21-78: row maximum of fp16 activations, row sum of fp32 exponentials) and the
+    # same matrix reduced the other way
+    ("row_max_f16", (8192, 8192), 1, W.F16, "max"),
+    ("row_sum_f32", (8192, 8192), 1, W.F32, "add"),
+    ("col_min_f16", (8192, 8192), 0, W.F16, "min"),
+)
+
+
+def time_reduce(torch, R, dev, steps, warmup, peaks, with_cpu):
+    """frisk.reduce on whole buffers: GB/s of algorithmic bytes (source read once + destination
+    written) against the measured copy bandwidth.  Three source copies are rotated so that no
+    launch finds its input in L2."""
+    out = {}
+    tdt = {W.F16: torch.float16, W.F32: torch.float32}
+    for name, shape, dim, dtype, kind in REDUCE_CASES:
+        n = shape[0] * shape[1]
+        g = torch.Generator(device=dev).manual_seed(17)
+        srcs = [torch.randn(n, generator=g, device=dev, dtype=torch.float32).to(tdt[dtype]) for _ in range(3)]
+        desc = R.reduce_desc(shape, dim, dtype, kind)
+        info = R.reduce_info(desc)
+        dst = torch.empty(desc.outer * desc.inner, device=dev, dtype=tdt[dtype])
+        ws = torch.empty(max(R.reduce_workspace_bytes(desc), 16), dtype=torch.uint8, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        for i in range(max(warmup, 3)):
+            R.reduce_run(desc, srcs[i % 3], dst, ws, stream)
+        torch.cuda.synchronize()
+        k = max(steps, 30)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(k):
+            R.reduce_run(desc, srcs[i % 3], dst, ws, stream)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / k
+        alg = (n + desc.outer * desc.inner) * W.ELEM_SIZE[dtype]
+        achieved = alg / (ms * 1e-3) / 1e9
+        entry = {"shape": list(shape), "dim": dim, "dtype": W.DTYPE_NAMES[dtype], "kind": kind,
+                 "ms": round(ms, 5), "launches_per_step": info["launches"], "ctas": info["ctas"],
+                 "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                              "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                              "peak_source": peaks["source"]},
+                 "l2": "three sources rotated (0.4 - 0.8 GB)"}
+        if with_cpu:  # the float64 restatement on a row sample, beside the kernel
+            from oracle import ref
+            rows = 256
+            sample = srcs[0].view(*shape)[:rows].cpu().numpy()
+            t0 = time.perf_counter()
+            ref.ref_reduce(sample, dim, dtype, kind)
+            dt = time.perf_counter() - t0
+            entry["cpu_baseline"] = {"value": round(sample.nbytes / dt / 1e9, 3), "unit": "GB/s", "cores": 1,
+                                     "kind": "port", "sample": f"{rows} rows of the source, {dt * 1e3:.0f} ms"}
+        out[name] = entry
+        del srcs, dst, ws
+    return out
+
+
 def host_threads() -> int:
     """All cores this process may use (torchrun sets OMP_NUM_THREADS=1; the CPU legs ignore that)."""
     try:
@@ -485,6 +543,7 @@ def main():
                              "launches_per_step": oinfo["launches"], "roofline": r,
                              "l2": l2_note}
         line["other_configs"] = others
+        line["reduce"] = time_reduce(torch, R, dev, args.steps, args.warmup, peaks, not args.no_cpu)
 
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(name)

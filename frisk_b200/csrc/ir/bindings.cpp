@@ -399,6 +399,10 @@ void initOperation(py::module_& m) {
       .def("to_gemm_op", [](PyOperation& o) -> py::object {  // addition (GemmOp.from_operation)
         if (o.op->name == "frisk.gemm") return py::cast(wrapOp<PyGemm>(o.op));
         return py::none();
+      })
+      .def("to_reduce_op", [](PyOperation& o) -> py::object {  // addition
+        if (o.op->name == "frisk.reduce") return py::cast(wrapOp<PyReduce>(o.op));
+        return py::none();
       });
 }
 
@@ -1173,6 +1177,8 @@ void initFrisk(py::module_ m) {
       .def("get_src_memref", [](PyReduce& r) { return castValue(r.op->operands[0]); })
       .def("get_dst_memref", [](PyReduce& r) { return castValue(r.op->operands[1]); })
       .def("get_reduce_dim", [](PyReduce& r) { return r.op->intAttr("dim"); })
+      .def("get_kind", [](PyReduce& r) { return std::get<std::string>(*r.op->attr("kind")); })  // addition
+      .def("get_clear", [](PyReduce& r) { return r.op->intAttr("clear") != 0; })              // addition
       // addition: ReduceOp::inferLayout (FriskOps_Reduce.cpp:214-357).  Returns the destination's
       // #frisk.layout, or None when there is nothing to infer; ValueError on a conflict.
       .def("infer_layout", [](PyReduce& r, py::object src, py::object existing) -> py::object {

@@ -43,9 +43,12 @@ int log2_ceil(int64_t v) {
 // are that wide (1 KiB contiguous per row and CTA) so that four row groups share a CTA; the second
 // launch reads partial results that are still in L2 and prefers many small CTAs (TX <= 32).
 // A short reduced dimension gets fewer TY rows and the threads go to the contiguous side.
-void columns_shape(int64_t inner, int64_t extent, int vec, bool first, int* tx_log2, int64_t* xblocks) {
+void columns_shape(int64_t inner, int64_t extent, int vec, bool first, bool plenty, int* tx_log2,
+                   int64_t* xblocks) {
   const int64_t ivecs = inner / vec;
-  const int ty_log2 = std::min(first ? 2 : 3, log2_ceil(std::max<int64_t>(extent, 1)));
+  // `plenty`: even CTAs that span 256 vectors of a row fill the device; then a CTA reads 4 KiB
+  // contiguous per row and keeps its four loads per thread in flight over four rows.
+  const int ty_log2 = plenty ? 0 : std::min(first ? 2 : 3, log2_ceil(std::max<int64_t>(extent, 1)));
   *tx_log2 = std::min(log2_ceil(ivecs), log2_ceil(kThreads) - ty_log2);
   *xblocks = ceil_div(ivecs, int64_t(1) << *tx_log2);
 }
@@ -55,7 +58,8 @@ int lanes_for(int64_t piece, int vec) {
   return std::min(5, log2_ceil(std::max<int64_t>(1, ceil_div(ceil_div(piece, vec), 4))));
 }
 
-int make_plan(const frisk_reduce_desc& d, bool src_align16, int sms, Plan* out) {
+// `slots`: CTAs the device holds at once for the first-launch kernel (SMs x CTAs per SM).
+int make_plan(const frisk_reduce_desc& d, bool src_align16, int64_t slots, Plan* out) {
   const int es = elem_bytes(d.dtype);
   if (d.outer < 0 || d.extent < 0 || d.inner < 0 || d.kind < 0 || d.kind > 3) {
     frisk_internal_set_error("reduce: negative size or unknown kind");
@@ -75,7 +79,7 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int sms, Plan* out) 
   if (p.lines) {
     // A warp per line.  With fewer lines than about half the warps the device holds, cut the
     // lines so that every SM has work; pieces stay at least 4096 elements long.
-    const int64_t want = (int64_t)sms * 32;
+    const int64_t want = slots * kWarpsPerCta;
     p.vec = 16 / es;
     if (d.outer * 2 < want && d.extent >= 2 * 4096) {
       int64_t chunks = std::min(ceil_div(want, d.outer), d.extent / 4096);
@@ -88,9 +92,10 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int sms, Plan* out) 
     p.ctas2 = p.chunks > 1 ? ceil_div(d.outer << p.lanes_log2_2, kThreads) : 0;
   } else {
     p.vec = (src_align16 && (d.inner * es) % 16 == 0) ? 16 / es : 1;
-    columns_shape(d.inner, d.extent, p.vec, true, &p.tx_log2, &p.xblocks);
+    const bool plenty = d.outer * ceil_div(d.inner / p.vec, kThreads) * 2 >= slots;
+    columns_shape(d.inner, d.extent, p.vec, true, plenty, &p.tx_log2, &p.xblocks);
     const int64_t ny = kThreads >> p.tx_log2;
-    const int64_t base = d.outer * p.xblocks, want = (int64_t)sms * 8;
+    const int64_t base = d.outer * p.xblocks, want = slots;
     if (base * 2 < want && d.extent >= 2 * 8 * ny) {
       int64_t chunks = std::min(std::max<int64_t>(1, want / base), d.extent / (8 * ny));  // one wave of CTAs
       p.chunk_len = ceil_div(ceil_div(d.extent, chunks), ny) * ny;
@@ -99,7 +104,7 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int sms, Plan* out) 
     p.ctas = base * p.chunks;
     if (p.chunks > 1) {
       p.vec2 = d.inner % 4 == 0 ? 4 : 1;  // the workspace is 256-byte aligned
-      columns_shape(d.inner, p.chunks, p.vec2, false, &p.tx_log2_2, &p.xblocks2);
+      columns_shape(d.inner, p.chunks, p.vec2, false, false, &p.tx_log2_2, &p.xblocks2);
       p.ctas2 = d.outer * p.xblocks2;
     }
   }
@@ -113,18 +118,28 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int sms, Plan* out) 
 }
 
 template <typename TIn, typename TOut, int KIND, bool FINAL>
-cudaError_t launch(bool lines, int vec, const void* src, void* dst, const Params& p, int64_t ctas,
-                   cudaStream_t st) {
+const void* kernel_of(bool lines, int vec) {
   using namespace frisk_reduce;
-  const TIn* s = static_cast<const TIn*>(src);
-  TOut* d = static_cast<TOut*>(dst);
-  if (lines)
-    reduce_lines_kernel<TIn, TOut, KIND, FINAL><<<(unsigned)ctas, kThreads, 0, st>>>(s, d, p);
-  else if (vec > 1)
-    reduce_columns_kernel<TIn, TOut, KIND, FINAL, Vec<TIn>::N><<<(unsigned)ctas, kThreads, 0, st>>>(s, d, p);
-  else
-    reduce_columns_kernel<TIn, TOut, KIND, FINAL, 1><<<(unsigned)ctas, kThreads, 0, st>>>(s, d, p);
-  return cudaGetLastError();
+  if (lines) return reinterpret_cast<const void*>(&reduce_lines_kernel<TIn, TOut, KIND, FINAL>);
+  if (vec > 1) return reinterpret_cast<const void*>(&reduce_columns_kernel<TIn, TOut, KIND, FINAL, Vec<TIn>::N>);
+  return reinterpret_cast<const void*>(&reduce_columns_kernel<TIn, TOut, KIND, FINAL, 1>);
+}
+
+// `dependent`: a programmatic dependent launch (it follows the first launch of the same reduce).
+cudaError_t launch(const void* kernel, const void* src, void* dst, const Params& p, int64_t ctas, bool dependent,
+                   cudaStream_t st) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)ctas);
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  Params pp = p;
+  void* args[] = {&src, &dst, &pp};
+  return cudaLaunchKernelExC(&cfg, kernel, args);
 }
 
 template <typename T, int KIND>
@@ -140,8 +155,9 @@ cudaError_t run_typed(const frisk_reduce_desc& d, const Plan& pl, const void* sr
   p.lanes_log2 = pl.lanes_log2;
   p.tx_log2 = pl.tx_log2;
   p.xblocks = pl.xblocks;
-  if (pl.chunks == 1) return launch<T, T, KIND, true>(pl.lines, pl.vec, src, dst, p, pl.ctas, st);
-  cudaError_t e = launch<T, float, KIND, false>(pl.lines, pl.vec, src, ws, p, pl.ctas, st);
+  if (pl.chunks == 1)
+    return launch(kernel_of<T, T, KIND, true>(pl.lines, pl.vec), src, dst, p, pl.ctas, false, st);
+  cudaError_t e = launch(kernel_of<T, float, KIND, false>(pl.lines, pl.vec), src, ws, p, pl.ctas, false, st);
   if (e != cudaSuccess) return e;
   Params q = p;  // the pieces are the reduced dimension of the second launch
   q.extent = pl.chunks;
@@ -150,7 +166,18 @@ cudaError_t run_typed(const frisk_reduce_desc& d, const Plan& pl, const void* sr
   q.lanes_log2 = pl.lanes_log2_2;
   q.tx_log2 = pl.tx_log2_2;
   q.xblocks = pl.xblocks2;
-  return launch<float, T, KIND, true>(pl.lines, pl.vec2, ws, dst, q, pl.ctas2, st);
+  return launch(kernel_of<float, T, KIND, true>(pl.lines, pl.vec2), ws, dst, q, pl.ctas2, true, st);
+}
+
+// The first-launch kernel of a shape that goes through the workspace, for the occupancy query.
+template <typename T>
+const void* partial_kernel(int kind, bool lines, int vec) {
+  switch (kind) {
+    case FRISK_REDUCE_ADD: return kernel_of<T, float, 0, false>(lines, vec);
+    case FRISK_REDUCE_MUL: return kernel_of<T, float, 1, false>(lines, vec);
+    case FRISK_REDUCE_MIN: return kernel_of<T, float, 2, false>(lines, vec);
+    default: return kernel_of<T, float, 3, false>(lines, vec);
+  }
 }
 
 template <typename T>
@@ -180,23 +207,43 @@ int sm_count_of(int device, int* sms) {
   return FRISK_OK;
 }
 
+// CTAs of the first-launch kernel that fit the device at once.  The column cut depends on the
+// vector width, which depends on the alignment; the two variants use about the same registers, so
+// the query is made for the one the alignment selects.
+int slots_for(const frisk_reduce_desc& d, bool aligned, int64_t* slots) {
+  int sms = 0;
+  if (int rc = sm_count_of(d.device, &sms)) return rc;
+  const int es = elem_bytes(d.dtype);
+  const bool lines = d.inner == 1;
+  const int vec = es && (lines || (aligned && (d.inner * es) % 16 == 0)) ? 16 / es : 1;
+  const void* k = d.dtype == FRISK_DT_F32   ? partial_kernel<float>(d.kind, lines, vec)
+                  : d.dtype == FRISK_DT_F16 ? partial_kernel<__half>(d.kind, lines, vec)
+                                            : partial_kernel<__nv_bfloat16>(d.kind, lines, vec);
+  int per_sm = 0;
+  cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kThreads, 0);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+  *slots = (int64_t)sms * std::max(per_sm, 1);
+  return FRISK_OK;
+}
+
 }  // namespace
 
 extern "C" {
 
 int frisk_b200_reduce_info(const frisk_reduce_desc* desc, int src_align16, frisk_reduce_info* out) {
   if (!desc || !out) return FRISK_ERR_INVALID_ARGUMENT;
-  // The cut depends on the SM count; without a device the B200's 148 is assumed so that the
-  // arithmetic can be inspected anywhere.
-  int sms = 148;
+  // The cut depends on how many CTAs the device holds; without a device a B200's 148 SMs with six
+  // CTAs each are assumed so that the arithmetic can be inspected anywhere.
+  int64_t slots = 148 * 6;
   int count = 0;
   if (cudaGetDeviceCount(&count) == cudaSuccess && count > 0) {
-    if (int rc = sm_count_of(desc->device, &sms)) return rc;
+    if (elem_bytes(desc->dtype) && desc->kind >= 0 && desc->kind <= 3)
+      if (int rc = slots_for(*desc, src_align16 != 0, &slots)) return rc;
   } else {
     (void)cudaGetLastError();
   }
   Plan p;
-  if (int rc = make_plan(*desc, src_align16 != 0, sms, &p)) return rc;
+  if (int rc = make_plan(*desc, src_align16 != 0, slots, &p)) return rc;
   out->lines = p.lines;
   out->vector = p.vec;
   out->chunks = (int32_t)p.chunks;
@@ -225,11 +272,12 @@ int frisk_b200_reduce_run(const frisk_reduce_desc* desc, const void* src, void* 
                           size_t ws_bytes, void* stream) {
   if (!desc) return FRISK_ERR_INVALID_ARGUMENT;
   const int es = elem_bytes(desc->dtype);
-  int sms = 0;
-  if (int rc = sm_count_of(desc->device, &sms)) return rc;
   const bool aligned = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  int64_t slots = 1;
+  if (es && desc->kind >= 0 && desc->kind <= 3)
+    if (int rc = slots_for(*desc, aligned, &slots)) return rc;
   Plan p;
-  if (int rc = make_plan(*desc, aligned, sms, &p)) return rc;
+  if (int rc = make_plan(*desc, aligned, slots, &p)) return rc;
   if (desc->outer == 0 || desc->inner == 0) return FRISK_OK;
   if (!dst || (!src && desc->extent > 0)) {
     frisk_internal_set_error("reduce: null src or dst");

@@ -32,6 +32,14 @@ struct Params {
   int64_t xblocks;    // columns kernel: CTAs along the contiguous dimension
 };
 
+// The second launch of a two-launch reduce is a programmatic dependent launch: its CTAs may be
+// scheduled while the first kernel drains, and wait here until that kernel's writes are visible.
+// In a kernel launched the ordinary way both instructions do nothing.
+__device__ __forceinline__ void dependent_launch_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 template <int KIND> struct Op;
 template <> struct Op<0> {
   static __device__ __forceinline__ float identity() { return 0.f; }
@@ -158,11 +166,12 @@ template <> struct Fold<__nv_bfloat16, 3> : FoldBf16<true> {};
 // A group of L = 1 << lanes_log2 lanes per (line, piece): a whole warp for long lines, fewer
 // lanes for short ones so that a warp covers several consecutive lines.
 template <typename TIn, typename TOut, int KIND, bool FINAL>
-__global__ void __launch_bounds__(kThreads, 8) reduce_lines_kernel(const TIn* __restrict__ src,
+__global__ void __launch_bounds__(kThreads) reduce_lines_kernel(const TIn* __restrict__ src,
                                                                 TOut* __restrict__ dst, Params p) {
   using O = Op<KIND>;
   using F = Fold<TIn, KIND>;
   constexpr int N = Vec<TIn>::N;
+  dependent_launch_prologue();
   const int L = 1 << p.lanes_log2;
   const int64_t unit = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> p.lanes_log2;
   const int sub = threadIdx.x & (L - 1);
@@ -210,10 +219,11 @@ __global__ void __launch_bounds__(kThreads, 8) reduce_lines_kernel(const TIn* __
 // VEC consecutive columns per thread (one 16-byte load when VEC > 1, which needs inner % VEC == 0
 // and an aligned base).  grid.x = outer * chunks * xblocks.
 template <typename TIn, typename TOut, int KIND, bool FINAL, int VEC>
-__global__ void __launch_bounds__(kThreads, 8) reduce_columns_kernel(const TIn* __restrict__ src,
+__global__ void __launch_bounds__(kThreads) reduce_columns_kernel(const TIn* __restrict__ src,
                                                                   TOut* __restrict__ dst, Params p) {
   using O = Op<KIND>;
   __shared__ float fold[kThreads * VEC];
+  dependent_launch_prologue();
   const int tx = threadIdx.x & ((1 << p.tx_log2) - 1), ty = threadIdx.x >> p.tx_log2;
   const int ny = kThreads >> p.tx_log2;
   int64_t b = blockIdx.x;

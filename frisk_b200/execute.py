@@ -1,6 +1,11 @@
-"""Running the ``frisk.gemm`` ops of a module: the step the reference stops short of.
+"""Running the ``frisk.gemm`` and ``frisk.reduce`` ops of a module: the step the reference stops
+short of.
 
-Two forms are executed, both through libfrisk_b200 on the buffers bound to the kernel arguments:
+Three forms are executed, all through libfrisk_b200 on the buffers bound to the kernel arguments:
+
+* a ``frisk.reduce`` whose source and destination are kernel arguments in the GLOBAL memory space:
+  one whole-buffer reduce per op, in program order with the gemms (so a gemm followed by a row
+  maximum of its result runs as written);
 
 * a ``frisk.gemm`` whose operands are kernel arguments in the GLOBAL memory space (what the
   reference's flagship script emits: test/python/bind_test.py:53, captured in tmp/log_11_18:12):
@@ -43,6 +48,17 @@ class GemmCall:
     arg_scale_b: Optional[int] = None
 
 
+@dataclass
+class ReduceCall:
+    shape: tuple
+    dim: int
+    dtype: int
+    kind: str
+    clear: bool
+    arg_src: int
+    arg_dst: int
+
+
 def _dtype_of(ty) -> int:
     s = str(ty)
     table = {"f32": W.F32, "f16": W.F16, "bf16": W.BF16, "f8E4M3FN": W.E4M3}
@@ -51,14 +67,29 @@ def _dtype_of(ty) -> int:
     return table[s]
 
 
-def find_gemms(module, kernel_name: str) -> List[GemmCall]:
+def find_gemms(module, kernel_name: str) -> list:
+    """The executable ops of the kernel in program order: GemmCall and ReduceCall records."""
     kernel = module.get_kernel(kernel_name)
     if kernel is None:
         raise KeyError(f"no frisk.kernel named {kernel_name!r} in the module")
     args = {kernel.arg(i).id(): i for i in range(kernel.get_num_arguments())}
-    calls: List[GemmCall] = []
+    calls: list = []
 
     def visit(op):
+        r = op.to_reduce_op()
+        if r is not None:
+            src, dst = r.get_src_memref(), r.get_dst_memref()
+            for name, v in (("source", src), ("destination", dst)):
+                if v.id() not in args or v.get_type().get_memory_space() != ir.MemorySpace.GLOBAL:
+                    raise R.FriskError(-2, f"frisk.reduce {name} is not a kernel argument in GLOBAL memory: "
+                                           "only whole-buffer reduces are executed")
+            ty = src.get_type()
+            dtype = _dtype_of(ty.get_element_ty())
+            if dtype == W.E4M3:
+                raise R.FriskError(-2, "frisk.reduce has no kernel for 8-bit floats")
+            calls.append(ReduceCall(tuple(ty.get_shape()), r.get_reduce_dim(), dtype, r.get_kind(),
+                                    r.get_clear(), args[src.id()], args[dst.id()]))
+            return
         g = op.to_gemm_op()
         if g is None:
             return
@@ -111,7 +142,7 @@ def parse_module(text: str):
 
 def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Optional[np.ndarray] = None,
         scale_b: Optional[np.ndarray] = None, plan_options: Optional[Dict] = None) -> None:
-    """Executes every ``frisk.gemm`` of the kernel (a module, or its text) on host buffers (one per kernel argument, raw
+    """Executes every ``frisk.gemm`` and ``frisk.reduce`` of the kernel (a module, or its text) on host buffers (one per kernel argument, raw
     storage bits in the memory order the op's trans flags state).  C buffers are updated in
     place.  Raises when the CUDA library or a device is missing: there is no CPU path."""
     if isinstance(module, str):  # the textual form
@@ -119,6 +150,15 @@ def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Opt
     if not module.verify():
         raise R.FriskError(-1, "module does not verify: " + module.verify_message())
     for call in find_gemms(module, kernel_name):
+        if isinstance(call, ReduceCall):
+            src = np.ascontiguousarray(buffers[call.arg_src])
+            dst = buffers[call.arg_dst]
+            if not dst.flags["C_CONTIGUOUS"]:
+                raise ValueError("the destination buffer must be C-contiguous (it is written in place)")
+            if tuple(src.shape) != call.shape:
+                raise ValueError(f"the source buffer has shape {tuple(src.shape)}, the op says {call.shape}")
+            R.reduce_host(src, dst, call.dim, call.dtype, call.kind, call.clear)
+            continue
         sa, sb = scale_a, scale_b
         if sa is None and call.arg_scale_a is not None:  # scale vectors bound as kernel arguments
             sa = np.ascontiguousarray(buffers[call.arg_scale_a], dtype=np.float32)

@@ -30,7 +30,7 @@ def test_modules_printed_by_the_reference_round_trip(name, text):
 
 def test_reference_flagship_text_yields_its_gemm():
     text = open(os.path.join(GOLDEN, "bind_test_module.mlir")).read()
-    (call,) = F.find_gemms(F.parse_module(text), "test_gemm")
+    _reduce, call = F.find_gemms(F.parse_module(text), "test_gemm")
     assert (call.M, call.N, call.K, call.ab_type) == (4096, 4096, 4096, W.F16)
     assert (call.arg_a, call.arg_b, call.arg_c) == (0, 1, 2) and not call.clear_accum
 
@@ -63,8 +63,10 @@ def test_other_constructs_round_trip():
 }"""
     m = F.parse_module(text)
     assert str(m).strip() == text
-    (call,) = F.find_gemms(m, "k")
+    call, red = F.find_gemms(m, "k")
     assert (call.arg_scale_a, call.arg_scale_b, call.transB, call.clear_accum) == (3, 4, True, True)
+    assert (red.kind, red.dim, red.clear, red.arg_src, red.arg_dst) == ("sum", 0, False, 2, 4)
+    assert not m.verify()  # "sum" is not a reduce kind and the element types differ: run() would refuse
 
 
 @pytest.mark.parametrize("text,what", [

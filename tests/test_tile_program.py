@@ -61,8 +61,9 @@ def test_reference_flagship_module_is_still_a_whole_problem_gemm():
     # bind_test.py's module (gemm on the kernel arguments inside for / block) is not a tile program
     from test_ir_builder import build_bind_test_module  # the reference script's program
     m = build_bind_test_module()[0]
-    (call,) = F.find_gemms(m, "test_gemm")
+    red, call = F.find_gemms(m, "test_gemm")  # the script also reduces its first argument
     assert (call.M, call.N, call.K) == (4096, 4096, 4096)
+    assert (red.shape, red.dim, red.kind, red.clear, red.arg_src, red.arg_dst) == ((4096, 4096), 1, "max", True, 0, 3)
     with pytest.raises(ValueError, match="not a tiled matrix product"):
         F.ir.frisk.lift_tiled_gemm(m.get_kernel("test_gemm"))
 
@@ -90,3 +91,47 @@ def test_lifted_program_runs_and_matches_the_oracle(dims, tile, dtype, acc):
     assert ok, f"{metric} = {err}"
     # one GEMM over the arguments: the same bits as planning that GEMM directly
     assert np.array_equal(C, R.gemm_host(w))
+
+
+def gemm_then_row_max(dtype="fp16", dims=(16, 32, 64)):
+    """A kernel that multiplies and then takes the row maxima of the product: the two ops of the
+    reference's attention sketches (tmp/ir.mlir:80-158) on whole buffers."""
+    M, N, K = dims
+    h = F.create_session()
+    tys = [h.memref_type((M, K), dtype), h.memref_type((K, N), dtype), h.memref_type((M, N), dtype),
+           h.memref_type((M,), dtype)]
+    _, entry = h.new_kernel("scores_max", tys)
+    h.create_gemm(entry.get_argument(0), entry.get_argument(1), entry.get_argument(2), clear_accum=True)
+    h.builder.create_reduce_op(entry.get_argument(2), entry.get_argument(3), "max", 1, True)
+    return h
+
+
+def test_reduce_ops_on_kernel_arguments_are_found_in_program_order():
+    from frisk_b200 import execute as X
+    h = gemm_then_row_max()
+    assert h.module.verify()
+    for module in (h.module, F.parse_module(str(h.module))):  # as built, and read back from text
+        gemm, red = X.find_gemms(module, "scores_max")
+        assert isinstance(gemm, X.GemmCall) and (gemm.arg_a, gemm.arg_b, gemm.arg_c) == (0, 1, 2)
+        assert red == X.ReduceCall((16, 32), 1, W.F16, "max", True, 2, 3)
+    # a reduce of a buffer that is not a kernel argument is refused, not guessed at
+    h = F.create_session()
+    _, entry = h.new_kernel("local_reduce", [h.memref_type((8,), "fp16")])
+    frag = h.alloc_buffer((8, 8), "fp16", space=F.MemorySpace.LOCAL)
+    h.builder.create_reduce_op(frag, entry.get_argument(0), "add", 1, True)
+    with pytest.raises(R.FriskError, match="frisk.reduce source is not a kernel argument"):
+        X.find_gemms(h.module, "local_reduce")
+
+
+@pytest.mark.gpu
+def test_gemm_followed_by_reduce_runs_as_written():
+    from oracle import ref
+    h = gemm_then_row_max("bf16", (64, 512, 256))
+    w = W.make_workload("cfg5", 64, 512, 256)
+    c = np.zeros((64, 512), np.uint16)
+    rowmax = np.zeros((64,), np.uint16)
+    F.run(h.module, "scores_max", [w.A, w.B, c, rowmax])
+    ok, err, metric = W.check(W.decode(c, W.BF16), ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
+    assert ok, (metric, err)
+    want, _ = ref.ref_reduce(c, 1, W.BF16, "max")  # exact: the maximum of the stored values
+    assert np.array_equal(W.decode(rowmax, W.BF16).astype(np.float64), want)

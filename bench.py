@@ -234,10 +234,10 @@ def time_reduce(torch, R, dev, steps, warmup, peaks, with_cpu):
         dst = torch.empty(desc.outer * desc.inner, device=dev, dtype=tdt[dtype])
         ws = torch.empty(max(R.reduce_workspace_bytes(desc), 16), dtype=torch.uint8, device=dev)
         stream = torch.cuda.current_stream().cuda_stream
-        for i in range(max(warmup, 3)):
+        for i in range(warmup):
             R.reduce_run(desc, srcs[i % 3], dst, ws, stream)
         torch.cuda.synchronize()
-        k = max(steps, 30)
+        k = steps
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(k):
@@ -361,9 +361,13 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
+    ap.add_argument("--reduce-only", action="store_true",
+                    help="time only the frisk.reduce cases, with exactly --warmup and --steps launches each "
+                         "(a small run for a profiler), and print their JSON")
     ap.add_argument("--band", type=int, default=0,
                     help="tile rows the rasterisation walks together (0: the plan's choice)")
     args = ap.parse_args()
+    asked_warmup = args.warmup
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args)
@@ -375,6 +379,11 @@ def main():
     R.lib()  # fail loudly when the CUDA library is missing: there is no other path
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (sm_100a); none is visible")
+    if args.reduce_only:
+        torch.cuda.set_device(0)
+        print(json.dumps(time_reduce(torch, R, torch.device("cuda:0"), max(args.steps, 1), asked_warmup,
+                                     load_peaks(), False)), flush=True)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -543,7 +552,8 @@ def main():
                              "launches_per_step": oinfo["launches"], "roofline": r,
                              "l2": l2_note}
         line["other_configs"] = others
-        line["reduce"] = time_reduce(torch, R, dev, args.steps, args.warmup, peaks, not args.no_cpu)
+        line["reduce"] = time_reduce(torch, R, dev, max(args.steps, 30), max(args.warmup, 3), peaks,
+                                     not args.no_cpu)
 
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(name)

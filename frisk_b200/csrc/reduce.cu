@@ -53,9 +53,9 @@ void columns_shape(int64_t inner, int64_t extent, int vec, bool first, bool plen
   *xblocks = ceil_div(ivecs, int64_t(1) << *tx_log2);
 }
 
-// Lanes per line piece: about four 16-byte loads per lane, at most a warp.
-int lanes_for(int64_t piece, int vec) {
-  return std::min(5, log2_ceil(std::max<int64_t>(1, ceil_div(ceil_div(piece, vec), 4))));
+// Lanes per line piece: about four 16-byte loads per lane, at most `cap` (log2; 8 = the CTA).
+int lanes_for(int64_t piece, int vec, int cap) {
+  return std::min(cap, log2_ceil(std::max<int64_t>(1, ceil_div(ceil_div(piece, vec), 4))));
 }
 
 // `slots`: CTAs the device holds at once for the first-launch kernel (SMs x CTAs per SM).
@@ -77,7 +77,7 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int64_t slots, Plan*
     return FRISK_OK;
   }
   if (p.lines) {
-    // A warp per line.  With fewer lines than about half the warps the device holds, cut the
+    // Up to a warp per line.  With fewer lines than about half the warps the device holds, cut the
     // lines so that every SM has work; pieces stay at least 4096 elements long.
     const int64_t want = slots * kWarpsPerCta;
     p.vec = 16 / es;
@@ -86,8 +86,11 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int64_t slots, Plan*
       p.chunk_len = ceil_div(ceil_div(d.extent, chunks), 1024) * 1024;
       p.chunks = ceil_div(d.extent, p.chunk_len);
     }
-    p.lanes_log2 = lanes_for(std::min(p.chunk_len, std::max<int64_t>(d.extent, 1)), p.vec);
-    p.lanes_log2_2 = lanes_for(p.chunks, 4);
+    // First launch: at most a warp per piece (measured on 8192 x 8192: groups of 2, 4 and 8 warps
+    // per line were 2 - 25 % slower; the work per CTA gets too short).  Second launch: one line of
+    // partial results per CTA if need be, it is the only work there is.
+    p.lanes_log2 = lanes_for(std::min(p.chunk_len, std::max<int64_t>(d.extent, 1)), p.vec, 5);
+    p.lanes_log2_2 = lanes_for(p.chunks, 4, 8);
     p.ctas = ceil_div((d.outer * p.chunks) << p.lanes_log2, kThreads);
     p.ctas2 = p.chunks > 1 ? ceil_div(d.outer << p.lanes_log2_2, kThreads) : 0;
   } else {

@@ -1,8 +1,9 @@
 // frisk.reduce on buffers in global memory: two kernels, both bound by HBM bandwidth (every source
 // element is read once, 16 bytes per load where alignment allows, streaming past L1).
 //
-//   reduce_lines_kernel    the reduced dimension is the innermost one: a warp per (line, piece of
-//                          the line), four independent accumulators per lane, a shuffle tree.
+//   reduce_lines_kernel    the reduced dimension is the innermost one: a group of lanes (a warp
+//                          for long lines) per (line, piece of the line), four independent
+//                          accumulators and four loads in flight per lane, a shuffle tree.
 //   reduce_columns_kernel  the reduced dimension has contiguous elements after it: a CTA is a
 //                          TY x TX sheet of threads, TX along the contiguous dimension (coalesced),
 //                          TY over the reduced one, folded through shared memory at the end.
@@ -163,8 +164,9 @@ template <> struct Fold<__nv_bfloat16, 2> : FoldBf16<false> {};
 template <> struct Fold<__nv_bfloat16, 3> : FoldBf16<true> {};
 
 // dst[line] (FINAL) or partial[line * chunks + chunk] = fold of src[line, begin .. end).
-// A group of L = 1 << lanes_log2 lanes per (line, piece): a whole warp for long lines, fewer
-// lanes for short ones so that a warp covers several consecutive lines.
+// A group of L = 1 << lanes_log2 lanes per (line, piece): fewer than a warp for short lines, so
+// that a warp covers several consecutive lines; a warp for long ones; several warps, up to the
+// CTA, when the lines are few (the second launch of a two-launch reduce).
 template <typename TIn, typename TOut, int KIND, bool FINAL>
 __global__ void __launch_bounds__(kThreads) reduce_lines_kernel(const TIn* __restrict__ src,
                                                                 TOut* __restrict__ dst, Params p) {
@@ -204,7 +206,14 @@ __global__ void __launch_bounds__(kThreads) reduce_lines_kernel(const TIn* __res
     for (int64_t t = i + sub; t < end; t += L) acc2 = F::one(s[t], acc2);  // fewer than N left
     r = F::finish(F::join(F::join(acc0, acc1), F::join(acc2, acc3)));
   }
-  for (int off = L >> 1; off > 0; off >>= 1) r = O::apply(r, __shfl_xor_sync(0xffffffffu, r, off));
+  for (int off = (L < 32 ? L : 32) >> 1; off > 0; off >>= 1) r = O::apply(r, __shfl_xor_sync(0xffffffffu, r, off));
+  if (L > 32) {  // a group of several warps: their results meet in shared memory
+    __shared__ float across[kWarpsPerCta];
+    if ((threadIdx.x & 31) == 0) across[threadIdx.x >> 5] = r;
+    __syncthreads();
+    if (sub == 0)
+      for (int w = 1; w < (L >> 5); ++w) r = O::apply(r, across[(threadIdx.x >> 5) + w]);
+  }
   if (live && sub == 0) {
     if (FINAL) {
       if (!p.clear) r = O::apply(to_f32(dst[line]), r);

@@ -3,7 +3,7 @@
 //
 //   reduce_lines_kernel    the reduced dimension is the innermost one: a group of lanes (a warp
 //                          for long lines) per (line, piece of the line), four independent
-//                          accumulators and four loads in flight per lane, a shuffle tree.
+//                          accumulators and four or eight loads in flight per lane, a shuffle tree.
 //   reduce_columns_kernel  the reduced dimension has contiguous elements after it: a CTA is a
 //                          TY x TX sheet of threads, TX along the contiguous dimension (coalesced),
 //                          TY over the reduced one, folded through shared memory at the end.
@@ -167,7 +167,10 @@ template <> struct Fold<__nv_bfloat16, 3> : FoldBf16<true> {};
 // A group of L = 1 << lanes_log2 lanes per (line, piece): fewer than a warp for short lines, so
 // that a warp covers several consecutive lines; a warp for long ones; several warps, up to the
 // CTA, when the lines are few (the second launch of a two-launch reduce).
-template <typename TIn, typename TOut, int KIND, bool FINAL>
+// DEPTH: 16-byte loads in flight per lane, 4 or 8.  Eight pay when folding is cheap next to the
+// load (fp32 elements, packed min / max); with a conversion per element (sums of 16-bit floats)
+// the extra registers cost more residency than the deeper queue returns.
+template <typename TIn, typename TOut, int KIND, bool FINAL, int DEPTH>
 __global__ void __launch_bounds__(kThreads) reduce_lines_kernel(const TIn* __restrict__ src,
                                                                 TOut* __restrict__ dst, Params p) {
   using O = Op<KIND>;
@@ -185,25 +188,33 @@ __global__ void __launch_bounds__(kThreads) reduce_lines_kernel(const TIn* __res
     const int64_t end = begin + p.chunk_len < p.extent ? begin + p.chunk_len : p.extent;
     const TIn* s = src + line * p.extent;
     typename F::Acc acc0 = F::init(), acc1 = F::init(), acc2 = F::init(), acc3 = F::init();
-    int64_t i = begin;
-    // up to the first 16-byte boundary (fewer than N elements)
-    int64_t head = (int64_t)((16 - (reinterpret_cast<uintptr_t>(s + i) & 15)) & 15) / (int64_t)sizeof(TIn);
-    if (head > end - i) head = end - i;
-    for (int64_t h = sub; h < head; h += L) acc1 = F::one(s[i + h], acc1);
-    i += head;
-    const int64_t nvec = (end - i) / N;
-    const uint4* v = reinterpret_cast<const uint4*>(s + i);
-    int64_t k = sub;
-    for (; k + 3 * L < nvec; k += 4 * L) {  // four loads in flight per lane
-      const uint4 a = __ldcs(v + k), b = __ldcs(v + k + L), c = __ldcs(v + k + 2 * L), d = __ldcs(v + k + 3 * L);
+    // a piece has fewer than 2^31 elements (the host cuts longer lines): 32-bit counters from here
+    const TIn* piece = s + begin;
+    const int len = (int)(end - begin);
+    int head = (int)(((16 - (reinterpret_cast<uintptr_t>(piece) & 15)) & 15) / sizeof(TIn));
+    if (head > len) head = len;  // up to the first 16-byte boundary: fewer than N elements
+    for (int h = sub; h < head; h += L) acc1 = F::one(piece[h], acc1);
+    const int nvec = (len - head) / N;
+    const uint4* v = reinterpret_cast<const uint4*>(piece + head) + sub;
+    int k = sub;
+    if (DEPTH == 8)
+    for (; k + 7 * L < nvec; k += 8 * L, v += 8 * L) {
+      const uint4 a = __ldcs(v), b = __ldcs(v + L), c = __ldcs(v + 2 * L), d = __ldcs(v + 3 * L);
+      const uint4 e = __ldcs(v + 4 * L), f = __ldcs(v + 5 * L), g = __ldcs(v + 6 * L), h = __ldcs(v + 7 * L);
+      acc0 = F::vec(e, F::vec(a, acc0));
+      acc1 = F::vec(f, F::vec(b, acc1));
+      acc2 = F::vec(g, F::vec(c, acc2));
+      acc3 = F::vec(h, F::vec(d, acc3));
+    }
+    for (; k + 3 * L < nvec; k += 4 * L, v += 4 * L) {  // four loads in flight per lane
+      const uint4 a = __ldcs(v), b = __ldcs(v + L), c = __ldcs(v + 2 * L), d = __ldcs(v + 3 * L);
       acc0 = F::vec(a, acc0);
       acc1 = F::vec(b, acc1);
       acc2 = F::vec(c, acc2);
       acc3 = F::vec(d, acc3);
     }
-    for (; k < nvec; k += L) acc0 = F::vec(__ldcs(v + k), acc0);
-    i += nvec * N;
-    for (int64_t t = i + sub; t < end; t += L) acc2 = F::one(s[t], acc2);  // fewer than N left
+    for (; k < nvec; k += L, v += L) acc0 = F::vec(__ldcs(v), acc0);
+    for (int t = head + nvec * N + sub; t < len; t += L) acc2 = F::one(piece[t], acc2);  // fewer than N left
     r = F::finish(F::join(F::join(acc0, acc1), F::join(acc2, acc3)));
   }
   for (int off = (L < 32 ? L : 32) >> 1; off > 0; off >>= 1) r = O::apply(r, __shfl_xor_sync(0xffffffffu, r, off));

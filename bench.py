@@ -48,6 +48,10 @@ NCU_TRAFFIC_BYTES = {
     # against the same B, walked band by band, so the traffic grows with the rows (roofline_for)
     # profiles/gemm_skinny_cluster_cfg3.md: 134.57 MB read + 4.01 MB written
     "cfg3": 138584832,
+    # profiles/reduce_8192.md: read + written per step (the column reduce: both of its launches)
+    "row_max_f16": 134233088 + 3560960,
+    "row_sum_f32": 268450048 + 3368960,
+    "col_min_f16": 134231040 + 3605248 + 1222144,
 }
 
 
@@ -250,7 +254,8 @@ def time_reduce(torch, R, dev, steps, warmup, peaks, with_cpu):
         entry = {"shape": list(shape), "dim": dim, "dtype": W.DTYPE_NAMES[dtype], "kind": kind,
                  "ms": round(ms, 5), "launches_per_step": info["launches"], "ctas": info["ctas"],
                  "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-                              "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+                              "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                              "traffic": NCU_TRAFFIC_BYTES.get(name),
                               "peak_source": peaks["source"]},
                  "l2": "three sources rotated (0.4 - 0.8 GB)"}
         if with_cpu:  # the float64 restatement on a row sample, beside the kernel

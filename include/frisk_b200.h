@@ -216,7 +216,9 @@ typedef struct frisk_reduce_info {
 } frisk_reduce_info;
 
 /* How the library would run `desc` for operands at addresses with the given alignment
- * (`src_align16` = 1 when src is 16-byte aligned).  Pure host arithmetic. */
+ * (`src_align16` = 1 when src is 16-byte aligned).  Host arithmetic; the cut into pieces depends on
+ * how many CTAs the device holds at once, which is asked of the current device when there is one
+ * and assumed to be 148 SMs x 6 CTAs otherwise. */
 int frisk_b200_reduce_info(const frisk_reduce_desc* desc, int src_align16, frisk_reduce_info* out);
 /* Bytes of device workspace frisk_b200_reduce_run needs (0 for most shapes). */
 int frisk_b200_reduce_workspace_bytes(const frisk_reduce_desc* desc, size_t* out);

@@ -38,7 +38,7 @@ FULL_DIMS = {
 AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3}
 C_TYPE = {"cfg1": W.F32, "cfg2": W.F16}
 TRANS_B = {"cfg2", "cfg4"}
-BOUND = {"cfg3": "hbm"}  # everything else is judged against the tensor-core peak
+BOUND = {"cfg3": "hbm"}  # everything else is measured against the tensor-core peak
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/; None where no capture exists.
 NCU_TRAFFIC_BYTES = {

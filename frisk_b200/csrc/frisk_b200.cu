@@ -89,8 +89,7 @@ struct frisk_gemm_plan {
   CUtensorMap tmap_a, tmap_b;
   const void* cached_a = nullptr;
   const void* cached_b = nullptr;
-  const void* clean_ws = nullptr;  // workspace known to hold zeros
-  bool smem_attr_set = false;
+  int64_t simt_fallback_runs = 0;  // runs a tensor-core plan sent to the CUDA-core kernel
   // device buffers of frisk_b200_gemm_run_host
   void *hA = nullptr, *hB = nullptr, *hC = nullptr, *hWs = nullptr;
   float *hSa = nullptr, *hSb = nullptr;
@@ -212,16 +211,18 @@ constexpr size_t kMaxDynSmem = 227 * 1024 - 1024;
 // another CTA on its SM holds (with CTA pairs such a wait could close a cycle across two SMs).
 constexpr size_t kLaunchDynSmem = kMaxDynSmem;
 
-bool tcgen05_eligible(const frisk_gemm_desc& d) {
+// Why a problem cannot take the tensor-core kernels (FRISK_TC_*; 0 = it can).
+int tcgen05_ineligible_reason(const frisk_gemm_desc& d) {
   if (d.a_type != FRISK_DT_F16 && d.a_type != FRISK_DT_BF16 && d.a_type != FRISK_DT_E4M3)
-    return false;
+    return FRISK_TC_INPUT_TYPE;
   const int es = elem_size(d.a_type);
-  if ((d.lda * es) % 16 || (d.ldb * es) % 16) return false;
-  if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31)) return false;
+  if ((d.lda * es) % 16 || (d.ldb * es) % 16) return FRISK_TC_PITCH;
+  if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31)) return FRISK_TC_EXTENT;
   // 8-bit operands are taken K-major only (A row-major, B column-major)
-  if (d.a_type == FRISK_DT_E4M3 && (d.transA || !d.transB)) return false;
-  return true;
+  if (d.a_type == FRISK_DT_E4M3 && (d.transA || !d.transB)) return FRISK_TC_FP8_ORDER;
+  return FRISK_TC_OK;
 }
+bool tcgen05_eligible(const frisk_gemm_desc& d) { return tcgen05_ineligible_reason(d) == FRISK_TC_OK; }
 
 // Few rows of A against a wide B: the shape the swapped, K-split plan is for.  The kernel counts
 // (tile, k-block) units in 32 bits and multiplies the count by the grid size, so the product has
@@ -424,17 +425,31 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     plan_tcgen05(pl, swap, pair, cluster_try + 1);
 }
 
+constexpr int kMaxDevices = 64;
+
+// Opts a kernel function into the large dynamic shared memory, once per function and device.
+// The limit belongs to the kernel function, not to a plan: every plan asks for the same value
+// (the most any plan uses), so plans with different pipeline depths do not lower it under one
+// another, and a plan that lives on the caller's stack does not pay for the call every time.
+// `Tag` names the kernel function: instantiations of one kernel template share a function TYPE, so
+// the flags cannot hang on the type of `kern`.
+template <typename Tag, typename Kern>
+int ensure_dyn_smem(Kern kern, int device) {
+  static bool done[kMaxDevices] = {};  // one array per Tag
+  const bool tracked = device >= 0 && device < kMaxDevices;
+  if (tracked && __atomic_load_n(&done[device], __ATOMIC_ACQUIRE)) return FRISK_OK;
+  FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kMaxDynSmem));
+  if (tracked) __atomic_store_n(&done[device], true, __ATOMIC_RELEASE);
+  return FRISK_OK;
+}
+template <typename TC, bool kSplit> struct OneCtaKernelTag {};
+template <typename TC> struct PairKernelTag {};
+
 template <typename TC, bool kSplit>
 int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
   auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit>;
-  if (!pl->smem_attr_set) {
-    // The opt-in limit belongs to the kernel function, not to the plan: every plan asks for the
-    // same value (the most any plan uses), so plans with different pipeline depths do not lower
-    // it under one another.
-    FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)kMaxDynSmem));
-    pl->smem_attr_set = true;
-  }
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -463,8 +478,7 @@ int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStrea
 template <typename TC>
 int max_active_clusters_t(frisk_gemm_plan* pl, int* out) {
   auto kern = frisk::gemm_tcgen05_kernel<TC, true>;
-  FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)kMaxDynSmem));
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, true>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -505,14 +519,7 @@ int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream
 template <typename TC>
 int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
   auto kern = frisk::gemm_tcgen05_pair_kernel<TC>;
-  if (!pl->smem_attr_set) {
-    // The opt-in limit belongs to the kernel function, not to the plan: every plan asks for the
-    // same value (the most any plan uses), so plans with different pipeline depths do not lower
-    // it under one another.
-    FRISK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)kMaxDynSmem));
-    pl->smem_attr_set = true;
-  }
+  if (int rc = ensure_dyn_smem<PairKernelTag<TC>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -593,6 +600,36 @@ size_t b_bytes(const frisk_gemm_desc& d) {
 }
 size_t c_bytes(const frisk_gemm_desc& d) { return (size_t)d.M * d.ldc * elem_size(d.c_type); }
 
+// Host -> device copies of the operands.  Only the elements of each stored row are read: a host
+// buffer sized the BLAS way, (rows - 1) * ld + row length, ends before rows * ld.
+int upload_rows(void* dst, const void* src, size_t pitch, size_t row_bytes, int64_t row0,
+                int64_t rows, cudaStream_t st) {
+  char* d = static_cast<char*>(dst) + (size_t)row0 * pitch;
+  const char* s = static_cast<const char*>(src) + (size_t)row0 * pitch;
+  if (pitch == row_bytes)
+    FRISK_CUDA(cudaMemcpyAsync(d, s, (size_t)rows * pitch, cudaMemcpyHostToDevice, st));
+  else
+    FRISK_CUDA(cudaMemcpy2DAsync(d, pitch, s, pitch, row_bytes, (size_t)rows,
+                                 cudaMemcpyHostToDevice, st));
+  return FRISK_OK;
+}
+// stored rows [row0, row0 + rows) of A: rows of M (transA == 0) or of K
+int upload_a(const frisk_gemm_desc& d, void* dst, const void* src, int64_t row0, int64_t rows,
+             cudaStream_t st) {
+  const size_t es = elem_size(d.a_type);
+  return upload_rows(dst, src, (size_t)d.lda * es, (size_t)(d.transA ? d.M : d.K) * es, row0, rows, st);
+}
+int upload_b(const frisk_gemm_desc& d, void* dst, const void* src, cudaStream_t st) {
+  const size_t es = elem_size(d.b_type);
+  return upload_rows(dst, src, (size_t)d.ldb * es, (size_t)(d.transB ? d.K : d.N) * es, 0,
+                     d.transB ? d.N : d.K, st);
+}
+int upload_c(const frisk_gemm_desc& d, void* dst, const void* src, int64_t row0, int64_t rows,
+             cudaStream_t st) {
+  const size_t es = elem_size(d.c_type);
+  return upload_rows(dst, src, (size_t)d.ldc * es, (size_t)d.N * es, row0, rows, st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -650,7 +687,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   } else {
     // Two SMs on one 256-row tile (each stages half of B) run about 1.12x faster per tile than
     // two one-CTA tiles, so the pair kernel is taken unless its coarser tiles lose more than that
-    // to the last, partly filled wave.  FRISK_B200_PAIR=0 / =1 overrides the estimate.
+    // to the last, partly filled wave (desc.force_kernel overrides the estimate).
     bool use_pair = false;
     if (pair_ok) {
       const uint64_t tn = d.tile_n ? (uint64_t)d.tile_n : (d.N > 128 ? 256u : 128u);
@@ -663,7 +700,9 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       if (pair_tail_split(tn, two_tiles, pairs)) two_waves -= 0.44;  // a wave of half-width items
       const double two_cost = two_waves / 1.12;
       use_pair = two_cost < one_cost;
+#ifdef FRISK_B200_MEASURE
       if (const char* want_pair = getenv("FRISK_B200_PAIR")) use_pair = want_pair[0] == '1';
+#endif
     }
     kind = skinny_ok ? FRISK_KERNEL_SKINNY
            : use_pair ? FRISK_KERNEL_TCGEN05_PAIR
@@ -672,6 +711,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   }
   if (kind == FRISK_KERNEL_SIMT) {
     pl->info.kernel = FRISK_KERNEL_SIMT;
+    pl->info.cuda_core_reason = d.force_kernel ? FRISK_TC_FORCED : tcgen05_ineligible_reason(d);
     // the same choice launch_simt_in makes: 32-row tiles when 64-row tiles would not fill the SMs
     const int64_t ctas64 = ((d.N + 63) / 64) * ((d.M + 63) / 64);
     const int tm = (d.M > 32 && ctas64 < 148) ? 32 : frisk::kSimtTile;
@@ -714,6 +754,7 @@ void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* pl) {
 int frisk_b200_gemm_plan_info(const frisk_gemm_plan* pl, frisk_gemm_plan_info* out) {
   if (!pl || !out) return FRISK_ERR_INVALID_ARGUMENT;
   *out = pl->info;
+  out->cuda_core_runs = pl->simt_fallback_runs;
   return FRISK_OK;
 }
 
@@ -736,6 +777,12 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   const float* sb = d.scale_mode ? scale_b : nullptr;
 
   const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
+  if (pl->info.kernel != FRISK_KERNEL_SIMT && !ptr_aligned) {
+    // TMA needs 16-byte aligned bases; the run still gives the right answer, about 100x slower,
+    // so it is counted (plan_info.cuda_core_runs) and noted where the caller can read it
+    ++pl->simt_fallback_runs;
+    g_last_error = "A or B is not 16-byte aligned: this run used the CUDA-core kernel";
+  }
   if (pl->info.kernel == FRISK_KERNEL_SIMT || !ptr_aligned)
     return launch_simt(d, A, B, C, sa, sb, st);  // the CUDA-core kernel has no alignment rule
 
@@ -772,10 +819,12 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
       g.ws = reinterpret_cast<float*>(workspace);
       g.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->slot_bytes);
     }
-    if (pl->ws_bytes && pl->clean_ws != workspace) {  // the counters must start at zero; the kernel re-zeroes them
+    // The arrival counters must start at zero.  The kernel leaves them at zero when it completes,
+    // but nothing guarantees what the caller hands in: a scratch buffer that was given to other
+    // code between two runs, one buffer shared by two plans, a run that gave up on a bounded wait.
+    // They are a few bytes per tile, so they are cleared on every run, in stream order.
+    if (pl->ws_bytes)
       FRISK_CUDA(cudaMemsetAsync(g.counters, 0, pl->ws_bytes - pl->slot_bytes, st));
-      pl->clean_ws = workspace;
-    }
   } else {
     g.row_scale = sa;
     g.col_scale = sb;
@@ -796,7 +845,6 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
       default: rc = FRISK_ERR_UNSUPPORTED;
     }
   }
-  if (rc) pl->clean_ws = nullptr;
   return rc;
 }
 
@@ -848,7 +896,7 @@ int run_host_pipelined(frisk_gemm_plan* pl, const void* A, const void* B, void* 
   cudaStream_t s_in = pl->s_in, s_cmp = pl->hstream, s_out = pl->s_out;
   // up: status word, B, scales, then the chunks of A (and of C when the GEMM accumulates into it)
   FRISK_CUDA(cudaMemsetAsync(pl->hStatus, 0, sizeof(int32_t), s_in));
-  FRISK_CUDA(cudaMemcpyAsync(pl->hB, B, b_bytes(d), cudaMemcpyHostToDevice, s_in));
+  if (int rc = upload_b(d, pl->hB, B, s_in)) return rc;
   if (d.scale_mode) {
     FRISK_CUDA(cudaMemcpyAsync(pl->hSa, scale_a, d.M * sizeof(float), cudaMemcpyHostToDevice, s_in));
     FRISK_CUDA(cudaMemcpyAsync(pl->hSb, scale_b, d.N * sizeof(float), cudaMemcpyHostToDevice, s_in));
@@ -857,13 +905,12 @@ int run_host_pipelined(frisk_gemm_plan* pl, const void* A, const void* B, void* 
     const int64_t r0 = (int64_t)i * pl->chunk_rows;
     const int64_t rows = std::min<int64_t>(pl->chunk_rows, d.M - r0);
     frisk_gemm_plan* sub = (rows == pl->chunk_rows) ? pl->chunk_plan : pl->tail_plan;
-    const char* a_src = static_cast<const char*>(A) + r0 * a_pitch;
     char* a_dst = static_cast<char*>(pl->hA) + r0 * a_pitch;
     char* c_host = static_cast<char*>(C) + r0 * c_pitch;
     char* c_dev = static_cast<char*>(pl->hC) + r0 * c_pitch;
-    FRISK_CUDA(cudaMemcpyAsync(a_dst, a_src, (size_t)rows * a_pitch, cudaMemcpyHostToDevice, s_in));
+    if (int rc = upload_a(d, pl->hA, A, r0, rows, s_in)) return rc;
     if (!d.clear_accum)
-      FRISK_CUDA(cudaMemcpyAsync(c_dev, c_host, (size_t)rows * c_pitch, cudaMemcpyHostToDevice, s_in));
+      if (int rc = upload_c(d, pl->hC, C, r0, rows, s_in)) return rc;
     FRISK_CUDA(cudaEventRecord(pl->ev_in[i], s_in));
     // compute
     FRISK_CUDA(cudaStreamWaitEvent(s_cmp, pl->ev_in[i], 0));
@@ -913,10 +960,10 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, 
   }
   if (pl->n_chunks > 1) return run_host_pipelined(pl, A, B, C, scale_a, scale_b);
   FRISK_CUDA(cudaMemsetAsync(pl->hStatus, 0, sizeof(int32_t), st));
-  FRISK_CUDA(cudaMemcpyAsync(pl->hA, A, a_bytes(d), cudaMemcpyHostToDevice, st));
-  FRISK_CUDA(cudaMemcpyAsync(pl->hB, B, b_bytes(d), cudaMemcpyHostToDevice, st));
+  if (int rc = upload_a(d, pl->hA, A, 0, d.transA ? d.K : d.M, st)) return rc;
+  if (int rc = upload_b(d, pl->hB, B, st)) return rc;
   if (!d.clear_accum)
-    FRISK_CUDA(cudaMemcpyAsync(pl->hC, C, c_bytes(d), cudaMemcpyHostToDevice, st));
+    if (int rc = upload_c(d, pl->hC, C, 0, d.M, st)) return rc;
   if (d.scale_mode) {
     FRISK_CUDA(cudaMemcpyAsync(pl->hSa, scale_a, d.M * sizeof(float), cudaMemcpyHostToDevice, st));
     FRISK_CUDA(cudaMemcpyAsync(pl->hSb, scale_b, d.N * sizeof(float), cudaMemcpyHostToDevice, st));
@@ -945,7 +992,6 @@ constexpr size_t kStaticScratchFloats = 1u << 20;  // 4 MiB: M * N <= 1,048,576 
 static __device__ __align__(256) float g_skinny_scratch[kStaticScratchFloats];
 
 namespace {
-constexpr int kMaxDevices = 64;
 // Device address of g_skinny_scratch per device.  In host code the array's name is only a
 // handle for the runtime, not an address a kernel could use; the address is asked for once per
 // device, with that device current.
@@ -975,6 +1021,8 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return FRISK_ERR_INVALID_ARGUMENT;
   if (!elem_size(d.a_type) || d.a_type != d.b_type || !elem_size(d.c_type) ||
       d.c_type == FRISK_DT_E4M3)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.scale_mode != FRISK_SCALE_NONE && d.scale_mode != FRISK_SCALE_ROW_COL)
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.scale_mode == FRISK_SCALE_ROW_COL && (!scale_a || !scale_b))
     return FRISK_ERR_INVALID_ARGUMENT;
@@ -1006,7 +1054,10 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   pl.d = d;
   memset(&pl.info, 0, sizeof pl.info);
   int dev = 0;
-  FRISK_CUDA(cudaGetDevice(&dev));
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return FRISK_ERR_NO_DEVICE;
+  }
   int major = 0, sms = 0;
   FRISK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
   FRISK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

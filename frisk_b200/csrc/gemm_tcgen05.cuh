@@ -29,6 +29,10 @@
 namespace frisk {
 
 constexpr int kMaxStages = 12;
+constexpr int kMaxPeers = 7;   // a node has eight GPUs: seven others
+// Staging area of the whole-tile epilogue: each of the four epilogue warps owns 32 rows x 128 bytes.
+constexpr uint32_t kEpiStageBytesPerWarp = 32u * 128u;
+constexpr uint32_t kEpiStageBytes = 4u * kEpiStageBytesPerWarp;
 // Measurement builds (-DFRISK_B200_MEASURE) keep the debug modes and the clock stamps of CTA 0;
 // the normal build compiles them out of the kernels.
 #ifdef FRISK_B200_MEASURE
@@ -100,6 +104,16 @@ struct GemmParams {
   uint32_t clear_accum;
   uint32_t c_vec_ok;       // C rows allow 16-byte stores
   uint32_t epilogue_backoff_ns;  // sleep between polls of the accumulator-ready barrier
+  // whole-tile epilogue (the one-CTA whole-tile kernel and the CTA-pair kernel)
+  uint32_t epi_staged;     // 1: rows go through shared memory and leave as 128-byte row pieces
+  uint32_t n_peers;        // other GPUs that receive a copy of every C tile (row-sharded all-gather)
+  void* peer_c[kMaxPeers]; // where this GPU's rows of C start in each peer's buffer (same ldc)
+  // frisk.reduce of C over its columns, folded into the epilogue
+  uint32_t rr_kind;        // 0: none; 1 + frisk_reduce_kind
+  uint32_t rr_clear;       // 1: dst = fold; 0: dst = dst (op) fold
+  float* rr_partials;      // [2 * tiles_c][rows] fp32: one fold per row and half tile
+  uint32_t* rr_counters;   // [ceil(rows / 128)] half tiles arrived per block of 128 rows (zero between launches)
+  void* rr_dst;            // [rows] of C's element type
   uint32_t debug_mode;     // measurement only: bit 0 = issue no loads, bit 1 = issue no MMAs
   long long* trace;        // measurement only: clock64 samples of CTA 0 (may be nullptr)
   int32_t* status;
@@ -317,12 +331,157 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs& p, uint32_t row, u
   }
 }
 
-// ---- split mode 2: partial tiles in private slots, reduced by the last CTA to arrive -----------
-// A slot holds one partial tile as [column][row] fp32 (rows fastest, so a warp's 32 rows of one
-// column are one 128-byte store).  Slot of CTA c for tile t: c * max_items + (t - first tile of c).
-__device__ __forceinline__ uint32_t unit_begin(uint32_t total_units, uint32_t cta, uint32_t grid) {
-  return total_units * cta / grid;
+// ---- whole-tile epilogue: values -> (row fold) -> C, directly or through shared memory ---------
+// What the whole-tile kernels need beyond EpiArgs, copied into locals like EpiArgs.
+struct EpiExt {
+  uint32_t staged, n_peers, rr_kind;
+  void* peer[kMaxPeers];
+};
+
+__device__ __forceinline__ float fold_identity(uint32_t rr_kind) {
+  // 1 add, 2 mul, 3 min, 4 max
+  return rr_kind == 1u ? 0.f : rr_kind == 2u ? 1.f : rr_kind == 3u ? __int_as_float(0x7f800000)
+                                                                   : __int_as_float(0xff800000);
 }
+__device__ __forceinline__ float fold_step(uint32_t rr_kind, float a, float b) {
+  // min / max skip NaN operands like fminf / fmaxf
+  return rr_kind == 1u ? a + b : rr_kind == 2u ? a * b : rr_kind == 3u ? fminf(a, b) : fmaxf(a, b);
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+
+// One warp's 32 rows x NC columns of D = C (lane = row, NC * sizeof(TC) = 128 bytes when staged):
+// scale, add the old C if asked, round once, fold the rounded values into `red` (the row fold
+// sees what a reduce of the stored C would see), and store.
+//   direct: every thread writes its own row piece (16-byte stores at row stride);
+//   staged: the rows go through the warp's 4 KiB of shared memory, written in the 128-byte
+//           swizzle (16-byte chunk j of row r at chunk j ^ (r & 7): a warp's 32 writes of one
+//           chunk column, and later its reads of four whole rows, each touch every bank exactly
+//           four times, the minimum), and leave as whole 128-byte row pieces, four rows per
+//           store instruction, to C and to every peer's copy.
+// `stage` is the warp's staging area (shared-memory address), `warp_row0` the D row of lane 0.
+template <typename TC, int NC>
+__device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x, uint32_t stage,
+                                               uint32_t lane, uint32_t warp_row0, uint32_t col0,
+                                               const uint32_t (&acc)[NC], float& red) {
+  constexpr int kPerVec = 16 / (int)sizeof(TC);
+  constexpr int kVecs = NC / kPerVec;
+  const uint32_t row = warp_row0 + lane;
+  const bool row_ok = row < p.rows;
+  const bool full = col0 + NC <= p.cols;          // warp-uniform
+  const bool vec = p.c_vec_ok && full;            // warp-uniform
+  TC* const crow = reinterpret_cast<TC*>(p.C) + (int64_t)row * p.ldc + col0;
+  union Pack {
+    uint4 u;
+    TC e[kPerVec];
+  };
+  Pack out[kVecs];
+  const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+  if (!p.clear_accum && row_ok) {
+    if (vec) {
+#pragma unroll
+      for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = *reinterpret_cast<const uint4*>(crow + v0 * kPerVec);
+    } else {
+#pragma unroll
+      for (int j = 0; j < NC; ++j)
+        if (col0 + j < p.cols) out[j / kPerVec].e[j % kPerVec] = crow[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    float v = __uint_as_float(acc[j]) * rs;
+    if (p.col_scale && (full || col0 + j < p.cols)) v *= __ldg(p.col_scale + col0 + j);
+    if (!p.clear_accum && row_ok && (full || col0 + j < p.cols)) v += cast_in<TC>(out[j / kPerVec].e[j % kPerVec]);
+    const TC o = cast_out<TC>(v);
+    out[j / kPerVec].e[j % kPerVec] = o;
+    if (x.rr_kind && (full || col0 + j < p.cols)) red = fold_step(x.rr_kind, red, cast_in<TC>(o));
+  }
+  if (x.staged && vec) {
+    const uint32_t my = stage + lane * 128u;
+#pragma unroll
+    for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(my + (((uint32_t)v0 ^ (lane & 7u)) << 4), out[v0].u);
+    __syncwarp();
+    static_assert(kVecs == 8, "a staged row piece is 128 bytes");
+    const uint32_t sub = lane >> 3, ch = lane & 7u;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const uint32_t rr = (uint32_t)it * 4u + sub;
+      const uint4 piece = ld_shared_v4(stage + rr * 128u + ((ch ^ (rr & 7u)) << 4));
+      if (warp_row0 + rr < p.rows) {
+        const int64_t off = (int64_t)(warp_row0 + rr) * p.ldc + col0 + ch * kPerVec;
+        *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(p.C) + off) = piece;
+#pragma unroll
+        for (int q = 0; q < kMaxPeers; ++q)
+          if (q < (int)x.n_peers) *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(x.peer[q]) + off) = piece;
+      }
+    }
+    __syncwarp();   // the staging area is rewritten by the next chunk
+    return;
+  }
+  if (!row_ok) return;
+  if (vec) {
+#pragma unroll
+    for (int v0 = 0; v0 < kVecs; ++v0) {
+      *reinterpret_cast<uint4*>(crow + v0 * kPerVec) = out[v0].u;
+#pragma unroll
+      for (int q = 0; q < kMaxPeers; ++q)
+        if (q < (int)x.n_peers)
+          *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(x.peer[q]) + (int64_t)row * p.ldc + col0 + v0 * kPerVec) = out[v0].u;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      if (col0 + j < p.cols) {
+        crow[j] = out[j / kPerVec].e[j % kPerVec];
+#pragma unroll
+        for (int q = 0; q < kMaxPeers; ++q)
+          if (q < (int)x.n_peers)
+            (reinterpret_cast<TC*>(x.peer[q]) + (int64_t)row * p.ldc + col0)[j] = out[j / kPerVec].e[j % kPerVec];
+      }
+    }
+  }
+}
+
+// The warp's 32 rows of one work item: `cols_item` columns from D column `col0`, accumulator
+// rows at tensor-memory address `t_row`.  Columns are taken 128 bytes of C at a time; the
+// tensor-memory loads of a piece are issued together and waited for once.
+template <typename TC>
+__device__ __forceinline__ void epilogue_item(const EpiArgs& ep, const EpiExt& ex, uint32_t stage,
+                                              uint32_t lane, uint32_t warp_row0, uint32_t col0,
+                                              uint32_t cols_item, uint32_t t_row, float& red) {
+  constexpr int CH = 128 / (int)sizeof(TC);
+  for (uint32_t cc = 0; cc < cols_item; cc += CH) {
+    uint32_t v[CH];
+#pragma unroll
+    for (int h = 0; h < CH / 32; ++h)
+      ptx::tmem_ld_32x32b_x32(t_row + cc + 32u * h, reinterpret_cast<uint32_t(&)[32]>(v[32 * h]));
+    ptx::tmem_ld_wait();
+    epilogue_chunk<TC, CH>(ep, ex, stage, lane, warp_row0, col0 + cc, v, red);
+  }
+}
+
+// ---- frisk.reduce over the columns of C, folded into the whole-tile epilogue -------------------
+// Every (row, half tile) fold goes to partials[slot][row]; a counter per block of 128 rows counts
+// the half tiles that have arrived, and the CTA that brings it to 2 * tiles_c folds the row's
+// slots in slot order (so the result does not depend on which CTA that is) into dst.
+struct RowFold {
+  uint32_t kind, clear, nslots;
+  float* partials;
+  uint32_t* counters;
+  void* dst;
+};
 
 // Rendezvous of the 128 epilogue threads on an mbarrier (count 128), bounded like every other
 // wait of the kernel: a named hardware barrier could not give up if one warp had left the loop.
@@ -332,6 +491,51 @@ __device__ __forceinline__ bool epilogue_rendezvous(uint32_t bar, uint32_t& phas
   const bool ok = bounded_wait(bar, phase, abort_flag, status, kStatusEpilogueTimeout);
   phase ^= 1u;
   return ok;
+}
+
+// Called by the 128 epilogue threads of a CTA after an item's last column; epi_tid = the thread's
+// row inside the CTA's 128 rows (32 * TMEM quarter + lane).
+// `weight` is 2 for a whole tile (which also marks the tile's second slot as empty), 1 for a half.
+template <typename TC>
+__device__ __forceinline__ bool row_fold_finish(const RowFold& f, uint32_t epi_tid, uint32_t row,
+                                                uint32_t rows, uint32_t slot, uint32_t weight,
+                                                float red, uint32_t epi_bar, uint32_t& epi_phase,
+                                                volatile uint32_t* abort_flag, int32_t* status,
+                                                volatile uint32_t* last_flag) {
+  const bool row_ok = row < rows;
+  const uint32_t blk = (row - epi_tid) >> 7;   // the CTA's rows start at a multiple of 128
+  if (row_ok) {
+    f.partials[(size_t)slot * rows + row] = red;
+    if (weight == 2u) f.partials[(size_t)(slot + 1u) * rows + row] = fold_identity(f.kind);
+  }
+  __threadfence();   // this thread's folds are visible device-wide before the count goes up
+  if (!epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status)) return false;
+  if (epi_tid == 0) {
+    const uint32_t before = atomicAdd(f.counters + blk, weight);
+    *last_flag = (before + weight == f.nslots) ? 1u : 0u;
+  }
+  if (!epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status)) return false;
+  if (*last_flag) {
+    __threadfence();
+    if (row_ok) {
+      float r = fold_identity(f.kind);
+      for (uint32_t sl = 0; sl < f.nslots; ++sl)
+        r = fold_step(f.kind, r, __ldcg(f.partials + (size_t)sl * rows + row));
+      TC* dst = reinterpret_cast<TC*>(f.dst) + row;
+      if (!f.clear) r = fold_step(f.kind, cast_in<TC>(*dst), r);
+      *dst = cast_out<TC>(r);
+    }
+    if (epi_tid == 0) f.counters[blk] = 0;   // ready for the next launch
+  }
+  // last_flag is rewritten by the next item
+  return epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
+}
+
+// ---- split mode 2: partial tiles in private slots, reduced by the last CTA to arrive -----------
+// A slot holds one partial tile as [column][row] fp32 (rows fastest, so a warp's 32 rows of one
+// column are one 128-byte store).  Slot of CTA c for tile t: c * max_items + (t - first tile of c).
+__device__ __forceinline__ uint32_t unit_begin(uint32_t total_units, uint32_t cta, uint32_t grid) {
+  return total_units * cta / grid;
 }
 
 template <int NC>
@@ -784,6 +988,67 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // ------------------------------------------------------------- epilogue
+    if constexpr (!kSplit) {
+      // whole tiles of 128 rows (mi == 1): lane = row, columns 128 bytes of C at a time
+      EpiArgs ep;
+      ep.C = p.C;
+      ep.ws = nullptr;
+      ep.row_scale = p.row_scale;
+      ep.col_scale = p.col_scale;
+      ep.ldc = p.ldc;
+      ep.ws_ld = 0;
+      ep.rows = p.rows;
+      ep.cols = p.cols;
+      ep.split_mode = 0;
+      ep.transposed_out = 0;
+      ep.clear_accum = p.clear_accum;
+      ep.c_vec_ok = p.c_vec_ok;
+      EpiExt ex;
+      ex.staged = p.epi_staged;
+      ex.n_peers = p.n_peers;
+      ex.rr_kind = p.rr_kind;
+#pragma unroll
+      for (int q = 0; q < kMaxPeers; ++q) ex.peer[q] = p.peer_c[q];
+      RowFold rf;
+      rf.kind = p.rr_kind;
+      rf.clear = p.rr_clear;
+      rf.nslots = 2u * tiles_c;
+      rf.partials = p.rr_partials;
+      rf.counters = p.rr_counters;
+      rf.dst = p.rr_dst;
+      const uint32_t quarter = warp & 3u;  // TMEM lanes 32*quarter .. +31 belong to this warp
+      const uint32_t stage_area = tiles_base + stages * stage_bytes + quarter * kEpiStageBytesPerWarp;
+      const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
+      const uint32_t epi_backoff = p.epilogue_backoff_ns;
+      uint32_t epi_phase = 0, item = 0;
+      bool ok = true;
+      while (ok && work.next()) {
+        const uint32_t acc = item % acc_bufs;
+        const uint32_t acc_phase = (item / acc_bufs) & 1u;
+        uint32_t tr, tc;
+        tile_coords(group_r, tiles_r, tiles_c, work.tile, tr, tc);
+        // the tcgen05.ld below is warp-collective: leave the loop only as a whole warp
+        ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
+                          epi_backoff);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + acc * tile_n;
+        float red = fold_identity(rf.kind);
+        epilogue_item<TC>(ep, ex, stage_area, lane, tr * 128u + quarter * 32u, tc * tile_n, tile_n,
+                          t_row, red);
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
+        if (rf.kind) {
+          ok = row_fold_finish<TC>(rf, quarter * 32u + lane, tr * 128u + quarter * 32u + lane, ep.rows,
+                                   2u * tc, 2u, red, epi_bar, epi_phase, abort_flag, status,
+                                   &last_flag);
+          if (!ok) break;
+        }
+        ++item;
+      }
+      __syncwarp();
+    } else {
     EpiArgs ep;
     ep.C = p.C;
     ep.ws = p.ws;
@@ -936,6 +1201,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       if (trace && threadIdx.x == 64) trace[327] = clock64() - t_entry;
     }
+    }  // kSplit
   }
 
   // ---------------------------------------------------------------- tear-down

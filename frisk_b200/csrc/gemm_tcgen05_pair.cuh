@@ -45,8 +45,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ __align__(8) uint64_t bar_epilogue;
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
+  __shared__ uint32_t last_flag;
 
   const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const uint32_t lane = threadIdx.x & 31;
@@ -89,6 +91,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::mbar_init(acc_full0 + 8 * i, 1);
       ptx::mbar_init(acc_empty0 + 8 * i, 8);  // four epilogue warps in each CTA
     }
+    ptx::mbar_init(ptx::smem_u32(&bar_epilogue), 128);
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
@@ -268,19 +271,35 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // ------------------------------------------------------------- epilogue (both CTAs)
     EpiArgs ep;
     ep.C = p.C;
-    ep.ws = p.ws;
+    ep.ws = nullptr;
     ep.row_scale = p.row_scale;
     ep.col_scale = p.col_scale;
     ep.ldc = p.ldc;
-    ep.ws_ld = p.ws_ld;
+    ep.ws_ld = 0;
     ep.rows = p.rows;
     ep.cols = p.cols;
     ep.split_mode = 0;
     ep.transposed_out = 0;
     ep.clear_accum = p.clear_accum;
     ep.c_vec_ok = p.c_vec_ok;
+    EpiExt ex;
+    ex.staged = p.epi_staged;
+    ex.n_peers = p.n_peers;
+    ex.rr_kind = p.rr_kind;
+#pragma unroll
+    for (int q = 0; q < kMaxPeers; ++q) ex.peer[q] = p.peer_c[q];
+    RowFold rf;
+    rf.kind = p.rr_kind;
+    rf.clear = p.rr_clear;
+    rf.nslots = 2u * tiles_c;
+    rf.partials = p.rr_partials;
+    rf.counters = p.rr_counters;
+    rf.dst = p.rr_dst;
     const uint32_t quarter = warp & 3u;
-    uint32_t item = 0;
+    // the staging area of the epilogue sits behind the pipeline stages
+    const uint32_t stage_area = tiles_base + stages * stage_bytes + quarter * kEpiStageBytesPerWarp;
+    const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
+    uint32_t epi_phase = 0, item = 0;
     bool ok = true;
     for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
       const PairItem it = pair_item(i, narrow_from);
@@ -294,17 +313,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         kEpilogueBackoffNs);
       if (!ok) break;
       ptx::tc_fence_after();
-      const uint32_t row = tr * 256u + rank * 128u + quarter * 32u + lane;
+      const uint32_t warp_row0 = tr * 256u + rank * 128u + quarter * 32u;
       const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + acc * tile_n;
-      for (uint32_t cc = 0; cc < cols_item; cc += 32) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(t_row + cc, v);
-        ptx::tmem_ld_wait();
-        epilogue_store<TC, 32>(ep, row, col0 + cc, v);
-      }
+      float red = fold_identity(rf.kind);
+      epilogue_item<TC>(ep, ex, stage_area, lane, warp_row0, col0, cols_item, t_row, red);
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(leader_acc_empty0 + 8 * acc);
+      if (rf.kind) {
+        ok = row_fold_finish<TC>(rf, quarter * 32u + lane, warp_row0 + lane, ep.rows,
+                                 2u * tc + it.half, it.narrow ? 1u : 2u, red, epi_bar, epi_phase,
+                                 abort_flag, status, &last_flag);
+        if (!ok) break;
+      }
       ++item;
     }
     if (!ok && lane == 0) ptx::st_shared_cluster_u32(peer_abort, 1);

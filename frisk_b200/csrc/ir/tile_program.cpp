@@ -162,6 +162,11 @@ TiledGemm liftTiledGemm(Operation* kernel) {
       else fail("unexpected " + op->name + " in the k loop");
     }
     if (!gemm || loads.size() != 2) fail("the k loop must be two frisk.copy and one frisk.gemm");
+    // scale vectors of an 8-bit float gemm have no meaning per tile, and the tiles are copied in
+    // row-major [TM,TK] / [TK,TN] order, so a transposed operand cannot be what the program means
+    if (gemm->operands.size() != 3) fail("the gemm in the loop must not carry scale operands");
+    if (gemm->intAttr("transA") || gemm->intAttr("transB"))
+      fail("the gemm in the loop must not transpose its tiles (transA = transB = false)");
     Value ta = gemm->operands.at(0), tb = gemm->operands.at(1), tc = gemm->operands.at(2);
     for (Value t : {ta, tb, tc})
       if (!t->defOp || t->defOp->name != "frisk.alloc_buffer" || t->defOp->parent != pbody)

@@ -37,6 +37,17 @@ class GemmDesc(C.Structure):
         ("clear_accum", C.c_int32), ("scale_mode", C.c_int32),
         ("force_kernel", C.c_int32), ("tile_n", C.c_int32), ("stages", C.c_int32),
         ("num_ctas", C.c_int32), ("band_tiles", C.c_int32),
+        ("epilogue", C.c_int32), ("row_reduce", C.c_int32), ("row_reduce_clear", C.c_int32),
+    ]
+
+
+class GemmRunArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p),
+        ("scale_a", C.c_void_p), ("scale_b", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("device_status", C.c_void_p), ("stream", C.c_void_p),
+        ("row_reduce_dst", C.c_void_p), ("n_peers", C.c_int32), ("peer_c", C.c_void_p * 7),
     ]
 
 
@@ -46,6 +57,7 @@ class PlanInfo(C.Structure):
         ("stages", C.c_int32), ("num_ctas", C.c_int32), ("swap_ab", C.c_int32),
         ("split_k", C.c_int32), ("smem_bytes", C.c_int32), ("launches", C.c_int32),
         ("swizzle_a", C.c_int32), ("swizzle_b", C.c_int32),
+        ("cuda_core_reason", C.c_int32), ("cuda_core_runs", C.c_int64),
     ]
 
     def as_dict(self) -> dict:
@@ -120,6 +132,16 @@ def lib() -> C.CDLL:
     L.frisk_b200_gemm_workspace_bytes.restype = C.c_int
     L.frisk_b200_gemm_run.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp, vp]
     L.frisk_b200_gemm_run.restype = C.c_int
+    L.frisk_b200_gemm_run_ex.argtypes = [vp, C.POINTER(GemmRunArgs)]
+    L.frisk_b200_gemm_run_ex.restype = C.c_int
+    L.frisk_b200_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), C.c_char_p]
+    L.frisk_b200_peer_alloc.restype = C.c_int
+    L.frisk_b200_peer_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+    L.frisk_b200_peer_open.restype = C.c_int
+    L.frisk_b200_peer_close.argtypes = [vp]
+    L.frisk_b200_peer_close.restype = C.c_int
+    L.frisk_b200_peer_free.argtypes = [vp]
+    L.frisk_b200_peer_free.restype = C.c_int
     L.frisk_b200_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp]
     L.frisk_b200_gemm_run_host.restype = C.c_int
     L.frisk_b200_gemm_skinny_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, vp]
@@ -187,7 +209,8 @@ class GemmPlan:
                  transA: bool = False, transB: bool = False, clear_accum: bool = True,
                  scales: bool = False, lda: int = 0, ldb: int = 0, ldc: int = 0,
                  force_kernel: Optional[str] = None, tile_n: int = 0, stages: int = 0,
-                 num_ctas: int = 0, band_tiles: int = 0):
+                 num_ctas: int = 0, band_tiles: int = 0, epilogue: int = 0,
+                 row_reduce: Optional[str] = None, row_reduce_clear: bool = True):
         L = lib()
         d = GemmDesc()
         d.M, d.N, d.K = M, N, K
@@ -199,6 +222,9 @@ class GemmPlan:
         d.scale_mode = 1 if scales else 0
         d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2, "tcgen05_pair": 3}[force_kernel]
         d.tile_n, d.stages, d.num_ctas, d.band_tiles = tile_n, stages, num_ctas, band_tiles
+        d.epilogue = epilogue
+        d.row_reduce = 0 if row_reduce is None else 1 + REDUCE_KINDS[row_reduce]
+        d.row_reduce_clear = int(row_reduce_clear)
         self.desc = d
         self._h = C.c_void_p()
         _check(L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(self._h)), "plan_create")
@@ -208,6 +234,13 @@ class GemmPlan:
         ws = C.c_size_t()
         _check(L.frisk_b200_gemm_workspace_bytes(self._h, C.byref(ws)), "workspace_bytes")
         self.workspace_bytes = int(ws.value)
+
+    def refresh_info(self) -> dict:
+        """Reads the plan's info again (its run counters change as the plan is used)."""
+        info = PlanInfo()
+        _check(lib().frisk_b200_gemm_plan_info(self._h, C.byref(info)), "plan_info")
+        self.info = info.as_dict()
+        return self.info
 
     @classmethod
     def for_workload(cls, w: W.GemmWorkload, **kw) -> "GemmPlan":
@@ -236,6 +269,24 @@ class GemmPlan:
                                        _ptr(scale_b), _ptr(workspace), ws_bytes, _ptr(status),
                                        stream or None)
         _check(rc, "gemm_run")
+
+    def run_ex(self, A, B, Cout, *, scale_a=None, scale_b=None, workspace=None, status=None,
+               stream: int = 0, row_reduce_dst=None, peers=()) -> None:
+        """``run`` with the destination of a fused row reduce and / or peer copies of C (device
+        addresses in other GPUs' memory: where this plan's rows start in each peer's whole C)."""
+        a = GemmRunArgs()
+        a.A, a.B, a.C = _ptr(A), _ptr(B), _ptr(Cout)
+        a.scale_a, a.scale_b = _ptr(scale_a), _ptr(scale_b)
+        a.workspace = _ptr(workspace)
+        a.workspace_bytes = 0 if workspace is None else (
+            workspace.numel() * workspace.element_size() if hasattr(workspace, "numel") else self.workspace_bytes)
+        a.device_status = _ptr(status)
+        a.stream = stream or None
+        a.row_reduce_dst = _ptr(row_reduce_dst)
+        a.n_peers = len(peers)
+        for i, q in enumerate(peers):
+            a.peer_c[i] = _ptr(q)
+        _check(lib().frisk_b200_gemm_run_ex(self._h, C.byref(a)), "gemm_run_ex")
 
     def run_host(self, A: np.ndarray, B: np.ndarray, Cout: np.ndarray,
                  scale_a: Optional[np.ndarray] = None, scale_b: Optional[np.ndarray] = None) -> None:

@@ -231,6 +231,37 @@ def max_rel_error(c: np.ndarray, ref: np.ndarray, absdot: np.ndarray | None = No
     return float(np.max(np.abs(c - ref) / den))
 
 
+def parity_metrics(c: np.ndarray, ref: np.ndarray, absdot: np.ndarray | None = None,
+                   bound: float | None = None) -> dict:
+    """Every error figure the parity tests report for one result, side by side:
+
+    * ``rel_frobenius``: ||c - r||_F / ||r||_F;
+    * ``max_rel_rms_floor``: max |c - r| / max(|r|, 1e-3 rms(r)) -- the floor relative to the
+      size of a typical output;
+    * ``max_rel_data_floor``: the same with the floor 1e-3 sum_k |a||b| (needs ``absdot``) --
+      relative to the data behind each output, the one that stays meaningful for long K;
+    * ``below_rms_floor``: the share of outputs whose |r| lies under the rms floor (the outputs
+      on which the two floors differ);
+    * ``over_bound_rms_floor`` (with ``bound``): the share of outputs whose rms-floor error exceeds
+      the bound, and ``over_bound_all_below_floor``: whether every one of them is an output under
+      the floor (a cancellation-sized value, where the floor, not |r|, is the denominator).
+    """
+    c = np.asarray(c, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    rms_floor = max(1e-3 * float(np.sqrt(np.mean(ref * ref))), 1e-300)
+    out = {
+        "rel_frobenius": rel_frobenius(c, ref),
+        "max_rel_rms_floor": max_rel_error(c, ref),
+        "max_rel_data_floor": None if absdot is None else max_rel_error(c, ref, absdot),
+        "below_rms_floor": float(np.mean(np.abs(ref) < rms_floor)),
+    }
+    if bound is not None:
+        over = np.abs(c - ref) / np.maximum(np.abs(ref), rms_floor) > bound
+        out["over_bound_rms_floor"] = float(np.mean(over))
+        out["over_bound_all_below_floor"] = bool(np.all(np.abs(ref)[over] < rms_floor))
+    return out
+
+
 TOLERANCE = {  # (metric, bound) per input type
     F32: ("rel_frobenius", 1e-4),
     F16: ("max_rel", 1e-2),

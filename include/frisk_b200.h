@@ -86,6 +86,17 @@ typedef struct frisk_gemm_desc {
   int32_t stages;       /* TMA pipeline depth                                                */
   int32_t num_ctas;     /* persistent grid size                                              */
   int32_t band_tiles;   /* tile rows walked together by the rasterisation (L2 reuse)         */
+  int32_t epilogue;     /* whole-tile tensor-core plans: 1 = every thread stores its own row
+                           pieces, 2 = rows staged through shared memory and stored as 128-byte
+                           pieces (needs a 16-byte aligned C and row pitch, else 1 is used)     */
+  /* A frisk.reduce of C over its columns (dim 1), executed inside the GEMM's epilogue instead of
+   * a second pass over C (the reference's sketches reduce the accumulator of a gemm this way:
+   * tmp/ir.mlir:116, 135).  row_reduce = 1 + frisk_reduce_kind, 0 = none.  The fold sees the
+   * values of C as stored (after the cast), so it equals frisk_b200_reduce_run on the finished C
+   * for min and max and differs from it only in summation order for add and mul.  The result,
+   * [M] of C's element type, goes to frisk_gemm_run_args.row_reduce_dst.                      */
+  int32_t row_reduce;
+  int32_t row_reduce_clear; /* 1: dst = fold, 0: dst = dst (op) fold (the op's `clear`)        */
 } frisk_gemm_desc;
 
 typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */
@@ -100,7 +111,20 @@ typedef struct frisk_gemm_plan_info {
   int32_t smem_bytes;  /* dynamic shared memory per CTA                                      */
   int32_t launches;    /* kernels launched per run                                           */
   int32_t swizzle_a, swizzle_b; /* TMA/UMMA swizzle width in bytes (0, 32, 64, 128)          */
+  int32_t cuda_core_reason; /* FRISK_TC_*: why a plan resolved to FRISK_KERNEL_SIMT (0 if not) */
+  int64_t cuda_core_runs;   /* runs of a tensor-core plan that took the CUDA-core kernel
+                               because A or B was not 16-byte aligned (about 100x slower)     */
 } frisk_gemm_plan_info;
+
+/* Why a problem cannot run on the tensor-core kernels (frisk_gemm_plan_info.cuda_core_reason). */
+enum {
+  FRISK_TC_OK = 0,
+  FRISK_TC_INPUT_TYPE = 1, /* A and B are not fp16, bf16 or e4m3                              */
+  FRISK_TC_PITCH = 2,      /* a row pitch of A or B is not a multiple of 16 bytes (TMA rule)   */
+  FRISK_TC_EXTENT = 3,     /* M, N or K is 2^31 or more                                        */
+  FRISK_TC_FP8_ORDER = 4,  /* e4m3 operands are taken K-inner only (transA = 0, transB = 1)    */
+  FRISK_TC_FORCED = 5      /* desc.force_kernel asked for the CUDA-core kernel                 */
+};
 
 /* Replaces: nothing executable in the reference.  The closest reference interface is
  * builder.create_gemm_op (ffi/ir.cpp:322-366), whose shape and dtype checks are repeated here:
@@ -110,8 +134,8 @@ void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* plan);
 int frisk_b200_gemm_plan_info(const frisk_gemm_plan* plan, frisk_gemm_plan_info* out);
 
 /* Bytes of device scratch `run` needs.  0 for every plan but the stream-K form of the few-row
- * plan (few-row shapes whose tiles cannot be covered by thread-block clusters); `run` then takes
- * a NULL workspace. */
+ * plan (few-row shapes whose tiles cannot be covered by thread-block clusters) and plans with a
+ * fused row reduce (one fp32 per row and half tile); `run` takes a NULL workspace when it is 0. */
 int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* plan, size_t* out);
 
 /*
@@ -119,12 +143,57 @@ int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* plan, size_t* out);
  * Asynchronous and stream-ordered.  scale_a ([M] fp32) and scale_b ([N] fp32) are used only
  * when desc.scale_mode == FRISK_SCALE_ROW_COL.  `device_status` may be NULL; otherwise it
  * points to one int32 in device memory that a kernel ORs a non-zero code into when one of its
- * bounded waits ran out (read it with frisk_b200_check_status after synchronising).
+ * bounded waits ran out (read it with frisk_b200_check_status after synchronising).  With a NULL
+ * device_status a wait that runs out is not reported at all: the kernel returns and C is left
+ * partly written.
+ * `workspace` (see frisk_b200_gemm_workspace_bytes) is scratch: it need not keep its contents
+ * between runs and may be shared by plans whose runs do not overlap on the GPU.
  * The executor behind the op created by ffi/ir.cpp:362.
  */
 int frisk_b200_gemm_run(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
                         const float* scale_a, const float* scale_b, void* workspace,
                         size_t workspace_bytes, int32_t* device_status, void* stream);
+
+/*
+ * frisk_b200_gemm_run with every argument in one struct, plus the two things the plain call has
+ * no room for: the destination of a fused row reduce, and copies of C for other GPUs.
+ *
+ * peer_c: the row-sharded GEMM (frisk_b200_shard_rows) with the all-gather of C folded into the
+ * kernel.  Entry q points, in the memory of another GPU of the node (a peer-mapped pointer:
+ * frisk_b200_peer_open, or any pointer this device can store to), to where THIS rank's rows
+ * start in that GPU's copy of the whole C; same element type and ldc as C.  The epilogue stores
+ * every tile to C and to each peer copy with ordinary global stores -- nothing is loaded from a
+ * peer.  The caller orders the ranks: every peer buffer must be allocated before the launch,
+ * and a rank may read its copy only after all ranks' launches have completed (a barrier after
+ * synchronising the stream).  Whole-tile tensor-core plans only; at most 7 peers.
+ */
+typedef struct frisk_gemm_run_args {
+  const void* A;
+  const void* B;
+  void* C;
+  const float* scale_a;
+  const float* scale_b;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* device_status;
+  void* stream;
+  void* row_reduce_dst; /* needed iff desc.row_reduce != 0                                    */
+  int32_t n_peers;
+  void* peer_c[7];
+} frisk_gemm_run_args;
+int frisk_b200_gemm_run_ex(frisk_gemm_plan* plan, const frisk_gemm_run_args* args);
+
+/*
+ * Device buffers another process of the node can store into (one process per GPU): peer_alloc
+ * allocates `bytes` on the current device and fills a 64-byte handle to send to the other
+ * processes (any byte transport); peer_open maps the buffer behind a handle received from another
+ * process into this one and enables peer access.  Thin wrappers of cudaMalloc / cudaIpcGetMemHandle
+ * / cudaIpcOpenMemHandle / cudaIpcCloseMemHandle / cudaFree.  No counterpart in the reference.
+ */
+int frisk_b200_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+int frisk_b200_peer_open(const unsigned char handle[64], void** ptr);
+int frisk_b200_peer_close(void* ptr);
+int frisk_b200_peer_free(void* ptr);
 
 /*
  * The same GEMM for callers that hold HOST buffers (what a binding of the reference's Python
@@ -133,6 +202,8 @@ int frisk_b200_gemm_run(frisk_gemm_plan* plan, const void* A, const void* B, voi
  * row-major A the rows go through in up to 16 chunks on three streams, so the upload of one chunk,
  * the GEMM of the previous and the download of the one before overlap.  Device buffers are
  * cached in the plan between calls.  Returns FRISK_ERR_DEVICE_TIMEOUT if the status word came back set.
+ * Only the elements of each stored row are read and written, so a host buffer may end after the
+ * last row's elements: (rows - 1) * ld + row length elements are enough.
  */
 int frisk_b200_gemm_run_host(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
                              const float* scale_a, const float* scale_b);

@@ -84,6 +84,27 @@ def test_plan_falls_back_to_simt_for_unaligned_leading_dimensions():
     p.close()
 
 
+def test_plan_info_says_why_a_plan_runs_on_cuda_cores():
+    """FRISK_TC_* of include/frisk_b200.h: a plan that resolved to the CUDA-core kernel names the
+    rule that kept it off the tensor cores, so a 100x slower run is never a silent one."""
+    cases = [
+        (dict(ab=W.F32), 1),                                   # FRISK_TC_INPUT_TYPE
+        (dict(ab=W.BF16, lda=101), 2),                         # FRISK_TC_PITCH
+        (dict(ab=W.E4M3, ct=W.BF16, transB=False), 4),         # FRISK_TC_FP8_ORDER
+        (dict(ab=W.BF16, force_kernel="simt"), 5),             # FRISK_TC_FORCED
+    ]
+    for kw, reason in cases:
+        kw = dict(kw)
+        ab, ct = kw.pop("ab"), kw.pop("ct", None)
+        p = R.GemmPlan(96, 112, 96, ab, ct, **kw)
+        assert p.info["kernel_name"] == "simt" and p.info["cuda_core_reason"] == reason, (kw, p.info)
+        assert p.info["cuda_core_runs"] == 0
+        p.close()
+    p = R.GemmPlan(256, 256, 256, W.BF16)
+    assert p.info["cuda_core_reason"] == 0
+    p.close()
+
+
 def test_plan_create_rejects_bad_descriptions():
     for kw in (dict(M=0), dict(K=-1), dict(lda=3), dict(ldc=5), dict(stages=-1), dict(band_tiles=-2)):
         args = dict(M=8, N=8, K=8)

@@ -48,6 +48,8 @@ def test_variants_lift(dims, tile, dtype, acc, kstep):
     ("grid_short", "cover A exactly"),
     ("extra_fill", "unexpected frisk.fill in the k loop"),
     ("gemm_clears", "must accumulate"),
+    ("gemm_trans_b", "must not transpose"),
+    ("gemm_scaled", "must not carry scale operands"),
 ])
 def test_everything_else_is_refused_with_the_reason(tweak, reason):
     m = build_tiled_matmul(512, 512, 256, 128, 128, 32, tweak=tweak)

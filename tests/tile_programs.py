@@ -10,7 +10,10 @@ def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kste
     b = F.builder(ctx)
     module = b.create_module()
     module.context = ctx
-    ty = {"fp16": b.get_f16_ty, "bf16": b.get_bf16_ty, "fp32": b.get_f32_ty}[dtype]()
+    if tweak == "gemm_scaled":  # scales go with 8-bit float tiles only
+        dtype = "e4m3fn"
+    ty = {"fp16": b.get_f16_ty, "bf16": b.get_bf16_ty, "fp32": b.get_f32_ty,
+          "e4m3fn": b.get_f8e4m3fn_ty}[dtype]()
     mk = lambda shape: b.get_memref_ty(ty, shape, F.AffineMap(), F.MemorySpace.GLOBAL)
     kernel = b.create_kernel_op(module, "matmul", b.get_kernel_ty([mk([M, K]), mk([K, N]), mk([M, N])]))
     module.push_back(kernel)
@@ -27,6 +30,9 @@ def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kste
     sA = b.create_alloc_buffer_op([TM, TK], dtype, F.MemorySpace.SHARED, 1024).get_result(0)
     sB = b.create_alloc_buffer_op([TK, TN], dtype, F.MemorySpace.SHARED, 1024).get_result(0)
     acc = b.create_alloc_buffer_op([TM, TN], dtype, F.MemorySpace.LOCAL).get_result(0)
+    if tweak == "gemm_scaled":
+        assert TM == TN
+        sS = b.create_alloc_buffer_op([TM], "fp32", F.MemorySpace.SHARED).get_result(0)
     d0, d1 = b.get_affine_dim_expr(0), b.get_affine_dim_expr(1)
     c = b.get_affine_constant_expr
     zero = F.AffineMap.get(0, 0, [c(0), c(0)], ctx)
@@ -46,7 +52,10 @@ def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kste
         b.create_copy_op(B, sB, [k, bx], [], map_b, zero, [TK, TN], [TK, TN])
         if tweak == "extra_fill":
             b.create_fill_op(sA, 0.0, dtype)
-        b.create_gemm_op(sA, sB, acc, False, False, tweak == "gemm_clears")
+        if tweak == "gemm_scaled":
+            b.create_gemm_op(sA, sB, acc, False, False, False, sS, sS)
+        else:
+            b.create_gemm_op(sA, sB, acc, False, tweak == "gemm_trans_b", tweak == "gemm_clears")
 
     b.create_for_op(0, (K // TK) * kstep, kstep, loop)
     if tweak != "no_store":

@@ -9,7 +9,9 @@ B replicated, no collective on the data path (strong scaling: the total work is 
 prints ONE JSON line: whole-job TFLOP/s with inputs resident in HBM (`value`), the same metric
 through the host-buffer C-ABI call with the copies inside the timed region (`e2e`), the roofline
 of the dominant kernel, the CPU baseline (the oracle port on the host cores) and, at N=1, the
-other benchmark configurations under `other_configs`.
+other benchmark configurations under `other_configs`.  At N > 1 the line also carries every
+rank's time and SM clock (`clocks_per_rank`, `clock_normalised`) and the all-gather of C measured
+two ways (`allgather`: NCCL after the GEMM, and folded into the GEMM's epilogue).
 
 `--impl reference` times the CPU restatement of the op (the reference has no GEMM implementation
 of its own to run) on a bounded sample of the same workload, with all host threads.
@@ -39,20 +41,25 @@ AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3}
 C_TYPE = {"cfg1": W.F32, "cfg2": W.F16}
 TRANS_B = {"cfg2", "cfg4"}
 BOUND = {"cfg3": "hbm"}  # everything else is measured against the tensor-core peak
-# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
-# from the ncu captures summarised under profiles/; None where no capture exists.
+# DRAM bytes per launch of the dominant kernel (ncu: dram__bytes_read.sum + dram__bytes_write.sum
+# of one captured launch, `--clock-control none`); None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    # profiles/gemm_tcgen05_pair_bf16_8192.md (bands of 8 tile rows): 1089.2 MB read + 126.2 MB written
+    # CTA-pair kernel, bf16 8192^3, bands of 8 tile rows: 1089.2 MB read + 126.2 MB written
     "bf16_8192": 1215415552,
-    # cfg5 is scaled from the 8192-row capture by the rows a rank holds: it is that many row slabs
-    # against the same B, walked band by band, so the traffic grows with the rows (roofline_for)
-    # profiles/gemm_skinny_cluster_cfg3.md: 134.57 MB read + 4.01 MB written
+    # cfg5: see CFG5_SLAB_TRAFFIC below
+    # few-row cluster plan, cfg3: 134.57 MB read + 4.01 MB written
     "cfg3": 138584832,
-    # profiles/reduce_8192.md: read + written per step (the column reduce: both of its launches)
+    # frisk.reduce, 8192 x 8192: read + written per step (the column reduce: both of its launches)
     "row_max_f16": 134233088 + 3560960,
     "row_sum_f32": 268450048 + 3368960,
     "col_min_f16": 134231040 + 3605248 + 1222144,
 }
+# cfg5's launch (2.1 GB resident, 6 ms) is beyond what a multi-pass capture should hold, so its
+# DRAM traffic is measured on a slab of CFG5_SLAB_ROWS rows of the same problem (same B, same
+# band walk) and scaled by the rows a rank holds: the bands are walked one after the other, each
+# streaming all of B past its own rows of A, so the bytes grow in proportion to the rows.
+CFG5_SLAB_ROWS = 8192
+CFG5_SLAB_TRAFFIC = 1215415552
 
 
 def load_peaks() -> dict:
@@ -118,18 +125,37 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+TORCH_BITS = {W.F32: "float32", W.F16: "float16", W.BF16: "bfloat16", W.E4M3: "float8_e4m3fn"}
+
+
 def device_inputs(torch, name, M, N, K, dev, seed):
-    """Synthetic inputs of the workload's shapes and distributions, drawn on the device."""
+    """Synthetic inputs of the workload's shapes and distributions.
+
+    cfg1, cfg2 and cfg3 at their full sizes are the bits the parity tests run on: drawn on the
+    host with the pinned generator (numpy default_rng(seed); A, then B, as float32 in C order,
+    rounded to nearest even) and copied up.  The large problems (cfg4, cfg5, bf16 8192^3, and any
+    row shard) are drawn on the device from a torch generator with the same distributions and,
+    for cfg4, the same quantisation: q = sat_e4m3(rne(X / s)), so the operands sit where the real
+    ones sit (most of the e4m3 range in use, part of it saturated), not near +-1.
+    """
     ab = AB_TYPE.get(name, W.BF16)
+    if name in ("cfg1", "cfg2", "cfg3") and (M, N, K) == FULL_DIMS[name]:
+        w = W.make_workload(name)
+        tdt = getattr(torch, TORCH_BITS[ab])
+        view = {W.F32: np.float32, W.F16: np.float16, W.BF16: np.int16}[ab]
+        A = torch.from_numpy(np.ascontiguousarray(w.A).view(view)).to(dev).view(tdt)
+        B = torch.from_numpy(np.ascontiguousarray(w.B).view(view)).to(dev).view(tdt)
+        return A, B, None, None
     g = torch.Generator(device=dev).manual_seed(seed)
     a_shape = (M, K)
     b_shape = (N, K) if name in TRANS_B else (K, N)
     sa = sb = None
     if ab == W.E4M3:
-        A = torch.randn(a_shape, generator=g, device=dev).clamp_(-448, 448).to(torch.float8_e4m3fn)
-        B = torch.randn(b_shape, generator=g, device=dev).clamp_(-448, 448).to(torch.float8_e4m3fn)
         sa = (torch.rand(M, generator=g, device=dev) * 1.5 + 0.5) / 448.0
         sb = (torch.rand(N, generator=g, device=dev) * 1.5 + 0.5) / 448.0
+        # B is stored [N, K] (K-inner): row n is column n of the logical B, scaled by 1 / sb[n]
+        A = (torch.randn(a_shape, generator=g, device=dev) / sa[:, None]).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        B = (torch.randn(b_shape, generator=g, device=dev) / sb[:, None]).clamp_(-448, 448).to(torch.float8_e4m3fn)
     elif ab == W.F32:
         A = torch.rand(a_shape, generator=g, device=dev) * 2 - 1
         B = torch.rand(b_shape, generator=g, device=dev) * 2 - 1
@@ -190,27 +216,88 @@ def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False)
     return ms, info, note
 
 
-def roofline_for(name, M, N, K, ms, peaks, sustained):
+def measure_tensor_peaks(torch, R, dev, like_ms):
+    """Tensor-pipe denominators measured on this device in this run, for the operand types the
+    driver-written peaks file does not cover (it holds a cuBLAS bf16 figure only):
+
+    * ``mma_only``: every SM pair issuing tcgen05.mma back to back from resident shared memory
+      (frisk_b200_measure_mma_peak), launch length matched to `like_ms` per type because the
+      clock under the power cap depends on how long the pipes stay busy;
+    * ``cublaslt_e4m3``: torch._scaled_mm (cuBLASLt) on e4m3 8192^3, best of 10 -- the library
+      figure of the same kind as the bf16 one in the peaks file.
+    """
+    out = {}
+    for key, ab in (("e4m3", W.E4M3), ("bf16", W.BF16)):
+        try:
+            probe = R.measure_mma_peak(ab, pair=True, k_blocks=1024, reps=5)
+            want = like_ms.get(key, probe["ms_per_launch"])
+            kb = int(max(32, round(1024 * want / probe["ms_per_launch"] / 32) * 32))
+            best = max((R.measure_mma_peak(ab, pair=True, k_blocks=kb, reps=10) for _ in range(3)),
+                       key=lambda r: r["tflops"])
+            out["mma_only_" + key] = {"tflops": round(best["tflops"], 1), "ms_per_launch": round(best["ms_per_launch"], 4),
+                                      "k_blocks": kb, "shape": "256x256x(32 bytes) two-SM MMAs, 74 pairs"}
+        except Exception as e:  # the figure is reported, never required
+            out["mma_only_" + key] = {"error": str(e)}
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev)
+        for _ in range(3):
+            torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        out["cublaslt_e4m3"] = {"tflops": round(2.0 * n ** 3 / (best * 1e-3) / 1e12, 1), "ms": round(best, 4),
+                                "how": "torch._scaled_mm e4m3 8192^3 -> bf16, best of 10, CUDA events"}
+        del a, b
+    except Exception as e:
+        out["cublaslt_e4m3"] = {"error": str(e)}
+    return out
+
+
+def roofline_for(name, M, N, K, ms, peaks, sustained, tensor_peaks=None):
     ab, ct = AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16)
+    extra = {}
     if BOUND.get(name) == "hbm":
         alg = M * K * W.ELEM_SIZE[ab] + K * N * W.ELEM_SIZE[ab] + M * N * W.ELEM_SIZE[ct]
         achieved = alg / (ms * 1e-3) / 1e9
         peak = peaks["hbm_gbs"]
         unit = "GB/s"
+        source = peaks["source"]
     else:
         achieved = 2.0 * M * N * K / (ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+        source = peaks["source"] + (" (sustained)" if sustained else " (burst)")
+        unit = "TFLOP/s"
         if ab == W.E4M3:
-            peak *= 2.0  # fp8 runs at twice the bf16 rate; only the bf16 peak is measured
+            # no e4m3 figure in the peaks file: the denominator is the tensor pipes' own rate
+            # measured in this run; the library figure and the nominal one are given beside it
+            tp = tensor_peaks or {}
+            mma = tp.get("mma_only_e4m3", {}).get("tflops")
+            lib = tp.get("cublaslt_e4m3", {}).get("tflops")
+            if mma:
+                peak, source = mma, "measured mma-only"
+            else:
+                peak, source = 2.0 * peak, "2 x " + source + " (no e4m3 peak could be measured)"
+            extra = {"frac_of_cublaslt_e4m3": None if not lib else round(achieved / lib, 4),
+                     "frac_of_nominal_4500": round(achieved / 4500.0, 4),
+                     "frac_of_2x_cublas_bf16": round(achieved / (2.0 * peaks["bf16_tflops"]), 4)}
         if ab == W.F32:
             peak = None  # CUDA-core kernel: no tensor roofline applies
-        unit = "TFLOP/s"
-    return {"bound": BOUND.get(name, "tensor"), "achieved": round(achieved, 2),
-            "peak": None if peak is None else round(peak, 1), "unit": unit,
-            "frac": None if peak is None else round(achieved / peak, 4),
-            "traffic": (NCU_TRAFFIC_BYTES["bf16_8192"] * M // 8192 if name == "cfg5"
-                        else NCU_TRAFFIC_BYTES.get(name)),
-            "peak_source": peaks["source"] + (" (sustained)" if sustained and unit == "TFLOP/s" else " (burst)" if unit == "TFLOP/s" else "")}
+    out = {"bound": BOUND.get(name, "tensor"), "achieved": round(achieved, 2),
+           "peak": None if peak is None else round(peak, 1), "unit": unit,
+           "frac": None if peak is None else round(achieved / peak, 4),
+           "traffic": (CFG5_SLAB_TRAFFIC * M // CFG5_SLAB_ROWS if name == "cfg5"
+                       else NCU_TRAFFIC_BYTES.get(name)),
+           "peak_source": source}
+    out.update(extra)
+    return out
 
 
 REDUCE_CASES = (
@@ -366,11 +453,16 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer measurement")
+    ap.add_argument("--no-allgather", action="store_true", help="skip the all-gather measurements (N > 1)")
     ap.add_argument("--reduce-only", action="store_true",
                     help="time only the frisk.reduce cases, with exactly --warmup and --steps launches each "
                          "(a small run for a profiler), and print their JSON")
     ap.add_argument("--band", type=int, default=0,
                     help="tile rows the rasterisation walks together (0: the plan's choice)")
+    ap.add_argument("--epilogue", type=int, default=0,
+                    help="1: per-thread row stores, 2: rows staged through shared memory (0: the plan's choice)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="run the workload on this many rows only (a small case for a profiler)")
     args = ap.parse_args()
     asked_warmup = args.warmup
     args.warmup = max(args.warmup, 3)
@@ -404,16 +496,20 @@ def main():
 
     name = args.workload
     M, N, K = FULL_DIMS[name]
+    if args.rows:
+        M = args.rows
+        args.warmup = asked_warmup   # a profiler's small case: exactly the launches asked for
     row0, rows = S.local_rows(M, world, rank)
     peaks = load_peaks()
+    ab, ct = AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16)
 
     # ---- device-resident timing: K steps, barrier + synchronize on both sides, max over ranks
     A, B, sa, sb = device_inputs(torch, name, rows, N, K, dev, seed=4 + 1000 * rank)
     if world > 1:  # B is replicated: every rank holds rank 0's B
         dist.broadcast(B, 0)
     C = torch.empty((rows, N), device=dev, dtype=out_dtype(torch, name))
-    plan = R.GemmPlan(rows, N, K, AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16),
-                      transB=name in TRANS_B, scales=sa is not None, band_tiles=args.band)
+    plan = R.GemmPlan(rows, N, K, ab, ct, transB=name in TRANS_B, scales=sa is not None,
+                      band_tiles=args.band, epilogue=args.epilogue)
     ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
@@ -424,9 +520,8 @@ def main():
     torch.cuda.synchronize()
     R.check_status(status, stream)
 
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
+    sampler = ClockSampler(local)   # every rank samples its own GPU
+    sampler.start()
     if dist:
         dist.barrier()
     torch.cuda.synchronize()
@@ -437,9 +532,9 @@ def main():
             plan.run(A, B, C, sa, sb, ws, status, stream)
         e1.record()
         torch.cuda.synchronize()
-        elapsed_ms = e0.elapsed_time(e1)
+        my_ms = e0.elapsed_time(e1)
     else:
-        elapsed_ms = 0.0
+        my_ms = 0.0
         for _ in range(args.steps):
             flush.fill_(1)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -447,33 +542,38 @@ def main():
             plan.run(A, B, C, sa, sb, ws, status, stream)
             e1.record()
             torch.cuda.synchronize()
-            elapsed_ms += e0.elapsed_time(e1)
+            my_ms += e0.elapsed_time(e1)
     if dist:
         dist.barrier()
     R.check_status(status, stream)
-    elapsed_ms = S.max_over_ranks(dist, elapsed_ms, dev)
-    clocks = sampler.stop() if sampler else None
+    my_clocks = sampler.stop()
+    elapsed_ms = S.max_over_ranks(dist, my_ms, dev)
     ms_per_step = elapsed_ms / args.steps
     total_flops = 2.0 * M * N * K
     value = total_flops / (ms_per_step * 1e-3) / 1e12
+    # per rank: time and the clock it ran at.  The product ms x MHz is the time in SM cycles: it
+    # separates what the sharding does from what the power cap does to the clock (a long 1-GPU step
+    # is pulled down by the cap, the short per-rank steps at 8 GPUs are not).
+    per_rank = [{"rank": rank, "ms_per_step": round(my_ms / args.steps, 4), "sm_mhz": my_clocks.get("sm_mhz"),
+                 "reasons": my_clocks.get("reasons")}]
+    if dist:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, per_rank[0])
+        per_rank = gathered
+    slowest = max(per_rank, key=lambda r: r["ms_per_step"])
+    clock_note = None
+    if slowest.get("sm_mhz"):
+        clock_note = {"slowest_rank": slowest["rank"], "slowest_rank_sm_mhz": slowest["sm_mhz"],
+                      "rank0_sm_mhz": per_rank[0].get("sm_mhz"),
+                      "mcycles_per_step": round(ms_per_step * slowest["sm_mhz"] * 1e-3, 3),
+                      "note": "ms_per_step x median SM MHz of the slowest rank = SM cycles per step (millions); "
+                              "compare this across N, not ms, to judge the sharding apart from the power cap"}
 
-    # ---- optional all-gather of C over NVLink (not on the data path; reported separately)
+    # ---- the all-gather of C over NVLink (not on the data path; never inside `value`)
     allgather = None
-    if dist and world > 1 and M % world == 0:
-        for _ in range(2):
-            full = S.allgather_rows(dist, C, M, world, rank)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(5):
-            full = S.allgather_rows(dist, C, M, world, rank)
-        e1.record()
-        torch.cuda.synchronize()
-        ag_ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / 5, dev)
-        recv = (world - 1) * rows * N * C.element_size()
-        allgather = {"ms": round(ag_ms, 3), "recv_GBps_per_gpu": round(recv / (ag_ms * 1e-3) / 1e9, 1),
-                     "note": "ncclAllGather of the C shards, after the GEMM, not in `value`"}
-        del full
+    if dist and world > 1 and M % world == 0 and not args.no_allgather:
+        allgather = time_allgather(torch, R, S, dist, plan, A, B, C, sa, sb, ws, status, stream, M, N, world, rank,
+                                   dev, ms_per_step, max(3, min(args.steps, 10)))
 
     # ---- end to end: host buffers through the C-ABI call, copies inside the timed region
     e2e = None
@@ -520,12 +620,15 @@ def main():
         return
 
     sustained = elapsed_ms > 500.0
-    roof = roofline_for(name, rows, N, K, ms_per_step, peaks, sustained)
+    tensor_peaks = None
+    if ab == W.E4M3:
+        tensor_peaks = measure_tensor_peaks(torch, R, dev, {"e4m3": ms_per_step})
+    roof = roofline_for(name, rows, N, K, ms_per_step, peaks, sustained, tensor_peaks)
     line = {
         "metric": "gemm_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": W.DTYPE_NAMES[AB_TYPE.get(name, W.BF16)], "data": "synthetic",
+        "dtype": W.DTYPE_NAMES[ab], "data": "synthetic",
         "config": {"workload": name, "M": M, "N": N, "K": K, "rows_per_gpu": rows,
                    "sharding": f"rows of A and C over {world} GPU(s), B replicated, no collective",
                    "accumulate": "fp32", "kernel": info["kernel_name"],
@@ -533,15 +636,19 @@ def main():
                    "stages": info["stages"], "ctas": info["num_ctas"],
                    "l2": "inputs larger than L2" if flush is None else "192 MiB written between iterations"},
         "roofline": roof,
-        "clocks": clocks,
+        "clocks": {k: my_clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "samples")},
+        "clocks_per_rank": per_rank,
+        "clock_normalised": clock_note,
         "gpu_launches": info["launches"] * args.steps,
         "e2e": e2e,
     }
     if allgather:
         line["allgather"] = allgather
 
-    if world == 1 and not args.no_others:
+    if world == 1 and not args.no_others and not args.rows:
         others = {}
+        tensor_peaks = measure_tensor_peaks(torch, R, dev, {"e4m3": 0.37, "bf16": 0.70})
+        line["tensor_peaks_measured"] = tensor_peaks
         for other in ("cfg1", "cfg2", "cfg3", "cfg4", "bf16_8192"):
             if other == name:
                 continue
@@ -551,22 +658,111 @@ def main():
                                              max(args.steps, 200 if small else 10), args.warmup, dev,
                                              seed=int(other[-1]) if other[-1].isdigit() else 5,
                                              rotate=small)
-            r = roofline_for(other, m, n, k, ms, peaks, sustained=False)
+            r = roofline_for(other, m, n, k, ms, peaks, False, tensor_peaks)
             others[other] = {"ms": round(ms, 5), "kernel": oinfo["kernel_name"],
                              "tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 2),
                              "launches_per_step": oinfo["launches"], "roofline": r,
                              "l2": l2_note}
+            if other == "cfg2":
+                others[other]["library_same_shape"] = library_matmul(torch, dev, m, n, k, torch.float16)
         line["other_configs"] = others
         line["reduce"] = time_reduce(torch, R, dev, max(args.steps, 30), max(args.warmup, 3), peaks,
                                      not args.no_cpu)
 
-    if world == 1 and not args.no_cpu:
+    if world == 1 and not args.no_cpu and not args.rows:
         line["cpu_baseline"] = cpu_baseline(name)
     else:
         line["cpu_baseline"] = None
     print(json.dumps(line), flush=True)
     if dist:
         dist.destroy_process_group()
+
+
+def library_matmul(torch, dev, m, n, k, dtype):
+    """torch.matmul (cuBLAS) on the same shape with rotating operands, for context beside a
+    configuration whose roofline denominator was measured on another shape."""
+    copies = 4
+    a = [torch.randn(m, k, device=dev).to(dtype) * k ** -0.5 for _ in range(copies)]
+    b = [torch.randn(n, k, device=dev).to(dtype) * k ** -0.5 for _ in range(copies)]
+    for i in range(copies):
+        torch.matmul(a[i], b[i].t())
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = 200
+    e0.record()
+    for i in range(steps):
+        torch.matmul(a[i % copies], b[i % copies].t())
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"ms": round(ms, 5), "tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 2),
+            "how": "torch.matmul, same rotation of operands, 200 launches"}
+
+
+def time_allgather(torch, R, S, dist, plan, A, B, C, sa, sb, ws, status, stream, M, N, world, rank, dev,
+                   gemm_ms, steps):
+    """The optional all-gather of the C shards, two ways, each timed on the device (max over ranks):
+
+    * ``nccl_after``: ncclAllGather of the finished shards (the library baseline);
+    * ``fused``: the GEMM itself stores every tile into every rank's copy of C
+      (frisk_b200_gemm_run_ex with peer pointers; plain stores over NVLink, nothing loaded from a
+      peer), so the transfer runs under the math.  `gemm_plus_allgather_ms` is what a caller who
+      needs all of C everywhere waits for; `hidden` is the share of the NCCL all-gather's time
+      that the fused form no longer adds to the GEMM.
+    """
+    rows = C.shape[0]
+    es = C.element_size()
+    out = {}
+    for _ in range(2):
+        full = S.allgather_rows(dist, C, M, world, rank)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        full = S.allgather_rows(dist, C, M, world, rank)
+    e1.record()
+    torch.cuda.synchronize()
+    ag_ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / steps, dev)
+    recv = (world - 1) * rows * N * es
+    out["nccl_after"] = {"ms": round(ag_ms, 3), "recv_GBps_per_gpu": round(recv / (ag_ms * 1e-3) / 1e9, 1),
+                         "gemm_plus_allgather_ms": round(gemm_ms + ag_ms, 3)}
+    want = full[:: max(1, M // 64)].clone()   # a sample of rows of the NCCL result, to check the fused one
+    del full
+    try:
+        pg = S.PeerGather(dist, M, N, es, world, rank)
+    except Exception as e:  # no peer access between these GPUs: report it, keep the NCCL figure
+        out["fused"] = {"error": str(e)}
+        return out
+    try:
+        dist.barrier()
+        for _ in range(2):
+            plan.run_ex(A, B, pg.local_c, scale_a=sa, scale_b=sb, workspace=ws, status=status, stream=stream,
+                        peers=pg.peer_dsts)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            plan.run_ex(A, B, pg.local_c, scale_a=sa, scale_b=sb, workspace=ws, status=status, stream=stream,
+                        peers=pg.peer_dsts)
+        e1.record()
+        torch.cuda.synchronize()
+        fused_ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / steps, dev)
+        dist.barrier()   # every rank's stores have landed
+        R.check_status(status, stream)
+        got = pg.as_tensor(C.dtype)[:: max(1, M // 64)]
+        same = bool(torch.equal(got.view(torch.int16) if es == 2 else got, want.view(torch.int16) if es == 2 else want))
+        sent = (world - 1) * rows * N * es
+        out["fused"] = {"ms": round(fused_ms, 3), "sent_GBps_per_gpu": round(sent / (fused_ms * 1e-3) / 1e9, 1),
+                        "gemm_plus_allgather_ms": round(fused_ms, 3),
+                        "hidden": round((gemm_ms + ag_ms - fused_ms) / ag_ms, 3),
+                        "equals_nccl_result_on_sampled_rows": same,
+                        "how": "epilogue stores each C tile to the local shard and to the 7 (N-1) peer copies"}
+    finally:
+        torch.cuda.synchronize()
+        pg.close(dist)
+    return out
 
 
 if __name__ == "__main__":

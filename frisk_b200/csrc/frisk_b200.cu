@@ -16,6 +16,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
+#include "mma_peak.cuh"
 
 namespace {
 
@@ -84,6 +85,8 @@ struct frisk_gemm_plan {
   frisk::GemmParams gp;  // everything but pointers
   size_t ws_bytes = 0;
   size_t slot_bytes = 0;  // split mode 2: bytes of partial-tile slots before the counters
+  // fused row reduce: [2 * tiles_c][M] fp32 folds, then one arrival counter per 128 rows
+  size_t rr_partial_bytes = 0, rr_counter_bytes = 0;
   size_t dyn_smem = 0;
   // run-time caches
   CUtensorMap tmap_a, tmap_b;
@@ -91,7 +94,7 @@ struct frisk_gemm_plan {
   const void* cached_b = nullptr;
   int64_t simt_fallback_runs = 0;  // runs a tensor-core plan sent to the CUDA-core kernel
   // device buffers of frisk_b200_gemm_run_host
-  void *hA = nullptr, *hB = nullptr, *hC = nullptr, *hWs = nullptr;
+  void *hA = nullptr, *hB = nullptr, *hC = nullptr, *hWs = nullptr, *hRr = nullptr;
   float *hSa = nullptr, *hSb = nullptr;
   int32_t* hStatus = nullptr;
   cudaStream_t hstream = nullptr;
@@ -332,8 +335,16 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // split mode 3 keeps one fp32 tile behind the stage buffers: the region the cluster's partials
   // are pushed into
   const size_t red_bytes = (swap && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
-  // stages * stage_bytes + 1024 (alignment slack) + red_bytes stays within kMaxDynSmem
-  uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes) / g.stage_bytes);
+  // Whole-tile plans stage the rows of C through 16 KiB of shared memory behind the pipeline
+  // stages and store them as 128-byte pieces (measured on bf16 8192^3 and e4m3 8192^3: five, six
+  // or seven stages of 32 KiB run within 1 % of each other, so the stage this costs the CTA-pair
+  // kernel is free).  desc.epilogue = 1 stores per thread instead.
+  // The area is reserved either way: the element-wise path of a C without 16-byte alignment goes
+  // through it too.
+  const size_t epi_bytes = swap ? 0 : frisk::kEpiStageBytes;
+  g.epi_staged = (!swap && d.epilogue != 1) ? 1u : 0u;
+  // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
+  uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
   if (d.stages > 0) stages = std::min<uint32_t>(stages, (uint32_t)d.stages);
   // at least two: a stage is released only after the first MMA of the NEXT k-block was issued,
@@ -386,8 +397,16 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     const uint64_t pairs = std::min<uint64_t>((uint64_t)g.n_items, slots);
     ctas = (uint32_t)(2 * pairs);
   }
-  pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes;
+  pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes + epi_bytes;
   pl->ws_bytes = 0;
+  pl->rr_partial_bytes = pl->rr_counter_bytes = 0;
+  if (!swap && d.row_reduce) {
+    g.rr_kind = (uint32_t)d.row_reduce;
+    g.rr_clear = d.row_reduce_clear ? 1u : 0u;
+    pl->rr_partial_bytes = ((size_t)2 * g.tiles_c * (size_t)rows * sizeof(float) + 15) / 16 * 16;
+    pl->rr_counter_bytes = (((size_t)rows + 127) / 128 * sizeof(uint32_t) + 15) / 16 * 16;
+    pl->ws_bytes = pl->rr_partial_bytes + pl->rr_counter_bytes;
+  }
   if (swap && use_cluster) {
     g.split_mode = 3;
     g.cluster_k = cluster_k;
@@ -443,13 +462,13 @@ int ensure_dyn_smem(Kern kern, int device) {
   if (tracked) __atomic_store_n(&done[device], true, __ATOMIC_RELEASE);
   return FRISK_OK;
 }
-template <typename TC, bool kSplit> struct OneCtaKernelTag {};
-template <typename TC> struct PairKernelTag {};
+template <typename TC, bool kSplit, bool kFold> struct OneCtaKernelTag {};
+template <typename TC, bool kFold> struct PairKernelTag {};
 
-template <typename TC, bool kSplit>
+template <typename TC, bool kSplit, bool kFold>
 int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit>;
-  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit, kFold>;
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit, kFold>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -477,8 +496,8 @@ int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStrea
 // How many clusters of the plan's size the device can hold at once, for one C type.
 template <typename TC>
 int max_active_clusters_t(frisk_gemm_plan* pl, int* out) {
-  auto kern = frisk::gemm_tcgen05_kernel<TC, true>;
-  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, true>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_kernel<TC, true, false>;
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, true, false>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -512,14 +531,15 @@ bool skinny_clusters_fit(frisk_gemm_plan* pl) {
 
 template <typename TC>
 int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  return g.split_mode ? launch_tcgen05_ts<TC, true>(pl, g, st)
-                      : launch_tcgen05_ts<TC, false>(pl, g, st);
+  if (g.split_mode) return launch_tcgen05_ts<TC, true, false>(pl, g, st);
+  return g.rr_kind ? launch_tcgen05_ts<TC, false, true>(pl, g, st)
+                   : launch_tcgen05_ts<TC, false, false>(pl, g, st);
 }
 
-template <typename TC>
-int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_pair_kernel<TC>;
-  if (int rc = ensure_dyn_smem<PairKernelTag<TC>>(kern, pl->device)) return rc;
+template <typename TC, bool kFold>
+int launch_pair_tf(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
+  auto kern = frisk::gemm_tcgen05_pair_kernel<TC, kFold>;
+  if (int rc = ensure_dyn_smem<PairKernelTag<TC, kFold>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -537,6 +557,11 @@ int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t 
   cfg.numAttrs = 2;
   FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
   return FRISK_OK;
+}
+
+template <typename TC>
+int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
+  return g.rr_kind ? launch_pair_tf<TC, true>(pl, g, st) : launch_pair_tf<TC, false>(pl, g, st);
 }
 
 template <typename TC>
@@ -656,6 +681,9 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.force_kernel < 0 || d.force_kernel > 4 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.epilogue < 0 || d.epilogue > 2 || d.row_reduce < 0 || d.row_reduce > 4)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  d.row_reduce_clear = d.row_reduce_clear != 0;
 
   frisk_gemm_plan* pl = new (std::nothrow) frisk_gemm_plan();
   if (!pl) return FRISK_ERR_INVALID_ARGUMENT;
@@ -704,10 +732,17 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       if (const char* want_pair = getenv("FRISK_B200_PAIR")) use_pair = want_pair[0] == '1';
 #endif
     }
-    kind = skinny_ok ? FRISK_KERNEL_SKINNY
-           : use_pair ? FRISK_KERNEL_TCGEN05_PAIR
-           : tc_ok    ? FRISK_KERNEL_TCGEN05
-                      : FRISK_KERNEL_SIMT;
+    kind = (skinny_ok && !d.row_reduce) ? FRISK_KERNEL_SKINNY
+           : use_pair                    ? FRISK_KERNEL_TCGEN05_PAIR
+           : tc_ok                       ? FRISK_KERNEL_TCGEN05
+                                         : FRISK_KERNEL_SIMT;
+  }
+  // the row reduce lives in the whole-tile epilogue of the tensor-core kernels
+  if (d.row_reduce && kind != FRISK_KERNEL_TCGEN05 && kind != FRISK_KERNEL_TCGEN05_PAIR) {
+    delete pl;
+    g_last_error = "a fused row reduce needs a whole-tile tensor-core plan (fp16 / bf16 / e4m3 "
+                   "inputs with 16-byte row pitches)";
+    return FRISK_ERR_UNSUPPORTED;
   }
   if (kind == FRISK_KERNEL_SIMT) {
     pl->info.kernel = FRISK_KERNEL_SIMT;
@@ -728,6 +763,10 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     // more tiles than SMs) whole tiles are as good or better (128 x 28672 x 4096: 45 against 79 us).
     if (kind == FRISK_KERNEL_SKINNY && d.M > 64 && !d.force_kernel && pl->gp.split_mode != 3)
       plan_tcgen05(pl, /*swap=*/false, /*pair=*/false);
+    if (pl->info.kernel == FRISK_KERNEL_SKINNY && d.row_reduce) {  // a forced few-row plan
+      delete pl;
+      return FRISK_ERR_UNSUPPORTED;
+    }
   }
   *out = pl;
   return FRISK_OK;
@@ -736,7 +775,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
 void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* pl) {
   if (!pl) return;
   cudaFree(pl->hA); cudaFree(pl->hB); cudaFree(pl->hC); cudaFree(pl->hWs);
-  cudaFree(pl->hSa); cudaFree(pl->hSb); cudaFree(pl->hStatus);
+  cudaFree(pl->hSa); cudaFree(pl->hSb); cudaFree(pl->hStatus); cudaFree(pl->hRr);
   if (pl->hstream) cudaStreamDestroy(pl->hstream);
   if (pl->s_in) cudaStreamDestroy(pl->s_in);
   if (pl->s_out) cudaStreamDestroy(pl->s_out);
@@ -767,16 +806,42 @@ int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* pl, size_t* out) {
 int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
                         const float* scale_a, const float* scale_b, void* workspace,
                         size_t workspace_bytes, int32_t* device_status, void* stream) {
-  if (!pl || !A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
+  frisk_gemm_run_args a;
+  memset(&a, 0, sizeof a);
+  a.A = A; a.B = B; a.C = C;
+  a.scale_a = scale_a; a.scale_b = scale_b;
+  a.workspace = workspace; a.workspace_bytes = workspace_bytes;
+  a.device_status = device_status;
+  a.stream = stream;
+  return frisk_b200_gemm_run_ex(pl, &a);
+}
+
+int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args) {
+  if (!pl || !args) return FRISK_ERR_INVALID_ARGUMENT;
+  const void *A = args->A, *B = args->B;
+  void* C = args->C;
+  void* workspace = args->workspace;
+  if (!A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
   const frisk_gemm_desc& d = pl->d;
-  if (d.scale_mode == FRISK_SCALE_ROW_COL && (!scale_a || !scale_b))
+  if (d.scale_mode == FRISK_SCALE_ROW_COL && (!args->scale_a || !args->scale_b))
     return FRISK_ERR_INVALID_ARGUMENT;
+  if (args->n_peers < 0 || args->n_peers > frisk::kMaxPeers) return FRISK_ERR_INVALID_ARGUMENT;
+  for (int q = 0; q < args->n_peers; ++q)
+    if (!args->peer_c[q]) return FRISK_ERR_INVALID_ARGUMENT;
+  if (d.row_reduce && !args->row_reduce_dst) return FRISK_ERR_INVALID_ARGUMENT;
   if (!pl->have_device) return FRISK_ERR_NO_DEVICE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const float* sa = d.scale_mode ? scale_a : nullptr;
-  const float* sb = d.scale_mode ? scale_b : nullptr;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(args->stream);
+  const float* sa = d.scale_mode ? args->scale_a : nullptr;
+  const float* sb = d.scale_mode ? args->scale_b : nullptr;
+  const bool whole_tile_tc =
+      pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR;
 
   const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
+  if ((args->n_peers > 0 || d.row_reduce) && !(whole_tile_tc && ptr_aligned)) {
+    g_last_error = "peer copies of C and the fused row reduce exist only in the whole-tile "
+                   "tensor-core kernels (16-byte aligned A and B)";
+    return FRISK_ERR_UNSUPPORTED;
+  }
   if (pl->info.kernel != FRISK_KERNEL_SIMT && !ptr_aligned) {
     // TMA needs 16-byte aligned bases; the run still gives the right answer, about 100x slower,
     // so it is counted (plan_info.cuda_core_runs) and noted where the caller can read it
@@ -787,8 +852,8 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
     return launch_simt(d, A, B, C, sa, sb, st);  // the CUDA-core kernel has no alignment rule
 
   const bool swap = pl->info.kernel == FRISK_KERNEL_SKINNY;
-  if (swap && pl->ws_bytes) {
-    if (!workspace || workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
+  if (pl->ws_bytes) {
+    if (!workspace || args->workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
     if ((uintptr_t)workspace % 16) return FRISK_ERR_MISALIGNED;
   }
   frisk::GemmParams g = pl->gp;
@@ -805,12 +870,18 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
     pl->cached_b = B;
   }
   g.C = C;
-  g.status = device_status;
+  g.status = args->device_status;
 #ifdef FRISK_B200_MEASURE
   if (const char* dbg = getenv("FRISK_B200_DEBUG_MODE")) g.debug_mode = (uint32_t)atoi(dbg);
   if (const char* tr = getenv("FRISK_B200_TRACE")) g.trace = reinterpret_cast<long long*>(strtoull(tr, nullptr, 0));
 #endif
   g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
+  g.n_peers = (uint32_t)args->n_peers;
+  for (int q = 0; q < args->n_peers; ++q) {
+    g.peer_c[q] = args->peer_c[q];
+    // a peer copy that cannot take 16-byte stores switches every copy to element stores
+    if ((uintptr_t)args->peer_c[q] % 16) g.c_vec_ok = 0;
+  }
   if (swap) {
     // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)
     g.row_scale = sb;
@@ -828,6 +899,12 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
   } else {
     g.row_scale = sa;
     g.col_scale = sb;
+    if (d.row_reduce) {
+      g.rr_partials = reinterpret_cast<float*>(workspace);
+      g.rr_counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->rr_partial_bytes);
+      g.rr_dst = args->row_reduce_dst;
+      FRISK_CUDA(cudaMemsetAsync(g.rr_counters, 0, pl->rr_counter_bytes, st));  // as above
+    }
   }
   int rc;
   if (pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) {
@@ -846,6 +923,44 @@ int frisk_b200_gemm_run(frisk_gemm_plan* pl, const void* A, const void* B, void*
     }
   }
   return rc;
+}
+
+int frisk_b200_peer_alloc(size_t bytes, void** ptr, unsigned char handle[64]) {
+  if (!ptr || !handle || bytes == 0) return FRISK_ERR_INVALID_ARGUMENT;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle crosses the ABI as 64 bytes");
+  *ptr = nullptr;
+  void* p = nullptr;
+  FRISK_CUDA(cudaMalloc(&p, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "cudaIpcGetMemHandle");
+  }
+  memcpy(handle, &h, sizeof h);
+  *ptr = p;
+  return FRISK_OK;
+}
+
+int frisk_b200_peer_open(const unsigned char handle[64], void** ptr) {
+  if (!ptr || !handle) return FRISK_ERR_INVALID_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  *ptr = nullptr;
+  FRISK_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return FRISK_OK;
+}
+
+int frisk_b200_peer_close(void* ptr) {
+  if (!ptr) return FRISK_OK;
+  FRISK_CUDA(cudaIpcCloseMemHandle(ptr));
+  return FRISK_OK;
+}
+
+int frisk_b200_peer_free(void* ptr) {
+  if (!ptr) return FRISK_OK;
+  FRISK_CUDA(cudaFree(ptr));
+  return FRISK_OK;
 }
 
 namespace {
@@ -936,11 +1051,17 @@ int run_host_pipelined(frisk_gemm_plan* pl, const void* A, const void* B, void* 
 
 int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
                              const float* scale_a, const float* scale_b) {
+  return frisk_b200_gemm_run_host_ex(pl, A, B, C, scale_a, scale_b, nullptr);
+}
+
+int frisk_b200_gemm_run_host_ex(frisk_gemm_plan* pl, const void* A, const void* B, void* C,
+                                const float* scale_a, const float* scale_b, void* row_reduce_dst) {
   if (!pl || !A || !B || !C) return FRISK_ERR_INVALID_ARGUMENT;
   if (!pl->have_device) return FRISK_ERR_NO_DEVICE;
   const frisk_gemm_desc& d = pl->d;
   if (d.scale_mode == FRISK_SCALE_ROW_COL && (!scale_a || !scale_b))
     return FRISK_ERR_INVALID_ARGUMENT;
+  if ((d.row_reduce != 0) != (row_reduce_dst != nullptr)) return FRISK_ERR_INVALID_ARGUMENT;
   if (!pl->hA) {
     FRISK_CUDA(cudaStreamCreateWithFlags(&pl->hstream, cudaStreamNonBlocking));
     FRISK_CUDA(cudaMalloc(&pl->hA, a_bytes(d)));
@@ -952,11 +1073,16 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, 
       FRISK_CUDA(cudaMalloc(&pl->hSa, d.M * sizeof(float)));
       FRISK_CUDA(cudaMalloc(&pl->hSb, d.N * sizeof(float)));
     }
+    if (d.row_reduce) FRISK_CUDA(cudaMalloc(&pl->hRr, (size_t)d.M * elem_size(d.c_type)));
   }
   cudaStream_t st = pl->hstream;
   if (pl->n_chunks == 0) {
-    int rc = plan_host_pipeline(pl);
-    if (rc) return rc;
+    if (d.row_reduce) {
+      pl->n_chunks = 1;  // the fold's workspace belongs to the whole problem: no row chunks
+    } else {
+      int rc = plan_host_pipeline(pl);
+      if (rc) return rc;
+    }
   }
   if (pl->n_chunks > 1) return run_host_pipelined(pl, A, B, C, scale_a, scale_b);
   FRISK_CUDA(cudaMemsetAsync(pl->hStatus, 0, sizeof(int32_t), st));
@@ -968,9 +1094,21 @@ int frisk_b200_gemm_run_host(frisk_gemm_plan* pl, const void* A, const void* B, 
     FRISK_CUDA(cudaMemcpyAsync(pl->hSa, scale_a, d.M * sizeof(float), cudaMemcpyHostToDevice, st));
     FRISK_CUDA(cudaMemcpyAsync(pl->hSb, scale_b, d.N * sizeof(float), cudaMemcpyHostToDevice, st));
   }
-  int rc = frisk_b200_gemm_run(pl, pl->hA, pl->hB, pl->hC, pl->hSa, pl->hSb, pl->hWs, pl->ws_bytes,
-                               pl->hStatus, st);
+  const size_t rr_bytes = (size_t)d.M * elem_size(d.c_type);
+  if (d.row_reduce && !d.row_reduce_clear)
+    FRISK_CUDA(cudaMemcpyAsync(pl->hRr, row_reduce_dst, rr_bytes, cudaMemcpyHostToDevice, st));
+  frisk_gemm_run_args ra;
+  memset(&ra, 0, sizeof ra);
+  ra.A = pl->hA; ra.B = pl->hB; ra.C = pl->hC;
+  ra.scale_a = pl->hSa; ra.scale_b = pl->hSb;
+  ra.workspace = pl->hWs; ra.workspace_bytes = pl->ws_bytes;
+  ra.device_status = pl->hStatus;
+  ra.stream = st;
+  ra.row_reduce_dst = pl->hRr;
+  int rc = frisk_b200_gemm_run_ex(pl, &ra);
   if (rc) return rc;
+  if (d.row_reduce)
+    FRISK_CUDA(cudaMemcpyAsync(row_reduce_dst, pl->hRr, rr_bytes, cudaMemcpyDeviceToHost, st));
   // only the N columns of each row come back: padding beyond them in the caller's C stays as it was
   const size_t c_pitch = (size_t)d.ldc * elem_size(d.c_type);
   FRISK_CUDA(cudaMemcpy2DAsync(C, c_pitch, pl->hC, c_pitch, (size_t)d.N * elem_size(d.c_type),
@@ -1112,6 +1250,78 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
 }
 
 size_t frisk_b200_gemm_skinny_static_capacity(void) { return kStaticScratchFloats; }
+
+int frisk_b200_measure_mma_peak(int32_t ab_type, int32_t pair, int32_t k_blocks, int32_t reps,
+                                double* tflops, double* ms_per_launch) {
+  if (!tflops || k_blocks < 32 || k_blocks % 32 || reps < 1) return FRISK_ERR_INVALID_ARGUMENT;
+  if (ab_type != FRISK_DT_F16 && ab_type != FRISK_DT_BF16 && ab_type != FRISK_DT_E4M3)
+    return FRISK_ERR_UNSUPPORTED;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return FRISK_ERR_NO_DEVICE;
+  }
+  int major = 0, sms = 0;
+  FRISK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  FRISK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (major != 10) return FRISK_ERR_NO_DEVICE;
+  const uint32_t es = (uint32_t)elem_size(ab_type);
+  const uint32_t m = pair ? 256u : 128u, n = 256u, k_step = 32u / es;
+  const uint32_t idesc = make_idesc(ab_type, false, false, m, n);
+  const int ctas = pair ? (sms / 2) * 2 : sms;
+  const size_t smem = 4 * (128 * 128 + (pair ? 128 : 256) * 128) + 1024;
+  int32_t* status = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  FRISK_CUDA(cudaMalloc(&status, sizeof(int32_t)));
+  int rc = FRISK_OK;
+  auto fail = [&](cudaError_t e, const char* what) { rc = cuda_fail(e, what); };
+  cudaError_t e = cudaMemset(status, 0, sizeof(int32_t));
+  if (e != cudaSuccess) fail(e, "cudaMemset");
+  if (!rc && (e = cudaEventCreate(&e0)) != cudaSuccess) fail(e, "cudaEventCreate");
+  if (!rc && (e = cudaEventCreate(&e1)) != cudaSuccess) fail(e, "cudaEventCreate");
+  auto launch = [&]() -> cudaError_t {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((unsigned)ctas, 1, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = pair ? 2 : 1;
+    attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const uint32_t f8 = ab_type == FRISK_DT_E4M3;
+    if (pair)
+      return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<1>, (uint32_t)k_blocks, idesc, f8, es, status);
+    return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<0>, (uint32_t)k_blocks, idesc, f8, es, status);
+  };
+  if (!rc) {
+    e = pair ? cudaFuncSetAttribute(frisk::mma_peak_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+             : cudaFuncSetAttribute(frisk::mma_peak_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) fail(e, "cudaFuncSetAttribute");
+  }
+  for (int i = 0; !rc && i < 2; ++i)   // warm-up
+    if ((e = launch()) != cudaSuccess) fail(e, "mma_peak_kernel launch");
+  if (!rc && (e = cudaEventRecord(e0, 0)) != cudaSuccess) fail(e, "cudaEventRecord");
+  for (int i = 0; !rc && i < reps; ++i)
+    if ((e = launch()) != cudaSuccess) fail(e, "mma_peak_kernel launch");
+  if (!rc && (e = cudaEventRecord(e1, 0)) != cudaSuccess) fail(e, "cudaEventRecord");
+  if (!rc && (e = cudaEventSynchronize(e1)) != cudaSuccess) fail(e, "cudaEventSynchronize");
+  float ms = 0.f;
+  if (!rc && (e = cudaEventElapsedTime(&ms, e0, e1)) != cudaSuccess) fail(e, "cudaEventElapsedTime");
+  if (!rc) rc = frisk_b200_check_status(status, nullptr);
+  if (!rc) {
+    const double issuers = pair ? ctas / 2 : ctas;
+    const double flop = issuers * (double)k_blocks * 4.0 * 2.0 * m * n * k_step * reps;
+    *tflops = flop / (ms * 1e-3) / 1e12;
+    if (ms_per_launch) *ms_per_launch = ms / reps;
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  cudaFree(status);
+  return rc;
+}
 
 int frisk_b200_check_status(const int32_t* device_status, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -332,10 +332,13 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs& p, uint32_t row, u
 }
 
 // ---- whole-tile epilogue: values -> (row fold) -> C, directly or through shared memory ---------
-// What the whole-tile kernels need beyond EpiArgs, copied into locals like EpiArgs.
+// What the whole-tile kernels need beyond EpiArgs.  `peers` points into the kernel's parameter
+// block (GemmParams::peer_c), which is indexed at run time: the loops over the peers are kept
+// rolled, because this code shares the SM's instruction cache with the MMA issue loop and every
+// kilobyte of unrolled stores showed up in the main loop's rate.
 struct EpiExt {
   uint32_t staged, n_peers, rr_kind;
-  void* peer[kMaxPeers];
+  void* const* peers;
 };
 
 __device__ __forceinline__ float fold_identity(uint32_t rr_kind) {
@@ -362,15 +365,58 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   return v;
 }
 
-// One warp's 32 rows x NC columns of D = C (lane = row, NC * sizeof(TC) = 128 bytes when staged):
-// scale, add the old C if asked, round once, fold the rounded values into `red` (the row fold
-// sees what a reduce of the stored C would see), and store.
+// A warp's staging area holds 32 rows x 128 bytes in the 128-byte swizzle: the 16-byte chunk j of
+// row r sits at chunk position j ^ (r & 7).  A warp's 32 writes of one chunk column (lane = row)
+// and its reads of four whole rows (8 lanes per row) both touch every bank exactly four times,
+// the minimum for 512 bytes.
+__device__ __forceinline__ uint32_t staged_chunk(uint32_t stage, uint32_t r, uint32_t j) {
+  return stage + r * 128u + ((j ^ (r & 7u)) << 4);
+}
+template <typename TC>
+__device__ __forceinline__ TC* staged_elem(uint32_t stage, uint32_t r, uint32_t c) {
+  constexpr uint32_t kPerVec = 16u / (uint32_t)sizeof(TC);
+  const uint32_t a = staged_chunk(stage, r, c / kPerVec) + (c % kPerVec) * (uint32_t)sizeof(TC);
+  return reinterpret_cast<TC*>(__cvta_shared_to_generic(a));
+}
+
+// Element-wise traffic between the staging area and C, with bounds: the path of a C that cannot
+// take 16-byte accesses and of the chunk that crosses the last column.  Rolled loops, out of line.
+template <typename TC, int NC>
+__device__ __noinline__ void stage_old_c(const TC* C, int64_t ldc, uint32_t rows, uint32_t cols,
+                                         uint32_t stage, uint32_t lane, uint32_t warp_row0,
+                                         uint32_t col0) {
+#pragma unroll 1
+  for (uint32_t e = lane; e < 32u * NC; e += 32u) {
+    const uint32_t r = e / NC, c = e % NC;
+    TC v = cast_out<TC>(0.f);
+    if (warp_row0 + r < rows && col0 + c < cols) v = C[(int64_t)(warp_row0 + r) * ldc + col0 + c];
+    *staged_elem<TC>(stage, r, c) = v;
+  }
+}
+template <typename TC, int NC>
+__device__ __noinline__ void staged_rows_out(TC* C, void* const* peers, uint32_t n_peers,
+                                             int64_t ldc, uint32_t rows, uint32_t cols,
+                                             uint32_t stage, uint32_t lane, uint32_t warp_row0,
+                                             uint32_t col0) {
+#pragma unroll 1
+  for (uint32_t e = lane; e < 32u * NC; e += 32u) {
+    const uint32_t r = e / NC, c = e % NC;
+    if (warp_row0 + r >= rows || col0 + c >= cols) continue;
+    const TC v = *staged_elem<TC>(stage, r, c);
+    const int64_t off = (int64_t)(warp_row0 + r) * ldc + col0 + c;
+    C[off] = v;
+#pragma unroll 1
+    for (uint32_t q = 0; q < n_peers; ++q) reinterpret_cast<TC*>(peers[q])[off] = v;
+  }
+}
+
+// One warp's 32 rows x NC columns of D = C (lane = row; NC * sizeof(TC) = 128 bytes): scale, add
+// the old C if asked, round once, fold the rounded values into `red` (the row fold sees what a
+// reduce of the stored C would see), and store:
+//   staged: the rows go through the warp's staging area and leave as whole 128-byte row pieces,
+//           four rows per store instruction, to C and to every peer's copy;
 //   direct: every thread writes its own row piece (16-byte stores at row stride);
-//   staged: the rows go through the warp's 4 KiB of shared memory, written in the 128-byte
-//           swizzle (16-byte chunk j of row r at chunk j ^ (r & 7): a warp's 32 writes of one
-//           chunk column, and later its reads of four whole rows, each touch every bank exactly
-//           four times, the minimum), and leave as whole 128-byte row pieces, four rows per
-//           store instruction, to C and to every peer's copy.
+//   a C without 16-byte alignment, or the chunk that crosses the last column, goes element-wise.
 // `stage` is the warp's staging area (shared-memory address), `warp_row0` the D row of lane 0.
 template <typename TC, int NC>
 __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x, uint32_t stage,
@@ -378,80 +424,77 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
                                                const uint32_t (&acc)[NC], float& red) {
   constexpr int kPerVec = 16 / (int)sizeof(TC);
   constexpr int kVecs = NC / kPerVec;
+  static_assert(kVecs == 8, "a chunk is 128 bytes of a C row");
   const uint32_t row = warp_row0 + lane;
   const bool row_ok = row < p.rows;
   const bool full = col0 + NC <= p.cols;          // warp-uniform
   const bool vec = p.c_vec_ok && full;            // warp-uniform
-  TC* const crow = reinterpret_cast<TC*>(p.C) + (int64_t)row * p.ldc + col0;
+  TC* const C = reinterpret_cast<TC*>(p.C);
+  TC* const crow = C + (int64_t)row * p.ldc + col0;
   union Pack {
     uint4 u;
     TC e[kPerVec];
   };
   Pack out[kVecs];
-  const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
-  if (!p.clear_accum && row_ok) {
+  if (!p.clear_accum) {
     if (vec) {
+      if (row_ok) {
 #pragma unroll
-      for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = *reinterpret_cast<const uint4*>(crow + v0 * kPerVec);
+        for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = *reinterpret_cast<const uint4*>(crow + v0 * kPerVec);
+      }
     } else {
+      stage_old_c<TC, NC>(C, p.ldc, p.rows, p.cols, stage, lane, warp_row0, col0);
+      __syncwarp();
 #pragma unroll
-      for (int j = 0; j < NC; ++j)
-        if (col0 + j < p.cols) out[j / kPerVec].e[j % kPerVec] = crow[j];
+      for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = ld_shared_v4(staged_chunk(stage, lane, (uint32_t)v0));
+      __syncwarp();
     }
   }
+  const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
 #pragma unroll
   for (int j = 0; j < NC; ++j) {
+    const bool col_ok = full || col0 + j < p.cols;
     float v = __uint_as_float(acc[j]) * rs;
-    if (p.col_scale && (full || col0 + j < p.cols)) v *= __ldg(p.col_scale + col0 + j);
-    if (!p.clear_accum && row_ok && (full || col0 + j < p.cols)) v += cast_in<TC>(out[j / kPerVec].e[j % kPerVec]);
+    if (p.col_scale && col_ok) v *= __ldg(p.col_scale + col0 + j);
+    if (!p.clear_accum) v += cast_in<TC>(out[j / kPerVec].e[j % kPerVec]);
     const TC o = cast_out<TC>(v);
     out[j / kPerVec].e[j % kPerVec] = o;
-    if (x.rr_kind && (full || col0 + j < p.cols)) red = fold_step(x.rr_kind, red, cast_in<TC>(o));
+    if (x.rr_kind && col_ok) red = fold_step(x.rr_kind, red, cast_in<TC>(o));
   }
-  if (x.staged && vec) {
-    const uint32_t my = stage + lane * 128u;
+  if (vec && !x.staged) {
+    if (row_ok) {
 #pragma unroll
-    for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(my + (((uint32_t)v0 ^ (lane & 7u)) << 4), out[v0].u);
-    __syncwarp();
-    static_assert(kVecs == 8, "a staged row piece is 128 bytes");
+      for (int v0 = 0; v0 < kVecs; ++v0) *reinterpret_cast<uint4*>(crow + v0 * kPerVec) = out[v0].u;
+#pragma unroll 1
+      for (uint32_t q = 0; q < x.n_peers; ++q) {
+        TC* prow = reinterpret_cast<TC*>(x.peers[q]) + (int64_t)row * p.ldc + col0;
+#pragma unroll
+        for (int v0 = 0; v0 < kVecs; ++v0) *reinterpret_cast<uint4*>(prow + v0 * kPerVec) = out[v0].u;
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(staged_chunk(stage, lane, (uint32_t)v0), out[v0].u);
+  __syncwarp();
+  if (vec) {
     const uint32_t sub = lane >> 3, ch = lane & 7u;
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
       const uint32_t rr = (uint32_t)it * 4u + sub;
-      const uint4 piece = ld_shared_v4(stage + rr * 128u + ((ch ^ (rr & 7u)) << 4));
+      const uint4 piece = ld_shared_v4(staged_chunk(stage, rr, ch));
       if (warp_row0 + rr < p.rows) {
         const int64_t off = (int64_t)(warp_row0 + rr) * p.ldc + col0 + ch * kPerVec;
-        *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(p.C) + off) = piece;
-#pragma unroll
-        for (int q = 0; q < kMaxPeers; ++q)
-          if (q < (int)x.n_peers) *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(x.peer[q]) + off) = piece;
+        *reinterpret_cast<uint4*>(C + off) = piece;
+#pragma unroll 1
+        for (uint32_t q = 0; q < x.n_peers; ++q)
+          *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(x.peers[q]) + off) = piece;
       }
-    }
-    __syncwarp();   // the staging area is rewritten by the next chunk
-    return;
-  }
-  if (!row_ok) return;
-  if (vec) {
-#pragma unroll
-    for (int v0 = 0; v0 < kVecs; ++v0) {
-      *reinterpret_cast<uint4*>(crow + v0 * kPerVec) = out[v0].u;
-#pragma unroll
-      for (int q = 0; q < kMaxPeers; ++q)
-        if (q < (int)x.n_peers)
-          *reinterpret_cast<uint4*>(reinterpret_cast<TC*>(x.peer[q]) + (int64_t)row * p.ldc + col0 + v0 * kPerVec) = out[v0].u;
     }
   } else {
-#pragma unroll
-    for (int j = 0; j < NC; ++j) {
-      if (col0 + j < p.cols) {
-        crow[j] = out[j / kPerVec].e[j % kPerVec];
-#pragma unroll
-        for (int q = 0; q < kMaxPeers; ++q)
-          if (q < (int)x.n_peers)
-            (reinterpret_cast<TC*>(x.peer[q]) + (int64_t)row * p.ldc + col0)[j] = out[j / kPerVec].e[j % kPerVec];
-      }
-    }
+    staged_rows_out<TC, NC>(C, x.peers, x.n_peers, p.ldc, p.rows, p.cols, stage, lane, warp_row0, col0);
   }
+  __syncwarp();   // the staging area is rewritten by the next chunk
 }
 
 // The warp's 32 rows of one work item: `cols_item` columns from D column `col0`, accumulator
@@ -726,7 +769,8 @@ __device__ __forceinline__ void reduce_share(const EpiArgs& p, uint32_t buf, uin
 // kSplit selects the K-split (stream-K) code at compile time.  The whole-tile instantiation carries
 // none of it: with the slot reduction inlined the kernel needs 200+ registers and measurably slows
 // the whole-tile main loop (8192^3 bf16: 0.98 ms against 0.83 ms), so the two are kept apart.
-template <typename TC, bool kSplit>
+// kFold (whole tiles only) compiles the fused row reduce in, for the same reason.
+template <typename TC, bool kSplit, bool kFold = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
@@ -1006,11 +1050,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       EpiExt ex;
       ex.staged = p.epi_staged;
       ex.n_peers = p.n_peers;
-      ex.rr_kind = p.rr_kind;
-#pragma unroll
-      for (int q = 0; q < kMaxPeers; ++q) ex.peer[q] = p.peer_c[q];
+      ex.rr_kind = kFold ? p.rr_kind : 0u;
+      ex.peers = p.peer_c;
       RowFold rf;
-      rf.kind = p.rr_kind;
+      rf.kind = kFold ? p.rr_kind : 0u;
       rf.clear = p.rr_clear;
       rf.nslots = 2u * tiles_c;
       rf.partials = p.rr_partials;
@@ -1039,7 +1082,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
-        if (rf.kind) {
+        if (kFold && rf.kind) {
           ok = row_fold_finish<TC>(rf, quarter * 32u + lane, tr * 128u + quarter * 32u + lane, ep.rows,
                                    2u * tc, 2u, red, epi_bar, epi_phase, abort_flag, status,
                                    &last_flag);

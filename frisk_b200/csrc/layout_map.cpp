@@ -156,4 +156,71 @@ int frisk_b200_bank_conflicts(int64_t rows, int64_t cols, int32_t elem_bits, int
   return FRISK_OK;
 }
 
+int frisk_b200_bank_conflicts_access(int64_t rows, int64_t cols, int32_t elem_bits, int32_t mode,
+                                     int32_t access, frisk_access_stats* out) {
+  if (!out || rows <= 0 || cols <= 0 || elem_bits <= 0 || elem_bits % 8 || !valid_mode(mode))
+    return FRISK_ERR_INVALID_ARGUMENT;
+  if (access != FRISK_ACCESS_CHUNK_COLUMN && access != FRISK_ACCESS_ROW_PIECES)
+    return FRISK_ERR_INVALID_ARGUMENT;
+  const int64_t es = elem_bits / 8;
+  const int64_t row_bytes = cols * es;
+  if (row_bytes % 16) return FRISK_ERR_MISALIGNED;
+  const int64_t span = mode ? span_bytes(mode) : row_bytes;
+  if (row_bytes % span) return FRISK_ERR_MISALIGNED;
+  const int64_t chunks_per_row = row_bytes / 16;
+  memset(out, 0, sizeof *out);
+  // byte address of 16-byte chunk `c` of row `r`: one box per column atom, as TMA lays a tile out
+  auto chunk_addr = [&](int64_t r, int64_t c) -> int64_t {
+    const int64_t cb = c * 16;
+    if (mode == 0) return r * row_bytes + cb;
+    return (cb / span) * rows * span + apply_swizzle(r * span + cb % span, mode);
+  };
+  // One warp request of 32 x 16 bytes.  The hardware serves 16-byte accesses a quarter warp (8
+  // lanes, 128 bytes) at a time; within a quarter every distinct 4-byte word that shares a bank
+  // with another costs one more pass over the banks (a wavefront).
+  auto request = [&](const int64_t (&addr)[32], int lanes) {
+    int wavefronts = 0;
+    for (int q = 0; q < lanes; q += 8) {
+      std::set<int64_t> words[32];
+      for (int l = q; l < std::min(lanes, q + 8); ++l)
+        for (int w = 0; w < 4; ++w) {
+          const int64_t word = addr[l] / 4 + w;
+          words[word % 32].insert(word);
+        }
+      size_t worst = 0;
+      for (int b = 0; b < 32; ++b) worst = std::max(worst, words[b].size());
+      wavefronts += (int)worst;
+    }
+    const int ideal = (lanes + 7) / 8;
+    out->requests++;
+    out->wavefronts += wavefronts;
+    out->ideal_wavefronts += ideal;
+    out->max_wavefronts_per_request = std::max<int32_t>(out->max_wavefronts_per_request, wavefronts);
+  };
+  int64_t addr[32];
+  if (access == FRISK_ACCESS_CHUNK_COLUMN) {
+    // lane = row, every lane the same chunk column: 32 consecutive rows x one 16-byte chunk
+    for (int64_t r0 = 0; r0 < rows; r0 += 32)
+      for (int64_t c = 0; c < chunks_per_row; ++c) {
+        const int lanes = (int)std::min<int64_t>(32, rows - r0);
+        for (int l = 0; l < lanes; ++l) addr[l] = chunk_addr(r0 + l, c);
+        request(addr, lanes);
+      }
+  } else {
+    // consecutive lanes walk the chunks of a row, then the next row
+    const int64_t total = rows * chunks_per_row;
+    for (int64_t i0 = 0; i0 < total; i0 += 32) {
+      const int lanes = (int)std::min<int64_t>(32, total - i0);
+      for (int l = 0; l < lanes; ++l) addr[l] = chunk_addr((i0 + l) / chunks_per_row, (i0 + l) % chunks_per_row);
+      request(addr, lanes);
+    }
+  }
+  out->conflict_degree = out->ideal_wavefronts ? (double)out->wavefronts / (double)out->ideal_wavefronts : 0.0;
+  // what the mode costs outside shared memory: boxes TMA has to issue for the tile and the
+  // length of the contiguous global segment behind each box row
+  out->tma_boxes = (int32_t)(mode ? row_bytes / span * ((rows + 255) / 256) : 0);
+  out->global_segment_bytes = (int32_t)(mode ? span : row_bytes);
+  return FRISK_OK;
+}
+
 }  // extern "C"

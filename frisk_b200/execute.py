@@ -129,6 +129,10 @@ def find_gemms(module, kernel_name: str) -> list:
     return calls
 
 
+# What the last `run` launched, in order: ("gemm" | "gemm+reduce" | "reduce", kernel family).
+LAST_RUN: List[tuple] = []
+
+
 def parse_module(text: str):
     """Reads a module from its textual form (``str(module)``, a ``.mlir`` file written by this
     package or printed by the reference) into a fresh context; ``ValueError`` names line and
@@ -149,7 +153,12 @@ def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Opt
         module = parse_module(module)
     if not module.verify():
         raise R.FriskError(-1, "module does not verify: " + module.verify_message())
-    for call in find_gemms(module, kernel_name):
+    del LAST_RUN[:]
+    calls = find_gemms(module, kernel_name)
+    skip = set()
+    for i, call in enumerate(calls):
+        if i in skip:
+            continue
         if isinstance(call, ReduceCall):
             src = np.ascontiguousarray(buffers[call.arg_src])
             dst = buffers[call.arg_dst]
@@ -158,20 +167,44 @@ def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Opt
             if tuple(src.shape) != call.shape:
                 raise ValueError(f"the source buffer has shape {tuple(src.shape)}, the op says {call.shape}")
             R.reduce_host(src, dst, call.dim, call.dtype, call.kind, call.clear)
+            LAST_RUN.append(("reduce", "reduce"))
             continue
         sa, sb = scale_a, scale_b
         if sa is None and call.arg_scale_a is not None:  # scale vectors bound as kernel arguments
             sa = np.ascontiguousarray(buffers[call.arg_scale_a], dtype=np.float32)
             sb = np.ascontiguousarray(buffers[call.arg_scale_b], dtype=np.float32)
-        plan = R.GemmPlan(call.M, call.N, call.K, call.ab_type, call.c_type, transA=call.transA,
-                          transB=call.transB, clear_accum=call.clear_accum,
-                          scales=sa is not None, **(plan_options or {}))
+        kw = dict(transA=call.transA, transB=call.transB, clear_accum=call.clear_accum,
+                  scales=sa is not None, **(plan_options or {}))
+        # A frisk.reduce over the columns of the C this gemm has just written (the row maximum /
+        # row sum after the first gemm of the reference's attention sketch, tmp/ir.mlir:112-135)
+        # runs inside the gemm's epilogue, when a whole-tile tensor-core plan exists for it.
+        plan, fused = None, None
+        nxt = calls[i + 1] if i + 1 < len(calls) else None
+        if (isinstance(nxt, ReduceCall) and nxt.arg_src == call.arg_c and nxt.dim == 1
+                and nxt.shape == (call.M, call.N) and nxt.dtype == call.c_type
+                and nxt.arg_dst not in (call.arg_a, call.arg_b, call.arg_c)):
+            try:
+                plan = R.GemmPlan(call.M, call.N, call.K, call.ab_type, call.c_type,
+                                  row_reduce=nxt.kind, row_reduce_clear=nxt.clear, **kw)
+                fused = nxt
+                skip.add(i + 1)
+            except R.FriskError as e:
+                if e.code != -2:
+                    raise
+        if plan is None:
+            plan = R.GemmPlan(call.M, call.N, call.K, call.ab_type, call.c_type, **kw)
         try:
             a = np.ascontiguousarray(buffers[call.arg_a])
             b = np.ascontiguousarray(buffers[call.arg_b])
             c = buffers[call.arg_c]
             if not c.flags["C_CONTIGUOUS"]:
                 raise ValueError("the C buffer must be C-contiguous (it is written in place)")
-            plan.run_host(a, b, c, sa, sb)
+            dst = None
+            if fused is not None:
+                dst = buffers[fused.arg_dst]
+                if not dst.flags["C_CONTIGUOUS"] or dst.size != call.M:
+                    raise ValueError("the reduce destination must be a C-contiguous buffer of M elements")
+            plan.run_host(a, b, c, sa, sb, dst)
+            LAST_RUN.append(("gemm+reduce" if fused else "gemm", plan.info["kernel_name"]))
         finally:
             plan.close()

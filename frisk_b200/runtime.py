@@ -106,6 +106,13 @@ class BankStats(C.Structure):
                 ("samples", C.c_int32)]
 
 
+class AccessStats(C.Structure):
+    _fields_ = [("requests", C.c_int64), ("wavefronts", C.c_int64), ("ideal_wavefronts", C.c_int64),
+                ("conflict_degree", C.c_double), ("max_wavefronts_per_request", C.c_int32),
+                ("tma_boxes", C.c_int32), ("global_segment_bytes", C.c_int32)]
+
+
+ACCESS_CHUNK_COLUMN, ACCESS_ROW_PIECES = 1, 2
 SWIZZLE_128B_ATOM_32B = 1032
 SWIZZLE_128B_ATOM_64B = 1064
 
@@ -144,6 +151,8 @@ def lib() -> C.CDLL:
     L.frisk_b200_peer_free.restype = C.c_int
     L.frisk_b200_gemm_run_host.argtypes = [vp, vp, vp, vp, vp, vp]
     L.frisk_b200_gemm_run_host.restype = C.c_int
+    L.frisk_b200_gemm_run_host_ex.argtypes = [vp, vp, vp, vp, vp, vp, vp]
+    L.frisk_b200_gemm_run_host_ex.restype = C.c_int
     L.frisk_b200_gemm_skinny_static.argtypes = [C.POINTER(GemmDesc), vp, vp, vp, vp, vp, vp, vp]
     L.frisk_b200_gemm_skinny_static.restype = C.c_int
     L.frisk_b200_gemm_skinny_static_capacity.argtypes = []
@@ -165,6 +174,9 @@ def lib() -> C.CDLL:
     L.frisk_b200_bank_conflicts.argtypes = [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                             C.c_int32, C.POINTER(BankStats)]
     L.frisk_b200_bank_conflicts.restype = C.c_int
+    L.frisk_b200_bank_conflicts_access.argtypes = [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                                   C.POINTER(AccessStats)]
+    L.frisk_b200_bank_conflicts_access.restype = C.c_int
     L.frisk_b200_reduce_info.argtypes = [C.POINTER(ReduceDesc), C.c_int, C.POINTER(ReduceInfo)]
     L.frisk_b200_reduce_info.restype = C.c_int
     L.frisk_b200_reduce_workspace_bytes.argtypes = [C.POINTER(ReduceDesc), C.POINTER(C.c_size_t)]
@@ -173,6 +185,9 @@ def lib() -> C.CDLL:
     L.frisk_b200_reduce_run.restype = C.c_int
     L.frisk_b200_reduce_run_host.argtypes = [C.POINTER(ReduceDesc), vp, vp]
     L.frisk_b200_reduce_run_host.restype = C.c_int
+    L.frisk_b200_measure_mma_peak.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                              C.POINTER(C.c_double), C.POINTER(C.c_double)]
+    L.frisk_b200_measure_mma_peak.restype = C.c_int
     L.frisk_b200_device_sm_count.argtypes = []
     L.frisk_b200_device_sm_count.restype = C.c_int
     L.frisk_b200_version.argtypes = []
@@ -289,10 +304,12 @@ class GemmPlan:
         _check(lib().frisk_b200_gemm_run_ex(self._h, C.byref(a)), "gemm_run_ex")
 
     def run_host(self, A: np.ndarray, B: np.ndarray, Cout: np.ndarray,
-                 scale_a: Optional[np.ndarray] = None, scale_b: Optional[np.ndarray] = None) -> None:
-        """Synchronous GEMM on host arrays (copies in, runs, copies C back)."""
-        rc = lib().frisk_b200_gemm_run_host(self._h, _ptr(A), _ptr(B), _ptr(Cout), _ptr(scale_a),
-                                            _ptr(scale_b))
+                 scale_a: Optional[np.ndarray] = None, scale_b: Optional[np.ndarray] = None,
+                 row_reduce_dst: Optional[np.ndarray] = None) -> None:
+        """Synchronous GEMM on host arrays (copies in, runs, copies C -- and the fused row
+        reduce's destination, for a plan that has one -- back)."""
+        rc = lib().frisk_b200_gemm_run_host_ex(self._h, _ptr(A), _ptr(B), _ptr(Cout), _ptr(scale_a),
+                                               _ptr(scale_b), _ptr(row_reduce_dst))
         _check(rc, "gemm_run_host")
 
 
@@ -383,6 +400,21 @@ def bank_conflicts(rows: int, cols: int, elem_bits: int, mode: int, lane_vector:
                                            int(distinct_words_only), C.byref(st)), "bank_conflicts")
     return {"avg_max_conflict": st.avg_max_conflict, "max_conflict": st.max_conflict,
             "samples": st.samples}
+
+
+def measure_mma_peak(ab_type: int, pair: bool = True, k_blocks: int = 1024, reps: int = 10) -> dict:
+    """Rate of back-to-back tcgen05.mma from resident shared memory on the current device."""
+    tf, ms = C.c_double(), C.c_double()
+    _check(lib().frisk_b200_measure_mma_peak(ab_type, int(pair), k_blocks, reps, C.byref(tf), C.byref(ms)),
+           "measure_mma_peak")
+    return {"tflops": tf.value, "ms_per_launch": ms.value, "k_blocks": k_blocks, "pair": bool(pair)}
+
+
+def bank_conflicts_access(rows: int, cols: int, elem_bits: int, mode: int, access: int) -> dict:
+    st = AccessStats()
+    _check(lib().frisk_b200_bank_conflicts_access(rows, cols, elem_bits, mode, access, C.byref(st)),
+           "bank_conflicts_access")
+    return {n: getattr(st, n) for n, _ in st._fields_}
 
 
 def device_sm_count() -> int:

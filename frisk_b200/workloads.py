@@ -243,8 +243,8 @@ def parity_metrics(c: np.ndarray, ref: np.ndarray, absdot: np.ndarray | None = N
     * ``below_rms_floor``: the share of outputs whose |r| lies under the rms floor (the outputs
       on which the two floors differ);
     * ``over_bound_rms_floor`` (with ``bound``): the share of outputs whose rms-floor error exceeds
-      the bound, and ``over_bound_all_below_floor``: whether every one of them is an output under
-      the floor (a cancellation-sized value, where the floor, not |r|, is the denominator).
+      the bound, and ``over_bound_largest_ref``: the largest |r| / rms(r) among them (how close
+      to a typical output the worst offender is; 1e-3 is the floor itself).
     """
     c = np.asarray(c, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
@@ -258,7 +258,7 @@ def parity_metrics(c: np.ndarray, ref: np.ndarray, absdot: np.ndarray | None = N
     if bound is not None:
         over = np.abs(c - ref) / np.maximum(np.abs(ref), rms_floor) > bound
         out["over_bound_rms_floor"] = float(np.mean(over))
-        out["over_bound_all_below_floor"] = bool(np.all(np.abs(ref)[over] < rms_floor))
+        out["over_bound_largest_ref"] = float(np.max(np.abs(ref)[over]) / (1e3 * rms_floor)) if over.any() else 0.0
     return out
 
 

@@ -207,6 +207,10 @@ int frisk_b200_peer_free(void* ptr);
  */
 int frisk_b200_gemm_run_host(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
                              const float* scale_a, const float* scale_b);
+/* The same for a plan with a fused row reduce (desc.row_reduce != 0): `row_reduce_dst` is the
+ * host array of M elements of C's type the fold goes to (and comes from, when clear is 0). */
+int frisk_b200_gemm_run_host_ex(frisk_gemm_plan* plan, const void* A, const void* B, void* C,
+                                const float* scale_a, const float* scale_b, void* row_reduce_dst);
 
 /*
  * No counterpart in the reference.  The few-row ("skinny") GEMM for callers that may not
@@ -359,6 +363,52 @@ typedef struct frisk_bank_stats {
 int frisk_b200_bank_conflicts(int64_t rows, int64_t cols, int32_t elem_bits, int32_t mode,
                               int32_t lane_vector, int32_t distinct_words_only,
                               frisk_bank_stats* out);
+
+/*
+ * The access patterns the reference's model does not walk.  Its windows are 32 * lane_vector
+ * consecutive ROW-MAJOR elements (gemm_layout_tool.cpp:150-176; `--ldmatrix` only widens the
+ * lane vector, 407-409), which every layout with 128-byte rows serves without conflicts,
+ * swizzled or not -- so it cannot tell the modes apart.  What a swizzle is for is the other
+ * direction:
+ *   FRISK_ACCESS_CHUNK_COLUMN  every lane a different row, all lanes the same 16-byte chunk
+ *                              column: the operand fetch of ldmatrix / UMMA (8 rows x 16 bytes
+ *                              per matrix) and the writes of an epilogue that stages one row per
+ *                              thread;
+ *   FRISK_ACCESS_ROW_PIECES    consecutive lanes walk the 16-byte chunks of a row, then the next
+ *                              row: the coalesced read-back of staged rows.
+ * The tile is laid out as frisk_b200_swizzled_offset lays it out (mode 0: plain rows of
+ * cols * elem_bytes).  16-byte accesses are served a quarter warp at a time; `wavefronts` counts,
+ * per quarter, the most distinct 4-byte words any bank has to deliver.  conflict_degree =
+ * wavefronts / ideal_wavefronts: 1.0 means conflict-free.  tma_boxes / global_segment_bytes are
+ * what the mode costs outside shared memory: copies to issue per tile, contiguous bytes per
+ * box row in global memory.
+ */
+enum { FRISK_ACCESS_CHUNK_COLUMN = 1, FRISK_ACCESS_ROW_PIECES = 2 };
+typedef struct frisk_access_stats {
+  int64_t requests;          /* warp-wide requests of up to 32 x 16 bytes                      */
+  int64_t wavefronts;        /* passes over the banks all requests took                        */
+  int64_t ideal_wavefronts;  /* one per quarter warp                                           */
+  double conflict_degree;
+  int32_t max_wavefronts_per_request;
+  int32_t tma_boxes;
+  int32_t global_segment_bytes;
+} frisk_access_stats;
+int frisk_b200_bank_conflicts_access(int64_t rows, int64_t cols, int32_t elem_bits, int32_t mode,
+                                     int32_t access, frisk_access_stats* out);
+
+/*
+ * Measures, on the current device, the rate the tensor pipes reach when every SM (pair = 0) or
+ * SM pair (pair = 1: two-SM MMAs, M = 256) issues tcgen05.mma of shape M x 256 x 32 bytes of K
+ * back to back on operand tiles resident in shared memory: no loads, no epilogue.  It is the
+ * denominator of a GEMM kernel's tensor-pipe roofline for operand types no library peak was
+ * measured for (e4m3).  `k_blocks` (a multiple of 32; one k-block = four MMAs) sets the length
+ * of one launch -- choose it so that a launch lasts about as long as the GEMM it is compared
+ * with, since the clock under the power cap depends on it; `reps` launches are timed with CUDA
+ * events on the default stream.  Synchronous.  No counterpart in the reference, whose timing
+ * method (exp/layout/analyze_bank_conflicts.py:112-178) has no roofline.
+ */
+int frisk_b200_measure_mma_peak(int32_t ab_type, int32_t pair, int32_t k_blocks, int32_t reps,
+                                double* tflops, double* ms_per_launch);
 
 /* Library / device facts: returns the SM count of the current device (or a negative code). */
 int frisk_b200_device_sm_count(void);

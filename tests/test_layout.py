@@ -131,10 +131,47 @@ def test_bank_model_blackwell_modes_and_distinct_word_counting():
     for mode in (0, 32, 64, 128, R.SWIZZLE_128B_ATOM_32B, R.SWIZZLE_128B_ATOM_64B):
         st = R.bank_conflicts(128, 64, 16, mode, 8, distinct_words_only=True)
         assert st["samples"] == 32 and st["max_conflict"] == 4
-    # column walk (one 16-byte chunk per lane, 8 rows x 4 chunk columns): what ldmatrix and the
-    # tensor-core operand fetch do.  Unswizzled 128-byte rows hit 8-way conflicts on words.
     with pytest.raises(R.FriskError):
         R.bank_conflicts(128, 60, 16, 128, 8)
+
+
+def test_access_patterns_tell_the_swizzle_modes_apart():
+    """The reference's model walks row-major windows only, which every layout serves without
+    conflicts.  The two patterns a swizzle exists for -- a chunk column (every lane another row,
+    the same 16-byte chunk: the ldmatrix / UMMA operand fetch, and the staged epilogue's writes)
+    and row pieces (consecutive lanes along a row: the staged epilogue's read-back) -- separate
+    the modes.  Tile: 32 rows x 128 bytes, the staging area of one epilogue warp."""
+    col = {m: R.bank_conflicts_access(32, 64, 16, m, R.ACCESS_CHUNK_COLUMN) for m in
+           (0, 32, 64, 128, R.SWIZZLE_128B_ATOM_32B, R.SWIZZLE_128B_ATOM_64B)}
+    row = {m: R.bank_conflicts_access(32, 64, 16, m, R.ACCESS_ROW_PIECES) for m in col}
+    # plain 128-byte rows: the 8 rows of a quarter warp all start in the same bank -> 8 passes
+    assert col[0]["conflict_degree"] == 8.0 and col[0]["max_wavefronts_per_request"] == 32
+    assert row[0]["conflict_degree"] == 1.0
+    # the three TMA swizzles spread a chunk column over all banks ...
+    for m in (32, 64, 128):
+        assert col[m]["conflict_degree"] == 1.0 and col[m]["max_wavefronts_per_request"] == 4
+    # ... but only the 128-byte one keeps a 128-byte row in one box: the narrower ones cut it
+    # into 2 or 4 boxes a multiple of 1 KiB apart, which collide when a row is read back
+    assert [row[m]["conflict_degree"] for m in (32, 64, 128)] == [4.0, 2.0, 1.0]
+    assert [col[m]["tma_boxes"] for m in (32, 64, 128)] == [4, 2, 1]
+    assert [col[m]["global_segment_bytes"] for m in (32, 64, 128)] == [32, 64, 128]
+    # the coarser atoms of the 128-byte swizzle move 32 or 64 bytes at a time: fine for accesses
+    # of that width, 2- and 4-way conflicts for 16-byte chunk columns
+    assert col[R.SWIZZLE_128B_ATOM_32B]["conflict_degree"] == 2.0
+    assert col[R.SWIZZLE_128B_ATOM_64B]["conflict_degree"] == 4.0
+    assert row[R.SWIZZLE_128B_ATOM_32B]["conflict_degree"] == 1.0
+    # so the one mode that is conflict-free both ways, with the fewest copies and the longest
+    # global segments, is the 128-byte swizzle: what the plans and the staged epilogue use
+    best = min(col, key=lambda m: (col[m]["conflict_degree"] * row[m]["conflict_degree"], col[m]["tma_boxes"] or 99))
+    assert best == 128
+    # the operand tiles of the kernels, fetched by chunk columns: conflict-free in the mapped mode
+    for rows, cols, bits in ((128, 64, 16), (256, 128, 8), (64, 128, 16)):
+        mode = R.layout_to_tma(rows, cols, bits, True)["swizzle_bytes"]
+        assert R.bank_conflicts_access(rows, cols, bits, mode, R.ACCESS_CHUNK_COLUMN)["conflict_degree"] == 1.0
+    with pytest.raises(R.FriskError):
+        R.bank_conflicts_access(32, 60, 16, 128, R.ACCESS_CHUNK_COLUMN)   # rows are not whole chunks
+    with pytest.raises(R.FriskError):
+        R.bank_conflicts_access(32, 64, 16, 128, 7)
 
 
 def test_accumulator_layout_on_sm100_is_the_tensor_memory_map():

@@ -95,7 +95,7 @@ def test_lifted_program_runs_and_matches_the_oracle(dims, tile, dtype, acc):
     assert np.array_equal(C, R.gemm_host(w))
 
 
-def gemm_then_row_max(dtype="fp16", dims=(16, 32, 64)):
+def gemm_then_row_max(dtype="fp16", dims=(16, 32, 64), kind="max", clear=True):
     """A kernel that multiplies and then takes the row maxima of the product: the two ops of the
     reference's attention sketches (tmp/ir.mlir:80-158) on whole buffers."""
     M, N, K = dims
@@ -104,7 +104,7 @@ def gemm_then_row_max(dtype="fp16", dims=(16, 32, 64)):
            h.memref_type((M,), dtype)]
     _, entry = h.new_kernel("scores_max", tys)
     h.create_gemm(entry.get_argument(0), entry.get_argument(1), entry.get_argument(2), clear_accum=True)
-    h.builder.create_reduce_op(entry.get_argument(2), entry.get_argument(3), "max", 1, True)
+    h.builder.create_reduce_op(entry.get_argument(2), entry.get_argument(3), kind, 1, clear)
     return h
 
 
@@ -137,3 +137,45 @@ def test_gemm_followed_by_reduce_runs_as_written():
     assert ok, (metric, err)
     want, _ = ref.ref_reduce(c, 1, W.BF16, "max")  # exact: the maximum of the stored values
     assert np.array_equal(W.decode(rowmax, W.BF16).astype(np.float64), want)
+    # the two ops ran as ONE launch: the reduce sits in the gemm's epilogue
+    from frisk_b200 import execute as X
+    assert X.LAST_RUN == [("gemm+reduce", "tcgen05")]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,dims,kind,clear", [("fp16", (512, 1024, 256), "add", True),
+                                                   ("bf16", (300, 520, 136), "max", False),
+                                                   ("fp16", (1024, 768, 64), "min", True)])
+def test_gemm_then_row_reduce_is_one_launch_and_matches_the_two_ops(dtype, dims, kind, clear):
+    """The pair of ops of the reference's attention sketch (tmp/ir.mlir:112-135: a gemm, then a
+    frisk.reduce of its result over dim 1) executed as one launch, against the same module's two
+    ops restated on the CPU: the product in float64, the reduce on the stored C."""
+    from frisk_b200 import execute as X
+    from oracle import ref
+    M, N, K = dims
+    dt = {"fp16": W.F16, "bf16": W.BF16}[dtype]
+    h = gemm_then_row_max(dtype, dims, kind, clear)
+    rng = np.random.default_rng(M + N)
+    w = W.GemmWorkload("scores", M, N, K, dt, dt,
+                       A=W.encode(rng.standard_normal((M, K)).astype(np.float32), dt),
+                       B=W.encode((rng.standard_normal((K, N)) * K ** -0.5).astype(np.float32), dt))
+    c = np.zeros((M, N), W.storage_numpy_dtype(dt))
+    init = W.encode(rng.standard_normal(M).astype(np.float32), dt)
+    dst = init.copy()
+    F.run(h.module, "scores_max", [w.A, w.B, c, dst])
+    assert X.LAST_RUN == [("gemm+reduce", "tcgen05_pair")]
+    ok, err, metric = W.check(W.decode(c, dt), ref.ref_gemm_f64(w), dt, absdot=ref.abs_dot(w))
+    assert ok, (metric, err)
+    want, mag = ref.ref_reduce(c, 1, dt, kind, clear, init)
+    err = np.abs(W.decode(dst, dt).astype(np.float64) - want)
+    ulp = {W.F16: 2.0 ** -10, W.BF16: 2.0 ** -7}[dt]
+    tol = 0.0 if kind != "add" else 1e-5 * mag + ulp * np.abs(want)
+    assert (err <= tol).all(), float(err.max())
+    # fp32 operands have no tensor-core plan: the same program runs as two launches
+    h32 = gemm_then_row_max("fp32", (96, 80, 64), kind, True)
+    w32 = W.make_workload("cfg1", 96, 80, 64)
+    c32, d32 = np.zeros((96, 80), np.float32), np.zeros(96, np.float32)
+    F.run(h32.module, "scores_max", [w32.A, w32.B, c32, d32])
+    assert X.LAST_RUN == [("gemm", "simt"), ("reduce", "reduce")]
+    want, mag = ref.ref_reduce(c32, 1, W.F32, kind)
+    assert (np.abs(d32 - want) <= (0.0 if kind != "add" else 1e-5 * mag + 2.0 ** -23 * np.abs(want))).all()

@@ -459,8 +459,13 @@ def main():
                          "(a small run for a profiler), and print their JSON")
     ap.add_argument("--band", type=int, default=0,
                     help="tile rows the rasterisation walks together (0: the plan's choice)")
+    ap.add_argument("--panel", type=int, default=0,
+                    help="walk the tiles in panels of this many tile columns (0: the plan's choice)")
+    ap.add_argument("--l2-hints", type=int, default=0,
+                    help="bit 0: A loads evict-first, bit 1: B loads evict-last (0: the plan's choice)")
     ap.add_argument("--epilogue", type=int, default=0,
-                    help="1: per-thread row stores, 2: rows staged through shared memory (0: the plan's choice)")
+                    help="1: per-thread row stores, 2: rows staged through swizzled shared memory, 3: staged through "
+                         "linear rows (0: the plan's choice)")
     ap.add_argument("--rows", type=int, default=0,
                     help="run the workload on this many rows only (a small case for a profiler)")
     args = ap.parse_args()
@@ -509,7 +514,8 @@ def main():
         dist.broadcast(B, 0)
     C = torch.empty((rows, N), device=dev, dtype=out_dtype(torch, name))
     plan = R.GemmPlan(rows, N, K, ab, ct, transB=name in TRANS_B, scales=sa is not None,
-                      band_tiles=args.band, epilogue=args.epilogue)
+                      band_tiles=args.band, epilogue=args.epilogue, panel_tiles=args.panel,
+                      l2_hints=args.l2_hints)
     ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream

@@ -88,6 +88,8 @@ struct frisk_gemm_plan {
   // fused row reduce: [2 * tiles_c][M] fp32 folds, then one arrival counter per 128 rows
   size_t rr_partial_bytes = 0, rr_counter_bytes = 0;
   size_t dyn_smem = 0;
+  frisk_tma_params lay_a, lay_b;  // the layout mapper's description of the staged operand tiles
+  int plan_error = 0;
   // run-time caches
   CUtensorMap tmap_a, tmap_b;
   const void* cached_a = nullptr;
@@ -110,40 +112,56 @@ struct frisk_gemm_plan {
 
 namespace {
 
-uint64_t make_desc_base(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// UMMA shared-memory descriptor without the start address: leading / stride byte offsets in
+// 16-byte units, the sm_100 descriptor version, and the swizzle (layout type) in bits 61..63.
+uint64_t make_desc_base(uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
   uint64_t d = 0;
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;  // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;  // 128-byte swizzle
+  d |= (uint64_t)(layout_type & 7u) << 61;
   return d;
 }
 
-// Fills the shared-memory side of one operand for a tile of `tile_mn` rows and 128 bytes of K.
-void fill_operand(frisk::OperandParams& o, bool mn_major, uint32_t tile_mn, uint32_t es,
-                  uint32_t bk_elems) {
-  o.mn_major = mn_major ? 1 : 0;
+// Fills the shared-memory side of one operand for a tile of `tile_mn` rows and 128 bytes of K
+// from what the layout mapper (frisk_b200_layout_to_tma: the reference's swizzle selection carried
+// to TMA / UMMA fields) says about that tile, and keeps the mapper's answer in `lay`: there is one
+// description of a staged tile, and the kernels run on it.
+int fill_operand(frisk::OperandParams& o, frisk_tma_params& lay, bool mn_major, uint32_t tile_mn,
+                 uint32_t es, uint32_t bk_elems) {
+  frisk_layout_desc l;
+  l.elem_bits = (int32_t)(8 * es);
+  l.k_inner = mn_major ? 0 : 1;
+  uint32_t mn_boxes = 1;  // K-major tiles taller than a TMA box (256 rows) are cut along M/N
+  if (mn_major) {
+    l.rows = bk_elems;    // the tile as stored: K rows of tile_mn contiguous elements
+    l.cols = tile_mn;
+  } else {
+    mn_boxes = tile_mn > 256 ? 2 : 1;
+    l.rows = tile_mn / mn_boxes;
+    l.cols = bk_elems;
+  }
+  int rc = frisk_b200_layout_to_tma(&l, &lay);
+  if (rc) return rc;
+  // the kernels stage 128 bytes of K (or of M/N) per box row: the mapper must agree
+  if (lay.swizzle_bytes != 128) return FRISK_ERR_UNSUPPORTED;
+  o.mn_major = (uint32_t)lay.umma_major;
   o.stage_bytes = tile_mn * 128u;  // tile_mn x bk_elems elements either way
+  o.box_bytes = (uint32_t)lay.box_outer * (uint32_t)lay.swizzle_bytes;
+  o.desc_base = make_desc_base((uint32_t)lay.leading_byte_offset, (uint32_t)lay.stride_byte_offset,
+                               (uint32_t)lay.umma_layout_type);
+  o.k_step_bytes = (uint32_t)lay.k_step_bytes;
   if (mn_major) {
     // boxes of (128 bytes of M/N) x (bk rows of K); each box is one column of swizzle atoms
-    const uint32_t mn_per_box = 128u / es;
-    o.box_mn = mn_per_box;
-    o.num_boxes = tile_mn / mn_per_box;
-    o.box_bytes = 128u * bk_elems;
-    o.desc_base = make_desc_base(/*LBO: next 128-byte column of M/N*/ o.box_bytes,
-                                 /*SBO: next group of 8 K rows*/ 1024u);
-    o.k_step_bytes = (32u / es) * 128u;  // one UMMA K step = 32 bytes of K = that many rows
-    o.sub_stride_bytes = (128u / mn_per_box) * o.box_bytes;
+    o.box_mn = (uint32_t)lay.box_inner;
+    o.num_boxes = (uint32_t)lay.num_boxes;
+    o.sub_stride_bytes = (128u / o.box_mn) * o.box_bytes;   // 128 rows further along M/N
   } else {
-    // one box: tile_mn rows x 128 bytes of K (split in two when it exceeds the 256-row box limit)
-    o.num_boxes = tile_mn > 256 ? 2 : 1;
-    o.box_mn = tile_mn / o.num_boxes;
-    o.box_bytes = o.box_mn * 128u;
-    o.desc_base = make_desc_base(/*LBO unused for swizzled K-major*/ 16u,
-                                 /*SBO: next group of 8 rows*/ 1024u);
-    o.k_step_bytes = 32u;
+    o.box_mn = (uint32_t)lay.box_outer;
+    o.num_boxes = mn_boxes;
     o.sub_stride_bytes = 128u * 128u;
   }
+  return FRISK_OK;
 }
 
 uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t m, uint32_t n) {
@@ -161,7 +179,7 @@ uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t m, u
 }
 
 int encode_operand_map(CUtensorMap* map, const OperandView& v, int dtype, uint32_t box_mn,
-                       uint32_t bk_elems) {
+                       uint32_t bk_elems, int swizzle_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) {
     g_last_error = "cuTensorMapEncodeTiled not available from the driver";
@@ -186,7 +204,11 @@ int encode_operand_map(CUtensorMap* map, const OperandView& v, int dtype, uint32
   }
   strides[0] = (cuuint64_t)v.ld * es;
   CUresult r = fn(map, dt, 2, const_cast<void*>(v.ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                  : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                        : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char buf[160];
@@ -249,6 +271,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   const frisk_gemm_desc& d = pl->d;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
+  pl->plan_error = 0;
   const uint32_t es = elem_size(d.a_type);
   const uint32_t bk = 128u / es;
   bool a_mn, b_mn;  // majors of the kernel's a-role / b-role operands
@@ -322,8 +345,11 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.bk_elems = bk;
   g.k_steps = 4;
   // a CTA of a pair stages its own 128 rows of A and half of the tile's B columns
-  fill_operand(g.a, a_mn, 128u * g.mi, es, bk);
-  fill_operand(g.b, b_mn, pair ? g.tile_n / 2 : g.tile_n, es, bk);
+  if (fill_operand(g.a, pl->lay_a, a_mn, 128u * g.mi, es, bk) ||
+      fill_operand(g.b, pl->lay_b, b_mn, pair ? g.tile_n / 2 : g.tile_n, es, bk)) {
+    pl->plan_error = FRISK_ERR_UNSUPPORTED;
+    return;
+  }
   if (pair && !b_mn && g.b.num_boxes == 1 && g.tile_n == 256) {
     // two boxes of 64 rows instead of one of 128 (same bytes in shared memory): a half-width item
     // of the last wave loads just the first
@@ -342,7 +368,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // The area is reserved either way: the element-wise path of a C without 16-byte alignment goes
   // through it too.
   const size_t epi_bytes = swap ? 0 : frisk::kEpiStageBytes;
-  g.epi_staged = (!swap && d.epilogue != 1) ? 1u : 0u;
+  g.epi_staged = swap ? 0u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
   uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
@@ -364,6 +390,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // kernel (DRAM bytes read per launch): bands of 4 / 6 / 8 / 10 / 12 / 16 tile rows give
   // 1.58 / 1.26 / 1.07 / 1.15 / 1.11 / 1.21 GB
   g.group_r = d.band_tiles > 0 ? (uint32_t)d.band_tiles : (pair ? 8u : 16u);
+  g.group_c = (pair && d.panel_tiles > 0) ? (uint32_t)d.panel_tiles : 0u;
+  g.l2_hints = pair ? (uint32_t)d.l2_hints : 0u;
   g.split_mode = swap ? 1 : 0;
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
@@ -437,7 +465,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   in.split_k = swap;
   in.smem_bytes = (int)pl->dyn_smem;
   in.launches = 1;
-  in.swizzle_a = in.swizzle_b = 128;
+  in.swizzle_a = pl->lay_a.swizzle_bytes;
+  in.swizzle_b = pl->lay_b.swizzle_bytes;
   // the clusters must all be resident at once for the plan to make sense; if this device cannot
   // place them, plan again without
   if (swap && use_cluster && pl->have_device && !skinny_clusters_fit(pl))
@@ -681,7 +710,8 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.force_kernel < 0 || d.force_kernel > 4 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
-  if (d.epilogue < 0 || d.epilogue > 2 || d.row_reduce < 0 || d.row_reduce > 4)
+  if (d.epilogue < 0 || d.epilogue > 3 || d.row_reduce < 0 || d.row_reduce > 4 ||
+      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3)
     return FRISK_ERR_INVALID_ARGUMENT;
   d.row_reduce_clear = d.row_reduce_clear != 0;
 
@@ -768,7 +798,24 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       return FRISK_ERR_UNSUPPORTED;
     }
   }
+  if (pl->plan_error) {
+    const int rc = pl->plan_error;
+    delete pl;
+    return rc;
+  }
   *out = pl;
+  return FRISK_OK;
+}
+
+int frisk_b200_gemm_plan_operand_layout(const frisk_gemm_plan* pl, int32_t operand,
+                                        frisk_tma_params* layout, uint64_t* umma_desc_base,
+                                        int32_t* tma_boxes_per_stage) {
+  if (!pl || operand < 0 || operand > 1) return FRISK_ERR_INVALID_ARGUMENT;
+  if (pl->info.kernel == FRISK_KERNEL_SIMT) return FRISK_ERR_UNSUPPORTED;  // nothing is staged by TMA
+  const frisk::OperandParams& o = operand ? pl->gp.b : pl->gp.a;
+  if (layout) *layout = operand ? pl->lay_b : pl->lay_a;
+  if (umma_desc_base) *umma_desc_base = o.desc_base;
+  if (tma_boxes_per_stage) *tma_boxes_per_stage = (int32_t)o.num_boxes;
   return FRISK_OK;
 }
 
@@ -862,9 +909,9 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     OperandView vb{B, d.N, d.K, d.ldb, d.transB == 0};
     const OperandView& ra = swap ? vb : va;  // a-role: the 128-row operand
     const OperandView& rb = swap ? va : vb;
-    int rc = encode_operand_map(&pl->tmap_a, ra, d.a_type, g.a.box_mn, g.bk_elems);
+    int rc = encode_operand_map(&pl->tmap_a, ra, d.a_type, g.a.box_mn, g.bk_elems, pl->lay_a.swizzle_bytes);
     if (rc) return rc;
-    rc = encode_operand_map(&pl->tmap_b, rb, d.a_type, g.b.box_mn, g.bk_elems);
+    rc = encode_operand_map(&pl->tmap_b, rb, d.a_type, g.b.box_mn, g.bk_elems, pl->lay_b.swizzle_bytes);
     if (rc) return rc;
     pl->cached_a = A;
     pl->cached_b = B;
@@ -1204,6 +1251,7 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   pl.sm_count = sms;
   pl.have_device = true;
   plan_tcgen05(&pl, /*swap=*/true, /*pair=*/false, /*cluster_try=*/-1);
+  if (pl.plan_error) return pl.plan_error;
   // this entry point keeps the atomic split (mode 1): its scratch is M x N fp32, independent of
   // the grid, which is what lets a fixed array serve it
   pl.gp.split_mode = 1;
@@ -1219,9 +1267,9 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   frisk::GemmParams g = pl.gp;
   OperandView va{A, d.M, d.K, d.lda, false};
   OperandView vb{B, d.N, d.K, d.ldb, d.transB == 0};
-  rc = encode_operand_map(&pl.tmap_a, vb, d.a_type, g.a.box_mn, g.bk_elems);  // weights: 128-row role
+  rc = encode_operand_map(&pl.tmap_a, vb, d.a_type, g.a.box_mn, g.bk_elems, pl.lay_a.swizzle_bytes);  // weights: 128-row role
   if (rc) return rc;
-  rc = encode_operand_map(&pl.tmap_b, va, d.a_type, g.b.box_mn, g.bk_elems);
+  rc = encode_operand_map(&pl.tmap_b, va, d.a_type, g.b.box_mn, g.bk_elems, pl.lay_b.swizzle_bytes);
   if (rc) return rc;
   g.C = C;
   g.status = device_status;

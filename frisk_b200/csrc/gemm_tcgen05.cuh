@@ -82,7 +82,9 @@ struct GemmParams {
   uint32_t tmem_cols;  // power of two >= 32
   uint32_t rows, cols; // extent of D
   uint32_t tiles_r, tiles_c, num_kb;
-  uint32_t group_r;    // tile rasterisation: rows of tiles walked together
+  uint32_t group_r;    // tile rasterisation: rows of tiles walked together (bands) ...
+  uint32_t group_c;    // ... or, when not 0, columns of tiles walked together (panels)
+  uint32_t l2_hints;   // bit 0: a-role loads evict-first in L2, bit 1: b-role loads evict-last
   uint32_t split_mode;  // 0: whole tiles; 1: stream-K, atomics into ws + finalize kernel;
                         // 2: stream-K, private partial slots, the last CTA of a tile reduces
                         // 3: one cluster per tile, each CTA a K slice, partials summed
@@ -106,6 +108,7 @@ struct GemmParams {
   uint32_t epilogue_backoff_ns;  // sleep between polls of the accumulator-ready barrier
   // whole-tile epilogue (the one-CTA whole-tile kernel and the CTA-pair kernel)
   uint32_t epi_staged;     // 1: rows go through shared memory and leave as 128-byte row pieces
+                           // (2: the same with linear instead of swizzled staging rows)
   uint32_t n_peers;        // other GPUs that receive a copy of every C tile (row-sharded all-gather)
   void* peer_c[kMaxPeers]; // where this GPU's rows of C start in each peer's buffer (same ldc)
   // frisk.reduce of C over its columns, folded into the epilogue
@@ -211,13 +214,29 @@ struct WorkIter {
   }
 };
 
-// Tile index -> (tile row, tile column).  Tiles are walked in bands of `group_r` tile rows,
-// down the band first, so that CTAs running at the same time share A rows and B columns in L2.
+// Tile index -> (tile row, tile column).  Two walks:
+//   bands  (group_c == 0): `group_r` tile rows at a time, down the band first, so that CTAs running
+//          at the same time share A rows and B columns in L2; every band streams all of B;
+//   panels (group_c != 0): `group_c` tile columns at a time, along the panel's columns first, then
+//          down all the rows: the panel of B (group_c x tile_n columns, all of K) stays in L2 while
+//          A streams past it once per panel -- the walk for a tall A against a B that does not
+//          fit in L2 as a whole.
 __device__ __forceinline__ void tile_coords(uint32_t group_r, uint32_t tiles_r, uint32_t tiles_c,
-                                            uint32_t tile, uint32_t& tr, uint32_t& tc) {
+                                            uint32_t tile, uint32_t& tr, uint32_t& tc,
+                                            uint32_t group_c = 0) {
   if (tiles_c == 1) {  // one column of tiles (every split plan): nothing to divide
     tr = tile;
     tc = 0;
+    return;
+  }
+  if (group_c) {
+    const uint32_t panel_tiles = group_c * tiles_r;
+    const uint32_t panel = tile / panel_tiles;
+    const uint32_t first_c = panel * group_c;
+    const uint32_t cols_in_panel = min(group_c, tiles_c - first_c);
+    const uint32_t in_panel = tile - panel * panel_tiles;
+    tr = in_panel / cols_in_panel;
+    tc = first_c + in_panel % cols_in_panel;
     return;
   }
   const uint32_t band_tiles = group_r * tiles_c;
@@ -369,13 +388,16 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
 // row r sits at chunk position j ^ (r & 7).  A warp's 32 writes of one chunk column (lane = row)
 // and its reads of four whole rows (8 lanes per row) both touch every bank exactly four times,
 // the minimum for 512 bytes.
-__device__ __forceinline__ uint32_t staged_chunk(uint32_t stage, uint32_t r, uint32_t j) {
-  return stage + r * 128u + ((j ^ (r & 7u)) << 4);
+// `xor_mask` is 7 for that layout; 0 leaves the rows linear (desc.epilogue = 3, kept to measure
+// what the swizzle buys: every chunk-column write then hits one bank group eight times).
+__device__ __forceinline__ uint32_t staged_chunk(uint32_t stage, uint32_t r, uint32_t j,
+                                                 uint32_t xor_mask) {
+  return stage + r * 128u + ((j ^ (r & xor_mask)) << 4);
 }
 template <typename TC>
-__device__ __forceinline__ TC* staged_elem(uint32_t stage, uint32_t r, uint32_t c) {
+__device__ __forceinline__ TC* staged_elem(uint32_t stage, uint32_t r, uint32_t c, uint32_t xor_mask) {
   constexpr uint32_t kPerVec = 16u / (uint32_t)sizeof(TC);
-  const uint32_t a = staged_chunk(stage, r, c / kPerVec) + (c % kPerVec) * (uint32_t)sizeof(TC);
+  const uint32_t a = staged_chunk(stage, r, c / kPerVec, xor_mask) + (c % kPerVec) * (uint32_t)sizeof(TC);
   return reinterpret_cast<TC*>(__cvta_shared_to_generic(a));
 }
 
@@ -384,25 +406,25 @@ __device__ __forceinline__ TC* staged_elem(uint32_t stage, uint32_t r, uint32_t 
 template <typename TC, int NC>
 __device__ __noinline__ void stage_old_c(const TC* C, int64_t ldc, uint32_t rows, uint32_t cols,
                                          uint32_t stage, uint32_t lane, uint32_t warp_row0,
-                                         uint32_t col0) {
+                                         uint32_t col0, uint32_t xor_mask) {
 #pragma unroll 1
   for (uint32_t e = lane; e < 32u * NC; e += 32u) {
     const uint32_t r = e / NC, c = e % NC;
     TC v = cast_out<TC>(0.f);
     if (warp_row0 + r < rows && col0 + c < cols) v = C[(int64_t)(warp_row0 + r) * ldc + col0 + c];
-    *staged_elem<TC>(stage, r, c) = v;
+    *staged_elem<TC>(stage, r, c, xor_mask) = v;
   }
 }
 template <typename TC, int NC>
 __device__ __noinline__ void staged_rows_out(TC* C, void* const* peers, uint32_t n_peers,
                                              int64_t ldc, uint32_t rows, uint32_t cols,
                                              uint32_t stage, uint32_t lane, uint32_t warp_row0,
-                                             uint32_t col0) {
+                                             uint32_t col0, uint32_t xor_mask) {
 #pragma unroll 1
   for (uint32_t e = lane; e < 32u * NC; e += 32u) {
     const uint32_t r = e / NC, c = e % NC;
     if (warp_row0 + r >= rows || col0 + c >= cols) continue;
-    const TC v = *staged_elem<TC>(stage, r, c);
+    const TC v = *staged_elem<TC>(stage, r, c, xor_mask);
     const int64_t off = (int64_t)(warp_row0 + r) * ldc + col0 + c;
     C[off] = v;
 #pragma unroll 1
@@ -429,6 +451,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
   const bool row_ok = row < p.rows;
   const bool full = col0 + NC <= p.cols;          // warp-uniform
   const bool vec = p.c_vec_ok && full;            // warp-uniform
+  const uint32_t xm = x.staged == 2u ? 0u : 7u;
   TC* const C = reinterpret_cast<TC*>(p.C);
   TC* const crow = C + (int64_t)row * p.ldc + col0;
   union Pack {
@@ -443,23 +466,39 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
         for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = *reinterpret_cast<const uint4*>(crow + v0 * kPerVec);
       }
     } else {
-      stage_old_c<TC, NC>(C, p.ldc, p.rows, p.cols, stage, lane, warp_row0, col0);
+      stage_old_c<TC, NC>(C, p.ldc, p.rows, p.cols, stage, lane, warp_row0, col0, xm);
       __syncwarp();
 #pragma unroll
-      for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = ld_shared_v4(staged_chunk(stage, lane, (uint32_t)v0));
+      for (int v0 = 0; v0 < kVecs; ++v0) out[v0].u = ld_shared_v4(staged_chunk(stage, lane, (uint32_t)v0, xm));
       __syncwarp();
     }
   }
   const float rs = (p.row_scale && row_ok) ? __ldg(p.row_scale + row) : 1.0f;
+  // The common cases get loops without per-element tests: on a shape whose main loop is short the
+  // epilogue's instruction count is the kernel's time (measured: 2.2 x the instructions, and 6 us
+  // more per tile, with the tests inside one generic loop).
+  if (full && p.clear_accum && !x.rr_kind) {
+    if (!p.col_scale) {
 #pragma unroll
-  for (int j = 0; j < NC; ++j) {
-    const bool col_ok = full || col0 + j < p.cols;
-    float v = __uint_as_float(acc[j]) * rs;
-    if (p.col_scale && col_ok) v *= __ldg(p.col_scale + col0 + j);
-    if (!p.clear_accum) v += cast_in<TC>(out[j / kPerVec].e[j % kPerVec]);
-    const TC o = cast_out<TC>(v);
-    out[j / kPerVec].e[j % kPerVec] = o;
-    if (x.rr_kind && col_ok) red = fold_step(x.rr_kind, red, cast_in<TC>(o));
+      for (int j = 0; j < NC; ++j)
+        out[j / kPerVec].e[j % kPerVec] = cast_out<TC>(__uint_as_float(acc[j]) * rs);
+    } else {
+      const float* cs = p.col_scale + col0;
+#pragma unroll
+      for (int j = 0; j < NC; ++j)
+        out[j / kPerVec].e[j % kPerVec] = cast_out<TC>(__uint_as_float(acc[j]) * rs * __ldg(cs + j));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const bool col_ok = full || col0 + j < p.cols;
+      float v = __uint_as_float(acc[j]) * rs;
+      if (p.col_scale && col_ok) v *= __ldg(p.col_scale + col0 + j);
+      if (!p.clear_accum) v += cast_in<TC>(out[j / kPerVec].e[j % kPerVec]);
+      const TC o = cast_out<TC>(v);
+      out[j / kPerVec].e[j % kPerVec] = o;
+      if (x.rr_kind && col_ok) red = fold_step(x.rr_kind, red, cast_in<TC>(o));
+    }
   }
   if (vec && !x.staged) {
     if (row_ok) {
@@ -475,14 +514,14 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
     return;
   }
 #pragma unroll
-  for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(staged_chunk(stage, lane, (uint32_t)v0), out[v0].u);
+  for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(staged_chunk(stage, lane, (uint32_t)v0, xm), out[v0].u);
   __syncwarp();
   if (vec) {
     const uint32_t sub = lane >> 3, ch = lane & 7u;
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
       const uint32_t rr = (uint32_t)it * 4u + sub;
-      const uint4 piece = ld_shared_v4(staged_chunk(stage, rr, ch));
+      const uint4 piece = ld_shared_v4(staged_chunk(stage, rr, ch, xm));
       if (warp_row0 + rr < p.rows) {
         const int64_t off = (int64_t)(warp_row0 + rr) * p.ldc + col0 + ch * kPerVec;
         *reinterpret_cast<uint4*>(C + off) = piece;
@@ -492,7 +531,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
       }
     }
   } else {
-    staged_rows_out<TC, NC>(C, x.peers, x.n_peers, p.ldc, p.rows, p.cols, stage, lane, warp_row0, col0);
+    staged_rows_out<TC, NC>(C, x.peers, x.n_peers, p.ldc, p.rows, p.cols, stage, lane, warp_row0, col0, xm);
   }
   __syncwarp();   // the staging area is rewritten by the next chunk
 }

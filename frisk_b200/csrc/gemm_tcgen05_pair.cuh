@@ -78,7 +78,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t stage_bytes = p.stage_bytes;  // per CTA
   const uint32_t tile_n = p.tile_n;
   const uint32_t tmem_cols = p.tmem_cols;
-  const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r;
+  const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r, group_c = p.group_c;
   const uint32_t n_items = p.n_items, narrow_from = p.narrow_from;
   const uint32_t num_kb = p.num_kb;
   int32_t* const status = p.status;
@@ -123,12 +123,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t a_stage_bytes = p.a.stage_bytes;
     const uint32_t bk_elems = p.bk_elems;
     const uint32_t my_turn = warp == 0 ? 0u : 1u;
+    const uint32_t l2_hints = p.l2_hints;
+    const uint64_t pol_a = ptx::l2_policy_evict_first(), pol_b = ptx::l2_policy_evict_last();
     uint32_t stage = 0, phase = 0, turn = 0;
     bool ok = true;
     for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
       const PairItem it = pair_item(i, narrow_from);
       uint32_t tr, tc;
-      tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc);
+      tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc, group_c);
       const int32_t r0 = (int32_t)(tr * 256u + rank * 128u);
       // a narrow item covers columns [half * tile_n/2, +tile_n/2) of the tile; each CTA stages half
       const uint32_t cols_item = it.narrow ? (tile_n >> 1) : tile_n;
@@ -164,12 +166,20 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (uint32_t bx = 0; bx < a_boxes; ++bx) {
           const int32_t mn = r0 + (int32_t)(bx * a_box_mn);
           const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
-          if (ptx::elect_one()) ptx::tma_load_2d_pair(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
+          if (l2_hints & 1u) {
+            if (ptx::elect_one()) ptx::tma_load_2d_pair_hint(a_dst + bx * a_box_bytes, &tmap_a, full, x, y, pol_a);
+          } else {
+            if (ptx::elect_one()) ptx::tma_load_2d_pair(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
+          }
         }
         for (uint32_t bx = 0; bx < b_boxes_item; ++bx) {
           const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
           const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
-          if (ptx::elect_one()) ptx::tma_load_2d_pair(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
+          if (l2_hints & 2u) {
+            if (ptx::elect_one()) ptx::tma_load_2d_pair_hint(b_dst + bx * b_box_bytes, &tmap_b, full, x, y, pol_b);
+          } else {
+            if (ptx::elect_one()) ptx::tma_load_2d_pair(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
+          }
         }
         __syncwarp();  // reconverge after the elected-lane issues (see the one-CTA kernel)
         if (++stage == stages) {
@@ -308,7 +318,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t acc = item & 1u;
       const uint32_t acc_phase = (item >> 1) & 1u;
       uint32_t tr, tc;
-      tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc);
+      tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc, group_c);
       const uint32_t cols_item = it.narrow ? (tile_n >> 1) : tile_n;
       const uint32_t col0 = tc * tile_n + it.half * (tile_n >> 1);
       ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,

@@ -38,6 +38,7 @@ class GemmDesc(C.Structure):
         ("force_kernel", C.c_int32), ("tile_n", C.c_int32), ("stages", C.c_int32),
         ("num_ctas", C.c_int32), ("band_tiles", C.c_int32),
         ("epilogue", C.c_int32), ("row_reduce", C.c_int32), ("row_reduce_clear", C.c_int32),
+        ("panel_tiles", C.c_int32), ("l2_hints", C.c_int32),
     ]
 
 
@@ -168,6 +169,9 @@ def lib() -> C.CDLL:
     L.frisk_b200_shard_rows.restype = C.c_int
     L.frisk_b200_layout_to_tma.argtypes = [C.POINTER(LayoutDesc), C.POINTER(TmaParams)]
     L.frisk_b200_layout_to_tma.restype = C.c_int
+    L.frisk_b200_gemm_plan_operand_layout.argtypes = [vp, C.c_int32, C.POINTER(TmaParams),
+                                                      C.POINTER(C.c_uint64), C.POINTER(C.c_int32)]
+    L.frisk_b200_gemm_plan_operand_layout.restype = C.c_int
     L.frisk_b200_swizzled_offset.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
                                              C.c_int32]
     L.frisk_b200_swizzled_offset.restype = C.c_int64
@@ -225,7 +229,8 @@ class GemmPlan:
                  scales: bool = False, lda: int = 0, ldb: int = 0, ldc: int = 0,
                  force_kernel: Optional[str] = None, tile_n: int = 0, stages: int = 0,
                  num_ctas: int = 0, band_tiles: int = 0, epilogue: int = 0,
-                 row_reduce: Optional[str] = None, row_reduce_clear: bool = True):
+                 row_reduce: Optional[str] = None, row_reduce_clear: bool = True,
+                 panel_tiles: int = 0, l2_hints: int = 0):
         L = lib()
         d = GemmDesc()
         d.M, d.N, d.K = M, N, K
@@ -240,6 +245,7 @@ class GemmPlan:
         d.epilogue = epilogue
         d.row_reduce = 0 if row_reduce is None else 1 + REDUCE_KINDS[row_reduce]
         d.row_reduce_clear = int(row_reduce_clear)
+        d.panel_tiles, d.l2_hints = panel_tiles, l2_hints
         self.desc = d
         self._h = C.c_void_p()
         _check(L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(self._h)), "plan_create")
@@ -256,6 +262,16 @@ class GemmPlan:
         _check(lib().frisk_b200_gemm_plan_info(self._h, C.byref(info)), "plan_info")
         self.info = info.as_dict()
         return self.info
+
+    def operand_layout(self, operand: int) -> dict:
+        """The staged tile of operand 0 (UMMA rows) or 1 (UMMA columns) as the plan uses it."""
+        lay, desc, boxes = TmaParams(), C.c_uint64(), C.c_int32()
+        _check(lib().frisk_b200_gemm_plan_operand_layout(self._h, operand, C.byref(lay), C.byref(desc),
+                                                         C.byref(boxes)), "plan_operand_layout")
+        out = lay.as_dict()
+        out["umma_desc_base"] = int(desc.value)
+        out["tma_boxes_per_stage"] = int(boxes.value)
+        return out
 
     @classmethod
     def for_workload(cls, w: W.GemmWorkload, **kw) -> "GemmPlan":

@@ -88,7 +88,10 @@ typedef struct frisk_gemm_desc {
   int32_t band_tiles;   /* tile rows walked together by the rasterisation (L2 reuse)         */
   int32_t epilogue;     /* whole-tile tensor-core plans: 1 = every thread stores its own row
                            pieces, 2 = rows staged through shared memory and stored as 128-byte
-                           pieces (needs a 16-byte aligned C and row pitch, else 1 is used)     */
+                           pieces (a C without 16-byte aligned rows is stored element-wise
+                           either way), 3 = as 2 with linear instead of swizzled staging rows:
+                           same results, shared-memory bank conflicts on every staging write
+                           (kept so that the swizzle's effect can be measured)                  */
   /* A frisk.reduce of C over its columns (dim 1), executed inside the GEMM's epilogue instead of
    * a second pass over C (the reference's sketches reduce the accumulator of a gemm this way:
    * tmp/ir.mlir:116, 135).  row_reduce = 1 + frisk_reduce_kind, 0 = none.  The fold sees the
@@ -97,6 +100,10 @@ typedef struct frisk_gemm_desc {
    * [M] of C's element type, goes to frisk_gemm_run_args.row_reduce_dst.                      */
   int32_t row_reduce;
   int32_t row_reduce_clear; /* 1: dst = fold, 0: dst = dst (op) fold (the op's `clear`)        */
+  /* More tuning overrides of the CTA-pair kernel; 0 = let the plan choose.                     */
+  int32_t panel_tiles;  /* > 0: walk the tiles in panels of this many tile columns (the panel
+                           of B stays in L2 while A streams past) instead of bands of rows      */
+  int32_t l2_hints;     /* bit 0: loads of A evict-first in L2; bit 1: loads of B evict-last    */
 } frisk_gemm_desc;
 
 typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */
@@ -336,6 +343,20 @@ typedef struct frisk_tma_params {
 
 /* The selection rule of FriskOps.cpp:608-617 carried over to TMA / UMMA descriptors. */
 int frisk_b200_layout_to_tma(const frisk_layout_desc* layout, frisk_tma_params* out);
+
+/*
+ * What a tensor-core plan stages per pipeline stage for its two operands (operand 0: the one
+ * that feeds the 128 UMMA rows, 1: the one that feeds the UMMA N columns; for a few-row plan the
+ * weights are operand 0).  `layout` is frisk_b200_layout_to_tma's answer for the staged tile --
+ * the plan fills its TMA boxes and UMMA descriptors from it and from nothing else --,
+ * `umma_desc_base` the 64-bit shared-memory descriptor the kernel adds start addresses to
+ * (bits 16..29 LBO / 16, 32..45 SBO / 16, 46 the sm_100 version, 61..63 the swizzle), and
+ * `tma_boxes_per_stage` how many copies fill the operand's part of a stage.  Any output
+ * pointer may be NULL.  FRISK_ERR_UNSUPPORTED for a CUDA-core plan.
+ */
+int frisk_b200_gemm_plan_operand_layout(const frisk_gemm_plan* plan, int32_t operand,
+                                        frisk_tma_params* layout, uint64_t* umma_desc_base,
+                                        int32_t* tma_boxes_per_stage);
 
 /*
  * Byte offset inside a swizzled rows x cols tile of element (row, col), as TMA writes it and

@@ -159,7 +159,7 @@ def test_run_ex_argument_errors():
     a.n_peers = 0                                             # a fused reduce needs its destination
     assert L.frisk_b200_gemm_run_ex(plan._h, C.byref(a)) == -1
     plan.close()
-    for bad in (dict(epilogue=3), dict(epilogue=-1)):
+    for bad in (dict(epilogue=4), dict(epilogue=-1)):
         with pytest.raises(R.FriskError) as e:
             R.GemmPlan(256, 256, 256, W.BF16, **bad)
         assert e.value.code == -1
@@ -277,7 +277,9 @@ def test_reduce_plans_cover_the_reduced_dimension_exactly_once():
             for aligned in (True, False):
                 info = R.reduce_info(d, aligned)
                 empty = d.outer == 0 or d.inner == 0
-                assert info["launches"] == (0 if empty else 2 if info["chunks"] > 1 else 1)
+                # a cut line reduce folds its pieces in a second launch; a cut column reduce in the
+                # same launch (the last CTA of each column block folds them)
+                assert info["launches"] == (0 if empty else 2 if info["chunks"] > 1 and info["lines"] else 1)
                 assert info["lines"] == int(d.inner == 1)
                 assert info["chunks"] >= 1 and info["chunk_len"] >= 1
                 if not empty:
@@ -285,6 +287,9 @@ def test_reduce_plans_cover_the_reduced_dimension_exactly_once():
                     assert (info["chunks"] - 1) * info["chunk_len"] < max(d.extent, 1)
                     assert info["ctas"] >= 1
                 want_ws = d.outer * info["chunks"] * d.inner * 4 if info["chunks"] > 1 else 0
+                if info["chunks"] > 1 and not info["lines"]:   # ... and keeps its arrival counters there
+                    assert want_ws < info["workspace_bytes"] <= want_ws + 32 + 4 * d.outer * d.inner
+                    want_ws = info["workspace_bytes"]
                 assert info["workspace_bytes"] == want_ws <= need
                 if not aligned and d.inner != 1:
                     assert info["vector"] == 1

@@ -99,6 +99,8 @@ def test_staged_and_direct_epilogues_give_the_same_bits(M, N, K, ab, ct, ta, tb,
     direct, _, _, info1 = device_run(w, epilogue=1, force_kernel=kernel)
     assert info["kernel_name"] == kernel == info1["kernel_name"]
     assert np.array_equal(staged, direct)
+    linear, _, _, _ = device_run(w, epilogue=3, force_kernel=kernel)   # unswizzled staging rows
+    assert np.array_equal(linear, direct)
     ok, err, metric = W.check(W.decode(staged, ct), ref.ref_gemm_f64(w), ab, absdot=ref.abs_dot(w))
     assert ok, f"{metric} = {err}"
     # a padded row pitch keeps the staged form as long as rows stay 16-byte aligned ...
@@ -166,3 +168,19 @@ def test_row_reduce_needs_a_whole_tile_tensor_core_plan():
     p = R.GemmPlan(16, 4096, 1024, W.BF16, row_reduce="max")   # a few-row shape: whole tiles instead
     assert p.info["kernel_name"] == "tcgen05" and p.workspace_bytes > 0
     p.close()
+
+
+@pytest.mark.parametrize("M,N,K,ab,ct,ta,tb", [(1536, 2304, 256, W.BF16, W.BF16, False, False),
+                                               (1000, 1000, 520, W.F16, W.F16, False, True),
+                                               (768, 1280, 512, W.E4M3, W.BF16, False, True)])
+def test_tile_walks_and_l2_hints_do_not_change_the_bits(M, N, K, ab, ct, ta, tb):
+    """Bands of tile rows, panels of tile columns, and the L2 eviction hints of the loads are
+    about where the bytes come from, never about what is computed."""
+    w = make(M, N, K, ab, ct, ta, tb, seed=8)
+    base, _, _, info = device_run(w, force_kernel="tcgen05_pair")
+    ok, err, metric = W.check(W.decode(base, ct), ref.ref_gemm_f64(w), ab, absdot=ref.abs_dot(w))
+    assert ok, f"{metric} = {err}"
+    for kw in (dict(panel_tiles=1), dict(panel_tiles=2), dict(panel_tiles=3, l2_hints=3), dict(panel_tiles=64),
+               dict(band_tiles=2, l2_hints=1), dict(l2_hints=2)):
+        got, _, _, _ = device_run(w, force_kernel="tcgen05_pair", **kw)
+        assert np.array_equal(got, base), kw

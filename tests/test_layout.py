@@ -9,6 +9,7 @@ import pytest
 
 import frisk as F
 from frisk_b200 import runtime as R
+from frisk_b200 import workloads as W
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -87,7 +88,7 @@ def test_swizzle_selection_rule_and_descriptor_fields(bits):
 
 
 def test_kernel_operand_layouts_are_the_mapped_ones():
-    """The tiles the tcgen05 kernel stages are what layout_to_tma yields for them."""
+    """The mapper's answers for the tile shapes the kernels stage, as literals."""
     a = R.layout_to_tma(128, 64, 16, True)    # A tile 128 x 64 bf16, K-major
     assert (a["swizzle_bytes"], a["num_boxes"], a["box_inner"], a["box_outer"]) == (128, 1, 64, 128)
     assert (a["stride_byte_offset"], a["k_step_bytes"]) == (1024, 32)
@@ -96,6 +97,44 @@ def test_kernel_operand_layouts_are_the_mapped_ones():
     assert (b["leading_byte_offset"], b["stride_byte_offset"], b["k_step_bytes"]) == (8192, 1024, 2048)
     f8 = R.layout_to_tma(256, 128, 8, True)   # e4m3 B tile 256 x 128, K-major
     assert (f8["swizzle_bytes"], f8["box_inner"], f8["k_step_bytes"]) == (128, 128, 32)
+
+
+@pytest.mark.parametrize("dims,ab,kw,tiles", [
+    # (M, N, K), input type, plan options, ((rows, cols, k_inner) of the staged A-role / B-role tile)
+    ((8192, 8192, 8192), W.BF16, {}, ((128, 64, True), (64, 128, False))),            # pair: half of B per CTA
+    ((4096, 4096, 4096), W.F16, dict(transB=True), ((128, 64, True), (128, 64, True))),
+    ((8192, 8192, 8192), W.E4M3, dict(transB=True, c_type=W.BF16, scales=True), ((128, 128, True), (128, 128, True))),
+    ((384, 1024, 2048), W.BF16, dict(transA=True), ((64, 128, False), (64, 128, False))),   # A stored [K, M]
+    ((128, 512, 256), W.BF16, dict(force_kernel="tcgen05"), ((128, 64, True), (64, 256, False))),
+    ((16, 8192, 8192), W.BF16, {}, ((64, 256, False), (16, 64, True))),               # few rows: weights first
+    ((64, 8192, 256), W.F16, dict(transB=True), ((256, 64, True), (64, 64, True))),
+])
+def test_plans_stage_exactly_what_the_layout_mapper_says(dims, ab, kw, tiles):
+    """The plan's TMA boxes and UMMA descriptors come from frisk_b200_layout_to_tma: for every
+    operand of every kernel family the plan reports the mapper's answer for the staged tile, and
+    the 64-bit descriptor base the kernel runs on is that answer bit for bit."""
+    kw = dict(kw)
+    plan = R.GemmPlan(*dims, ab, kw.pop("c_type", None), **kw)
+    bits = 8 * W.ELEM_SIZE[ab]
+    for operand, (rows, cols, k_inner) in enumerate(tiles):
+        got = plan.operand_layout(operand)
+        want = R.layout_to_tma(rows, cols, bits, k_inner)
+        for key, value in want.items():
+            assert got[key] == value, (operand, key, got[key], value)
+        assert got["swizzle_bytes"] == 128 == plan.info["swizzle_a"] == plan.info["swizzle_b"]
+        d = got["umma_desc_base"]
+        assert (d >> 16) & 0x3FFF == want["leading_byte_offset"] // 16
+        assert (d >> 32) & 0x3FFF == want["stride_byte_offset"] // 16
+        assert (d >> 46) & 1 == 1 and (d >> 61) & 7 == want["umma_layout_type"] == 2
+        assert d & 0x3FFF == 0                       # the start address is added per stage
+        # the copies of a stage cover the tile: the mapper's boxes, or (a K-major half of B in the
+        # CTA-pair kernel, so that a half-width item can load half of it) two boxes of half the rows
+        assert got["tma_boxes_per_stage"] in (want["num_boxes"], 2 * want["num_boxes"])
+    plan.close()
+    p = R.GemmPlan(64, 64, 64, W.F32)
+    with pytest.raises(R.FriskError):
+        p.operand_layout(0)   # the CUDA-core kernel stages nothing by TMA
+    p.close()
 
 
 def test_swizzled_offsets_are_a_permutation_of_the_tile():

@@ -74,18 +74,57 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs.
+
+    NVML is read directly from a thread every 2 ms (a timed region can be a few milliseconds long
+    at 8 GPUs, far shorter than one round of `nvidia-smi`); when the NVML binding is missing the
+    sampler falls back to an `nvidia-smi -lms` child process.  Reading only: no setting is touched.
+    """
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index = index
+    def __init__(self, index: int, uuid=None):
+        self.index, self.uuid = index, uuid
         self.proc = None
         self.lines: list[str] = []
+        self.samples: list[tuple] = []   # (sm MHz, max MHz, reasons bit mask)
+        self.nvml = None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        if self.uuid is not None:
+            try:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(self.uuid)).encode())
+            except Exception:
+                pass
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def start(self):
+        try:
+            self.nvml, handle = self._nvml_handle()
+            mx = self.nvml.nvmlDeviceGetMaxClockInfo(handle, self.nvml.NVML_CLOCK_SM)
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        sm = self.nvml.nvmlDeviceGetClockInfo(handle, self.nvml.NVML_CLOCK_SM)
+                        why = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        self.samples.append((float(sm), float(mx), int(why)))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
@@ -100,6 +139,24 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self) -> dict:
+        if self.nvml is not None:
+            self._stop.set()
+            self._thread.join(timeout=1.0)
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+            n = self.nvml
+            names = (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown),
+                     ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown),
+                     ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap))
+            mask = 0
+            for _, _, why in self.samples:
+                mask |= why
+            sm = [x[0] for x in self.samples]
+            busy = [x for x in sm if x > 0.5 * max(sm)] or sm
+            return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": self.samples[0][1],
+                    "reasons": sorted(k for k, bit in names if mask & bit), "samples": len(sm),
+                    "how": "NVML every 2 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -122,7 +179,7 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         busy = [s for s in sm if s > 0.5 * max(sm)] or sm
         return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(mx)),
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "how": "nvidia-smi -lms 20"}
 
 
 TORCH_BITS = {W.F32: "float32", W.F16: "float16", W.BF16: "bfloat16", W.E4M3: "float8_e4m3fn"}
@@ -526,7 +583,7 @@ def main():
     torch.cuda.synchronize()
     R.check_status(status, stream)
 
-    sampler = ClockSampler(local)   # every rank samples its own GPU
+    sampler = ClockSampler(local, getattr(torch.cuda.get_device_properties(local), "uuid", None))   # every rank its own GPU
     sampler.start()
     if dist:
         dist.barrier()
@@ -642,7 +699,7 @@ def main():
                    "stages": info["stages"], "ctas": info["num_ctas"],
                    "l2": "inputs larger than L2" if flush is None else "192 MiB written between iterations"},
         "roofline": roof,
-        "clocks": {k: my_clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "samples")},
+        "clocks": {k: my_clocks.get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons", "samples", "how")},
         "clocks_per_rank": per_rank,
         "clock_normalised": clock_note,
         "gpu_launches": info["launches"] * args.steps,

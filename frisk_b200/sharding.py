@@ -81,7 +81,10 @@ class PeerGather:
         self.row0, self.rows = local_rows(M, world, rank)
         offset = self.row0 * N * elem_size
         self.local_c = self.ptr + offset
-        self.peer_dsts = [self.peer_ptrs[r] + offset for r in sorted(self.peer_ptrs)]
+        # each rank walks its peers starting with its right-hand neighbour, so that at any moment
+        # the ranks' epilogues aim at different GPUs instead of all at the same one
+        order = [(rank + k) % world for k in range(1, world)]
+        self.peer_dsts = [self.peer_ptrs[r] + offset for r in order]
 
     def as_tensor(self, dtype):
         """The rank's whole-C buffer as a torch tensor [M, N] (no copy)."""

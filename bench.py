@@ -36,9 +36,10 @@ from frisk_b200 import workloads as W  # noqa: E402
 FULL_DIMS = {
     "cfg1": (512, 512, 512), "cfg2": (4096, 4096, 4096), "cfg3": (16, 8192, 8192),
     "cfg4": (8192, 8192, 8192), "cfg5": (65536, 8192, 8192), "bf16_8192": (8192, 8192, 8192),
+    "fp32_4096": (4096, 4096, 4096),   # cfg1's layout and distribution at a size the 3xTF32 plan takes
 }
-AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3}
-C_TYPE = {"cfg1": W.F32, "cfg2": W.F16}
+AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3, "fp32_4096": W.F32}
+C_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "fp32_4096": W.F32}
 TRANS_B = {"cfg2", "cfg4"}
 BOUND = {"cfg3": "hbm"}  # everything else is measured against the tensor-core peak
 # DRAM bytes per launch of the dominant kernel (ncu: dram__bytes_read.sum + dram__bytes_write.sum
@@ -233,7 +234,7 @@ def out_dtype(torch, name):
 L2_BYTES = 126 * 1024 * 1024
 
 
-def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False):
+def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False, **plan_kw):
     """`steps` back-to-back launches of the plan on device-resident inputs.
 
     Returns (ms_per_step, plan info, l2 note).  With `rotate` (workloads whose operands would
@@ -248,7 +249,7 @@ def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False)
         copies = min(64, max(2, -(-2 * L2_BYTES // per_set) + 1))
     sets = [(A, B, C)] + [(A.clone(), B.clone(), torch.empty_like(C)) for _ in range(copies - 1)]
     plan = R.GemmPlan(M, N, K, AB_TYPE.get(name, W.BF16), C_TYPE.get(name, W.BF16),
-                      transB=name in TRANS_B, scales=sa is not None)
+                      transB=name in TRANS_B, scales=sa is not None, **plan_kw)
     ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream
@@ -284,7 +285,7 @@ def measure_tensor_peaks(torch, R, dev, like_ms):
       figure of the same kind as the bf16 one in the peaks file.
     """
     out = {}
-    for key, ab in (("e4m3", W.E4M3), ("bf16", W.BF16)):
+    for key, ab in (("e4m3", W.E4M3), ("bf16", W.BF16), ("tf32", W.F32)):
         try:
             probe = R.measure_mma_peak(ab, pair=True, k_blocks=1024, reps=5)
             want = like_ms.get(key, probe["ms_per_launch"])
@@ -346,7 +347,14 @@ def roofline_for(name, M, N, K, ms, peaks, sustained, tensor_peaks=None):
                      "frac_of_nominal_4500": round(achieved / 4500.0, 4),
                      "frac_of_2x_cublas_bf16": round(achieved / (2.0 * peaks["bf16_tflops"]), 4)}
         if ab == W.F32:
-            peak = None  # CUDA-core kernel: no tensor roofline applies
+            # the 3xTF32 plan spends three tf32 products per fp32 product: its ceiling is a third
+            # of the tensor pipes' tf32 rate measured in this run; the CUDA-core kernel (small
+            # problems) has no tensor roofline
+            mma = (tensor_peaks or {}).get("mma_only_tf32", {}).get("tflops")
+            if mma and name != "cfg1":
+                peak, source = mma / 3.0, "measured mma-only tf32 / 3"
+            else:
+                peak = None
     out = {"bound": BOUND.get(name, "tensor"), "achieved": round(achieved, 2),
            "peak": None if peak is None else round(peak, 1), "unit": unit,
            "frac": None if peak is None else round(achieved / peak, 4),
@@ -710,16 +718,16 @@ def main():
 
     if world == 1 and not args.no_others and not args.rows:
         others = {}
-        tensor_peaks = measure_tensor_peaks(torch, R, dev, {"e4m3": 0.37, "bf16": 0.70})
+        tensor_peaks = measure_tensor_peaks(torch, R, dev, {"e4m3": 0.37, "bf16": 0.70, "tf32": 0.45})
         line["tensor_peaks_measured"] = tensor_peaks
-        for other in ("cfg1", "cfg2", "cfg3", "cfg4", "bf16_8192"):
+        for other in ("cfg1", "cfg2", "cfg3", "cfg4", "bf16_8192", "fp32_4096"):
             if other == name:
                 continue
             m, n, k = FULL_DIMS[other]
             small = other in ("cfg1", "cfg2", "cfg3")  # operands (nearly) fit in L2: rotate copies
             ms, oinfo, l2_note = time_device(torch, R, other, m, n, k,
                                              max(args.steps, 200 if small else 10), args.warmup, dev,
-                                             seed=int(other[-1]) if other[-1].isdigit() else 5,
+                                             seed=int(other[-1]) if other.startswith("cfg") else 5,
                                              rotate=small)
             r = roofline_for(other, m, n, k, ms, peaks, False, tensor_peaks)
             others[other] = {"ms": round(ms, 5), "kernel": oinfo["kernel_name"],
@@ -728,6 +736,13 @@ def main():
                              "l2": l2_note}
             if other == "cfg2":
                 others[other]["library_same_shape"] = library_matmul(torch, dev, m, n, k, torch.float16)
+            if other == "cfg1":   # the same problem forced onto the 3xTF32 plan (three launches)
+                ms3, _, _ = time_device(torch, R, other, m, n, k, 200, args.warmup, dev, seed=1, rotate=True,
+                                        force_kernel="tf32x3")
+                others[other]["tf32x3_forced_ms"] = round(ms3, 5)
+            if other == "fp32_4096":   # ... and the large one on the CUDA-core kernel
+                ms1, _, _ = time_device(torch, R, other, m, n, k, 3, 1, dev, seed=5, force_kernel="simt")
+                others[other]["cuda_core_ms"] = round(ms1, 3)
         line["other_configs"] = others
         line["reduce"] = time_reduce(torch, R, dev, max(args.steps, 30), max(args.warmup, 3), peaks,
                                      not args.no_cpu)

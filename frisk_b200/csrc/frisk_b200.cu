@@ -17,6 +17,7 @@
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
 #include "mma_peak.cuh"
+#include "tf32_split.cuh"
 
 namespace {
 
@@ -77,7 +78,13 @@ struct OperandView {
 }  // namespace
 
 struct frisk_gemm_plan {
-  frisk_gemm_desc d;
+  frisk_gemm_desc d;   // the caller's problem
+  // The problem the tensor-core kernel sees.  Equal to `d` except for a 3xTF32 plan, where A and B
+  // are the split operands in the workspace: K three times as long, their own leading dimensions.
+  frisk_gemm_desc kd;
+  bool tf32 = false;
+  bool tf32_pair = false;        // which whole-tile kernel runs the split problem
+  size_t tf32_a_bytes = 0, tf32_b_bytes = 0;
   int device = -1;
   int sm_count = 148;
   bool have_device = false;
@@ -165,8 +172,9 @@ int fill_operand(frisk::OperandParams& o, frisk_tma_params& lay, bool mn_major, 
 }
 
 uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t m, uint32_t n) {
-  uint32_t fmt = 0;  // kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3
+  uint32_t fmt = 0;  // kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3; kind::tf32: 2 = tf32
   if (ab_type == FRISK_DT_BF16) fmt = 1;
+  if (ab_type == FRISK_DT_F32) fmt = 2;
   uint32_t d = 0;
   d |= 1u << 4;  // fp32 accumulator
   d |= fmt << 7;
@@ -188,6 +196,7 @@ int encode_operand_map(CUtensorMap* map, const OperandView& v, int dtype, uint32
   const uint32_t es = elem_size(dtype);
   CUtensorMapDataType dt = dtype == FRISK_DT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                            : dtype == FRISK_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                           : dtype == FRISK_DT_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   cuuint64_t dims[2], strides[1];
   cuuint32_t box[2], estr[2] = {1, 1};
@@ -249,6 +258,23 @@ int tcgen05_ineligible_reason(const frisk_gemm_desc& d) {
 }
 bool tcgen05_eligible(const frisk_gemm_desc& d) { return tcgen05_ineligible_reason(d) == FRISK_TC_OK; }
 
+// fp32 problems the 3xTF32 plan can take: fp32 C, 16-byte row pitches (TMA), extents that stay
+// below 2^31 after K is tripled, no scales, plain C = or += (the fold and the peers would work
+// too; they are not wired to this plan).
+bool tf32_eligible(const frisk_gemm_desc& d) {
+  if (d.a_type != FRISK_DT_F32 || d.c_type != FRISK_DT_F32) return false;
+  if ((d.lda % 4) || (d.ldb % 4)) return false;
+  if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || 3 * d.K + 4 >= (1ll << 31)) return false;
+  if (d.scale_mode != FRISK_SCALE_NONE || d.row_reduce) return false;
+  return true;
+}
+// ... and the ones it pays for: the split costs a pass over A and B and two more launches, and the
+// tensor-core tiles are coarse; measured against the CUDA-core kernel the break-even is near
+// 1 GFLOP (fp32 512^3, 0.27 GFLOP: 22 us on CUDA cores).
+bool tf32_worthwhile(const frisk_gemm_desc& d) {
+  return 2.0 * (double)d.M * (double)d.N * (double)d.K >= 1.0e9 && d.N >= 64 && d.K >= 64;
+}
+
 // Few rows of A against a wide B: the shape the swapped, K-split plan is for.  The kernel counts
 // (tile, k-block) units in 32 bits and multiplies the count by the grid size, so the product has
 // to stay below 2^32 (conservatively: the smallest tile and k-block the plan could pick).
@@ -268,7 +294,7 @@ bool pair_tail_split(uint64_t tile_n, uint64_t tiles, uint64_t pairs) {
 
 // cluster_try: which cluster candidate of a skinny plan to take (-1: none, plan stream-K).
 void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0) {
-  const frisk_gemm_desc& d = pl->d;
+  const frisk_gemm_desc& d = pl->kd;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
   pl->plan_error = 0;
@@ -491,13 +517,13 @@ int ensure_dyn_smem(Kern kern, int device) {
   if (tracked) __atomic_store_n(&done[device], true, __ATOMIC_RELEASE);
   return FRISK_OK;
 }
-template <typename TC, bool kSplit, bool kFold> struct OneCtaKernelTag {};
-template <typename TC, bool kFold> struct PairKernelTag {};
+template <typename TC, bool kSplit, bool kFold, bool kTf32 = false> struct OneCtaKernelTag {};
+template <typename TC, bool kFold, bool kTf32 = false> struct PairKernelTag {};
 
-template <typename TC, bool kSplit, bool kFold>
+template <typename TC, bool kSplit, bool kFold, bool kTf32 = false>
 int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit, kFold>;
-  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit, kFold>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit, kFold, kTf32>;
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit, kFold, kTf32>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -565,10 +591,10 @@ int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream
                    : launch_tcgen05_ts<TC, false, false>(pl, g, st);
 }
 
-template <typename TC, bool kFold>
+template <typename TC, bool kFold, bool kTf32 = false>
 int launch_pair_tf(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_pair_kernel<TC, kFold>;
-  if (int rc = ensure_dyn_smem<PairKernelTag<TC, kFold>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_pair_kernel<TC, kFold, kTf32>;
+  if (int rc = ensure_dyn_smem<PairKernelTag<TC, kFold, kTf32>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -602,6 +628,24 @@ int launch_finalize_t(const frisk_gemm_plan* pl, float* ws, void* C, const float
   const int blocks = (int)std::min<int64_t>((work + threads - 1) / threads, 4 * (int64_t)pl->sm_count);
   frisk::splitk_finalize_kernel<TC><<<blocks, threads, 0, st>>>(
       ws, d.N, reinterpret_cast<TC*>(C), d.ldc, d.M, d.N, sa, sb, d.clear_accum);
+  FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
+// One operand of a 3xTF32 plan (`mn` x `k` logically) into its three K segments, K innermost.
+// `k_along_rows`: the source is stored [k, mn] (mn contiguous) and is transposed on the way.
+int launch_tf32_split(const float* src, float* dst, int64_t mn, int64_t k, int64_t ld_src,
+                      int64_t ld_dst, bool k_along_rows, uint32_t lo_mask, int sm_count,
+                      cudaStream_t st) {
+  if (k_along_rows) {
+    const dim3 grid((unsigned)((mn + 31) / 32), (unsigned)((k + 31) / 32));
+    if (grid.y > 65535) return FRISK_ERR_UNSUPPORTED;
+    frisk::tf32_split_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(src, dst, k, mn, ld_src, ld_dst, lo_mask);
+  } else {
+    const int64_t work = mn * ((k + 3) / 4);
+    const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, 8 * (int64_t)sm_count));
+    frisk::tf32_split_kernel<<<blocks, 256, 0, st>>>(src, dst, mn, k, ld_src, ld_dst, 1, lo_mask);
+  }
   FRISK_CUDA(cudaGetLastError());
   return FRISK_OK;
 }
@@ -708,7 +752,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.tile_n != 0 && d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256)
     return FRISK_ERR_INVALID_ARGUMENT;
-  if (d.force_kernel < 0 || d.force_kernel > 4 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
+  if (d.force_kernel < 0 || d.force_kernel > 5 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.epilogue < 0 || d.epilogue > 3 || d.row_reduce < 0 || d.row_reduce > 4 ||
       d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3)
@@ -718,6 +762,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   frisk_gemm_plan* pl = new (std::nothrow) frisk_gemm_plan();
   if (!pl) return FRISK_ERR_INVALID_ARGUMENT;
   pl->d = d;
+  pl->kd = d;
   memset(&pl->info, 0, sizeof pl->info);
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) {
@@ -731,6 +776,37 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     cudaGetLastError();  // plans can be made (and inspected) on a machine without a GPU
   }
 
+  // fp32 inputs: three tf32 products on the tensor cores when the problem is large enough
+  if ((d.force_kernel == 1 + FRISK_KERNEL_TF32X3) ||
+      (!d.force_kernel && tf32_eligible(d) && tf32_worthwhile(d))) {
+    if (!tf32_eligible(d)) {
+      delete pl;
+      return d.a_type == FRISK_DT_F32 ? FRISK_ERR_MISALIGNED : FRISK_ERR_UNSUPPORTED;
+    }
+    frisk_gemm_desc& k = pl->kd;
+    k.K = 3 * d.K;
+    // A' is [M, 3K] and B' is [N, 3K], K innermost (kind::tf32 reads 32-bit operands K-inner
+    // only), rows padded to a 16-byte multiple, whatever the order A and B are stored in
+    k.transA = 0;
+    k.transB = 1;
+    k.lda = k.ldb = (3 * d.K + 3) / 4 * 4;
+    k.force_kernel = 0;
+    pl->tf32 = true;
+    pl->tf32_a_bytes = ((size_t)d.M * k.lda * sizeof(float) + 255) / 256 * 256;
+    pl->tf32_b_bytes = ((size_t)d.N * k.ldb * sizeof(float) + 255) / 256 * 256;
+    pl->tf32_pair = d.M > 128 && d.N > 64 && d.tile_n != 64 && pl->sm_count >= 2;
+    plan_tcgen05(pl, /*swap=*/false, pl->tf32_pair);
+    if (pl->plan_error) {
+      const int rc = pl->plan_error;
+      delete pl;
+      return rc;
+    }
+    pl->info.kernel = FRISK_KERNEL_TF32X3;
+    pl->info.launches = 3;   // the split of A, the split of B, the GEMM
+    pl->ws_bytes = pl->tf32_a_bytes + pl->tf32_b_bytes;
+    *out = pl;
+    return FRISK_OK;
+  }
   const bool tc_ok = tcgen05_eligible(d);
   const bool skinny_ok = tc_ok && skinny_shape(d, pl->sm_count);
   const bool pair_ok = tc_ok && d.M > 128 && d.N > 64 && d.tile_n != 64 && pl->sm_count >= 2;
@@ -882,6 +958,37 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
   const float* sb = d.scale_mode ? args->scale_b : nullptr;
   const bool whole_tile_tc =
       pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR;
+
+  if (pl->tf32) {
+    // fp32 on the tensor cores: split A and B into the workspace, then run the tensor-core
+    // kernel on the split operands (K three times as long).  Any alignment of A and B will do:
+    // the split reads them with plain loads.
+    if (args->n_peers > 0) return FRISK_ERR_UNSUPPORTED;
+    if (!workspace || args->workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
+    if ((uintptr_t)workspace % 256) return FRISK_ERR_MISALIGNED;
+    float* a3 = reinterpret_cast<float*>(workspace);
+    float* b3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + pl->tf32_a_bytes);
+    const frisk_gemm_desc& k = pl->kd;
+    // A' = [A_lo | A_hi | A_hi], B' = [B_hi ; B_lo ; B_hi] along K: small terms first
+    int rc = launch_tf32_split(static_cast<const float*>(A), a3, d.M, d.K, d.lda, k.lda,
+                               /*k_along_rows=*/d.transA != 0, 0x1u, pl->sm_count, st);
+    if (rc) return rc;
+    rc = launch_tf32_split(static_cast<const float*>(B), b3, d.N, d.K, d.ldb, k.ldb,
+                           /*k_along_rows=*/d.transB == 0, 0x2u, pl->sm_count, st);
+    if (rc) return rc;
+    frisk::GemmParams g = pl->gp;
+    OperandView va{a3, k.M, k.K, k.lda, k.transA != 0};
+    OperandView vb{b3, k.N, k.K, k.ldb, k.transB == 0};
+    rc = encode_operand_map(&pl->tmap_a, va, FRISK_DT_F32, g.a.box_mn, g.bk_elems, pl->lay_a.swizzle_bytes);
+    if (rc) return rc;
+    rc = encode_operand_map(&pl->tmap_b, vb, FRISK_DT_F32, g.b.box_mn, g.bk_elems, pl->lay_b.swizzle_bytes);
+    if (rc) return rc;
+    g.C = C;
+    g.status = args->device_status;
+    g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
+    return pl->tf32_pair ? launch_pair_tf<float, false, true>(pl, g, st)
+                         : launch_tcgen05_ts<float, false, false, true>(pl, g, st);
+  }
 
   const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
   if ((args->n_peers > 0 || d.row_reduce) && !(whole_tile_tc && ptr_aligned)) {
@@ -1237,6 +1344,7 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
 
   frisk_gemm_plan pl;  // lives on the stack: nothing is allocated on the host heap either
   pl.d = d;
+  pl.kd = d;
   memset(&pl.info, 0, sizeof pl.info);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {
@@ -1302,8 +1410,7 @@ size_t frisk_b200_gemm_skinny_static_capacity(void) { return kStaticScratchFloat
 int frisk_b200_measure_mma_peak(int32_t ab_type, int32_t pair, int32_t k_blocks, int32_t reps,
                                 double* tflops, double* ms_per_launch) {
   if (!tflops || k_blocks < 32 || k_blocks % 32 || reps < 1) return FRISK_ERR_INVALID_ARGUMENT;
-  if (ab_type != FRISK_DT_F16 && ab_type != FRISK_DT_BF16 && ab_type != FRISK_DT_E4M3)
-    return FRISK_ERR_UNSUPPORTED;
+  if (!elem_size(ab_type)) return FRISK_ERR_UNSUPPORTED;   // fp32 is measured as kind::tf32
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     cudaGetLastError();
@@ -1339,10 +1446,10 @@ int frisk_b200_measure_mma_peak(int32_t ab_type, int32_t pair, int32_t k_blocks,
     attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const uint32_t f8 = ab_type == FRISK_DT_E4M3;
+    const uint32_t kind = ab_type == FRISK_DT_E4M3 ? 1u : ab_type == FRISK_DT_F32 ? 2u : 0u;
     if (pair)
-      return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<1>, (uint32_t)k_blocks, idesc, f8, es, status);
-    return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<0>, (uint32_t)k_blocks, idesc, f8, es, status);
+      return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<1>, (uint32_t)k_blocks, idesc, kind, es, status);
+    return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<0>, (uint32_t)k_blocks, idesc, kind, es, status);
   };
   if (!rc) {
     e = pair ? cudaFuncSetAttribute(frisk::mma_peak_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)

@@ -809,7 +809,8 @@ __device__ __forceinline__ void reduce_share(const EpiArgs& p, uint32_t buf, uin
 // none of it: with the slot reduction inlined the kernel needs 200+ registers and measurably slows
 // the whole-tile main loop (8192^3 bf16: 0.98 ms against 0.83 ms), so the two are kept apart.
 // kFold (whole tiles only) compiles the fused row reduce in, for the same reason.
-template <typename TC, bool kSplit, bool kFold = false>
+// kTf32 (whole tiles, C fp32) issues kind::tf32 MMAs: the 3xTF32 plan of fp32 GEMMs.
+template <typename TC, bool kSplit, bool kFold = false, bool kTf32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
@@ -1035,7 +1036,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               // phase is not complete, and after the CTA's last k-block it never completes)
               if (ks == 3)
                 ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8 * next_stage, next_phase));
-              if (kind_f8) {
+              if (kTf32) {
+                if (ptx::elect_one()) ptx::mma_tf32(d_base, adesc, bdesc, idesc, accumulate);
+              } else if (kind_f8) {
                 if (ptx::elect_one()) ptx::mma_f8(d_base, adesc, bdesc, idesc, accumulate);
                 if (mi > 1 && ptx::elect_one())
                   ptx::mma_f8(d_base + tile_n, adesc + (a_sub_stride >> 4), bdesc, idesc, accumulate);

@@ -38,7 +38,8 @@ __device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t narrow_from) 
 // kFold compiles the fused row reduce in.  It is a template parameter, not a run-time switch:
 // with the fold's rendezvous / counter / re-read code present in the kernel -- even though a plain
 // GEMM never executes it -- the same launch ran 19 % slower (bf16 8192^3: 0.83 against 0.70 ms).
-template <typename TC, bool kFold>
+// kTf32 (C fp32 only) issues kind::tf32 MMAs on fp32 operand tiles: the 3xTF32 plan of fp32 GEMMs.
+template <typename TC, bool kFold, bool kTf32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
@@ -253,7 +254,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const uint32_t accumulate = first | (ks > 0 ? 1u : 0u);
             if (ks == 3)
               ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8 * next_stage, next_phase));
-            if (kind_f8) {
+            if (kTf32) {
+              if (ptx::elect_one()) ptx::mma_tf32_pair(d_base, adesc, bdesc, idesc, accumulate);
+            } else if (kind_f8) {
               if (ptx::elect_one()) ptx::mma_f8_pair(d_base, adesc, bdesc, idesc, accumulate);
             } else {
               if (ptx::elect_one()) ptx::mma_f16_pair(d_base, adesc, bdesc, idesc, accumulate);

@@ -17,8 +17,8 @@ __device__ __forceinline__ uint32_t peak_hash(uint32_t x) {
 
 template <int kPair>
 __global__ void __launch_bounds__(128, 1)
-mma_peak_kernel(uint32_t k_blocks, uint32_t idesc, uint32_t kind_f8, uint32_t elem_bytes,
-                int32_t* status) {
+mma_peak_kernel(uint32_t k_blocks, uint32_t idesc, uint32_t kind /* 0 f16, 1 f8f6f4, 2 tf32 */,
+                uint32_t elem_bytes, int32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_done[2];
   __shared__ uint32_t tmem_base_slot;
@@ -37,7 +37,9 @@ mma_peak_kernel(uint32_t k_blocks, uint32_t idesc, uint32_t kind_f8, uint32_t el
   for (uint32_t i = threadIdx.x; i < kStages * kStageBytes / 4; i += blockDim.x) {
     const uint32_t h = peak_hash(i * 2654435761u + blockIdx.x);
     uint32_t w;
-    if (elem_bytes == 2) {  // two 16-bit floats, exponent field near the bias, any sign / mantissa
+    if (elem_bytes == 4) {  // one fp32 with a tf32 mantissa: 0.5 .. 1, any sign
+      w = (h & 0x807FE000u) | 0x3F000000u;
+    } else if (elem_bytes == 2) {  // two 16-bit floats, exponent field near the bias, any sign / mantissa
       w = (h & 0x807F807Fu) | 0x3F003F00u;   // valid as bf16 (about 0.5 .. 1) and as fp16 (about 1.75)
     } else {                // four e4m3: exponent 6 .. 7, any sign / mantissa
       w = (h & 0x87878787u) | 0x30303030u;
@@ -80,7 +82,10 @@ mma_peak_kernel(uint32_t k_blocks, uint32_t idesc, uint32_t kind_f8, uint32_t el
 #pragma unroll
       for (uint32_t ks = 0; ks < 4; ++ks) {
         const uint32_t accumulate = ((kb & 63u) | ks) ? 1u : 0u;
-        if (kind_f8) {
+        if (kind == 2u) {
+          if (kPair) { if (ptx::elect_one()) ptx::mma_tf32_pair(d, ad + 2 * ks, bd + 2 * ks, idesc, accumulate); }
+          else { if (ptx::elect_one()) ptx::mma_tf32(d, ad + 2 * ks, bd + 2 * ks, idesc, accumulate); }
+        } else if (kind == 1u) {
           if (kPair) { if (ptx::elect_one()) ptx::mma_f8_pair(d, ad + 2 * ks, bd + 2 * ks, idesc, accumulate); }
           else { if (ptx::elect_one()) ptx::mma_f8(d, ad + 2 * ks, bd + 2 * ks, idesc, accumulate); }
         } else {

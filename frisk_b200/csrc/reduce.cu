@@ -31,8 +31,6 @@ struct Plan {
   int64_t chunks = 1;
   int64_t ctas = 0, ctas2 = 0;
   size_t ws_bytes = 0;
-  bool fold_in_kernel = false;  // columns, cut reduced dimension: one launch, the last CTA folds
-  size_t counter_off = 0, counter_bytes = 0;
 };
 
 int log2_ceil(int64_t v) {
@@ -124,15 +122,6 @@ int make_plan(const frisk_reduce_desc& d, bool src_align16, int64_t slots, Plan*
     }
   }
   if (p.chunks > 1) p.ws_bytes = (size_t)(d.outer * p.chunks * d.inner) * sizeof(float);
-  if (p.chunks > 1 && !p.lines) {
-    // the pieces are folded by the last CTA to arrive at each column block: the workspace carries
-    // one arrival counter per block behind the partial rows
-    p.fold_in_kernel = true;
-    p.counter_off = (p.ws_bytes + 15) / 16 * 16;
-    p.counter_bytes = ((size_t)(d.outer * p.xblocks) * sizeof(uint32_t) + 15) / 16 * 16;
-    p.ws_bytes = p.counter_off + p.counter_bytes;
-    p.ctas2 = 0;
-  }
   if (p.ctas > 0x7fffffffll || p.ctas2 > 0x7fffffffll || p.chunks > 0x7fffffffll) {
     frisk_internal_set_error("reduce: the shape needs more than 2^31 - 1 CTAs");
     return FRISK_ERR_TOO_LARGE;
@@ -148,13 +137,6 @@ const void* kernel_of(bool lines, int vec, bool deep = false) {
   if (lines) return reinterpret_cast<const void*>(&reduce_lines_kernel<TIn, TOut, KIND, FINAL, 4>);
   if (vec > 1) return reinterpret_cast<const void*>(&reduce_columns_kernel<TIn, TOut, KIND, FINAL, Vec<TIn>::N>);
   return reinterpret_cast<const void*>(&reduce_columns_kernel<TIn, TOut, KIND, FINAL, 1>);
-}
-
-template <typename T, int KIND>
-const void* fold_columns_kernel(int vec) {
-  using namespace frisk_reduce;
-  return vec > 1 ? reinterpret_cast<const void*>(&reduce_columns_kernel<T, float, KIND, false, Vec<T>::N, true>)
-                 : reinterpret_cast<const void*>(&reduce_columns_kernel<T, float, KIND, false, 1, true>);
 }
 
 // `dependent`: a programmatic dependent launch (it follows the first launch of the same reduce).
@@ -189,16 +171,6 @@ cudaError_t run_typed(const frisk_reduce_desc& d, const Plan& pl, const void* sr
   p.xblocks = pl.xblocks;
   if (pl.chunks == 1)
     return launch(kernel_of<T, T, KIND, true>(pl.lines, pl.vec, pl.deep), src, dst, p, pl.ctas, false, st);
-  if (pl.fold_in_kernel) {
-    using namespace frisk_reduce;
-    p.final_dst = dst;
-    p.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(ws) + pl.counter_off);
-    // the counters must be zero at launch; the kernel leaves them so, but the workspace is the
-    // caller's scratch and may come back with anything in it
-    cudaError_t e = cudaMemsetAsync(p.counters, 0, pl.counter_bytes, st);
-    if (e != cudaSuccess) return e;
-    return launch(fold_columns_kernel<T, KIND>(pl.vec), src, ws, p, pl.ctas, false, st);
-  }
   cudaError_t e = launch(kernel_of<T, float, KIND, false>(pl.lines, pl.vec, pl.deep), src, ws, p, pl.ctas, false, st);
   if (e != cudaSuccess) return e;
   Params q = p;  // the pieces are the reduced dimension of the second launch
@@ -214,14 +186,6 @@ cudaError_t run_typed(const frisk_reduce_desc& d, const Plan& pl, const void* sr
 // The first-launch kernel of a shape that goes through the workspace, for the occupancy query.
 template <typename T>
 const void* partial_kernel(int kind, bool lines, int vec) {
-  if (!lines) {  // a cut column reduce runs the variant whose last CTA folds the pieces
-    switch (kind) {
-      case FRISK_REDUCE_ADD: return fold_columns_kernel<T, 0>(vec);
-      case FRISK_REDUCE_MUL: return fold_columns_kernel<T, 1>(vec);
-      case FRISK_REDUCE_MIN: return fold_columns_kernel<T, 2>(vec);
-      default: return fold_columns_kernel<T, 3>(vec);
-    }
-  }
   switch (kind) {
     case FRISK_REDUCE_ADD: return kernel_of<T, float, 0, false>(lines, vec);
     case FRISK_REDUCE_MUL: return kernel_of<T, float, 1, false>(lines, vec);
@@ -297,7 +261,7 @@ int frisk_b200_reduce_info(const frisk_reduce_desc* desc, int src_align16, frisk
   out->lines = p.lines;
   out->vector = p.vec;
   out->chunks = (int32_t)p.chunks;
-  out->launches = (desc->outer == 0 || desc->inner == 0) ? 0 : (p.chunks > 1 && !p.fold_in_kernel) ? 2 : 1;
+  out->launches = (desc->outer == 0 || desc->inner == 0) ? 0 : p.chunks > 1 ? 2 : 1;
   out->chunk_len = p.chunk_len;
   out->ctas = p.ctas;
   out->workspace_bytes = p.ws_bytes;

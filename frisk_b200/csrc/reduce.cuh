@@ -31,11 +31,6 @@ struct Params {
   int32_t lanes_log2; // lines kernel: lanes per (line, piece)
   int32_t tx_log2;    // columns kernel: TX = 1 << tx_log2 threads along the contiguous dimension
   int64_t xblocks;    // columns kernel: CTAs along the contiguous dimension
-  // columns kernel, one-launch form of a cut reduced dimension: where the last CTA of a column
-  // block folds the pieces to (the source's element type), and one arrival counter per
-  // (outer index, column block), zero at launch
-  void* final_dst;
-  uint32_t* counters;
 };
 
 // The second launch of a two-launch reduce is a programmatic dependent launch: its CTAs may be
@@ -243,15 +238,11 @@ __global__ void __launch_bounds__(kThreads) reduce_lines_kernel(const TIn* __res
 // dst[o, c] (FINAL) or partial[(o * chunks + chunk) * inner + c] = fold over e of src[o, e, c].
 // VEC consecutive columns per thread (one 16-byte load when VEC > 1, which needs inner % VEC == 0
 // and an aligned base).  grid.x = outer * chunks * xblocks.
-// LAST (with FINAL = false, TOut = float): the CTA that writes the last piece of a column block --
-// an arrival counter per block tells which -- folds the block's pieces, in piece order whoever
-// arrives last, into p.final_dst: a cut reduced dimension then takes one launch instead of two.
-template <typename TIn, typename TOut, int KIND, bool FINAL, int VEC, bool LAST = false>
+template <typename TIn, typename TOut, int KIND, bool FINAL, int VEC>
 __global__ void __launch_bounds__(kThreads) reduce_columns_kernel(const TIn* __restrict__ src,
                                                                   TOut* __restrict__ dst, Params p) {
   using O = Op<KIND>;
   __shared__ float fold[kThreads * VEC];
-  __shared__ uint32_t is_last;
   dependent_launch_prologue();
   const int tx = threadIdx.x & ((1 << p.tx_log2) - 1), ty = threadIdx.x >> p.tx_log2;
   const int ny = kThreads >> p.tx_log2;
@@ -331,63 +322,6 @@ __global__ void __launch_bounds__(kThreads) reduce_columns_kernel(const TIn* __r
         *d = from_f32<TOut>(r);
       } else {
         dst[(o * p.chunks + chunk) * p.inner + col + v] = from_f32<TOut>(r);
-      }
-    }
-  }
-  if (LAST) {
-    __threadfence();   // this thread's piece is visible device-wide before the count goes up
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      uint32_t* ctr = p.counters + o * p.xblocks + xb;
-      const uint32_t before = atomicAdd(ctr, 1u);
-      is_last = before + 1u == (uint32_t)p.chunks ? 1u : 0u;
-      if (is_last) *ctr = 0;   // as the launch found it
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // the pieces of this column block: thread row ty takes pieces ty, ty + ny, ..., then the same
-    // tree over ty as above
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) acc[v] = O::identity();
-    if (live) {
-      const float* part = reinterpret_cast<const float*>(dst) + o * p.chunks * p.inner + col;
-      for (int64_t c = ty; c < p.chunks; c += ny) {
-        const float* q = part + c * p.inner;
-        if (VEC % 4 == 0) {
-#pragma unroll
-          for (int v = 0; v < VEC; v += 4) {
-            const float4 t = __ldcg(reinterpret_cast<const float4*>(q + v));
-            acc[v] = O::apply(acc[v], t.x);
-            acc[v + 1] = O::apply(acc[v + 1], t.y);
-            acc[v + 2] = O::apply(acc[v + 2], t.z);
-            acc[v + 3] = O::apply(acc[v + 3], t.w);
-          }
-        } else {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) acc[v] = O::apply(acc[v], __ldcg(q + v));
-        }
-      }
-    }
-#pragma unroll
-    for (int v = 0; v < VEC; ++v) fold[threadIdx.x * VEC + v] = acc[v];
-    __syncthreads();
-    for (int half = ny >> 1; half > 0; half >>= 1) {
-      if (ty < half) {
-#pragma unroll
-        for (int v = 0; v < VEC; ++v)
-          fold[threadIdx.x * VEC + v] =
-              O::apply(fold[threadIdx.x * VEC + v], fold[(threadIdx.x + (half << p.tx_log2)) * VEC + v]);
-      }
-      __syncthreads();
-    }
-    if (ty == 0 && live) {
-      TIn* out = reinterpret_cast<TIn*>(p.final_dst) + o * p.inner + col;
-#pragma unroll
-      for (int v = 0; v < VEC; ++v) {
-        float r = fold[tx * VEC + v];
-        if (!p.clear) r = O::apply(to_f32(out[v]), r);
-        out[v] = from_f32<TIn>(r);
       }
     }
   }

@@ -5,10 +5,13 @@
 // low 13 bits cleared: both are exactly representable in tf32, x - hi is exact in fp32, and
 // |x - hi - lo| <= 2^-21 |x|.  Then
 //     A B  =  A_lo B_hi + A_hi B_lo + A_hi B_hi   (+ A_lo B_lo, dropped: <= 2^-20 |a||b| per product)
-// with every product exact in the tensor core's fp32 accumulator.  The three products run as one
-// GEMM whose K loop walks three segments (small terms first); the split itself is one pass over
-// A and B into a workspace of twice their size.  Because hi and lo are exact tf32 numbers the
-// result does not depend on whether the hardware truncates or rounds fp32 operands to tf32.
+// with every product exact in the tensor core's fp32 accumulator.  The three products run as ONE
+// ordinary GEMM over a K three times as long: a pass over A and B writes
+//     A' = [A_lo | A_hi | A_hi]  (along K)      B' = [B_hi ; B_lo ; B_hi]  (along K)
+// into a workspace (small terms first), both with K innermost whatever the order A and B are
+// stored in, and the tensor-core kernels run on A' and B' unchanged.
+// Because hi and lo are exact tf32 numbers the result does not depend on whether the hardware
+// truncates or rounds fp32 operands to tf32.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -19,27 +22,78 @@ __device__ __forceinline__ float tf32_trunc(float x) {
   return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
 }
 
-// hi[i] = trunc(src[i]), lo[i] = trunc(src[i] - hi[i]) for i in [0, n); n4 = n / 4 float4 pieces
-// plus a scalar tail.  src, hi and lo are 16-byte aligned (the plan requires it).
+// src: rows x cols fp32, pitch ld_src.  dst: the three K segments of the operand, each a copy of
+// the matrix as hi or lo parts (`lo_mask` bit s = segment s holds lo).  K runs along the columns
+// (k_cols = 1: segment s starts at column s * cols) or along the rows (k_cols = 0: at row
+// s * rows); pitch ld_dst.  One thread handles four consecutive columns (a 16-byte load when the
+// row allows it).
 __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict__ src,
-                                                         float* __restrict__ hi,
-                                                         float* __restrict__ lo, int64_t n) {
-  const int64_t n4 = n >> 2;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-    const float4 x = __ldcs(reinterpret_cast<const float4*>(src) + i);
-    float4 h, l;
-    h.x = tf32_trunc(x.x); h.y = tf32_trunc(x.y); h.z = tf32_trunc(x.z); h.w = tf32_trunc(x.w);
-    l.x = tf32_trunc(x.x - h.x); l.y = tf32_trunc(x.y - h.y);
-    l.z = tf32_trunc(x.z - h.z); l.w = tf32_trunc(x.w - h.w);
-    reinterpret_cast<float4*>(hi)[i] = h;
-    reinterpret_cast<float4*>(lo)[i] = l;
+                                                         float* __restrict__ dst, int64_t rows,
+                                                         int64_t cols, int64_t ld_src,
+                                                         int64_t ld_dst, int k_cols,
+                                                         uint32_t lo_mask) {
+  const int64_t quads = (cols + 3) >> 2;
+  const int64_t total = rows * quads;
+  const bool vec = ((ld_src | ld_dst | (k_cols ? cols : 0)) & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
+  const int64_t seg_stride = k_cols ? cols : rows * ld_dst;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / quads, c = (i - r * quads) << 2;
+    const float* s = src + r * ld_src + c;
+    float* d = dst + r * ld_dst + c;
+    float x[4], h[4], l[4];
+    const int n = (int)(cols - c < 4 ? cols - c : 4);
+    if (vec && n == 4) {
+      const float4 t = __ldcs(reinterpret_cast<const float4*>(s));
+      x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+    } else {
+      for (int j = 0; j < 4; ++j) x[j] = j < n ? s[j] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      h[j] = tf32_trunc(x[j]);
+      l[j] = tf32_trunc(x[j] - h[j]);
+    }
+#pragma unroll
+    for (int seg = 0; seg < 3; ++seg) {
+      const float* v = (lo_mask >> seg) & 1u ? l : h;
+      float* o = d + seg * seg_stride;
+      if (vec && n == 4) {
+        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+        for (int j = 0; j < n; ++j) o[j] = v[j];
+      }
+    }
   }
-  for (int64_t i = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const float x = src[i];
-    const float h = tf32_trunc(x);
-    hi[i] = h;
-    lo[i] = tf32_trunc(x - h);
+}
+
+// The same split for an operand stored with K along its ROWS (A stored [K, M], B stored [K, N]):
+// kind::tf32 takes its operands K-inner only (an M/N-inner tile of 32-bit elements reads as
+// zeros), so the three segments are written transposed, dst[mn, s * K + k], through a 32 x 32
+// tile in shared memory (reads coalesced along M/N, writes along K).  grid = (ceil(mn / 32),
+// ceil(K / 32)), block = (32, 8).
+__global__ void __launch_bounds__(256) tf32_split_transpose_kernel(const float* __restrict__ src,
+                                                                   float* __restrict__ dst,
+                                                                   int64_t k_rows, int64_t mn_cols,
+                                                                   int64_t ld_src, int64_t ld_dst,
+                                                                   uint32_t lo_mask) {
+  __shared__ float tile[32][33];
+  const int64_t mn0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    const int64_t k = k0 + r, mn = mn0 + threadIdx.x;
+    tile[r][threadIdx.x] = (k < k_rows && mn < mn_cols) ? __ldcs(src + k * ld_src + mn) : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += 8) {
+    const int64_t mn = mn0 + r, k = k0 + threadIdx.x;
+    if (mn < mn_cols && k < k_rows) {
+      const float x = tile[threadIdx.x][r];
+      const float h = tf32_trunc(x), l = tf32_trunc(x - h);
+      float* o = dst + mn * ld_dst + k;
+#pragma unroll
+      for (int seg = 0; seg < 3; ++seg) o[seg * k_rows] = (lo_mask >> seg) & 1u ? l : h;
+    }
   }
 }
 

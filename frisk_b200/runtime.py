@@ -19,7 +19,7 @@ from . import workloads as W
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfrisk_b200.so")
 
-KERNEL_NAMES = {0: "simt", 1: "tcgen05", 2: "skinny", 3: "tcgen05_pair"}
+KERNEL_NAMES = {0: "simt", 1: "tcgen05", 2: "skinny", 3: "tcgen05_pair", 4: "tf32x3"}
 
 
 class FriskError(RuntimeError):
@@ -240,7 +240,7 @@ class GemmPlan:
         d.transA, d.transB = int(transA), int(transB)
         d.clear_accum = int(clear_accum)
         d.scale_mode = 1 if scales else 0
-        d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2, "tcgen05_pair": 3}[force_kernel]
+        d.force_kernel = 0 if force_kernel is None else 1 + {"simt": 0, "tcgen05": 1, "skinny": 2, "tcgen05_pair": 3, "tf32x3": 4}[force_kernel]
         d.tile_n, d.stages, d.num_ctas, d.band_tiles = tile_n, stages, num_ctas, band_tiles
         d.epilogue = epilogue
         d.row_reduce = 0 if row_reduce is None else 1 + REDUCE_KINDS[row_reduce]

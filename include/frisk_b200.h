@@ -64,7 +64,10 @@ typedef enum {
   FRISK_KERNEL_SIMT = 0,    /* CUDA-core fp32-FMA tiles: fp32 inputs and every odd shape   */
   FRISK_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma, accumulators in TMEM, whole-tile output   */
   FRISK_KERNEL_SKINNY = 2,  /* few rows (M <= 128): operands swapped, K split over a cluster / SMs */
-  FRISK_KERNEL_TCGEN05_PAIR = 3 /* CTA pairs with two-SM MMAs on 256 x tile_n output tiles   */
+  FRISK_KERNEL_TCGEN05_PAIR = 3, /* CTA pairs with two-SM MMAs on 256 x tile_n output tiles  */
+  FRISK_KERNEL_TF32X3 = 4   /* fp32 inputs and C: A and B split into tf32 hi + lo parts in the
+                               workspace, three products in one tensor-core GEMM (fp32-level
+                               accuracy: relative error about 1e-6); larger problems only      */
 } frisk_kernel_kind;
 
 /*
@@ -141,8 +144,9 @@ void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* plan);
 int frisk_b200_gemm_plan_info(const frisk_gemm_plan* plan, frisk_gemm_plan_info* out);
 
 /* Bytes of device scratch `run` needs.  0 for every plan but the stream-K form of the few-row
- * plan (few-row shapes whose tiles cannot be covered by thread-block clusters) and plans with a
- * fused row reduce (one fp32 per row and half tile); `run` takes a NULL workspace when it is 0. */
+ * plan (few-row shapes whose tiles cannot be covered by thread-block clusters), plans with a
+ * fused row reduce (one fp32 per row and half tile) and 3xTF32 plans (three times the bytes of A
+ * and B; 256-byte aligned); `run` takes a NULL workspace when it is 0. */
 int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* plan, size_t* out);
 
 /*
@@ -422,7 +426,7 @@ int frisk_b200_bank_conflicts_access(int64_t rows, int64_t cols, int32_t elem_bi
  * SM pair (pair = 1: two-SM MMAs, M = 256) issues tcgen05.mma of shape M x 256 x 32 bytes of K
  * back to back on operand tiles resident in shared memory: no loads, no epilogue.  It is the
  * denominator of a GEMM kernel's tensor-pipe roofline for operand types no library peak was
- * measured for (e4m3).  `k_blocks` (a multiple of 32; one k-block = four MMAs) sets the length
+ * measured for (e4m3; FRISK_DT_F32 is measured as kind::tf32, the rate behind the 3xTF32 plan).  `k_blocks` (a multiple of 32; one k-block = four MMAs) sets the length
  * of one launch -- choose it so that a launch lasts about as long as the GEMM it is compared
  * with, since the clock under the power cap depends on it; `reps` launches are timed with CUDA
  * events on the default stream.  Synchronous.  No counterpart in the reference, whose timing

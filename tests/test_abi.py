@@ -142,6 +142,34 @@ def test_run_without_device_reports_no_device_or_runs():
     plan.close()
 
 
+def test_fp32_plans_split_into_tf32_when_large():
+    """fp32 inputs: the CUDA-core kernel for small problems (cfg1), three tf32 products on the
+    tensor cores from about 1 GFLOP on; the split operands live in the workspace."""
+    small = R.GemmPlan(512, 512, 512, W.F32)
+    assert small.info["kernel_name"] == "simt" and small.workspace_bytes == 0
+    small.close()
+    big = R.GemmPlan(4096, 4096, 4096, W.F32)
+    assert big.info["kernel_name"] == "tf32x3" and big.info["launches"] == 3
+    assert (big.info["tile_m"], big.info["tile_n"], big.info["tile_k"]) == (256, 256, 32)
+    assert big.workspace_bytes == 2 * 3 * 4096 * 4096 * 4       # A' and B': three K segments each
+    lay = big.operand_layout(0)
+    assert (lay["swizzle_bytes"], lay["box_inner"], lay["k_step_bytes"]) == (128, 32, 32)
+    big.close()
+    forced = R.GemmPlan(512, 512, 512, W.F32, force_kernel="tf32x3")
+    assert forced.info["kernel_name"] == "tf32x3"
+    forced.close()
+    few = R.GemmPlan(64, 8192, 4096, W.F32)                      # few rows: one-CTA whole tiles
+    assert few.info["kernel_name"] == "tf32x3" and few.info["tile_m"] == 128
+    few.close()
+    odd = R.GemmPlan(4096, 4096, 4095, W.F32)                    # 16380-byte rows: no TMA
+    assert odd.info["kernel_name"] == "simt"
+    odd.close()
+    for kw, code in ((dict(ab=W.BF16), -2), (dict(ab=W.F32, lda=4098), -3), (dict(ab=W.F32, ct=W.BF16), -3)):
+        with pytest.raises(R.FriskError) as e:
+            R.GemmPlan(4096, 4096, 4096, kw["ab"], kw.get("ct"), force_kernel="tf32x3", lda=kw.get("lda", 0))
+        assert e.value.code == code, kw
+
+
 def test_run_ex_argument_errors():
     """Host-side checks of frisk_b200_gemm_run_ex that come before any device work."""
     L = R.lib()
@@ -182,7 +210,7 @@ def test_run_ex_argument_errors():
     assert L.frisk_b200_peer_close(None) == 0 and L.frisk_b200_peer_free(None) == 0
     tf = C.c_double()
     assert L.frisk_b200_measure_mma_peak(W.BF16, 1, 33, 1, C.byref(tf), None) == -1   # k_blocks % 32
-    assert L.frisk_b200_measure_mma_peak(W.F32, 1, 64, 1, C.byref(tf), None) == -2
+    assert L.frisk_b200_measure_mma_peak(9, 1, 64, 1, C.byref(tf), None) == -2
 
 
 @pytest.mark.parametrize("M,P", [(65536, 1), (65536, 2), (65536, 4), (65536, 8), (10, 3), (7, 8), (0, 4)])
@@ -223,8 +251,10 @@ def test_planner_invariants_over_random_shapes():
         p = R.GemmPlan(M, N, K, ab, ct, transA=ta, transB=tb, scales=ab == W.E4M3)
         i = p.info
         seen.add(i["kernel_name"])
-        assert i["kernel_name"] in ("simt", "tcgen05", "tcgen05_pair", "skinny")
-        assert i["launches"] == 1 and i["num_ctas"] >= 1
+        assert i["kernel_name"] in ("simt", "tcgen05", "tcgen05_pair", "skinny", "tf32x3")
+        assert i["launches"] == (3 if i["kernel_name"] == "tf32x3" else 1) and i["num_ctas"] >= 1
+        if i["kernel_name"] == "tf32x3":   # fp32 in and out, at least about a GFLOP, TMA-able rows
+            assert ab == W.F32 and 2.0 * M * N * K >= 1e9 and p.workspace_bytes >= 3 * 4 * (M * K + K * N)
         if i["kernel_name"] != "simt":
             assert 2 <= i["stages"] <= 12 and i["smem_bytes"] <= 227 * 1024
             assert i["num_ctas"] <= 148 and i["tile_k"] * W.ELEM_SIZE[ab] == 128
@@ -238,10 +268,10 @@ def test_planner_invariants_over_random_shapes():
                 assert i["num_ctas"] % tiles == 0 and i["num_ctas"] // tiles in (2, 4, 8)
             else:                        # stream-K: slots + one counter per tile
                 assert p.workspace_bytes % 4 == 0 and i["num_ctas"] <= 14 * -(-N // i["tile_n"])
-        else:
+        elif i["kernel_name"] != "tf32x3":
             assert p.workspace_bytes == 0
         p.close()
-    assert seen == {"simt", "tcgen05", "tcgen05_pair", "skinny"}
+    assert seen == {"simt", "tcgen05", "tcgen05_pair", "skinny", "tf32x3"}
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
@@ -277,9 +307,7 @@ def test_reduce_plans_cover_the_reduced_dimension_exactly_once():
             for aligned in (True, False):
                 info = R.reduce_info(d, aligned)
                 empty = d.outer == 0 or d.inner == 0
-                # a cut line reduce folds its pieces in a second launch; a cut column reduce in the
-                # same launch (the last CTA of each column block folds them)
-                assert info["launches"] == (0 if empty else 2 if info["chunks"] > 1 and info["lines"] else 1)
+                assert info["launches"] == (0 if empty else 2 if info["chunks"] > 1 else 1)
                 assert info["lines"] == int(d.inner == 1)
                 assert info["chunks"] >= 1 and info["chunk_len"] >= 1
                 if not empty:
@@ -287,9 +315,6 @@ def test_reduce_plans_cover_the_reduced_dimension_exactly_once():
                     assert (info["chunks"] - 1) * info["chunk_len"] < max(d.extent, 1)
                     assert info["ctas"] >= 1
                 want_ws = d.outer * info["chunks"] * d.inner * 4 if info["chunks"] > 1 else 0
-                if info["chunks"] > 1 and not info["lines"]:   # ... and keeps its arrival counters there
-                    assert want_ws < info["workspace_bytes"] <= want_ws + 32 + 4 * d.outer * d.inner
-                    want_ws = info["workspace_bytes"]
                 assert info["workspace_bytes"] == want_ws <= need
                 if not aligned and d.inner != 1:
                     assert info["vector"] == 1

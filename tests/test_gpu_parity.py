@@ -631,3 +631,36 @@ def test_back_to_back_dependent_launches_see_each_others_results():
     for plan, *_ in steps:
         plan.close()
     f32_plan.close()
+
+
+# ----------------------------------------------------------------------------- fp32 on tensor cores
+@pytest.mark.parametrize("M,N,K,ta,tb,clear", [
+    (512, 512, 512, False, False, True),       # cfg1's shape, forced onto the 3xTF32 plan
+    (1000, 776, 520, False, True, True),       # ragged tiles, K-inner B
+    (384, 1024, 2052, True, False, False),     # A stored [K, M], C += A x B
+    (260, 520, 1096, True, True, True),
+    (64, 2048, 1024, False, False, True),      # few rows: the one-CTA whole-tile kernel
+    (2048, 2048, 2048, False, False, True),    # large enough for the plan to choose it itself
+])
+def test_fp32_on_tensor_cores_keeps_fp32_accuracy(M, N, K, ta, tb, clear):
+    """3xTF32: A = A_hi + A_lo, B = B_hi + B_lo in tf32, three products accumulated in fp32.  The
+    bound is the fp32 one (relative Frobenius error <= 1e-4); what is reached is 4e-7 at K = 512
+    and 5e-6 at K = 2052 (the tensor core's fp32 accumulation over 3K products), and the largest
+    element error stays below 1e-5 of the data behind it (a single-pass tf32 product would sit
+    near 5e-4)."""
+    rng = np.random.default_rng(M + N + K)
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    w = W.GemmWorkload("fp32-tc", M, N, K, W.F32, W.F32, transA=ta, transB=tb, clear_accum=clear,
+                       A=np.ascontiguousarray(a.T) if ta else a, B=np.ascontiguousarray(b.T) if tb else b,
+                       C0=None if clear else rng.standard_normal((M, N)).astype(np.float32))
+    forced = {} if 2.0 * M * N * K >= 1e9 else dict(force_kernel="tf32x3")
+    out, info = run_and_check(w, **forced)
+    assert info["kernel_name"] == "tf32x3"
+    want = ref.ref_gemm_f64(w)
+    assert W.rel_frobenius(out, want) <= 1e-5
+    assert float(np.max(np.abs(out - want) / ref.abs_dot(w))) <= 1e-5
+    assert np.array_equal(out, R.gemm_host(w, **forced))          # same bits on a second run
+    simt, info2 = run_and_check(w, force_kernel="simt")
+    assert info2["kernel_name"] == "simt"
+    assert W.rel_frobenius(out, simt) <= 1e-5

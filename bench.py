@@ -45,8 +45,8 @@ BOUND = {"cfg3": "hbm"}  # everything else is measured against the tensor-core p
 # DRAM bytes per launch of the dominant kernel (ncu: dram__bytes_read.sum + dram__bytes_write.sum
 # of one captured launch, `--clock-control none`); None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    # CTA-pair kernel, bf16 8192^3, bands of 8 tile rows: 1089.2 MB read + 126.2 MB written
-    "bf16_8192": 1215415552,
+    # CTA-pair kernel, bf16 8192^3, bands of 8 tile rows: 1060.3 MB read + 127.3 MB written
+    "bf16_8192": 1187610032,
     # cfg5: see CFG5_SLAB_TRAFFIC below
     # few-row cluster plan, cfg3: 134.57 MB read + 4.01 MB written
     "cfg3": 138584832,
@@ -59,8 +59,8 @@ NCU_TRAFFIC_BYTES = {
 # DRAM traffic is measured on a slab of CFG5_SLAB_ROWS rows of the same problem (same B, same
 # band walk) and scaled by the rows a rank holds: the bands are walked one after the other, each
 # streaming all of B past its own rows of A, so the bytes grow in proportion to the rows.
-CFG5_SLAB_ROWS = 8192
-CFG5_SLAB_TRAFFIC = 1215415552
+CFG5_SLAB_ROWS = 16384
+CFG5_SLAB_TRAFFIC = 2893966763   # mean of three captured launches: 2633.5 MB read + 260.5 MB written
 
 
 def load_peaks() -> dict:

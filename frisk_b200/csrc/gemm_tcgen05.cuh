@@ -37,8 +37,18 @@ constexpr uint32_t kEpiStageBytes = 4u * kEpiStageBytesPerWarp;
 // the normal build compiles them out of the kernels.
 #ifdef FRISK_B200_MEASURE
 constexpr bool kMeasureBuild = true;
+// FRISK_STAMP(cond, slot): CTA 0 records its clock, relative to kernel entry, in trace[slot].
+#define FRISK_STAMP(cond, slot)                                  \
+  do {                                                           \
+    if (trace && (cond)) trace[(slot)] = clock64() - t_entry;    \
+  } while (0)
+#define FRISK_MEASURE_ONLY(...) __VA_ARGS__
 #else
 constexpr bool kMeasureBuild = false;
+#define FRISK_STAMP(cond, slot) \
+  do {                          \
+  } while (0)
+#define FRISK_MEASURE_ONLY(...)
 #endif
 // Warps that wait for a long time sleep between polls: a tight polling loop takes issue slots
 // from the MMA warp on the same SM sub-partition and nearly halves its issue rate.
@@ -852,17 +862,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
   int32_t* const status = p.status;
   const bool cluster_sync = kSplit && p.split_mode == 3 && p.cluster_k > 1;
-  long long* const trace = (kMeasureBuild && blockIdx.x == 0) ? p.trace : nullptr;
-
-  // every stamp is relative to the stamping thread's own clock at kernel entry
-  const long long t_entry = trace ? clock64() : 0;
-  // (measurement builds) wall-clock entry and exit of every CTA at [1024 + 2 * CTA]
-  if (kMeasureBuild && p.trace && threadIdx.x == 64)
-    p.trace[1024 + 2 * blockIdx.x] = (long long)ptx::globaltimer_ns();
-  if (trace && threadIdx.x == 64) {
-    trace[320] = 0;
-    trace[324] = (long long)ptx::globaltimer_ns();
-  }
+  // (measurement builds only) clock stamps of CTA 0, each relative to the stamping thread's own
+  // clock at kernel entry, and the wall-clock entry and exit of every CTA at [1024 + 2 * CTA]
+  FRISK_MEASURE_ONLY(
+      long long* const trace = blockIdx.x == 0 ? p.trace : nullptr;
+      const long long t_entry = trace ? clock64() : 0;
+      if (p.trace && threadIdx.x == 64) p.trace[1024 + 2 * blockIdx.x] = (long long)ptx::globaltimer_ns();
+      if (trace && threadIdx.x == 64) {
+        trace[320] = 0;
+        trace[324] = (long long)ptx::globaltimer_ns();
+      })
   if (threadIdx.x == 0) {
     abort_word = 0;
     for (uint32_t s = 0; s < stages; ++s) {
@@ -892,7 +901,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // written, the workspace a previous launch of this plan still uses) is touched only from here.
   ptx::griddep_launch_dependents();
   ptx::griddep_wait();
-  if (trace && threadIdx.x == 64) trace[321] = clock64() - t_entry;
+  FRISK_STAMP(threadIdx.x == 64, 321);
 
   WorkIter work;
   work.init(p.num_kb, kSplit ? p.split_mode : 0u, tiles_r * tiles_c, kSplit ? p.cluster_k : 1u);
@@ -928,13 +937,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             kStatusProducerTimeout, kProducerBackoffNs);
           if (!ok) break;
           const uint32_t full = full0 + 8 * stage;
-          const bool tr_on = trace && issued < 32 && warp == 0;
-          if (tr_on && ptx::elect_one()) trace[2 * issued] = clock64() - t_entry;
+          FRISK_MEASURE_ONLY(const bool tr_on = trace && issued < 32 && warp == 0;)
+          FRISK_STAMP(tr_on && ptx::elect_one(), 2 * issued);
           if (debug_mode & 1u) {
             if (ptx::elect_one()) ptx::mbar_arrive(full);
           } else {
             if (ptx::elect_one()) ptx::mbar_arrive_expect_tx(full, stage_bytes);
-            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued] = clock64() - t_entry;
+            FRISK_STAMP(tr_on && ptx::elect_one(), 256 + 4 * issued);
             const uint32_t a_dst = tiles_base + stage * stage_bytes;
             const uint32_t b_dst = a_dst + a_stage_bytes;
             const int32_t k0 = (int32_t)(kb * bk_elems);
@@ -943,14 +952,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
               if (ptx::elect_one()) ptx::tma_load_2d(a_dst + bx * a_box_bytes, &tmap_a, full, x, y);
             }
-            if (tr_on && ptx::elect_one()) trace[256 + 4 * issued + 1] = clock64() - t_entry;
+            FRISK_STAMP(tr_on && ptx::elect_one(), 256 + 4 * issued + 1);
             for (uint32_t bx = 0; bx < b_boxes; ++bx) {
               const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
               const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
               if (ptx::elect_one()) ptx::tma_load_2d(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
             }
           }
-          if (tr_on && ptx::elect_one()) trace[2 * issued + 1] = clock64() - t_entry;
+          FRISK_STAMP(tr_on && ptx::elect_one(), 2 * issued + 1);
           // Reconverge here: without it the warp stays split after the elected-lane issues above
           // and walks the next wait that way (measured: 8192^3 bf16 0.89 ms without, 0.82 ms with).
           __syncwarp();
@@ -1014,8 +1023,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint64_t adesc0 = a_desc_base | (uint64_t)((a_addr & 0x3FFFFu) >> 4);
           const uint64_t bdesc0 = b_desc_base | (uint64_t)((b_addr & 0x3FFFFu) >> 4);
           const uint32_t first = (kb > work.kb0) ? 1u : 0u;
-          const bool tr_on = trace && item == 0 && (kb - work.kb0) < 32;
-          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0)] = clock64() - t_entry;
+          FRISK_MEASURE_ONLY(const bool tr_on = trace && item == 0 && (kb - work.kb0) < 32;)
+          FRISK_STAMP(tr_on && ptx::elect_one(), 64 + 3 * (kb - work.kb0));
           uint32_t next_stage = stage + 1, next_phase = phase;
           if (next_stage == stages) {
             next_stage = 0;
@@ -1049,11 +1058,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
               if (ks == 0 && have_prev && ptx::elect_one()) ptx::tc_commit(empty0 + 8 * prev_stage);
             }
-            if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 1] = clock64() - t_entry;
+            FRISK_STAMP(tr_on && ptx::elect_one(), 64 + 3 * (kb - work.kb0) + 1);
             prev_stage = stage;
             have_prev = true;
           }
-          if (tr_on && ptx::elect_one()) trace[64 + 3 * (kb - work.kb0) + 2] = clock64() - t_entry;
+          FRISK_STAMP(tr_on && ptx::elect_one(), 64 + 3 * (kb - work.kb0) + 2);
           stage = next_stage;
           phase = next_phase;
         }
@@ -1062,7 +1071,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (have_prev && ptx::elect_one()) ptx::tc_commit(empty0 + 8 * prev_stage);
         if (!ok) break;
         if (ptx::elect_one()) ptx::tc_commit(acc_full0 + 8 * acc);
-        if (trace && item == 0 && ptx::elect_one()) trace[323] = clock64() - t_entry;
+        FRISK_STAMP(item == 0 && ptx::elect_one(), 323);
         __syncwarp();
         ++item;
       }
@@ -1192,7 +1201,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         epi_backoff);
       if (!ok) break;
       ptx::tc_fence_after();
-      if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item] = clock64() - t_entry;
+      FRISK_STAMP(threadIdx.x == 64 && item < 4, 330 + 8 * item);
       for (uint32_t sub = 0; sub < mi; ++sub) {
         const uint32_t r_local = sub * 128u + quarter * 32u + lane;
         const uint32_t row = tr * tile_rows + r_local;
@@ -1226,7 +1235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
-      if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 1] = clock64() - t_entry;
+      FRISK_STAMP(threadIdx.x == 64 && item < 4, 330 + 8 * item + 1);
       if (to_slot) {
         __threadfence();      // this thread's partial is visible device-wide ...
         // ... and so is every epilogue thread's, before the count goes up
@@ -1239,7 +1248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
         if (!ok) break;
-        if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 2] = clock64() - t_entry;
+        FRISK_STAMP(threadIdx.x == 64 && item < 4, 330 + 8 * item + 2);
         if (last_flag) {
           __threadfence();
           if (contrib_n <= kMaxContrib) {
@@ -1258,13 +1267,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           }
           if (threadIdx.x == 64) p.counters[work.tile] = 0;  // ready for the next launch
-          if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 3] = clock64() - t_entry;
+          FRISK_STAMP(threadIdx.x == 64 && item < 4, 330 + 8 * item + 3);
         }
         // last_flag is rewritten by the next item
         ok = epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
         if (!ok) break;
       }
-      if (trace && threadIdx.x == 64 && item < 4) trace[330 + 8 * item + 5] = clock64() - t_entry;
+      FRISK_STAMP(threadIdx.x == 64 && item < 4, 330 + 8 * item + 5);
       ++item;
     }
     __syncwarp();
@@ -1275,7 +1284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       // another CTA's shared memory again, so each CTA leaves on its own.
       ptx::cluster_arrive();
       ptx::cluster_wait();
-      if (trace && threadIdx.x == 64) trace[326] = clock64() - t_entry;
+      FRISK_STAMP(threadIdx.x == 64, 326);
       if (!*abort_flag) {
         uint32_t tr, tc;
         tile_coords(group_r, tiles_r, tiles_c, blockIdx.x >> cluster_sh, tr, tc);
@@ -1284,7 +1293,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         reduce_share<TC>(ep_out, red_base, cluster_k, my_rank, share, tile_n, tr * tile_rows,
                          tc * tile_n, threadIdx.x - 64u);
       }
-      if (trace && threadIdx.x == 64) trace[327] = clock64() - t_entry;
+      FRISK_STAMP(threadIdx.x == 64, 327);
     }
     }  // kSplit
   }
@@ -1292,12 +1301,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ---------------------------------------------------------------- tear-down
   ptx::tc_fence_before();
   __syncthreads();
-  if (kMeasureBuild && p.trace && threadIdx.x == 64)
-    p.trace[1024 + 2 * blockIdx.x + 1] = (long long)ptx::globaltimer_ns();
-  if (trace && threadIdx.x == 64) {
-    trace[322] = clock64() - t_entry;
-    trace[325] = (long long)ptx::globaltimer_ns();
-  }
+  FRISK_MEASURE_ONLY(
+      if (p.trace && threadIdx.x == 64) p.trace[1024 + 2 * blockIdx.x + 1] = (long long)ptx::globaltimer_ns();
+      if (trace && threadIdx.x == 64) {
+        trace[322] = clock64() - t_entry;
+        trace[325] = (long long)ptx::globaltimer_ns();
+      })
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, tmem_cols);

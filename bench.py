@@ -746,6 +746,7 @@ def main():
         line["other_configs"] = others
         line["reduce"] = time_reduce(torch, R, dev, max(args.steps, 30), max(args.warmup, 3), peaks,
                                      not args.no_cpu)
+        line["gemm_with_row_reduce"] = time_fused_row_reduce(torch, R, dev, 10, 3)
 
     if world == 1 and not args.no_cpu and not args.rows:
         line["cpu_baseline"] = cpu_baseline(name)
@@ -754,6 +755,50 @@ def main():
     print(json.dumps(line), flush=True)
     if dist:
         dist.destroy_process_group()
+
+
+def time_fused_row_reduce(torch, R, dev, steps, warmup):
+    """bf16 8192^3 followed by the row maxima of its result (the gemm + reduce pair of the
+    reference's attention sketch, tmp/ir.mlir:112-116), two ways: the fold in the GEMM's epilogue
+    (`desc.row_reduce`: the rows are folded as they leave tensor memory, a small second launch folds
+    the per-tile results), and the GEMM followed by the separate reduce kernel reading C again."""
+    M = N = K = 8192
+    A, B, _, _ = device_inputs(torch, "bf16_8192", M, N, K, dev, 5)
+    C = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+    rowmax = torch.empty(M, device=dev, dtype=torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    fused = R.GemmPlan(M, N, K, W.BF16, row_reduce="max")
+    plain = R.GemmPlan(M, N, K, W.BF16)
+    ws = torch.empty(max(fused.workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    rdesc = R.reduce_desc((M, N), 1, W.BF16, "max")
+
+    def fold_in_epilogue():
+        fused.run_ex(A, B, C, workspace=ws, status=status, stream=stream, row_reduce_dst=rowmax)
+
+    def two_launches():
+        plain.run(A, B, C, None, None, None, status, stream)
+        R.reduce_run(rdesc, C, rowmax, None, stream)
+
+    out = {}
+    for key, fn in (("fold_in_epilogue", fold_in_epilogue), ("gemm_then_reduce", two_launches)):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[key + "_ms"] = round(e0.elapsed_time(e1) / steps, 4)
+        out[key + "_rowmax_checksum"] = float(rowmax.float().sum().item())
+    R.check_status(status, stream)
+    out["same_result"] = out.pop("fold_in_epilogue_rowmax_checksum") == out.pop("gemm_then_reduce_rowmax_checksum")
+    out["shape"] = "bf16 8192^3, max over the 8192 columns of each row of C"
+    fused.close()
+    plain.close()
+    return out
 
 
 def library_matmul(torch, dev, m, n, k, dtype):

@@ -92,8 +92,8 @@ struct frisk_gemm_plan {
   frisk::GemmParams gp;  // everything but pointers
   size_t ws_bytes = 0;
   size_t slot_bytes = 0;  // split mode 2: bytes of partial-tile slots before the counters
-  // fused row reduce: [2 * tiles_c][M] fp32 folds, then one arrival counter per 128 rows
-  size_t rr_partial_bytes = 0, rr_counter_bytes = 0;
+  // fused row reduce: [2 * tiles_c][M] fp32 folds, one per row and half tile
+  size_t rr_partial_bytes = 0;
   size_t dyn_smem = 0;
   frisk_tma_params lay_a, lay_b;  // the layout mapper's description of the staged operand tiles
   int plan_error = 0;
@@ -453,13 +453,11 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   }
   pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes + epi_bytes;
   pl->ws_bytes = 0;
-  pl->rr_partial_bytes = pl->rr_counter_bytes = 0;
+  pl->rr_partial_bytes = 0;
   if (!swap && d.row_reduce) {
     g.rr_kind = (uint32_t)d.row_reduce;
-    g.rr_clear = d.row_reduce_clear ? 1u : 0u;
     pl->rr_partial_bytes = ((size_t)2 * g.tiles_c * (size_t)rows * sizeof(float) + 15) / 16 * 16;
-    pl->rr_counter_bytes = (((size_t)rows + 127) / 128 * sizeof(uint32_t) + 15) / 16 * 16;
-    pl->ws_bytes = pl->rr_partial_bytes + pl->rr_counter_bytes;
+    pl->ws_bytes = pl->rr_partial_bytes;
   }
   if (swap && use_cluster) {
     g.split_mode = 3;
@@ -490,7 +488,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   in.swap_ab = swap;
   in.split_k = swap;
   in.smem_bytes = (int)pl->dyn_smem;
-  in.launches = 1;
+  in.launches = (!swap && d.row_reduce) ? 2 : 1;   // the fold's finalize launch
   in.swizzle_a = pl->lay_a.swizzle_bytes;
   in.swizzle_b = pl->lay_b.swizzle_bytes;
   // the clusters must all be resident at once for the plan to make sense; if this device cannot
@@ -517,13 +515,13 @@ int ensure_dyn_smem(Kern kern, int device) {
   if (tracked) __atomic_store_n(&done[device], true, __ATOMIC_RELEASE);
   return FRISK_OK;
 }
-template <typename TC, bool kSplit, bool kFold, bool kTf32 = false> struct OneCtaKernelTag {};
-template <typename TC, bool kFold, bool kTf32 = false> struct PairKernelTag {};
+template <typename TC, bool kSplit, bool kTf32 = false> struct OneCtaKernelTag {};
+template <typename TC, bool kTf32 = false> struct PairKernelTag {};
 
-template <typename TC, bool kSplit, bool kFold, bool kTf32 = false>
+template <typename TC, bool kSplit, bool kTf32 = false>
 int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit, kFold, kTf32>;
-  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit, kFold, kTf32>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_kernel<TC, kSplit, kTf32>;
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, kSplit, kTf32>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -551,8 +549,8 @@ int launch_tcgen05_ts(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStrea
 // How many clusters of the plan's size the device can hold at once, for one C type.
 template <typename TC>
 int max_active_clusters_t(frisk_gemm_plan* pl, int* out) {
-  auto kern = frisk::gemm_tcgen05_kernel<TC, true, false>;
-  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, true, false>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_kernel<TC, true>;
+  if (int rc = ensure_dyn_smem<OneCtaKernelTag<TC, true>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -586,15 +584,13 @@ bool skinny_clusters_fit(frisk_gemm_plan* pl) {
 
 template <typename TC>
 int launch_tcgen05_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  if (g.split_mode) return launch_tcgen05_ts<TC, true, false>(pl, g, st);
-  return g.rr_kind ? launch_tcgen05_ts<TC, false, true>(pl, g, st)
-                   : launch_tcgen05_ts<TC, false, false>(pl, g, st);
+  return g.split_mode ? launch_tcgen05_ts<TC, true>(pl, g, st) : launch_tcgen05_ts<TC, false>(pl, g, st);
 }
 
-template <typename TC, bool kFold, bool kTf32 = false>
+template <typename TC, bool kTf32 = false>
 int launch_pair_tf(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  auto kern = frisk::gemm_tcgen05_pair_kernel<TC, kFold, kTf32>;
-  if (int rc = ensure_dyn_smem<PairKernelTag<TC, kFold, kTf32>>(kern, pl->device)) return rc;
+  auto kern = frisk::gemm_tcgen05_pair_kernel<TC, kTf32>;
+  if (int rc = ensure_dyn_smem<PairKernelTag<TC, kTf32>>(kern, pl->device)) return rc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
@@ -616,7 +612,26 @@ int launch_pair_tf(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t
 
 template <typename TC>
 int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
-  return g.rr_kind ? launch_pair_tf<TC, true>(pl, g, st) : launch_pair_tf<TC, false>(pl, g, st);
+  return launch_pair_tf<TC>(pl, g, st);
+}
+
+// The second launch of a plan with a fused row reduce: folds the per-tile results of every row.
+template <typename TC>
+int launch_row_fold_t(const frisk_gemm_plan* pl, const frisk::GemmParams& g, void* dst, cudaStream_t st) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3((g.rows + 255u) / 256u, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  FRISK_CUDA(cudaLaunchKernelEx(&cfg, frisk::row_fold_finalize_kernel<TC>, (const float*)g.rr_partials,
+                                reinterpret_cast<TC*>(dst), g.rows, 2u * g.tiles_c, g.rr_kind,
+                                (uint32_t)(pl->d.row_reduce_clear ? 1 : 0)));
+  return FRISK_OK;
 }
 
 template <typename TC>
@@ -986,8 +1001,8 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     g.C = C;
     g.status = args->device_status;
     g.c_vec_ok = ((uintptr_t)C % 16 == 0) && ((d.ldc * elem_size(d.c_type)) % 16 == 0);
-    return pl->tf32_pair ? launch_pair_tf<float, false, true>(pl, g, st)
-                         : launch_tcgen05_ts<float, false, false, true>(pl, g, st);
+    return pl->tf32_pair ? launch_pair_tf<float, true>(pl, g, st)
+                         : launch_tcgen05_ts<float, false, true>(pl, g, st);
   }
 
   const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
@@ -1053,12 +1068,7 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
   } else {
     g.row_scale = sa;
     g.col_scale = sb;
-    if (d.row_reduce) {
-      g.rr_partials = reinterpret_cast<float*>(workspace);
-      g.rr_counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->rr_partial_bytes);
-      g.rr_dst = args->row_reduce_dst;
-      FRISK_CUDA(cudaMemsetAsync(g.rr_counters, 0, pl->rr_counter_bytes, st));  // as above
-    }
+    if (d.row_reduce) g.rr_partials = reinterpret_cast<float*>(workspace);
   }
   int rc;
   if (pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) {
@@ -1073,6 +1083,14 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
       case FRISK_DT_F32: rc = launch_tcgen05_t<float>(pl, g, st); break;
       case FRISK_DT_F16: rc = launch_tcgen05_t<__half>(pl, g, st); break;
       case FRISK_DT_BF16: rc = launch_tcgen05_t<__nv_bfloat16>(pl, g, st); break;
+      default: rc = FRISK_ERR_UNSUPPORTED;
+    }
+  }
+  if (!rc && d.row_reduce) {
+    switch (d.c_type) {
+      case FRISK_DT_F32: rc = launch_row_fold_t<float>(pl, g, args->row_reduce_dst, st); break;
+      case FRISK_DT_F16: rc = launch_row_fold_t<__half>(pl, g, args->row_reduce_dst, st); break;
+      case FRISK_DT_BF16: rc = launch_row_fold_t<__nv_bfloat16>(pl, g, args->row_reduce_dst, st); break;
       default: rc = FRISK_ERR_UNSUPPORTED;
     }
   }

@@ -123,10 +123,7 @@ struct GemmParams {
   void* peer_c[kMaxPeers]; // where this GPU's rows of C start in each peer's buffer (same ldc)
   // frisk.reduce of C over its columns, folded into the epilogue
   uint32_t rr_kind;        // 0: none; 1 + frisk_reduce_kind
-  uint32_t rr_clear;       // 1: dst = fold; 0: dst = dst (op) fold
   float* rr_partials;      // [2 * tiles_c][rows] fp32: one fold per row and half tile
-  uint32_t* rr_counters;   // [ceil(rows / 128)] half tiles arrived per block of 128 rows (zero between launches)
-  void* rr_dst;            // [rows] of C's element type
   uint32_t debug_mode;     // measurement only: bit 0 = issue no loads, bit 1 = issue no MMAs
   long long* trace;        // measurement only: clock64 samples of CTA 0 (may be nullptr)
   int32_t* status;
@@ -487,7 +484,31 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
   // The common cases get loops without per-element tests: on a shape whose main loop is short the
   // epilogue's instruction count is the kernel's time (measured: 2.2 x the instructions, and 6 us
   // more per tile, with the tests inside one generic loop).
-  if (full && p.clear_accum && !x.rr_kind) {
+  if (full && p.clear_accum && !p.col_scale && (x.rr_kind == 1u || x.rr_kind >= 3u)) {
+    // the fold of the rounded values with the kind fixed outside the loop (add, min, max)
+    if (x.rr_kind == 1u) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        const TC o = cast_out<TC>(__uint_as_float(acc[j]) * rs);
+        out[j / kPerVec].e[j % kPerVec] = o;
+        red += cast_in<TC>(o);
+      }
+    } else if (x.rr_kind == 3u) {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        const TC o = cast_out<TC>(__uint_as_float(acc[j]) * rs);
+        out[j / kPerVec].e[j % kPerVec] = o;
+        red = fminf(red, cast_in<TC>(o));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NC; ++j) {
+        const TC o = cast_out<TC>(__uint_as_float(acc[j]) * rs);
+        out[j / kPerVec].e[j % kPerVec] = o;
+        red = fmaxf(red, cast_in<TC>(o));
+      }
+    }
+  } else if (full && p.clear_accum && !x.rr_kind) {
     if (!p.col_scale) {
 #pragma unroll
       for (int j = 0; j < NC; ++j)
@@ -565,15 +586,25 @@ __device__ __forceinline__ void epilogue_item(const EpiArgs& ep, const EpiExt& e
 }
 
 // ---- frisk.reduce over the columns of C, folded into the whole-tile epilogue -------------------
-// Every (row, half tile) fold goes to partials[slot][row]; a counter per block of 128 rows counts
-// the half tiles that have arrived, and the CTA that brings it to 2 * tiles_c folds the row's
-// slots in slot order (so the result does not depend on which CTA that is) into dst.
+// Every thread folds the rounded values of its row as they pass (epilogue_chunk) and writes one
+// fp32 per (row, half tile) to partials[slot][row]; row_fold_finalize_kernel, launched behind the
+// GEMM, folds a row's slots in slot order into the destination.  (A last-arriving CTA folding the
+// slots inside the GEMM kernel -- an arrival counter, a fence, three rendezvous of the epilogue
+// threads -- was measured first: with that code merely present, a GEMM that never ran it executed
+// 34 % more instructions and kept the tensor pipe busy 70 % instead of 95 % of the cycles.)
 struct RowFold {
-  uint32_t kind, clear, nslots;
+  uint32_t kind, nslots;
   float* partials;
-  uint32_t* counters;
-  void* dst;
 };
+
+// `weight` is 2 for a whole tile (which also marks the tile's second slot as empty), 1 for a half.
+__device__ __forceinline__ void row_fold_store(const RowFold& f, uint32_t row, uint32_t rows,
+                                               uint32_t slot, uint32_t weight, float red) {
+  if (row < rows) {
+    f.partials[(size_t)slot * rows + row] = red;
+    if (weight == 2u) f.partials[(size_t)(slot + 1u) * rows + row] = fold_identity(f.kind);
+  }
+}
 
 // Rendezvous of the 128 epilogue threads on an mbarrier (count 128), bounded like every other
 // wait of the kernel: a named hardware barrier could not give up if one warp had left the loop.
@@ -583,44 +614,6 @@ __device__ __forceinline__ bool epilogue_rendezvous(uint32_t bar, uint32_t& phas
   const bool ok = bounded_wait(bar, phase, abort_flag, status, kStatusEpilogueTimeout);
   phase ^= 1u;
   return ok;
-}
-
-// Called by the 128 epilogue threads of a CTA after an item's last column; epi_tid = the thread's
-// row inside the CTA's 128 rows (32 * TMEM quarter + lane).
-// `weight` is 2 for a whole tile (which also marks the tile's second slot as empty), 1 for a half.
-template <typename TC>
-__device__ __forceinline__ bool row_fold_finish(const RowFold& f, uint32_t epi_tid, uint32_t row,
-                                                uint32_t rows, uint32_t slot, uint32_t weight,
-                                                float red, uint32_t epi_bar, uint32_t& epi_phase,
-                                                volatile uint32_t* abort_flag, int32_t* status,
-                                                volatile uint32_t* last_flag) {
-  const bool row_ok = row < rows;
-  const uint32_t blk = (row - epi_tid) >> 7;   // the CTA's rows start at a multiple of 128
-  if (row_ok) {
-    f.partials[(size_t)slot * rows + row] = red;
-    if (weight == 2u) f.partials[(size_t)(slot + 1u) * rows + row] = fold_identity(f.kind);
-  }
-  __threadfence();   // this thread's folds are visible device-wide before the count goes up
-  if (!epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status)) return false;
-  if (epi_tid == 0) {
-    const uint32_t before = atomicAdd(f.counters + blk, weight);
-    *last_flag = (before + weight == f.nslots) ? 1u : 0u;
-  }
-  if (!epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status)) return false;
-  if (*last_flag) {
-    __threadfence();
-    if (row_ok) {
-      float r = fold_identity(f.kind);
-      for (uint32_t sl = 0; sl < f.nslots; ++sl)
-        r = fold_step(f.kind, r, __ldcg(f.partials + (size_t)sl * rows + row));
-      TC* dst = reinterpret_cast<TC*>(f.dst) + row;
-      if (!f.clear) r = fold_step(f.kind, cast_in<TC>(*dst), r);
-      *dst = cast_out<TC>(r);
-    }
-    if (epi_tid == 0) f.counters[blk] = 0;   // ready for the next launch
-  }
-  // last_flag is rewritten by the next item
-  return epilogue_rendezvous(epi_bar, epi_phase, abort_flag, status);
 }
 
 // ---- split mode 2: partial tiles in private slots, reduced by the last CTA to arrive -----------
@@ -818,9 +811,8 @@ __device__ __forceinline__ void reduce_share(const EpiArgs& p, uint32_t buf, uin
 // kSplit selects the K-split (stream-K) code at compile time.  The whole-tile instantiation carries
 // none of it: with the slot reduction inlined the kernel needs 200+ registers and measurably slows
 // the whole-tile main loop (8192^3 bf16: 0.98 ms against 0.83 ms), so the two are kept apart.
-// kFold (whole tiles only) compiles the fused row reduce in, for the same reason.
 // kTf32 (whole tiles, C fp32) issues kind::tf32 MMAs: the 3xTF32 plan of fp32 GEMMs.
-template <typename TC, bool kSplit, bool kFold = false, bool kTf32 = false>
+template <typename TC, bool kSplit, bool kTf32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
@@ -1101,20 +1093,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       EpiExt ex;
       ex.staged = p.epi_staged;
       ex.n_peers = p.n_peers;
-      ex.rr_kind = kFold ? p.rr_kind : 0u;
+      ex.rr_kind = p.rr_kind;
       ex.peers = p.peer_c;
       RowFold rf;
-      rf.kind = kFold ? p.rr_kind : 0u;
-      rf.clear = p.rr_clear;
+      rf.kind = p.rr_kind;
       rf.nslots = 2u * tiles_c;
       rf.partials = p.rr_partials;
-      rf.counters = p.rr_counters;
-      rf.dst = p.rr_dst;
       const uint32_t quarter = warp & 3u;  // TMEM lanes 32*quarter .. +31 belong to this warp
       const uint32_t stage_area = tiles_base + stages * stage_bytes + quarter * kEpiStageBytesPerWarp;
-      const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
       const uint32_t epi_backoff = p.epilogue_backoff_ns;
-      uint32_t epi_phase = 0, item = 0;
+      uint32_t item = 0;
       bool ok = true;
       while (ok && work.next()) {
         const uint32_t acc = item % acc_bufs;
@@ -1133,12 +1121,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(acc_empty0 + 8 * acc);
-        if (kFold && rf.kind) {
-          ok = row_fold_finish<TC>(rf, quarter * 32u + lane, tr * 128u + quarter * 32u + lane, ep.rows,
-                                   2u * tc, 2u, red, epi_bar, epi_phase, abort_flag, status,
-                                   &last_flag);
-          if (!ok) break;
-        }
+        if (rf.kind) row_fold_store(rf, tr * 128u + quarter * 32u + lane, ep.rows, 2u * tc, 2u, red);
         ++item;
       }
       __syncwarp();
@@ -1311,6 +1294,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, tmem_cols);
   }
+}
+
+// dst[row] = (clear ? fold : dst[row] (op) fold) of partials[0 .. nslots)[row], in slot order.
+// Launched behind the GEMM as a programmatic dependent launch: it may be scheduled while the GEMM
+// drains and waits here until the GEMM's writes are visible.
+template <typename TC>
+__global__ void __launch_bounds__(256) row_fold_finalize_kernel(const float* __restrict__ partials,
+                                                                TC* __restrict__ dst, uint32_t rows,
+                                                                uint32_t nslots, uint32_t kind,
+                                                                uint32_t clear) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
+  const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float r = fold_identity(kind);
+  for (uint32_t sl = 0; sl < nslots; ++sl) r = fold_step(kind, r, __ldcg(partials + (size_t)sl * rows + row));
+  if (!clear) r = fold_step(kind, cast_in<TC>(dst[row]), r);
+  dst[row] = cast_out<TC>(r);
 }
 
 // Casts the fp32 partial sums of a split plan into C and clears them for the next run.

@@ -35,11 +35,8 @@ __device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t narrow_from) 
   return it;
 }
 
-// kFold compiles the fused row reduce in.  It is a template parameter, not a run-time switch:
-// with the fold's rendezvous / counter / re-read code present in the kernel -- even though a plain
-// GEMM never executes it -- the same launch ran 19 % slower (bf16 8192^3: 0.83 against 0.70 ms).
 // kTf32 (C fp32 only) issues kind::tf32 MMAs on fp32 operand tiles: the 3xTF32 plan of fp32 GEMMs.
-template <typename TC, bool kFold, bool kTf32 = false>
+template <typename TC, bool kTf32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
@@ -49,10 +46,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
   __shared__ __align__(8) uint64_t bar_acc_full[2];
   __shared__ __align__(8) uint64_t bar_acc_empty[2];
-  __shared__ __align__(8) uint64_t bar_epilogue;
   __shared__ uint32_t tmem_base_slot;
   __shared__ uint32_t abort_word;
-  __shared__ uint32_t last_flag;
 
   const uint32_t warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const uint32_t lane = threadIdx.x & 31;
@@ -95,7 +90,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::mbar_init(acc_full0 + 8 * i, 1);
       ptx::mbar_init(acc_empty0 + 8 * i, 8);  // four epilogue warps in each CTA
     }
-    ptx::mbar_init(ptx::smem_u32(&bar_epilogue), 128);
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
@@ -301,20 +295,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     EpiExt ex;
     ex.staged = p.epi_staged;
     ex.n_peers = p.n_peers;
-    ex.rr_kind = kFold ? p.rr_kind : 0u;
+    ex.rr_kind = p.rr_kind;
     ex.peers = p.peer_c;
     RowFold rf;
-    rf.kind = kFold ? p.rr_kind : 0u;
-    rf.clear = p.rr_clear;
+    rf.kind = p.rr_kind;
     rf.nslots = 2u * tiles_c;
     rf.partials = p.rr_partials;
-    rf.counters = p.rr_counters;
-    rf.dst = p.rr_dst;
     const uint32_t quarter = warp & 3u;
     // the staging area of the epilogue sits behind the pipeline stages
     const uint32_t stage_area = tiles_base + stages * stage_bytes + quarter * kEpiStageBytesPerWarp;
-    const uint32_t epi_bar = ptx::smem_u32(&bar_epilogue);
-    uint32_t epi_phase = 0, item = 0;
+    uint32_t item = 0;
     bool ok = true;
     for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
       const PairItem it = pair_item(i, narrow_from);
@@ -335,12 +325,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(leader_acc_empty0 + 8 * acc);
-      if (kFold && rf.kind) {
-        ok = row_fold_finish<TC>(rf, quarter * 32u + lane, warp_row0 + lane, ep.rows,
-                                 2u * tc + it.half, it.narrow ? 1u : 2u, red, epi_bar, epi_phase,
-                                 abort_flag, status, &last_flag);
-        if (!ok) break;
-      }
+      if (rf.kind) row_fold_store(rf, warp_row0 + lane, ep.rows, 2u * tc + it.half, it.narrow ? 1u : 2u, red);
       ++item;
     }
     if (!ok && lane == 0) ptx::st_shared_cluster_u32(peer_abort, 1);

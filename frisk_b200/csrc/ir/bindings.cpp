@@ -1013,6 +1013,11 @@ void initFrisk(py::module_ m) {
     d["c_type"] = castType(t.elemC);
     d["tile"] = t.tile;
     d["grid"] = t.grid;
+    if (t.argR >= 0) {  // a row fold of the accumulator rides along
+      d["arg_r"] = t.argR;
+      d["reduce_kind"] = t.reduceKind;
+      d["reduce_clear"] = t.reduceClear;
+    }
     return d;
   });
 

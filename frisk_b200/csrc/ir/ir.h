@@ -251,6 +251,12 @@ struct TiledGemm {
   Type elemAB, elemC;
   std::vector<int64_t> tile;            // TM, TN, TK of the program (a hint; not used to execute)
   std::vector<int64_t> grid;            // GY, GX
+  // A frisk.reduce of the accumulator tile over its columns, written out to a rank-1 kernel
+  // argument of M elements (only when the grid has one tile column, so that a tile row holds a
+  // whole row of C): the fold the GEMM's epilogue can do.  argR < 0: the program has none.
+  int argR = -1;
+  std::string reduceKind;
+  bool reduceClear = true;
 };
 TiledGemm liftTiledGemm(Operation* kernel);
 

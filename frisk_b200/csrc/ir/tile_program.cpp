@@ -135,16 +135,21 @@ TiledGemm liftTiledGemm(Operation* kernel) {
     ivs.by = pbody->args[0];
     ivs.bx = pbody->args[1];
 
-    // ---- the block body: allocs, at most one fill / one load of the accumulator, one for, one store
+    // ---- the block body: allocs, at most one fill / one load of the accumulator, one for, one
+    // store; then, optionally, a frisk.reduce of the accumulator tile and the copy of its result
     const Operation *loop = nullptr, *fill = nullptr, *store = nullptr, *preload = nullptr;
+    const Operation *reduce = nullptr, *rstore = nullptr;
     for (const Operation* op : pbody->ops) {
       if (isTerminatorOrNothing(op) || op->name == "frisk.alloc_buffer") continue;
       if (op->name == "frisk.fill" && !loop && !fill) fill = op;
       else if (op->name == "frisk.for" && !loop) loop = op;
       else if (op->name == "frisk.copy" && !loop && !preload) preload = op;
       else if (op->name == "frisk.copy" && loop && !store) store = op;
+      else if (op->name == "frisk.reduce" && store && !reduce) reduce = op;
+      else if (op->name == "frisk.copy" && reduce && !rstore) rstore = op;
       else fail("unexpected " + op->name + " in the block body");
     }
+    if (reduce && !rstore) fail("the reduce of the accumulator tile needs a frisk.copy of its result after it");
     if (!loop || !store) fail("the block body needs a frisk.for and a frisk.copy of the result after it");
     const Block* lbody = loop->regions.at(0)->blocks.at(0);
     ivs.k = lbody->args.at(0);
@@ -264,6 +269,52 @@ TiledGemm liftTiledGemm(Operation* kernel) {
     if (!typeEqual(ga->element, gb->element)) fail("A and B must have one element type");
     out.tile = {TM, TN, TK};
     out.grid = {grid[0], grid[1]};
+
+    // ---- the row fold behind the product (the reference's attention sketch reduces the
+    // accumulator of its first gemm this way, tmp/ir.mlir:112-135)
+    if (reduce) {
+      if (grid[1] != 1) fail("a reduce of the accumulator tile is lifted only when a tile holds whole rows of C (one tile column)");
+      if (reduce->operands.at(0) != tc) fail("the reduce must read the accumulator tile");
+      if (reduce->intAttr("dim") != 1) fail("the reduce must fold the accumulator's columns (dim = 1)");
+      const Attribute* kind = reduce->attr("kind");
+      if (!kind || !std::holds_alternative<std::string>(*kind)) fail("frisk.reduce: missing kind");
+      Value rt = reduce->operands.at(1);
+      if (!rt->defOp || rt->defOp->name != "frisk.alloc_buffer" || rt->defOp->parent != pbody)
+        fail("the reduce must write a buffer allocated in the block body");
+      if (!rt->type || rt->type->kind != TypeKind::MemRef || rt->type->shape != std::vector<int64_t>{TM})
+        fail("the reduce's destination must have one element per row of the tile");
+      if (rstore->operands.at(0) != rt) fail("the copy after the reduce must read its destination");
+      out.argR = argIndex(entry, rstore->operands.at(1));
+      if (out.argR < 0) fail("the reduce's result is not copied to a kernel argument");
+      const TypeStorage* gr = rstore->operands.at(1)->type.get();
+      if (!gr || gr->kind != TypeKind::MemRef || gr->memorySpace != 1 || gr->shape != std::vector<int64_t>{out.M})
+        fail("the reduce's result must go to a GLOBAL buffer of M elements");
+      if (!typeEqual(gr->element, gc->element)) fail("the reduce's result must have C's element type");
+      if (out.argR == out.argA || out.argR == out.argB || out.argR == out.argC)
+        fail("the reduce's result must not alias A, B or C");
+      if (dense(rstore, "srcExtents") != std::vector<int64_t>{TM} || dense(rstore, "dstExtents") != std::vector<int64_t>{TM})
+        fail("the copy of the reduce's result must cover exactly the tile's rows");
+      // rank-1 origins: the source from 0, the destination at by * TM
+      const AffineMap& sm = mapAttr(rstore, "srcMap");
+      const AffineMap& dm = mapAttr(rstore, "dstMap");
+      if (sm.results.size() != 1 || dm.results.size() != 1) fail("the copy of the reduce's result must be rank 1");
+      const int nsrc = rstore->segmentSizes[2], ndst = rstore->segmentSizes[3];
+      auto eval1 = [&](const AffineMap& map, int first, int count, int64_t by) {
+        if ((int)(map.numDims + map.numSymbols) != count) fail("frisk.copy: map inputs and indices differ");
+        std::vector<int64_t> dims(map.numDims), syms(map.numSymbols);
+        for (int i = 0; i < count; ++i) {
+          if (rstore->operands[first + i] != ivs.by) fail("the reduce's result may be placed by the row block index only");
+          if (i < (int)map.numDims) dims[i] = by;
+          else syms[i - map.numDims] = by;
+        }
+        return evaluate(map.results[0], dims, syms);
+      };
+      if (eval1(sm, 2, nsrc, 0) != 0 || eval1(sm, 2, nsrc, 3) != 0) fail("the reduce's result must be read from its origin");
+      if (eval1(dm, 2 + nsrc, ndst, 0) != 0 || eval1(dm, 2 + nsrc, ndst, 1) != TM || eval1(dm, 2 + nsrc, ndst, 5) != 5 * TM)
+        fail("the reduce's result must land at by * TM");
+      out.reduceKind = std::get<std::string>(*kind);
+      out.reduceClear = reduce->intAttr("clear", 1) != 0;
+    }
     out.ok = true;
   } catch (const Fail& f) {
     out.ok = false;

@@ -124,8 +124,12 @@ def find_gemms(module, kernel_name: str) -> list:
             t = ir.frisk.lift_tiled_gemm(kernel)
         except ValueError as e:
             raise R.FriskError(-2, f"{whole_problem_error}; and the kernel is {e}") from None
-        return [GemmCall(t["M"], t["N"], t["K"], _dtype_of(t["ab_type"]), _dtype_of(t["c_type"]),
-                         False, False, t["clear_accum"], t["arg_a"], t["arg_b"], t["arg_c"])]
+        lifted = [GemmCall(t["M"], t["N"], t["K"], _dtype_of(t["ab_type"]), _dtype_of(t["c_type"]),
+                           False, False, t["clear_accum"], t["arg_a"], t["arg_b"], t["arg_c"])]
+        if "arg_r" in t:  # the tile program folds the accumulator's rows: a reduce of C behind the gemm
+            lifted.append(ReduceCall((t["M"], t["N"]), 1, _dtype_of(t["c_type"]), t["reduce_kind"],
+                                     t["reduce_clear"], t["arg_c"], t["arg_r"]))
+        return lifted
     return calls
 
 

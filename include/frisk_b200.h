@@ -95,8 +95,8 @@ typedef struct frisk_gemm_desc {
                            either way), 3 = as 2 with linear instead of swizzled staging rows:
                            same results, shared-memory bank conflicts on every staging write
                            (kept so that the swizzle's effect can be measured)                  */
-  /* A frisk.reduce of C over its columns (dim 1), executed inside the GEMM's epilogue instead of
-   * a second pass over C (the reference's sketches reduce the accumulator of a gemm this way:
+  /* A frisk.reduce of C over its columns (dim 1), folded inside the GEMM's epilogue (a small
+   * second launch folds the per-tile results) instead of a second pass over C (the reference's sketches reduce the accumulator of a gemm this way:
    * tmp/ir.mlir:116, 135).  row_reduce = 1 + frisk_reduce_kind, 0 = none.  The fold sees the
    * values of C as stored (after the cast), so it equals frisk_b200_reduce_run on the finished C
    * for min and max and differs from it only in summation order for add and mul.  The result,

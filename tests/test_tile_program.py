@@ -59,6 +59,48 @@ def test_everything_else_is_refused_with_the_reason(tweak, reason):
         F.find_gemms(m, "matmul")
 
 
+def test_tiled_matmul_with_a_row_reduce_of_the_accumulator_lifts_to_a_fused_plan():
+    """One tile column (TN = N): a tile row holds whole rows of C, so the program's reduce of the
+    accumulator tile over its columns is a reduce of C over dim 1 and rides in the GEMM's epilogue."""
+    from frisk_b200 import execute as X
+    m = build_tiled_matmul(512, 256, 128, 128, 256, 32, dtype="bf16", row_reduce=("max", True))
+    assert m.verify(), m.verify_message()
+    t = F.ir.frisk.lift_tiled_gemm(m.get_kernel("matmul"))
+    assert (t["M"], t["N"], t["K"], t["arg_r"], t["reduce_kind"], t["reduce_clear"]) == (512, 256, 128, 3, "max", True)
+    gemm, red = X.find_gemms(m, "matmul")
+    assert isinstance(gemm, X.GemmCall) and red == X.ReduceCall((512, 256), 1, W.BF16, "max", True, 2, 3)
+    # read back from text, the same program lifts the same way
+    t2 = F.ir.frisk.lift_tiled_gemm(F.parse_module(str(m)).get_kernel("matmul"))
+    assert {k: t2[k] for k in ("M", "N", "K", "arg_r", "reduce_kind")} == {k: t[k] for k in ("M", "N", "K", "arg_r", "reduce_kind")}
+    for kw, reason in ((dict(N=512), "one tile column"), (dict(tweak="reduce_dim0"), "dim = 1"),
+                       (dict(tweak="reduce_rows_off"), "by \\* TM")):
+        kw = dict(kw)
+        mm = build_tiled_matmul(512, kw.pop("N", 256), 128, 128, 256, 32, dtype="bf16", row_reduce=("add", True), **kw)
+        with pytest.raises(ValueError, match=reason):
+            F.ir.frisk.lift_tiled_gemm(mm.get_kernel("matmul"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,clear", [("max", True), ("add", False)])
+def test_tiled_matmul_with_row_reduce_folds_in_the_epilogue(kind, clear):
+    from frisk_b200 import execute as X
+    from oracle import ref
+    M, N, K = 512, 256, 384
+    m = build_tiled_matmul(M, N, K, 128, 256, 32, dtype="bf16", row_reduce=(kind, clear))
+    w = W.make_workload("cfg5", M, N, K)
+    c = np.zeros((M, N), np.uint16)
+    init = W.encode(np.random.default_rng(3).standard_normal(M).astype(np.float32), W.BF16)
+    r = init.copy()
+    F.run(m, "matmul", [w.A, w.B, c, r])
+    assert X.LAST_RUN == [("gemm+reduce", "tcgen05_pair")]
+    ok, err, metric = W.check(W.decode(c, W.BF16), ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
+    assert ok, (metric, err)
+    want, mag = ref.ref_reduce(c, 1, W.BF16, kind, clear, init)
+    err = np.abs(W.decode(r, W.BF16).astype(np.float64) - want)
+    tol = 0.0 if kind == "max" else 1e-5 * mag + 2.0 ** -7 * np.abs(want)
+    assert (err <= tol).all(), float(err.max())
+
+
 def test_reference_flagship_module_is_still_a_whole_problem_gemm():
     # bind_test.py's module (gemm on the kernel arguments inside for / block) is not a tile program
     from test_ir_builder import build_bind_test_module  # the reference script's program
@@ -137,7 +179,7 @@ def test_gemm_followed_by_reduce_runs_as_written():
     assert ok, (metric, err)
     want, _ = ref.ref_reduce(c, 1, W.BF16, "max")  # exact: the maximum of the stored values
     assert np.array_equal(W.decode(rowmax, W.BF16).astype(np.float64), want)
-    # the two ops ran as ONE launch: the reduce sits in the gemm's epilogue
+    # the two ops ran as one fused plan: the reduce sits in the gemm's epilogue
     from frisk_b200 import execute as X
     assert X.LAST_RUN == [("gemm+reduce", "tcgen05")]
 
@@ -146,9 +188,9 @@ def test_gemm_followed_by_reduce_runs_as_written():
 @pytest.mark.parametrize("dtype,dims,kind,clear", [("fp16", (512, 1024, 256), "add", True),
                                                    ("bf16", (300, 520, 136), "max", False),
                                                    ("fp16", (1024, 768, 64), "min", True)])
-def test_gemm_then_row_reduce_is_one_launch_and_matches_the_two_ops(dtype, dims, kind, clear):
+def test_gemm_then_row_reduce_is_fused_and_matches_the_two_ops(dtype, dims, kind, clear):
     """The pair of ops of the reference's attention sketch (tmp/ir.mlir:112-135: a gemm, then a
-    frisk.reduce of its result over dim 1) executed as one launch, against the same module's two
+    frisk.reduce of its result over dim 1) executed as one fused plan, against the same module's two
     ops restated on the CPU: the product in float64, the reduce on the stored C."""
     from frisk_b200 import execute as X
     from oracle import ref

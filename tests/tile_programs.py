@@ -4,7 +4,11 @@ gemm, a copy of the accumulator tile to C).  `tweak` lets a test break one aspec
 import frisk as F
 
 
-def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kstep=1, tweak=None):
+def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kstep=1, tweak=None,
+                       row_reduce=None):
+    """`row_reduce` = (kind, clear): after the accumulator tile is stored, reduce it over its columns
+    into a [TM] buffer and copy that to a fourth kernel argument of M elements -- the gemm + reduce
+    pair of the reference's attention sketch (tmp/ir.mlir:112-135) written as a tile program."""
     ctx = F.context()
     F.frisk.load_dialects(ctx)
     b = F.builder(ctx)
@@ -15,7 +19,8 @@ def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kste
     ty = {"fp16": b.get_f16_ty, "bf16": b.get_bf16_ty, "fp32": b.get_f32_ty,
           "e4m3fn": b.get_f8e4m3fn_ty}[dtype]()
     mk = lambda shape: b.get_memref_ty(ty, shape, F.AffineMap(), F.MemorySpace.GLOBAL)
-    kernel = b.create_kernel_op(module, "matmul", b.get_kernel_ty([mk([M, K]), mk([K, N]), mk([M, N])]))
+    arg_tys = [mk([M, K]), mk([K, N]), mk([M, N])] + ([mk([M])] if row_reduce else [])
+    kernel = b.create_kernel_op(module, "matmul", b.get_kernel_ty(arg_tys))
     module.push_back(kernel)
     entry = kernel.add_entry_block()
     b.set_insertion_point_to_start(entry)
@@ -61,4 +66,12 @@ def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kste
     if tweak != "no_store":
         out_map = F.AffineMap.get(2, 0, [d1 * c(TM), d0 * c(TN)], ctx) if tweak == "c_swapped" else map_c
         b.create_copy_op(acc, C, [], [by, bx], zero, out_map, [TM, TN], [TM, TN])
+    if row_reduce:
+        kind, clear = row_reduce
+        Rg = entry.get_argument(3)
+        rt = b.create_alloc_buffer_op([TM], dtype, F.MemorySpace.LOCAL).get_result(0)
+        b.create_reduce_op(acc, rt, kind, 0 if tweak == "reduce_dim0" else 1, clear)
+        zero1 = F.AffineMap.get(0, 0, [c(0)], ctx)
+        row_map = F.AffineMap.get(1, 0, [d0 * c(TM if tweak != "reduce_rows_off" else TM + 1)], ctx)
+        b.create_copy_op(rt, Rg, [], [by], zero1, row_map, [TM], [TM])
     return module

@@ -61,7 +61,7 @@ typedef enum { FRISK_SCALE_NONE = 0, FRISK_SCALE_ROW_COL = 1 } frisk_scale_mode;
 
 /* Which kernel family a plan resolved to (reported by frisk_b200_gemm_plan_info). */
 typedef enum {
-  FRISK_KERNEL_SIMT = 0,    /* CUDA-core fp32-FMA tiles: fp32 inputs and every odd shape   */
+  FRISK_KERNEL_SIMT = 0,    /* CUDA-core fp32-FMA tiles: small fp32 problems, every odd shape */
   FRISK_KERNEL_TCGEN05 = 1, /* TMA + tcgen05.mma, accumulators in TMEM, whole-tile output   */
   FRISK_KERNEL_SKINNY = 2,  /* few rows (M <= 128): operands swapped, K split over a cluster / SMs */
   FRISK_KERNEL_TCGEN05_PAIR = 3, /* CTA pairs with two-SM MMAs on 256 x tile_n output tiles  */
@@ -96,8 +96,9 @@ typedef struct frisk_gemm_desc {
                            same results, shared-memory bank conflicts on every staging write
                            (kept so that the swizzle's effect can be measured)                  */
   /* A frisk.reduce of C over its columns (dim 1), folded inside the GEMM's epilogue (a small
-   * second launch folds the per-tile results) instead of a second pass over C (the reference's sketches reduce the accumulator of a gemm this way:
-   * tmp/ir.mlir:116, 135).  row_reduce = 1 + frisk_reduce_kind, 0 = none.  The fold sees the
+   * second launch folds the per-tile results) instead of a second pass over C.  The reference's
+   * sketches reduce the accumulator of a gemm this way: tmp/ir.mlir:116, 135.
+   * row_reduce = 1 + frisk_reduce_kind, 0 = none.  The fold sees the
    * values of C as stored (after the cast), so it equals frisk_b200_reduce_run on the finished C
    * for min and max and differs from it only in summation order for add and mul.  The result,
    * [M] of C's element type, goes to frisk_gemm_run_args.row_reduce_dst.                      */

@@ -881,7 +881,7 @@ def time_allgather(torch, R, S, dist, plan, A, B, C, sa, sb, ws, status, stream,
                         "gemm_plus_allgather_ms": round(fused_ms, 3),
                         "hidden": round((gemm_ms + ag_ms - fused_ms) / ag_ms, 3),
                         "equals_nccl_result_on_sampled_rows": same,
-                        "how": f"the epilogue stores each C tile to the local shard and to the {world - 1} peer copies"}
+                        "how": f"the epilogue stores each C tile to the local shard and to the {world - 1} peer cop{"y" if world == 2 else "ies"}"}
     finally:
         torch.cuda.synchronize()
         pg.close(dist)

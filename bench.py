@@ -591,7 +591,8 @@ def main():
     torch.cuda.synchronize()
     R.check_status(status, stream)
 
-    sampler = ClockSampler(local, getattr(torch.cuda.get_device_properties(local), "uuid", None))   # every rank its own GPU
+    sampler_index, sampler_uuid = local, getattr(torch.cuda.get_device_properties(local), "uuid", None)
+    sampler = ClockSampler(sampler_index, sampler_uuid)   # every rank its own GPU
     sampler.start()
     if dist:
         dist.barrier()
@@ -644,7 +645,7 @@ def main():
     allgather = None
     if dist and world > 1 and M % world == 0 and not args.no_allgather:
         allgather = time_allgather(torch, R, S, dist, plan, A, B, C, sa, sb, ws, status, stream, M, N, world, rank,
-                                   dev, ms_per_step, max(3, min(args.steps, 10)))
+                                   dev, ms_per_step, 20, gpu_index=sampler_index, gpu_uuid=sampler_uuid)
 
     # ---- end to end: host buffers through the C-ABI call, copies inside the timed region
     e2e = None
@@ -823,65 +824,88 @@ def library_matmul(torch, dev, m, n, k, dtype):
 
 
 def time_allgather(torch, R, S, dist, plan, A, B, C, sa, sb, ws, status, stream, M, N, world, rank, dev,
-                   gemm_ms, steps):
+                   gemm_ms, steps, gpu_index=0, gpu_uuid=None):
     """The optional all-gather of the C shards, two ways, each timed on the device (max over ranks):
 
-    * ``nccl_after``: ncclAllGather of the finished shards (the library baseline);
+    * ``nccl_after``: the GEMM, then ncclAllGather of the finished shards (the library baseline),
+      timed as the sequence a caller would run, step after step;
     * ``fused``: the GEMM itself stores every tile into every rank's copy of C
       (frisk_b200_gemm_run_ex with peer pointers; plain stores over NVLink, nothing loaded from a
-      peer), so the transfer runs under the math.  `gemm_plus_allgather_ms` is what a caller who
-      needs all of C everywhere waits for; `hidden` is the share of the NCCL all-gather's time
-      that the fused form no longer adds to the GEMM.
+      peer), so the transfer runs under the math.
+
+    Every loop runs the same number of steps after its own warm-up with the SM clock sampled
+    beside it, and the plain GEMM is timed once more directly behind the fused loop: a B200 under
+    its power cap runs a GEMM that follows tens of milliseconds of GEMMs slower than one that
+    follows an idle GPU, so only loops in the same state compare.  `hidden` is the share of the
+    all-gather's own time that the fused form no longer adds to a GEMM in that state.
     """
     rows = C.shape[0]
     es = C.element_size()
-    out = {}
-    for _ in range(2):
-        full = S.allgather_rows(dist, C, M, world, rank)
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        full = S.allgather_rows(dist, C, M, world, rank)
-    e1.record()
-    torch.cuda.synchronize()
-    ag_ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / steps, dev)
+    out = {"steps_per_loop": steps}
+
+    def loop(step, warm=3):
+        dist.barrier()
+        for _ in range(warm):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        sampler = ClockSampler(gpu_index, gpu_uuid)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        clk = sampler.stop()
+        ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / steps, dev)
+        return ms, clk.get("sm_mhz")
+
+    def gemm_only():
+        plan.run(A, B, C, sa, sb, ws, status, stream)
+
+    keep = {}
+
+    def nccl_only():
+        keep["full"] = S.allgather_rows(dist, C, M, world, rank)
+
+    def gemm_then_nccl():
+        gemm_only()
+        nccl_only()
+
+    ag_ms, _ = loop(nccl_only, warm=2)
+    seq_ms, seq_mhz = loop(gemm_then_nccl)
     recv = (world - 1) * rows * N * es
-    out["nccl_after"] = {"ms": round(ag_ms, 3), "recv_GBps_per_gpu": round(recv / (ag_ms * 1e-3) / 1e9, 1),
-                         "gemm_plus_allgather_ms": round(gemm_ms + ag_ms, 3)}
-    want = full[:: max(1, M // 64)].clone()   # a sample of rows of the NCCL result, to check the fused one
-    del full
+    out["nccl_after"] = {"allgather_alone_ms": round(ag_ms, 3),
+                         "recv_GBps_per_gpu": round(recv / (ag_ms * 1e-3) / 1e9, 1),
+                         "gemm_plus_allgather_ms": round(seq_ms, 3), "sm_mhz": seq_mhz,
+                         "how": "GEMM, then all_gather_into_tensor, step after step on one stream"}
+    want = keep["full"][:: max(1, M // 64)].clone()   # a sample of rows of the NCCL result, to check the fused one
+    keep.clear()
     try:
         pg = S.PeerGather(dist, M, N, es, world, rank)
     except Exception as e:  # no peer access between these GPUs: report it, keep the NCCL figure
         out["fused"] = {"error": str(e)}
         return out
     try:
-        dist.barrier()
-        for _ in range(2):
+        def fused():
             plan.run_ex(A, B, pg.local_c, scale_a=sa, scale_b=sb, workspace=ws, status=status, stream=stream,
                         peers=pg.peer_dsts)
-        torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            plan.run_ex(A, B, pg.local_c, scale_a=sa, scale_b=sb, workspace=ws, status=status, stream=stream,
-                        peers=pg.peer_dsts)
-        e1.record()
-        torch.cuda.synchronize()
-        fused_ms = S.max_over_ranks(dist, e0.elapsed_time(e1) / steps, dev)
+
+        fused_ms, fused_mhz = loop(fused)
+        again_ms, again_mhz = loop(gemm_only, warm=0)   # the plain GEMM in the state the fused loop left
         dist.barrier()   # every rank's stores have landed
         R.check_status(status, stream)
         got = pg.as_tensor(C.dtype)[:: max(1, M // 64)]
         same = bool(torch.equal(got.view(torch.int16) if es == 2 else got, want.view(torch.int16) if es == 2 else want))
         sent = (world - 1) * rows * N * es
-        out["fused"] = {"ms": round(fused_ms, 3), "sent_GBps_per_gpu": round(sent / (fused_ms * 1e-3) / 1e9, 1),
-                        "gemm_plus_allgather_ms": round(fused_ms, 3),
-                        "hidden": round((gemm_ms + ag_ms - fused_ms) / ag_ms, 3),
+        out["fused"] = {"gemm_plus_allgather_ms": round(fused_ms, 3), "sm_mhz": fused_mhz,
+                        "sent_GBps_per_gpu": round(sent / (fused_ms * 1e-3) / 1e9, 1),
+                        "gemm_alone_right_after_ms": round(again_ms, 3), "gemm_alone_right_after_sm_mhz": again_mhz,
+                        "hidden": round(1.0 - max(0.0, fused_ms - again_ms) / ag_ms, 3),
+                        "vs_nccl_after": round(seq_ms / fused_ms, 3),
                         "equals_nccl_result_on_sampled_rows": same,
-                        "how": f"the epilogue stores each C tile to the local shard and to the {world - 1} peer cop{"y" if world == 2 else "ies"}"}
+                        "how": f"the epilogue stores each C tile to the local shard and to the {world - 1} peer cop{'y' if world == 2 else 'ies'}"}
     finally:
         torch.cuda.synchronize()
         pg.close(dist)

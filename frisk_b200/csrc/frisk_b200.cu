@@ -101,6 +101,8 @@ struct frisk_gemm_plan {
   CUtensorMap tmap_a, tmap_b;
   const void* cached_a = nullptr;
   const void* cached_b = nullptr;
+  frisk::CStoreMaps c_maps;      // TMA-store epilogue: C and the peers' copies
+  const void* cached_c[1 + frisk::kMaxPeers] = {};
   int64_t simt_fallback_runs = 0;  // runs a tensor-core plan sent to the CUDA-core kernel
   // device buffers of frisk_b200_gemm_run_host
   void *hA = nullptr, *hB = nullptr, *hC = nullptr, *hWs = nullptr, *hRr = nullptr;
@@ -225,6 +227,34 @@ int encode_operand_map(CUtensorMap* map, const OperandView& v, int dtype, uint32
              "cuTensorMapEncodeTiled failed (%d): dims %llu x %llu, stride %llu, box %u x %u", (int)r,
              (unsigned long long)dims[0], (unsigned long long)dims[1],
              (unsigned long long)strides[0], box[0], box[1]);
+    g_last_error = buf;
+    return FRISK_ERR_CUDA;
+  }
+  return FRISK_OK;
+}
+
+// Tensor map of a destination of the TMA-store epilogue: `rows` x `cols` elements of `dtype` at
+// pitch `ld`, stored in boxes of 32 rows x 128 bytes out of 128-byte-swizzled shared memory.
+int encode_store_map(CUtensorMap* map, void* ptr, int dtype, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    g_last_error = "cuTensorMapEncodeTiled not available from the driver";
+    return FRISK_ERR_CUDA;
+  }
+  const uint32_t es = elem_size(dtype);
+  CUtensorMapDataType dt = dtype == FRISK_DT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : dtype == FRISK_DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * es};
+  cuuint32_t box[2] = {128u / es, 32u}, estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (%d) for C: %lld x %lld, pitch %lld",
+             (int)r, (long long)rows, (long long)cols, (long long)ld);
     g_last_error = buf;
     return FRISK_ERR_CUDA;
   }
@@ -393,8 +423,11 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // kernel is free).  desc.epilogue = 1 stores per thread instead.
   // The area is reserved either way: the element-wise path of a C without 16-byte alignment goes
   // through it too.
-  const size_t epi_bytes = swap ? 0 : frisk::kEpiStageBytes;
-  g.epi_staged = swap ? 0u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
+  // desc.epilogue = 4 on a CTA-pair plan: TMA tensor stores out of two staging buffers per warp
+  // (needs rows of C that start on 16-byte boundaries, like every tensor map).
+  const bool epi_tma = pair && !pl->tf32 && d.epilogue == 4 && (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
+  const size_t epi_bytes = swap ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
+  g.epi_staged = swap ? 0u : epi_tma ? 3u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
   uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
@@ -606,7 +639,7 @@ int launch_pair_tf(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
+  FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g, pl->c_maps));
   return FRISK_OK;
 }
 
@@ -769,7 +802,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.force_kernel < 0 || d.force_kernel > 5 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
-  if (d.epilogue < 0 || d.epilogue > 3 || d.row_reduce < 0 || d.row_reduce > 4 ||
+  if (d.epilogue < 0 || d.epilogue > 4 || d.row_reduce < 0 || d.row_reduce > 4 ||
       d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3)
     return FRISK_ERR_INVALID_ARGUMENT;
   d.row_reduce_clear = d.row_reduce_clear != 0;
@@ -1050,6 +1083,20 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     g.peer_c[q] = args->peer_c[q];
     // a peer copy that cannot take 16-byte stores switches every copy to element stores
     if ((uintptr_t)args->peer_c[q] % 16) g.c_vec_ok = 0;
+  }
+  if (g.epi_staged == 3u) {
+    if (!g.c_vec_ok) {
+      g.epi_staged = 1u;  // a base off the 16-byte grid: this run stores without TMA
+    } else {
+      // one map per destination: [rows of this plan, N] of C's type at pitch ldc, boxes of
+      // 32 rows x 128 bytes in the 128-byte swizzle the staging buffers are written in
+      for (int q = 0; q <= args->n_peers; ++q) {
+        void* dst = q == 0 ? C : args->peer_c[q - 1];
+        if (dst == pl->cached_c[q]) continue;
+        if (int rc = encode_store_map(&pl->c_maps.m[q], dst, d.c_type, d.M, d.N, d.ldc)) return rc;
+        pl->cached_c[q] = dst;
+      }
+    }
   }
   if (swap) {
     // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)

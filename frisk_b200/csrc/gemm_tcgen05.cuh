@@ -78,6 +78,11 @@ struct OperandParams {
   uint32_t sub_stride_bytes;  // distance between 128-row sub-tiles inside a stage
 };
 
+// Tensor maps of the destinations of a TMA-store epilogue: C, then every peer's copy.
+struct CStoreMaps {
+  CUtensorMap m[1 + kMaxPeers];
+};
+
 struct GemmParams {
   OperandParams a, b;  // a: 128-row (UMMA M) operand, b: UMMA N operand
   uint32_t idesc;      // tcgen05 instruction descriptor
@@ -119,6 +124,8 @@ struct GemmParams {
   // whole-tile epilogue (the one-CTA whole-tile kernel and the CTA-pair kernel)
   uint32_t epi_staged;     // 1: rows go through shared memory and leave as 128-byte row pieces
                            // (2: the same with linear instead of swizzled staging rows)
+                           // 3: rows go through shared memory and leave as TMA tensor stores
+                           //    (CTA-pair kernel; two staging buffers per warp)
   uint32_t n_peers;        // other GPUs that receive a copy of every C tile (row-sharded all-gather)
   void* peer_c[kMaxPeers]; // where this GPU's rows of C start in each peer's buffer (same ldc)
   // frisk.reduce of C over its columns, folded into the epilogue
@@ -365,6 +372,10 @@ __device__ __forceinline__ void epilogue_store(const EpiArgs& p, uint32_t row, u
 struct EpiExt {
   uint32_t staged, n_peers, rr_kind;
   void* const* peers;
+  // staged == 3: the rows leave through TMA stores.  c_maps[0] describes C, c_maps[1 + q] peer q's
+  // copy; tma_seq counts the warp's chunks (the staging buffer alternates with it).
+  const CUtensorMap* c_maps = nullptr;
+  uint32_t tma_seq = 0;
 };
 
 __device__ __forceinline__ float fold_identity(uint32_t rr_kind) {
@@ -444,11 +455,14 @@ __device__ __noinline__ void staged_rows_out(TC* C, void* const* peers, uint32_t
 // reduce of the stored C would see), and store:
 //   staged: the rows go through the warp's staging area and leave as whole 128-byte row pieces,
 //           four rows per store instruction, to C and to every peer's copy;
+//   TMA:    the rows go into one of the warp's two staging buffers and one lane issues a tensor
+//           store (cp.async.bulk.tensor, clipped at C's extents by the hardware) per destination;
+//           the buffer is written again only after those stores have read it;
 //   direct: every thread writes its own row piece (16-byte stores at row stride);
 //   a C without 16-byte alignment, or the chunk that crosses the last column, goes element-wise.
 // `stage` is the warp's staging area (shared-memory address), `warp_row0` the D row of lane 0.
 template <typename TC, int NC>
-__device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x, uint32_t stage,
+__device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, EpiExt& x, uint32_t stage,
                                                uint32_t lane, uint32_t warp_row0, uint32_t col0,
                                                const uint32_t (&acc)[NC], float& red) {
   constexpr int kPerVec = 16 / (int)sizeof(TC);
@@ -466,6 +480,16 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
     TC e[kPerVec];
   };
   Pack out[kVecs];
+  const bool tma = x.staged == 3u;  // warp-uniform; the plan guarantees a 16-byte aligned C
+  if (tma) {
+    // The stores of the chunk before last read the buffer this chunk goes into; the element-wise
+    // read of an old C below uses the first buffer whatever the turn, so it waits for all of them.
+    if (lane == 0) {
+      if (!p.clear_accum && !vec) ptx::bulk_wait_group_read<0>();
+      else ptx::bulk_wait_group_read<1>();
+    }
+    __syncwarp();
+  }
   if (!p.clear_accum) {
     if (vec) {
       if (row_ok) {
@@ -544,6 +568,23 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
     }
     return;
   }
+  if (tma) {
+    const uint32_t buf = stage + (x.tma_seq & 1u) * kEpiStageBytesPerWarp;
+    ++x.tma_seq;
+#pragma unroll
+    for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(staged_chunk(buf, lane, (uint32_t)v0, 7u), out[v0].u);
+    ptx::fence_proxy_async_smem();   // the writes above, made visible to the TMA unit
+    __syncwarp();
+    if (lane == 0) {
+      if (warp_row0 < p.rows && col0 < p.cols) {
+#pragma unroll 1
+        for (uint32_t q = 0; q <= x.n_peers; ++q)
+          ptx::tma_store_2d(x.c_maps + q, buf, (int32_t)col0, (int32_t)warp_row0);
+      }
+      ptx::bulk_commit_group();   // one group per chunk, empty or not: the waits count groups
+    }
+    return;
+  }
 #pragma unroll
   for (int v0 = 0; v0 < kVecs; ++v0) st_shared_v4(staged_chunk(stage, lane, (uint32_t)v0, xm), out[v0].u);
   __syncwarp();
@@ -571,7 +612,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiArgs& p, const EpiExt& x
 // rows at tensor-memory address `t_row`.  Columns are taken 128 bytes of C at a time; the
 // tensor-memory loads of a piece are issued together and waited for once.
 template <typename TC>
-__device__ __forceinline__ void epilogue_item(const EpiArgs& ep, const EpiExt& ex, uint32_t stage,
+__device__ __forceinline__ void epilogue_item(const EpiArgs& ep, EpiExt& ex, uint32_t stage,
                                               uint32_t lane, uint32_t warp_row0, uint32_t col0,
                                               uint32_t cols_item, uint32_t t_row, float& red) {
   constexpr int CH = 128 / (int)sizeof(TC);

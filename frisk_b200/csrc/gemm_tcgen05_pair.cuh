@@ -40,7 +40,8 @@ template <typename TC, bool kTf32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ GemmParams p) {
+                         const __grid_constant__ GemmParams p,
+                         const __grid_constant__ CStoreMaps c_maps) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kMaxStages];
@@ -297,13 +298,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ex.n_peers = p.n_peers;
     ex.rr_kind = p.rr_kind;
     ex.peers = p.peer_c;
+    ex.c_maps = c_maps.m;
     RowFold rf;
     rf.kind = p.rr_kind;
     rf.nslots = 2u * tiles_c;
     rf.partials = p.rr_partials;
     const uint32_t quarter = warp & 3u;
     // the staging area of the epilogue sits behind the pipeline stages
-    const uint32_t stage_area = tiles_base + stages * stage_bytes + quarter * kEpiStageBytesPerWarp;
+    // (two buffers per warp when the rows leave through TMA stores)
+    const uint32_t stage_area = tiles_base + stages * stage_bytes +
+                                quarter * kEpiStageBytesPerWarp * (ex.staged == 3u ? 2u : 1u);
     uint32_t item = 0;
     bool ok = true;
     for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
@@ -329,6 +333,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ++item;
     }
     if (!ok && lane == 0) ptx::st_shared_cluster_u32(peer_abort, 1);
+    // shared memory must outlive the reads of the tensor stores still in flight
+    if (ex.staged == 3u && lane == 0) ptx::bulk_wait_group_read<0>();
     __syncwarp();
   }
 

@@ -94,7 +94,10 @@ typedef struct frisk_gemm_desc {
                            pieces (a C without 16-byte aligned rows is stored element-wise
                            either way), 3 = as 2 with linear instead of swizzled staging rows:
                            same results, shared-memory bank conflicts on every staging write
-                           (kept so that the swizzle's effect can be measured)                  */
+                           (kept so that the swizzle's effect can be measured), 4 = rows
+                           staged as in 2 and stored by TMA tensor stores, one instruction per
+                           32 x 128-byte piece and destination (CTA-pair plans with 16-byte
+                           aligned C rows; other plans take it as 2)                            */
   /* A frisk.reduce of C over its columns (dim 1), folded inside the GEMM's epilogue (a small
    * second launch folds the per-tile results) instead of a second pass over C.  The reference's
    * sketches reduce the accumulator of a gemm this way: tmp/ir.mlir:116, 135.

@@ -187,7 +187,7 @@ def test_run_ex_argument_errors():
     a.n_peers = 0                                             # a fused reduce needs its destination
     assert L.frisk_b200_gemm_run_ex(plan._h, C.byref(a)) == -1
     plan.close()
-    for bad in (dict(epilogue=4), dict(epilogue=-1)):
+    for bad in (dict(epilogue=5), dict(epilogue=-1)):
         with pytest.raises(R.FriskError) as e:
             R.GemmPlan(256, 256, 256, W.BF16, **bad)
         assert e.value.code == -1
@@ -204,6 +204,11 @@ def test_run_ex_argument_errors():
     assert p2.info["smem_bytes"] <= 226 * 1024
     p1.close()
     p2.close()
+    # TMA stores take two staging buffers per warp (32 KiB) and still leave six stages
+    p4 = R.GemmPlan(4096, 4096, 4096, W.BF16, epilogue=4)
+    assert p4.info["kernel_name"] == "tcgen05_pair" and p4.info["stages"] == 6
+    assert p2.info["smem_bytes"] + 16 * 1024 == p4.info["smem_bytes"] <= 226 * 1024
+    p4.close()
     # peer buffers: argument errors need no device
     assert L.frisk_b200_peer_alloc(0, C.byref(h), C.create_string_buffer(64)) == -1
     assert L.frisk_b200_peer_open(None, C.byref(h)) == -1

@@ -110,10 +110,23 @@ def test_staged_and_direct_epilogues_give_the_same_bits(M, N, K, ab, ct, ta, tb,
     shifted, _, _, _ = device_run(w, epilogue=2, force_kernel=kernel, ldc=N + 3,
                                   c_offset_bytes=W.ELEM_SIZE[ct])
     assert np.array_equal(shifted, direct)
+    # TMA tensor stores out of the staging buffers (the CTA-pair kernel; the one-CTA kernel takes
+    # the option as "staged"): the hardware clips the ragged last rows and columns
+    tma, _, _, _ = device_run(w, epilogue=4, force_kernel=kernel)
+    assert np.array_equal(tma, direct)
+    tma_padded, _, _, _ = device_run(w, epilogue=4, force_kernel=kernel, ldc=N + 32)
+    assert np.array_equal(tma_padded, direct)
+    # rows off the 16-byte grid (pitch, then base): no tensor map exists, the run stores without TMA
+    tma_shifted, _, _, _ = device_run(w, epilogue=4, force_kernel=kernel, ldc=N + 3,
+                                      c_offset_bytes=W.ELEM_SIZE[ct])
+    assert np.array_equal(tma_shifted, direct)
+    tma_base, _, _, _ = device_run(w, epilogue=4, force_kernel=kernel, ldc=N + 32,
+                                   c_offset_bytes=W.ELEM_SIZE[ct])
+    assert np.array_equal(tma_base, direct)
 
 
 @pytest.mark.parametrize("M,N,K,ab,ct,ta,tb,clear,kernel", CASES[:5])
-@pytest.mark.parametrize("epilogue", [1, 2])
+@pytest.mark.parametrize("epilogue", [1, 2, 4])
 def test_peer_copies_equal_c(M, N, K, ab, ct, ta, tb, clear, kernel, epilogue):
     """The all-gather folded into the epilogue: every destination gets the bits of C.  The peer
     buffers live on the same GPU here; across GPUs only the pointers differ."""
@@ -139,7 +152,7 @@ def reduce_tolerance(kind, want, mag, dtype):
 def test_row_reduce_in_the_epilogue_matches_a_reduce_of_the_stored_c(M, N, K, ab, ct, ta, tb, clear, kernel, kind):
     w = make(M, N, K, ab, ct, ta, tb, clear, seed=5)
     plain, _, _, _ = device_run(w, force_kernel=kernel)
-    for epilogue in (1, 2):
+    for epilogue in (1, 2, 4):
         c, _, got, info = device_run(w, force_kernel=kernel, epilogue=epilogue, row_reduce=kind)
         assert info["kernel_name"] == kernel
         assert np.array_equal(c, plain), "the fold must not change C"

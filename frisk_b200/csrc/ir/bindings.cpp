@@ -1020,6 +1020,23 @@ void initFrisk(py::module_ m) {
     }
     return d;
   });
+  // addition: the tiled reduce (a grid of tiles folded into a rank-1 accumulator with frisk.reduce)
+  // lifted to one whole-buffer reduce; raises ValueError with the reason for anything else
+  m.def("lift_tiled_reduce", [](PyKernel& k) {
+    TiledReduce t = liftTiledReduce(k.op);
+    if (!t.ok) throw std::invalid_argument("not a tiled reduce: " + t.why);
+    py::dict d;
+    d["shape"] = t.shape;
+    d["dim"] = t.dim;
+    d["kind"] = t.kind;
+    d["clear"] = t.clear;
+    d["arg_src"] = t.argSrc;
+    d["arg_dst"] = t.argDst;
+    d["type"] = castType(t.elem);
+    d["tile"] = t.tile;
+    d["grid"] = t.grid;
+    return d;
+  });
 
   py::class_<PyGemm, PyOpState>(m, "GemmOp", py::module_local())
       .def_static("from_operation", [](PyOperation& o) -> py::object {

@@ -141,7 +141,23 @@ std::string printAttribute(const Attribute& a) {
     if (i->width == 1) return i->value ? "true" : "false";
     os << i->value << " : i" << i->width;
   } else if (auto* f = std::get_if<FloatAttr>(&a)) {
-    os << printFloat(f->value) << " : " << printType(f->type);
+    if (std::isfinite(f->value)) {
+      os << printFloat(f->value);
+    } else {
+      // MLIR prints infinities and NaNs as the bit pattern of the attribute's type
+      const bool neg = std::signbit(f->value), nan = std::isnan(f->value);
+      char buf[32];
+      switch (f->type ? f->type->kind : TypeKind::F64) {
+        case TypeKind::F16: snprintf(buf, sizeof buf, "0x%04X", (nan ? 0x7E00u : 0x7C00u) | (neg ? 0x8000u : 0u)); break;
+        case TypeKind::BF16: snprintf(buf, sizeof buf, "0x%04X", (nan ? 0x7FC0u : 0x7F80u) | (neg ? 0x8000u : 0u)); break;
+        case TypeKind::F32: snprintf(buf, sizeof buf, "0x%08X", (nan ? 0x7FC00000u : 0x7F800000u) | (neg ? 0x80000000u : 0u)); break;
+        default:
+          snprintf(buf, sizeof buf, "0x%016llX",
+                   (unsigned long long)((nan ? 0x7FF8000000000000ull : 0x7FF0000000000000ull) | (neg ? 0x8000000000000000ull : 0ull)));
+      }
+      os << buf;
+    }
+    os << " : " << printType(f->type);
   } else if (auto* s = std::get_if<std::string>(&a)) {
     os << '"' << *s << '"';
   } else if (auto* t = std::get_if<Type>(&a)) {

@@ -260,6 +260,24 @@ struct TiledGemm {
 };
 TiledGemm liftTiledGemm(Operation* kernel);
 
+// A tiled reduce (tile_program.cpp): a one-dimensional frisk.parallel grid whose body walks the
+// reduced dimension of a rank-2 GLOBAL argument tile by tile (copy into a tile buffer,
+// frisk.reduce of the tile into a rank-1 accumulator buffer with clear = false) and copies the
+// accumulator out, recognised and lifted to one whole-buffer frisk.reduce over kernel arguments.
+struct TiledReduce {
+  bool ok = false;
+  std::string why;
+  std::vector<int64_t> shape;  // of the source argument: [R, C]
+  int64_t dim = 0;             // the reduced dimension
+  std::string kind;
+  bool clear = true;           // false: the accumulator is loaded from the destination first
+  int argSrc = -1, argDst = -1;
+  Type elem;
+  std::vector<int64_t> tile;   // the program's tile [TR, TC] (a hint; not used to execute)
+  int64_t grid = 0;
+};
+TiledReduce liftTiledReduce(Operation* kernel);
+
 // Reads a module from its textual form (the custom assembly the printers above and the reference's
 // own printers emit).  Returns nullptr and sets *error ("line L, column C: what") on anything it
 // cannot read.  The module's objects belong to `ctx`.

@@ -9,6 +9,10 @@
 // error names them): func.func bodies, the generic "quoted" op form, #frisk.layout attributes.
 #include "ir.h"
 
+#include <cstring>
+
+#include <cmath>
+
 #include <cctype>
 #include <cstdlib>
 #include <map>
@@ -366,6 +370,30 @@ class Parser {
     }
     if (peekStr("#frisk.layout")) fail("#frisk.layout attributes are not read back");
     if (peekStr("memref<") || peekStr("tensor<")) return parseType();
+    // a bit pattern "0x..." : type -- how infinities and NaNs of float attributes are printed
+    if (peekStr("0x") || peekStr("0X")) {
+      pos_ += 2;
+      const size_t h = pos_;
+      while (pos_ < s_.size() && std::isxdigit((unsigned char)s_[pos_])) ++pos_;
+      if (h == pos_) fail("expected hexadecimal digits");
+      const unsigned long long bits = std::strtoull(s_.substr(h, pos_ - h).c_str(), nullptr, 16);
+      if (!accept(':')) return IntAttr{(int64_t)bits, 64};
+      Type t = parseType();
+      switch (t->kind) {
+        case TypeKind::Integer: return IntAttr{(int64_t)bits, t->width};
+        case TypeKind::Index: return IntAttr{(int64_t)bits, 64};
+        case TypeKind::F64: { double d; const uint64_t u = bits; memcpy(&d, &u, 8); return FloatAttr{d, t}; }
+        case TypeKind::F32: { float f; const uint32_t u = (uint32_t)bits; memcpy(&f, &u, 4); return FloatAttr{(double)f, t}; }
+        case TypeKind::BF16: { float f; const uint32_t u = (uint32_t)bits << 16; memcpy(&f, &u, 4); return FloatAttr{(double)f, t}; }
+        case TypeKind::F16: {
+          const uint32_t sign = (bits >> 15) & 1u, ex = (bits >> 10) & 0x1Fu, man = bits & 0x3FFu;
+          double v = ex == 0x1F ? (man ? std::nan("") : INFINITY)
+                                : ex == 0 ? std::ldexp((double)man, -24) : std::ldexp(1.0 + man / 1024.0, (int)ex - 15);
+          return FloatAttr{sign ? -v : v, t};
+        }
+        default: fail("a bit pattern needs an integer or a 16-, 32- or 64-bit float type");
+      }
+    }
     // number: integer ": iN" or float ": fN"
     const size_t b = pos_;
     if (pos_ < s_.size() && (s_[pos_] == '-' || s_[pos_] == '+')) ++pos_;

@@ -21,6 +21,7 @@
 #include "ir.h"
 
 #include <array>
+#include <limits>
 #include <stdexcept>
 #include <string>
 
@@ -315,6 +316,213 @@ TiledGemm liftTiledGemm(Operation* kernel) {
       out.reduceKind = std::get<std::string>(*kind);
       out.reduceClear = reduce->intAttr("clear", 1) != 0;
     }
+    out.ok = true;
+  } catch (const Fail& f) {
+    out.ok = false;
+    out.why = f.why;
+  } catch (const std::out_of_range&) {
+    out.ok = false;
+    out.why = "malformed operation (missing operand or region)";
+  }
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The tiled reduce.  The reference's online-softmax sketch (tmp/ir.mlir:22-36) walks a row of a
+// GLOBAL matrix in tiles inside a frisk.parallel body and reduces every tile with frisk.reduce;
+// written with the ops the builder has (FriskOps.td:81-228 parallel / for / alloc_buffer, 348-410
+// copy / fill, FriskOps_Reduce.cpp reduce) the whole-row fold is
+//
+//   frisk.kernel @k(%X: [R, C] global, %Y: [R] global)            (dim = 1; dim = 0 mirrored)
+//     frisk.parallel %b : ((G), threads)
+//       %x = alloc_buffer [TR, TC]        %m = alloc_buffer [TR]
+//       frisk.fill %m, identity of the kind      |  frisk.copy Y[b*TR] -> %m
+//       frisk.for %i = lb to ub step st
+//         frisk.copy X[b*TR, i*..] -> %x
+//         frisk.reduce %x -> %m  {dim = 1, clear = false}
+//       frisk.copy %m -> Y[b*TR]
+//
+// (without the loop when one tile spans the reduced dimension).  As with the matrix product, the
+// program is checked to be exactly this fold -- every element of X visited once, every element of
+// Y written once -- and run as ONE whole-buffer reduce; tile sizes and the grid are the back end's.
+namespace {
+
+// origin of a rank-1 copy side as a * b + c, the only index allowed being the block index
+std::array<int64_t, 2> origin1(const Operation* copy, bool srcSide, Value b) {
+  const AffineMap& map = mapAttr(copy, srcSide ? "srcMap" : "dstMap");
+  if (map.results.size() != 1) fail("frisk.copy: the accumulator moves as a rank-1 buffer");
+  const int first = srcSide ? 2 : 2 + copy->segmentSizes[2];
+  const int count = srcSide ? copy->segmentSizes[2] : copy->segmentSizes[3];
+  if ((int)(map.numDims + map.numSymbols) != count) fail("frisk.copy: map inputs and indices differ");
+  auto at = [&](int64_t v) {
+    std::vector<int64_t> dims(map.numDims), syms(map.numSymbols);
+    for (int i = 0; i < count; ++i) {
+      if (copy->operands[first + i] != b) fail("frisk.copy: the accumulator may be placed by the block index only");
+      if (i < (int)map.numDims) dims[i] = v;
+      else syms[i - map.numDims] = v;
+    }
+    return evaluate(map.results[0], dims, syms);
+  };
+  const int64_t c = at(0), a = at(1) - c;
+  if (at(5) != 5 * a + c) fail("frisk.copy: the origin is not linear in the block index");
+  return {a, c};
+}
+
+double identityOf(const std::string& kind) {
+  if (kind == "add") return 0.0;
+  if (kind == "mul") return 1.0;
+  if (kind == "min") return std::numeric_limits<double>::infinity();
+  return -std::numeric_limits<double>::infinity();
+}
+
+}  // namespace
+
+TiledReduce liftTiledReduce(Operation* kernel) {
+  TiledReduce out;
+  try {
+    if (!kernel || kernel->name != "frisk.kernel" || kernel->regions.empty() ||
+        kernel->regions[0]->blocks.empty())
+      fail("not a frisk.kernel with a body");
+    const Block* entry = kernel->regions[0]->blocks[0];
+    const Operation* par = nullptr;
+    for (const Operation* op : entry->ops) {
+      if (isTerminatorOrNothing(op)) continue;
+      if (op->name != "frisk.parallel" || par) fail("the kernel body must be one frisk.parallel");
+      par = op;
+    }
+    if (!par || par->regions.empty() || par->regions[0]->blocks.empty())
+      fail("the kernel body must be one frisk.parallel");
+    const std::vector<int64_t>& grid = dense(par, "ranges");
+    const Block* pbody = par->regions[0]->blocks[0];
+    if (grid.size() != 1 || pbody->args.size() != 1) fail("the grid of a tiled reduce has one dimension");
+    Ivs ivs;
+    ivs.by = pbody->args[0];
+
+    // ---- the block body: allocs, a fill or a load of the accumulator, a loop (or the bare tile
+    // load and reduce), the store of the accumulator
+    const Operation *loop = nullptr, *fill = nullptr, *preload = nullptr, *store = nullptr;
+    const Operation *load = nullptr, *reduce = nullptr;
+    auto body = [&](const Block* blk, bool inLoop) {
+      for (const Operation* op : blk->ops) {
+        if (isTerminatorOrNothing(op)) continue;
+        if (!inLoop && op->name == "frisk.alloc_buffer") continue;
+        if (!inLoop && op->name == "frisk.for" && !loop && !load && !store) { loop = op; continue; }
+        if (!inLoop && loop) {
+          if (op->name == "frisk.copy" && !store) { store = op; continue; }
+          fail("unexpected " + op->name + " behind the loop");
+        }
+        if (op->name == "frisk.fill" && !inLoop && !fill && !load) fill = op;
+        else if (op->name == "frisk.copy" && !reduce && !load && !inLoop && !preload && !fill &&
+                 op->operands.at(1)->type && op->operands.at(1)->type->shape.size() == 1) preload = op;
+        else if (op->name == "frisk.copy" && !load) load = op;
+        else if (op->name == "frisk.reduce" && load && !reduce) reduce = op;
+        else if (op->name == "frisk.copy" && reduce && !inLoop && !store) store = op;
+        else fail("unexpected " + op->name + (inLoop ? " in the loop" : " in the block body"));
+      }
+    };
+    body(pbody, false);
+    int64_t lb = 0, st = 1, trips = 1;
+    if (loop) {
+      const Block* lbody = loop->regions.at(0)->blocks.at(0);
+      ivs.k = lbody->args.at(0);
+      lb = loop->intAttr("lower");
+      st = loop->intAttr("step");
+      const int64_t ub = loop->intAttr("upper");
+      if (st <= 0 || ub <= lb) fail("the loop must run forwards at least once");
+      trips = (ub - lb + st - 1) / st;
+      body(lbody, true);
+    }
+    if (!load || !reduce) fail("the body needs a frisk.copy into a tile and a frisk.reduce of the tile");
+    if (!store) fail("the accumulator is not copied out");
+
+    // ---- the tile, the accumulator, the reduce between them
+    Value tx = reduce->operands.at(0), tm = reduce->operands.at(1);
+    for (Value t : {tx, tm})
+      if (!t->defOp || t->defOp->name != "frisk.alloc_buffer" || t->defOp->parent != pbody)
+        fail("the reduce must work on buffers allocated in the block body");
+    const TypeStorage* xt = memref2d(tx, "the tile");
+    const int64_t dim = reduce->intAttr("dim");
+    if (dim != 0 && dim != 1) fail("the reduce must fold dimension 0 or 1 of the tile");
+    const int64_t keep = 1 - dim;   // the tile dimension that survives
+    const int64_t T[2] = {xt->shape[0], xt->shape[1]};
+    if (T[0] <= 0 || T[1] <= 0) fail("the tile must have a static shape");
+    if (!tm->type || tm->type->kind != TypeKind::MemRef || tm->type->shape != std::vector<int64_t>{T[keep]})
+      fail("the accumulator must have one element per kept row or column of the tile");
+    const Attribute* kind = reduce->attr("kind");
+    if (!kind || !std::holds_alternative<std::string>(*kind)) fail("frisk.reduce: missing kind");
+    out.kind = std::get<std::string>(*kind);
+    const bool opClear = reduce->intAttr("clear", 1) != 0;
+    if (loop && trips > 1 && opClear)
+      fail("the reduce in the loop must fold into the accumulator (clear = false): with clear = true only the last tile would count");
+
+    // ---- the load: GLOBAL argument -> whole tile, walking the reduced dimension with the loop
+    if (load->operands.at(1) != tx) fail("the copy before the reduce must fill the tile the reduce reads");
+    out.argSrc = argIndex(entry, load->operands.at(0));
+    if (out.argSrc < 0) fail("the tile is not loaded from a kernel argument");
+    const TypeStorage* gx = memref2d(load->operands.at(0), "the source");
+    if (gx->memorySpace != 1) fail("the source must live in GLOBAL memory");
+    const std::vector<int64_t> whole{T[0], T[1]};
+    if (dense(load, "srcExtents") != whole || dense(load, "dstExtents") != whole)
+      fail("the load must cover exactly the tile");
+    if (!isZeroOrigin(originOf(load, false, ivs))) fail("the tile must be filled from its origin");
+    const Origin ox = originOf(load, true, ivs);
+    const std::array<int64_t, 4> keptWant{T[keep], 0, 0, 0};
+    if (ox.coef[keep] != keptWant) fail("the kept dimension of the tile must start at block index * tile extent");
+    const auto& rc = ox.coef[dim];
+    if (rc[0] != 0 || rc[1] != 0) fail("the offset along the reduced dimension may depend on the loop variable only");
+    if (loop) {
+      if (rc[2] * lb + rc[3] != 0 || (trips > 1 && rc[2] * st != T[dim]))
+        fail("the loop must visit consecutive tiles of the reduced dimension");
+    } else if (rc[2] != 0 || rc[3] != 0) {
+      fail("without a loop the tile must start at the origin of the reduced dimension");
+    }
+    std::vector<int64_t> shape(2);
+    shape[keep] = grid[0] * T[keep];
+    shape[dim] = trips * T[dim];
+    if (gx->shape != shape) fail("the grid and the loop must cover the source exactly");
+
+    // ---- the store: accumulator -> GLOBAL argument at block index * tile extent
+    if (store->operands.at(0) != tm) fail("the copy at the end must read the accumulator");
+    out.argDst = argIndex(entry, store->operands.at(1));
+    if (out.argDst < 0) fail("the result is not copied to a kernel argument");
+    const TypeStorage* gy = store->operands.at(1)->type.get();
+    if (!gy || gy->kind != TypeKind::MemRef || gy->memorySpace != 1 || gy->shape != std::vector<int64_t>{shape[keep]})
+      fail("the result must go to a GLOBAL buffer with one element per kept row or column");
+    if (!typeEqual(gy->element, gx->element)) fail("source and result must have one element type");
+    if (out.argDst == out.argSrc) fail("the result must not alias the source");
+    const std::vector<int64_t> accAll{T[keep]};
+    if (dense(store, "srcExtents") != accAll || dense(store, "dstExtents") != accAll)
+      fail("the copy of the result must cover exactly the accumulator");
+    if (origin1(store, true, ivs.by) != std::array<int64_t, 2>{0, 0}) fail("the accumulator must be read from its origin");
+    if (origin1(store, false, ivs.by) != std::array<int64_t, 2>{T[keep], 0}) fail("the result must land at block index * tile extent");
+
+    // ---- how the accumulator starts
+    if (fill) {
+      if (fill->operands.at(0) != tm) fail("the fill must set the accumulator");
+      const Attribute* v = fill->attr("value");
+      if (!v || !std::holds_alternative<FloatAttr>(*v) || std::get<FloatAttr>(*v).value != identityOf(out.kind))
+        fail("the accumulator must start at the identity of the reduce kind (0 for add, 1 for mul, +inf for min, -inf for max)");
+      out.clear = true;
+    } else if (preload) {
+      if (preload->operands.at(1) != tm || preload->operands.at(0) != store->operands.at(1))
+        fail("the copy before the loop must load the accumulator from the result buffer");
+      if (dense(preload, "srcExtents") != accAll || dense(preload, "dstExtents") != accAll)
+        fail("the load of the accumulator must cover it exactly");
+      if (origin1(preload, false, ivs.by) != std::array<int64_t, 2>{0, 0} ||
+          origin1(preload, true, ivs.by) != std::array<int64_t, 2>{T[keep], 0})
+        fail("the accumulator must be loaded from block index * tile extent");
+      out.clear = false;
+    } else if (opClear) {
+      out.clear = true;   // a single tile, cleared by the reduce itself
+    } else {
+      fail("the accumulator is neither filled nor loaded before it is folded into");
+    }
+    if ((fill || preload) && opClear) fail("the reduce clears the accumulator that was just set");
+    out.shape = shape;
+    out.dim = dim;
+    out.elem = gx->element;
+    out.tile = {T[0], T[1]};
+    out.grid = grid[0];
     out.ok = true;
   } catch (const Fail& f) {
     out.ok = false;

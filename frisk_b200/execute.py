@@ -1,7 +1,7 @@
 """Running the ``frisk.gemm`` and ``frisk.reduce`` ops of a module: the step the reference stops
 short of.
 
-Three forms are executed, all through libfrisk_b200 on the buffers bound to the kernel arguments:
+Four forms are executed, all through libfrisk_b200 on the buffers bound to the kernel arguments:
 
 * a ``frisk.reduce`` whose source and destination are kernel arguments in the GLOBAL memory space:
   one whole-buffer reduce per op, in program order with the gemms (so a gemm followed by a row
@@ -15,7 +15,12 @@ Three forms are executed, all through libfrisk_b200 on the buffers bound to the 
   two ``frisk.copy`` and a ``frisk.gemm`` on the tiles, and copies the accumulator out.  The
   program is checked to be exactly that product (``frisk_ffi.ir.frisk.lift_tiled_gemm``) and run as
   ONE GEMM over the kernel's arguments: tile sizes, staging and grid are the B200 back end's own
-  choice, so the copy / fill / for / parallel ops are recognised, not interpreted one by one.
+  choice, so the copy / fill / for / parallel ops are recognised, not interpreted one by one;
+* the tile-by-tile fold of a matrix -- a one-dimensional ``frisk.parallel`` grid whose body walks a
+  row (or column) block of a GLOBAL argument in tiles, ``frisk.reduce``-ing each tile into a
+  rank-1 accumulator buffer, as the reference's online-softmax sketch does for its row maximum
+  (tmp/ir.mlir:22-36) -- recognised the same way (``lift_tiled_reduce``) and run as ONE
+  whole-buffer reduce.
 
 Anything else around a gemm is refused with the reason; there is no CPU path.
 """
@@ -123,7 +128,13 @@ def find_gemms(module, kernel_name: str) -> list:
         try:
             t = ir.frisk.lift_tiled_gemm(kernel)
         except ValueError as e:
-            raise R.FriskError(-2, f"{whole_problem_error}; and the kernel is {e}") from None
+            # ... or the tile-by-tile fold of a matrix (no gemm in it)
+            try:
+                r = ir.frisk.lift_tiled_reduce(kernel)
+            except ValueError as e2:
+                raise R.FriskError(-2, f"{whole_problem_error}; and the kernel is {e}; and {e2}") from None
+            return [ReduceCall(tuple(r["shape"]), r["dim"], _dtype_of(r["type"]), r["kind"], r["clear"],
+                               r["arg_src"], r["arg_dst"])]
         lifted = [GemmCall(t["M"], t["N"], t["K"], _dtype_of(t["ab_type"]), _dtype_of(t["c_type"]),
                            False, False, t["clear_accum"], t["arg_a"], t["arg_b"], t["arg_c"])]
         if "arg_r" in t:  # the tile program folds the accumulator's rows: a reduce of C behind the gemm

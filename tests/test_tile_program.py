@@ -221,3 +221,80 @@ def test_gemm_then_row_reduce_is_fused_and_matches_the_two_ops(dtype, dims, kind
     assert X.LAST_RUN == [("gemm", "simt"), ("reduce", "reduce")]
     want, mag = ref.ref_reduce(c32, 1, W.F32, kind)
     assert (np.abs(d32 - want) <= (0.0 if kind != "add" else 1e-5 * mag + 2.0 ** -23 * np.abs(want))).all()
+
+
+# ---- the tile-by-tile fold of a matrix (the reduce of the reference's online-softmax sketch) ----
+from tile_programs import build_tiled_reduce
+
+
+def test_tiled_reduce_lifts_to_one_whole_buffer_reduce():
+    from frisk_b200 import execute as X
+    # the sketch's shape (tmp/ir.mlir:22-36): 8192 rows, tiles of 1024 columns, one row per block
+    m = build_tiled_reduce(8192, 8192, 1, 1024, kind="max")
+    assert m.verify(), m.verify_message()
+    text = str(m)
+    assert "frisk.parallel (%arg2) = (8192), threads = 128" in text
+    assert "frisk.fill %1 {value = 0xFC00 : f16}" in text          # -inf, printed as MLIR prints it
+    assert 'frisk.reduce %0, %1 {clear = false, dim = 1 : i64, kind = "max"}' in text
+    t = F.ir.frisk.lift_tiled_reduce(m.get_kernel("fold"))
+    assert (t["shape"], t["dim"], t["kind"], t["clear"]) == ([8192, 8192], 1, "max", True)
+    assert (t["arg_src"], t["arg_dst"], t["tile"], t["grid"]) == (0, 1, [1, 1024], 8192)
+    for module in (m, F.parse_module(text)):                        # as built, and read back from text
+        assert X.find_gemms(module, "fold") == [X.ReduceCall((8192, 8192), 1, W.F16, "max", True, 0, 1)]
+    assert str(F.parse_module(text)) == text
+
+
+@pytest.mark.parametrize("kw,want", [
+    (dict(R=4096, C=256, TR=512, TC=64, dim=0, kind="add", dtype="fp32"), ((4096, 256), 0, W.F32, "add", True)),
+    (dict(R=256, C=4096, TR=32, TC=1024, kind="min", dtype="bf16", start="load"), ((256, 4096), 1, W.BF16, "min", False)),
+    (dict(R=256, C=4096, TR=32, TC=4096, kind="mul", loop=False, start="reduce_clears"), ((256, 4096), 1, W.F16, "mul", True)),
+    (dict(R=64, C=512, TR=64, TC=512, dim=0, kind="max", loop=False, start="fill"), ((64, 512), 0, W.F16, "max", True)),
+])
+def test_tiled_reduce_variants_lift(kw, want):
+    from frisk_b200 import execute as X
+    m = build_tiled_reduce(**kw)
+    assert m.verify(), m.verify_message()
+    assert X.find_gemms(m, "fold") == [X.ReduceCall(*want, 0, 1)]
+
+
+@pytest.mark.parametrize("tweak,reason", [
+    ("grid_short", "cover the source exactly"),
+    ("result_off", "must land at block index"),
+    ("fill_other", "identity of the reduce kind"),
+    ("reduce_clears_in_loop", "only the last tile would count"),
+    ("gap", "consecutive tiles"),
+    ("extra_fill", "unexpected frisk.fill in the loop"),
+    ("no_store", "not copied out"),
+])
+def test_tiled_reduce_refusals_name_the_reason(tweak, reason):
+    m = build_tiled_reduce(256, 4096, 32, 1024, tweak=tweak)
+    with pytest.raises(ValueError, match=reason):
+        F.ir.frisk.lift_tiled_reduce(m.get_kernel("fold"))
+    with pytest.raises(R.FriskError, match="not a tiled reduce"):
+        F.find_gemms(m, "fold")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kw", [
+    dict(R=2048, C=4096, TR=1, TC=1024, kind="max", dtype="fp16"),
+    dict(R=4096, C=1024, TR=512, TC=64, dim=0, kind="add", dtype="fp32"),
+    dict(R=512, C=2048, TR=32, TC=512, kind="min", dtype="bf16", start="load"),
+])
+def test_tiled_reduce_runs_and_matches_the_oracle(kw):
+    from frisk_b200 import execute as X
+    from oracle import ref
+    dt = {"fp16": W.F16, "bf16": W.BF16, "fp32": W.F32}[kw["dtype"]]
+    dim, kind = kw.get("dim", 1), kw["kind"]
+    m = build_tiled_reduce(**kw)
+    rng = np.random.default_rng(kw["R"] + kw["C"])
+    x = W.encode(rng.standard_normal((kw["R"], kw["C"])).astype(np.float32), dt)
+    init = W.encode(rng.standard_normal(x.shape[1 - dim]).astype(np.float32), dt)
+    dst = init.copy()
+    F.run(m, "fold", [x, dst])
+    assert X.LAST_RUN == [("reduce", "reduce")]
+    clear = kw.get("start", "fill") != "load"
+    want, mag = ref.ref_reduce(x, dim, dt, kind, clear, init)
+    err = np.abs(W.decode(dst, dt).astype(np.float64) - want)
+    ulp = {W.F32: 2.0 ** -23, W.F16: 2.0 ** -10, W.BF16: 2.0 ** -7}[dt]
+    tol = 0.0 if kind in ("min", "max") else 1e-5 * mag + ulp * np.abs(want)
+    assert (err <= tol).all(), float(err.max())

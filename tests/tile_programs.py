@@ -75,3 +75,66 @@ def build_tiled_matmul(M, N, K, TM, TN, TK, dtype="fp16", accumulate=False, kste
         row_map = F.AffineMap.get(1, 0, [d0 * c(TM if tweak != "reduce_rows_off" else TM + 1)], ctx)
         b.create_copy_op(rt, Rg, [], [by], zero1, row_map, [TM], [TM])
     return module
+
+
+def build_tiled_reduce(R, C, TR, TC, kind="max", dim=1, dtype="fp16", start="fill", loop=True, tweak=None):
+    """The tile-by-tile fold of the reference's online-softmax sketch (tmp/ir.mlir:22-36: a
+    frisk.parallel over the rows, a frisk.for over tiles of the row, frisk.copy into a fragment,
+    frisk.reduce of the fragment) with the ops the builder has: a [R, C] GLOBAL source reduced over
+    `dim` into a GLOBAL vector.  `start`: "fill" (the accumulator starts at the kind's identity),
+    "load" (it starts from the destination: clear = false for the whole reduce), "reduce_clears"
+    (single tile, the reduce op clears)."""
+    ctx = F.context()
+    F.frisk.load_dialects(ctx)
+    b = F.builder(ctx)
+    module = b.create_module()
+    module.context = ctx
+    ty = {"fp16": b.get_f16_ty, "bf16": b.get_bf16_ty, "fp32": b.get_f32_ty}[dtype]()
+    mk = lambda shape: b.get_memref_ty(ty, shape, F.AffineMap(), F.MemorySpace.GLOBAL)
+    keep = 1 - dim
+    shape, T = [R, C], [TR, TC]
+    kernel = b.create_kernel_op(module, "fold", b.get_kernel_ty([mk(shape), mk([shape[keep]])]))
+    module.push_back(kernel)
+    entry = kernel.add_entry_block()
+    b.set_insertion_point_to_start(entry)
+    X, Y = entry.get_argument(0), entry.get_argument(1)
+    grid = shape[keep] // T[keep] - (1 if tweak == "grid_short" else 0)
+    par = b.create_parallel_op([grid], 128)
+    body = par.add_entry_block()
+    b.set_insertion_point_to_start(body)
+    blk = body.get_argument(0)
+    x = b.create_alloc_buffer_op(T, dtype, F.MemorySpace.LOCAL).get_result(0)
+    m = b.create_alloc_buffer_op([T[keep]], dtype, F.MemorySpace.LOCAL).get_result(0)
+    d0, d1 = b.get_affine_dim_expr(0), b.get_affine_dim_expr(1)
+    c = b.get_affine_constant_expr
+    zero2 = F.AffineMap.get(0, 0, [c(0), c(0)], ctx)
+    zero1 = F.AffineMap.get(0, 0, [c(0)], ctx)
+    place = F.AffineMap.get(1, 0, [d0 * c(T[keep] + (1 if tweak == "result_off" else 0))], ctx)
+    identity = {"add": 0.0, "mul": 1.0, "min": float("inf"), "max": float("-inf")}[kind]
+    if start == "fill":
+        b.create_fill_op(m, 0.5 if tweak == "fill_other" else identity, dtype)
+    elif start == "load":
+        b.create_copy_op(Y, m, [blk], [], place, zero1, [T[keep]], [T[keep]])
+    op_clear = start == "reduce_clears" or tweak == "reduce_clears_in_loop"
+
+    def tile(iv):
+        # the source tile: the kept dimension follows the block index, the reduced one the loop
+        step = T[dim] * (2 if tweak == "gap" else 1)
+        if iv is None:
+            exprs = [d0 * c(T[keep]), c(0)] if dim == 1 else [c(0), d0 * c(T[keep])]
+            src_map, idx = F.AffineMap.get(1, 0, exprs, ctx), [blk]
+        else:
+            exprs = [d0 * c(T[0]), d1 * c(step)] if dim == 1 else [d1 * c(step), d0 * c(T[1])]
+            src_map, idx = F.AffineMap.get(2, 0, exprs, ctx), [blk, iv]
+        b.create_copy_op(X, x, idx, [], src_map, zero2, T, T)
+        if tweak == "extra_fill":
+            b.create_fill_op(x, 0.0, dtype)
+        b.create_reduce_op(x, m, kind, dim, op_clear)
+
+    if loop:
+        b.create_for_op(0, shape[dim] // T[dim], 1, lambda _, iv: tile(iv))
+    else:
+        tile(None)
+    if tweak != "no_store":
+        b.create_copy_op(m, Y, [], [blk], zero1, place, [T[keep]], [T[keep]])
+    return module

@@ -680,19 +680,20 @@ int launch_finalize_t(const frisk_gemm_plan* pl, float* ws, void* C, const float
   return FRISK_OK;
 }
 
-// One operand of a 3xTF32 plan (`mn` x `k` logically) into its three K segments, K innermost.
+// One operand of a 3xTF32 plan (`mn` x `k` logically) into its two K segments of `seg` columns
+// (k rounded up to a k-block), K innermost.
 // `k_along_rows`: the source is stored [k, mn] (mn contiguous) and is transposed on the way.
-int launch_tf32_split(const float* src, float* dst, int64_t mn, int64_t k, int64_t ld_src,
+int launch_tf32_split(const float* src, float* dst, int64_t mn, int64_t k, int64_t seg, int64_t ld_src,
                       int64_t ld_dst, bool k_along_rows, uint32_t lo_mask, int sm_count,
                       cudaStream_t st) {
   if (k_along_rows) {
-    const dim3 grid((unsigned)((mn + 31) / 32), (unsigned)((k + 31) / 32));
+    const dim3 grid((unsigned)((mn + 31) / 32), (unsigned)(seg / 32));
     if (grid.y > 65535) return FRISK_ERR_UNSUPPORTED;
-    frisk::tf32_split_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(src, dst, k, mn, ld_src, ld_dst, lo_mask);
+    frisk::tf32_split_transpose_kernel<<<grid, dim3(32, 8), 0, st>>>(src, dst, k, mn, seg, ld_src, ld_dst, lo_mask);
   } else {
-    const int64_t work = mn * ((k + 3) / 4);
+    const int64_t work = mn * (seg / 4);
     const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, 8 * (int64_t)sm_count));
-    frisk::tf32_split_kernel<<<blocks, 256, 0, st>>>(src, dst, mn, k, ld_src, ld_dst, 1, lo_mask);
+    frisk::tf32_split_kernel<<<blocks, 256, 0, st>>>(src, dst, mn, k, seg, ld_src, ld_dst, lo_mask);
   }
   FRISK_CUDA(cudaGetLastError());
   return FRISK_OK;
@@ -832,12 +833,14 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       return d.a_type == FRISK_DT_F32 ? FRISK_ERR_MISALIGNED : FRISK_ERR_UNSUPPORTED;
     }
     frisk_gemm_desc& k = pl->kd;
-    k.K = 3 * d.K;
-    // A' is [M, 3K] and B' is [N, 3K], K innermost (kind::tf32 reads 32-bit operands K-inner
-    // only), rows padded to a 16-byte multiple, whatever the order A and B are stored in
+    // A' = [A_lo | A_hi] is [M, 2 Ks] and B' = [B_hi | B_lo] is [N, 2 Ks], K innermost (kind::tf32
+    // reads 32-bit operands K-inner only) whatever the order A and B are stored in, Ks = K rounded
+    // up to a k-block of 32; the kernel walks 3 Ks of K (tf32_split.cuh)
+    const int64_t ks = (d.K + 31) / 32 * 32;
+    k.K = 3 * ks;
     k.transA = 0;
     k.transB = 1;
-    k.lda = k.ldb = (3 * d.K + 3) / 4 * 4;
+    k.lda = k.ldb = 2 * ks;
     k.force_kernel = 0;
     pl->tf32 = true;
     pl->tf32_a_bytes = ((size_t)d.M * k.lda * sizeof(float) + 255) / 256 * 256;
@@ -849,6 +852,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       delete pl;
       return rc;
     }
+    pl->gp.seg_kb = (uint32_t)(ks / 32);
     pl->info.kernel = FRISK_KERNEL_TF32X3;
     pl->info.launches = 3;   // the split of A, the split of B, the GEMM
     pl->ws_bytes = pl->tf32_a_bytes + pl->tf32_b_bytes;
@@ -1017,16 +1021,17 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     float* a3 = reinterpret_cast<float*>(workspace);
     float* b3 = reinterpret_cast<float*>(static_cast<char*>(workspace) + pl->tf32_a_bytes);
     const frisk_gemm_desc& k = pl->kd;
-    // A' = [A_lo | A_hi | A_hi], B' = [B_hi ; B_lo ; B_hi] along K: small terms first
-    int rc = launch_tf32_split(static_cast<const float*>(A), a3, d.M, d.K, d.lda, k.lda,
+    // A' = [A_lo | A_hi], B' = [B_hi | B_lo] along K
+    const int64_t ks = k.K / 3;
+    int rc = launch_tf32_split(static_cast<const float*>(A), a3, d.M, d.K, ks, d.lda, k.lda,
                                /*k_along_rows=*/d.transA != 0, 0x1u, pl->sm_count, st);
     if (rc) return rc;
-    rc = launch_tf32_split(static_cast<const float*>(B), b3, d.N, d.K, d.ldb, k.ldb,
+    rc = launch_tf32_split(static_cast<const float*>(B), b3, d.N, d.K, ks, d.ldb, k.ldb,
                            /*k_along_rows=*/d.transB == 0, 0x2u, pl->sm_count, st);
     if (rc) return rc;
     frisk::GemmParams g = pl->gp;
-    OperandView va{a3, k.M, k.K, k.lda, k.transA != 0};
-    OperandView vb{b3, k.N, k.K, k.ldb, k.transB == 0};
+    OperandView va{a3, k.M, 2 * ks, k.lda, k.transA != 0};
+    OperandView vb{b3, k.N, 2 * ks, k.ldb, k.transB == 0};
     rc = encode_operand_map(&pl->tmap_a, va, FRISK_DT_F32, g.a.box_mn, g.bk_elems, pl->lay_a.swizzle_bytes);
     if (rc) return rc;
     rc = encode_operand_map(&pl->tmap_b, vb, FRISK_DT_F32, g.b.box_mn, g.bk_elems, pl->lay_b.swizzle_bytes);

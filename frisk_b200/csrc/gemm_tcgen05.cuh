@@ -97,6 +97,7 @@ struct GemmParams {
   uint32_t tmem_cols;  // power of two >= 32
   uint32_t rows, cols; // extent of D
   uint32_t tiles_r, tiles_c, num_kb;
+  uint32_t seg_kb;     // 3xTF32 plans: k-blocks per K segment (num_kb = 3 * seg_kb)
   uint32_t group_r;    // tile rasterisation: rows of tiles walked together (bands) ...
   uint32_t group_c;    // ... or, when not 0, columns of tiles walked together (panels)
   uint32_t l2_hints;   // bit 0: a-role loads evict-first in L2, bit 1: b-role loads evict-last
@@ -979,7 +980,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             FRISK_STAMP(tr_on && ptx::elect_one(), 256 + 4 * issued);
             const uint32_t a_dst = tiles_base + stage * stage_bytes;
             const uint32_t b_dst = a_dst + a_stage_bytes;
-            const int32_t k0 = (int32_t)(kb * bk_elems);
+            // (3xTF32: the k-blocks of segment 0 read A_lo B_hi, of segment 1 A_hi B_lo, of segment 2
+            // A_hi B_hi, out of A' = [lo | hi] and B' = [hi | lo])
+            int32_t k0 = (int32_t)(kb * bk_elems), k0b = k0;
+            if (kTf32) {
+              const uint32_t seg = kb / p.seg_kb, kk = kb - seg * p.seg_kb;
+              k0 = (int32_t)(((seg == 0u ? 0u : p.seg_kb) + kk) * bk_elems);
+              k0b = (int32_t)(((seg == 1u ? p.seg_kb : 0u) + kk) * bk_elems);
+            }
             for (uint32_t bx = 0; bx < a_boxes; ++bx) {
               const int32_t mn = r0 + (int32_t)(bx * a_box_mn);
               const int32_t x = a_mn_major ? mn : k0, y = a_mn_major ? k0 : mn;
@@ -988,7 +996,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             FRISK_STAMP(tr_on && ptx::elect_one(), 256 + 4 * issued + 1);
             for (uint32_t bx = 0; bx < b_boxes; ++bx) {
               const int32_t mn = c0 + (int32_t)(bx * b_box_mn);
-              const int32_t x = b_mn_major ? mn : k0, y = b_mn_major ? k0 : mn;
+              const int32_t x = b_mn_major ? mn : k0b, y = b_mn_major ? k0b : mn;
               if (ptx::elect_one()) ptx::tma_load_2d(b_dst + bx * b_box_bytes, &tmap_b, full, x, y);
             }
           }

@@ -6,10 +6,11 @@
 // |x - hi - lo| <= 2^-21 |x|.  Then
 //     A B  =  A_lo B_hi + A_hi B_lo + A_hi B_hi   (+ A_lo B_lo, dropped: <= 2^-20 |a||b| per product)
 // with every product exact in the tensor core's fp32 accumulator.  The three products run as ONE
-// ordinary GEMM over a K three times as long: a pass over A and B writes
-//     A' = [A_lo | A_hi | A_hi]  (along K)      B' = [B_hi ; B_lo ; B_hi]  (along K)
-// into a workspace (small terms first), both with K innermost whatever the order A and B are
-// stored in, and the tensor-core kernels run on A' and B' unchanged.
+// GEMM over a K three times as long.  A pass over A and B writes, K innermost whatever the order
+// A and B are stored in and every segment padded with zeros to a whole k-block of 32,
+//     A' = [A_lo | A_hi]  (along K)      B' = [B_hi | B_lo]  (along K)
+// into a workspace, and the kernels' producers read the k-blocks of the first third of that K from
+// (A_lo, B_hi), of the second from (A_hi, B_lo), of the last from (A_hi, B_hi): small terms first.
 // Because hi and lo are exact tf32 numbers the result does not depend on whether the hardware
 // truncates or rounds fp32 operands to tf32.
 #pragma once
@@ -22,28 +23,27 @@ __device__ __forceinline__ float tf32_trunc(float x) {
   return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
 }
 
-// src: rows x cols fp32, pitch ld_src.  dst: the three K segments of the operand, each a copy of
-// the matrix as hi or lo parts (`lo_mask` bit s = segment s holds lo).  K runs along the columns
-// (k_cols = 1: segment s starts at column s * cols) or along the rows (k_cols = 0: at row
-// s * rows); pitch ld_dst.  One thread handles four consecutive columns (a 16-byte load when the
-// row allows it).
+// src: rows x cols fp32 (cols = K), pitch ld_src.  dst: the two K segments of the operand side by
+// side in every row, each `seg_cols` wide (K rounded up to a k-block, the tail zero): segment s
+// holds the lo parts when bit s of `lo_mask` is set, else the hi parts.  Pitch ld_dst, a multiple
+// of four like seg_cols.  One thread handles four consecutive columns (a 16-byte load when the
+// source row allows it, 16-byte stores always).
 __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict__ src,
                                                          float* __restrict__ dst, int64_t rows,
-                                                         int64_t cols, int64_t ld_src,
-                                                         int64_t ld_dst, int k_cols,
+                                                         int64_t cols, int64_t seg_cols,
+                                                         int64_t ld_src, int64_t ld_dst,
                                                          uint32_t lo_mask) {
-  const int64_t quads = (cols + 3) >> 2;
+  const int64_t quads = seg_cols >> 2;
   const int64_t total = rows * quads;
-  const bool vec = ((ld_src | ld_dst | (k_cols ? cols : 0)) & 3) == 0 &&
-                   ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0;
-  const int64_t seg_stride = k_cols ? cols : rows * ld_dst;
+  const bool vec = (ld_src & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / quads, c = (i - r * quads) << 2;
     const float* s = src + r * ld_src + c;
     float* d = dst + r * ld_dst + c;
     float x[4], h[4], l[4];
-    const int n = (int)(cols - c < 4 ? cols - c : 4);
+    const int64_t left = cols - c;
+    const int n = (int)(left < 0 ? 0 : left < 4 ? left : 4);
     if (vec && n == 4) {
       const float4 t = __ldcs(reinterpret_cast<const float4*>(s));
       x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
@@ -56,28 +56,23 @@ __global__ void __launch_bounds__(256) tf32_split_kernel(const float* __restrict
       l[j] = tf32_trunc(x[j] - h[j]);
     }
 #pragma unroll
-    for (int seg = 0; seg < 3; ++seg) {
+    for (int seg = 0; seg < 2; ++seg) {
       const float* v = (lo_mask >> seg) & 1u ? l : h;
-      float* o = d + seg * seg_stride;
-      if (vec && n == 4) {
-        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
-      } else {
-        for (int j = 0; j < n; ++j) o[j] = v[j];
-      }
+      *reinterpret_cast<float4*>(d + seg * seg_cols) = make_float4(v[0], v[1], v[2], v[3]);
     }
   }
 }
 
 // The same split for an operand stored with K along its ROWS (A stored [K, M], B stored [K, N]):
 // kind::tf32 takes its operands K-inner only (an M/N-inner tile of 32-bit elements reads as
-// zeros), so the three segments are written transposed, dst[mn, s * K + k], through a 32 x 32
-// tile in shared memory (reads coalesced along M/N, writes along K).  grid = (ceil(mn / 32),
-// ceil(K / 32)), block = (32, 8).
+// zeros), so the two segments are written transposed, dst[mn, s * seg_cols + k] with
+// seg_cols = K rounded up to 32 and zeros behind K, through a 32 x 32 tile in shared memory (reads
+// coalesced along M/N, writes along K).  grid = (ceil(mn / 32), ceil(K / 32)), block = (32, 8).
 __global__ void __launch_bounds__(256) tf32_split_transpose_kernel(const float* __restrict__ src,
                                                                    float* __restrict__ dst,
                                                                    int64_t k_rows, int64_t mn_cols,
-                                                                   int64_t ld_src, int64_t ld_dst,
-                                                                   uint32_t lo_mask) {
+                                                                   int64_t seg_cols, int64_t ld_src,
+                                                                   int64_t ld_dst, uint32_t lo_mask) {
   __shared__ float tile[32][33];
   const int64_t mn0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
   for (int r = threadIdx.y; r < 32; r += 8) {
@@ -87,12 +82,12 @@ __global__ void __launch_bounds__(256) tf32_split_transpose_kernel(const float* 
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += 8) {
     const int64_t mn = mn0 + r, k = k0 + threadIdx.x;
-    if (mn < mn_cols && k < k_rows) {
+    if (mn < mn_cols) {   // k < seg_cols always; the tile holds zeros behind K
       const float x = tile[threadIdx.x][r];
       const float h = tf32_trunc(x), l = tf32_trunc(x - h);
       float* o = dst + mn * ld_dst + k;
 #pragma unroll
-      for (int seg = 0; seg < 3; ++seg) o[seg * k_rows] = (lo_mask >> seg) & 1u ? l : h;
+      for (int seg = 0; seg < 2; ++seg) o[seg * seg_cols] = (lo_mask >> seg) & 1u ? l : h;
     }
   }
 }

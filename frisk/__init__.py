@@ -7,6 +7,6 @@ from frisk_b200.frisk_ffi.ir import *  # noqa: F401,F403
 from frisk_b200.frisk_ffi import ir  # noqa: F401
 from frisk_b200.common.utils import FriskHelper, create_context, create_session  # noqa: F401
 from frisk_b200 import runtime  # noqa: F401
-from frisk_b200.execute import find_gemms, parse_module, run  # noqa: F401
+from frisk_b200.execute import FriskWarning, find_gemms, parse_module, run  # noqa: F401
 
 __all__ = [name for name in globals().keys() if not name.startswith("_")]

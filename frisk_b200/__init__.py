@@ -12,7 +12,7 @@ from . import workloads  # noqa: F401
 
 _HELPERS = {"FriskHelper": ".common.utils", "create_context": ".common.utils",
             "create_session": ".common.utils", "find_gemms": ".execute", "run": ".execute",
-            "parse_module": ".execute"}
+            "parse_module": ".execute", "FriskWarning": ".execute"}
 
 
 def __getattr__(name):

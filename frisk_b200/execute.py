@@ -22,10 +22,21 @@ Four forms are executed, all through libfrisk_b200 on the buffers bound to the k
   (tmp/ir.mlir:22-36) -- recognised the same way (``lift_tiled_reduce``) and run as ONE
   whole-buffer reduce.
 
-Anything else around a gemm is refused with the reason; there is no CPU path.
+A gemm or reduce on anything but kernel arguments, outside those two tile programs, is refused
+with the reason; there is no CPU path.
+
+Only ``frisk.gemm`` and ``frisk.reduce`` are executed, each once, in program order.  The loops,
+blocks, fills and copies that the reference's flagship script wraps around its whole-problem gemm
+(test/python/bind_test.py:29-53: the gemm sits inside parallel / for / block ops and next to a fill
+and a copy of the same kernel arguments) are builder exercises, not a meaning this back end could
+execute; they are not run.  A ``frisk.fill`` or ``frisk.copy`` that touches a kernel argument is
+therefore reported: ``run`` raises a ``FriskWarning`` naming every such op (``SKIPPED`` lists them),
+so that a program which relies on, say, clearing C with a fill before an accumulating gemm does not
+go wrong silently -- fill or copy the bound buffers on the host instead.
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
@@ -64,6 +75,14 @@ class ReduceCall:
     arg_dst: int
 
 
+class FriskWarning(UserWarning):
+    """An op of the kernel that touches a kernel argument was not executed."""
+
+
+# fills and copies of kernel arguments the last `find_gemms` walked past: (op name, argument indices)
+SKIPPED: List[tuple] = []
+
+
 def _dtype_of(ty) -> int:
     s = str(ty)
     table = {"f32": W.F32, "f16": W.F16, "bf16": W.BF16, "f8E4M3FN": W.E4M3}
@@ -79,8 +98,15 @@ def find_gemms(module, kernel_name: str) -> list:
         raise KeyError(f"no frisk.kernel named {kernel_name!r} in the module")
     args = {kernel.arg(i).id(): i for i in range(kernel.get_num_arguments())}
     calls: list = []
+    del SKIPPED[:]
 
     def visit(op):
+        if op.get_name() in ("frisk.fill", "frisk.copy"):
+            touched = [args[v.id()] for v in (op.get_operand(i) for i in range(op.get_num_operands()))
+                       if v.id() in args]
+            if touched:
+                SKIPPED.append((op.get_name(), tuple(touched)))
+            return
         r = op.to_reduce_op()
         if r is not None:
             src, dst = r.get_src_memref(), r.get_dst_memref()
@@ -133,8 +159,10 @@ def find_gemms(module, kernel_name: str) -> list:
                 r = ir.frisk.lift_tiled_reduce(kernel)
             except ValueError as e2:
                 raise R.FriskError(-2, f"{whole_problem_error}; and the kernel is {e}; and {e2}") from None
+            del SKIPPED[:]
             return [ReduceCall(tuple(r["shape"]), r["dim"], _dtype_of(r["type"]), r["kind"], r["clear"],
                                r["arg_src"], r["arg_dst"])]
+        del SKIPPED[:]   # in a lifted tile program the copies ARE the program
         lifted = [GemmCall(t["M"], t["N"], t["K"], _dtype_of(t["ab_type"]), _dtype_of(t["c_type"]),
                            False, False, t["clear_accum"], t["arg_a"], t["arg_b"], t["arg_c"])]
         if "arg_r" in t:  # the tile program folds the accumulator's rows: a reduce of C behind the gemm
@@ -170,6 +198,9 @@ def run(module, kernel_name: str, buffers: Sequence[np.ndarray], *, scale_a: Opt
         raise R.FriskError(-1, "module does not verify: " + module.verify_message())
     del LAST_RUN[:]
     calls = find_gemms(module, kernel_name)
+    if SKIPPED:
+        what = ", ".join(f"{name} of argument{'s' if len(a) > 1 else ''} {', '.join(map(str, a))}" for name, a in SKIPPED)
+        warnings.warn(f"not executed (only frisk.gemm and frisk.reduce run): {what}", FriskWarning, stacklevel=2)
     skip = set()
     for i, call in enumerate(calls):
         if i in skip:

@@ -298,3 +298,48 @@ def test_tiled_reduce_runs_and_matches_the_oracle(kw):
     ulp = {W.F32: 2.0 ** -23, W.F16: 2.0 ** -10, W.BF16: 2.0 ** -7}[dt]
     tol = 0.0 if kind in ("min", "max") else 1e-5 * mag + ulp * np.abs(want)
     assert (err <= tol).all(), float(err.max())
+
+
+def test_fills_and_copies_of_kernel_arguments_are_reported_not_silently_dropped():
+    """Only gemm and reduce ops are executed; a fill or copy that touches a kernel argument is
+    named in a FriskWarning (the reference's flagship module has both next to its gemm)."""
+    import warnings
+    from frisk_b200 import execute as X
+    h = F.create_session()
+    _, entry = h.new_kernel("k", [h.memref_type((64, 64), "fp16")] * 3)
+    A, B, C = (entry.get_argument(i) for i in range(3))
+    h.builder.create_fill_op(C, 1.0, "fp16")          # a program that relies on this fill ...
+    h.create_gemm(A, B, C, clear_accum=False)
+    (call,) = X.find_gemms(h.module, "k")
+    assert not call.clear_accum and X.SKIPPED == [("frisk.fill", (2,))]   # ... is told that it did not run
+    import pathlib
+    flagship = F.parse_module((pathlib.Path(__file__).parent / "golden" / "bind_test_module.mlir").read_text())
+    X.find_gemms(flagship, "test_gemm")
+    assert X.SKIPPED == [("frisk.fill", (0,)), ("frisk.copy", (0, 1))]
+    # tile programs are made of copies: lifting one reports nothing
+    X.find_gemms(build_tiled_matmul(256, 256, 256, 128, 128, 32), "matmul")
+    assert X.SKIPPED == []
+    X.find_gemms(build_tiled_reduce(256, 4096, 32, 1024), "fold")
+    assert X.SKIPPED == []
+    # fills of local / shared buffers next to a whole-problem gemm are hints, not reported
+    h = F.create_session()
+    _, entry = h.new_kernel("k2", [h.memref_type((64, 64), "fp16")] * 3)
+    frag = h.alloc_buffer((8, 8), "fp16", space=F.MemorySpace.LOCAL)
+    h.builder.create_fill_op(frag, 0.0, "fp16")
+    h.create_gemm(*(entry.get_argument(i) for i in range(3)), clear_accum=True)
+    X.find_gemms(h.module, "k2")
+    assert X.SKIPPED == []
+
+
+@pytest.mark.gpu
+def test_run_warns_about_ops_it_does_not_execute():
+    h = F.create_session()
+    _, entry = h.new_kernel("k", [h.memref_type((64, 64), "fp16")] * 3)
+    A, B, C = (entry.get_argument(i) for i in range(3))
+    h.builder.create_fill_op(C, 1.0, "fp16")
+    h.create_gemm(A, B, C, clear_accum=True)
+    a = W.encode(np.eye(64, dtype=np.float32), W.F16)
+    c = np.zeros((64, 64), np.uint16)
+    with pytest.warns(F.FriskWarning, match="frisk.fill of argument 2"):
+        F.run(h.module, "k", [a, a, c])
+    assert np.array_equal(c, a)

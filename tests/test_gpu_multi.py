@@ -39,7 +39,7 @@ def _worker(rank, world, port, M, N, K, out_dir):
         full.fill_(0x7FC0)
         torch.cuda.synchronize()
         dist.barrier()
-        for epilogue in (2, 1):
+        for epilogue in (2, 1, 4):   # 128-byte pieces, per-thread stores, TMA tensor stores
             plan = R.GemmPlan(rows, N, K, W.BF16, epilogue=epilogue)
             plan.run_ex(A, B, pg.local_c, status=status, peers=pg.peer_dsts)
             torch.cuda.synchronize()
@@ -79,7 +79,7 @@ def test_two_ranks_gather_c_through_the_epilogue(tmp_path):
     mp.spawn(_worker, args=(2, port, M, N, K, str(tmp_path)), nprocs=2, join=True)
     w = W.make_workload("cfg5", M, N, K)
     whole = R.gemm_host(w).view(np.int16)   # the same product on one GPU
-    for tag in ("epi2", "epi1", "nccl"):
+    for tag in ("epi2", "epi1", "epi4", "nccl"):
         for rank in (0, 1):
             got = np.load(tmp_path / f"c_rank{rank}_{tag}.npy")
             assert np.array_equal(got, whole), f"rank {rank}, {tag}: the gathered C differs from the one-GPU product"

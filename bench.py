@@ -110,6 +110,9 @@ class ClockSampler:
         try:
             self.nvml, handle = self._nvml_handle()
             mx = self.nvml.nvmlDeviceGetMaxClockInfo(handle, self.nvml.NVML_CLOCK_SM)
+            # the first query of a kind can take tens of milliseconds: make it here, not in the loop
+            self.nvml.nvmlDeviceGetClockInfo(handle, self.nvml.NVML_CLOCK_SM)
+            self.nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
 
             def loop():
                 while not self._stop.is_set():
@@ -234,12 +237,14 @@ def out_dtype(torch, name):
 L2_BYTES = 126 * 1024 * 1024
 
 
-def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False, **plan_kw):
+def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False, graph=False, **plan_kw):
     """`steps` back-to-back launches of the plan on device-resident inputs.
 
     Returns (ms_per_step, plan info, l2 note).  With `rotate` (workloads whose operands would
     stay in L2 from one launch to the next) the launches cycle through enough copies of A, B and
     C that more than two L2 sizes of other data pass between two uses of the same copy.
+    With `graph` the same rotation is also captured into one CUDA graph and replayed
+    (info["cuda_graph_ms"], per launch): what a caller with a launch-bound loop would do.
     """
     A, B, sa, sb = device_inputs(torch, name, M, N, K, dev, seed)
     C = torch.empty((M, N), device=dev, dtype=out_dtype(torch, name))
@@ -268,6 +273,26 @@ def time_device(torch, R, name, M, N, K, steps, warmup, dev, seed, rotate=False,
     ms = e0.elapsed_time(e1) / steps
     R.check_status(status, stream)
     info = plan.info
+    if graph:
+        per_replay = copies * max(1, 24 // copies)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            cs = torch.cuda.current_stream().cuda_stream
+            for i in range(per_replay):
+                a, b, c = sets[i % copies]
+                plan.run(a, b, c, sa, sb, ws, status, cs)
+        g.replay()
+        torch.cuda.synchronize()
+        replays = max(1, steps // per_replay)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        R.check_status(status, stream)
+        info["cuda_graph_ms"] = e0.elapsed_time(e1) / (replays * per_replay)
+        info["cuda_graph_launches"] = per_replay
+        del g
     plan.close()
     note = ("inputs larger than L2" if copies == 1 else
             f"{copies} rotating copies of A, B, C ({copies * per_set >> 20} MiB) so no launch finds its operands in L2")
@@ -729,12 +754,15 @@ def main():
             ms, oinfo, l2_note = time_device(torch, R, other, m, n, k,
                                              max(args.steps, 200 if small else 10), args.warmup, dev,
                                              seed=int(other[-1]) if other.startswith("cfg") else 5,
-                                             rotate=small)
+                                             rotate=small, graph=other in ("cfg1", "cfg3"))
             r = roofline_for(other, m, n, k, ms, peaks, False, tensor_peaks)
             others[other] = {"ms": round(ms, 5), "kernel": oinfo["kernel_name"],
                              "tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 2),
                              "launches_per_step": oinfo["launches"], "roofline": r,
                              "l2": l2_note}
+            if "cuda_graph_ms" in oinfo:   # the same launches replayed from one captured CUDA graph
+                others[other]["cuda_graph"] = {"ms": round(oinfo["cuda_graph_ms"], 5),
+                                               "launches_per_graph": oinfo["cuda_graph_launches"]}
             if other == "cfg2":
                 others[other]["library_same_shape"] = library_matmul(torch, dev, m, n, k, torch.float16)
             if other == "cfg1":   # the same problem forced onto the 3xTF32 plan (three launches)

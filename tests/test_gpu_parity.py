@@ -633,6 +633,72 @@ def test_back_to_back_dependent_launches_see_each_others_results():
     f32_plan.close()
 
 
+def test_runs_are_capturable_in_a_cuda_graph_and_replay_with_new_inputs():
+    """Every launch of the library is stream-ordered work on the caller's stream, so a chain of GEMMs
+    can be captured into a CUDA graph once and replayed: CTA-pair kernel with the row fold in its
+    epilogue (two launches) -> few-row cluster plan -> few-row stream-K plan (a memset and a launch)
+    -> 3xTF32 plan (three launches).  The replay must give the bits of the same chain launched
+    directly, also after the inputs' contents have changed."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(23)
+    bf = torch.bfloat16
+    K = 512
+
+    def rnd(*shape, scale=1.0, dtype=bf):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+    x0 = rnd(512, K)
+    w0, w_wide, w_narrow = rnd(K, K, scale=K ** -0.5), rnd(K, 4096, scale=K ** -0.5), rnd(4096, 512, scale=4096 ** -0.5)
+    a32, b32 = rnd(512, 1024, dtype=torch.float32), rnd(1024, 1024, scale=1 / 32, dtype=torch.float32)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    y1 = torch.empty(512, K, device=dev, dtype=bf)
+    rowmax = torch.empty(512, device=dev, dtype=bf)
+    y2 = torch.empty(16, 4096, device=dev, dtype=bf)
+    y3 = torch.empty(16, 512, device=dev, dtype=bf)
+    y4 = torch.empty(512, 1024, device=dev, dtype=torch.float32)
+    plans = [R.GemmPlan(512, K, K, W.BF16, row_reduce="max"), R.GemmPlan(16, 4096, K, W.BF16),
+             R.GemmPlan(16, 512, 4096, W.BF16), R.GemmPlan(512, 1024, 1024, W.F32, W.F32, force_kernel="tf32x3")]
+    assert [p.info["kernel_name"] for p in plans] == ["tcgen05_pair", "skinny", "skinny", "tf32x3"]
+    assert plans[1].workspace_bytes == 0 and plans[2].workspace_bytes > 0   # clusters, then stream-K
+    wss = [torch.zeros(max(p.workspace_bytes, 256), dtype=torch.uint8, device=dev) for p in plans]
+
+    def chain(stream):
+        plans[0].run_ex(x0, w0, y1, workspace=wss[0], status=status, stream=stream, row_reduce_dst=rowmax)
+        plans[1].run(y1[:16], w_wide, y2, None, None, wss[1], status, stream)
+        plans[2].run(y2, w_narrow, y3, None, None, wss[2], status, stream)
+        plans[3].run(a32, b32, y4, None, None, wss[3], status, stream)
+
+    outs = (y1, rowmax, y2, y3, y4)
+    chain(torch.cuda.current_stream().cuda_stream)          # also loads every kernel before the capture
+    torch.cuda.synchronize()
+    want = [t.clone() for t in outs]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain(torch.cuda.current_stream().cuda_stream)
+    for t in outs:
+        t.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    R.check_status(status)
+    for got, ref_t in zip(outs, want):
+        assert torch.equal(got, ref_t)
+    # new contents in the same buffers: the replay computes on what is there now
+    x0.copy_(rnd(512, K))
+    a32.copy_(rnd(512, 1024, dtype=torch.float32))
+    graph.replay()
+    torch.cuda.synchronize()
+    replayed = [t.clone() for t in outs]
+    chain(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    R.check_status(status)
+    for got, ref_t in zip(replayed, outs):
+        assert torch.equal(got, ref_t)
+    assert not torch.equal(replayed[0], want[0])
+    for p in plans:
+        p.close()
+
+
 # ----------------------------------------------------------------------------- fp32 on tensor cores
 @pytest.mark.parametrize("M,N,K,ta,tb,clear", [
     (512, 512, 512, False, False, True),       # cfg1's shape, forced onto the 3xTF32 plan

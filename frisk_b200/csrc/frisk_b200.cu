@@ -45,9 +45,11 @@ int elem_size(int dt) {
     case FRISK_DT_F16: return 2;
     case FRISK_DT_BF16: return 2;
     case FRISK_DT_E4M3: return 1;
+    case FRISK_DT_E5M2: return 1;
     default: return 0;
   }
 }
+bool is_fp8(int dt) { return dt == FRISK_DT_E4M3 || dt == FRISK_DT_E5M2; }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -174,8 +176,8 @@ int fill_operand(frisk::OperandParams& o, frisk_tma_params& lay, bool mn_major, 
 }
 
 uint32_t make_idesc(int ab_type, bool a_mn_major, bool b_mn_major, uint32_t m, uint32_t n) {
-  uint32_t fmt = 0;  // kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3; kind::tf32: 2 = tf32
-  if (ab_type == FRISK_DT_BF16) fmt = 1;
+  uint32_t fmt = 0;  // kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = e4m3, 1 = e5m2; kind::tf32: 2 = tf32
+  if (ab_type == FRISK_DT_BF16 || ab_type == FRISK_DT_E5M2) fmt = 1;
   if (ab_type == FRISK_DT_F32) fmt = 2;
   uint32_t d = 0;
   d |= 1u << 4;  // fp32 accumulator
@@ -277,13 +279,13 @@ constexpr size_t kLaunchDynSmem = kMaxDynSmem;
 
 // Why a problem cannot take the tensor-core kernels (FRISK_TC_*; 0 = it can).
 int tcgen05_ineligible_reason(const frisk_gemm_desc& d) {
-  if (d.a_type != FRISK_DT_F16 && d.a_type != FRISK_DT_BF16 && d.a_type != FRISK_DT_E4M3)
+  if (d.a_type != FRISK_DT_F16 && d.a_type != FRISK_DT_BF16 && !is_fp8(d.a_type))
     return FRISK_TC_INPUT_TYPE;
   const int es = elem_size(d.a_type);
   if ((d.lda * es) % 16 || (d.ldb * es) % 16) return FRISK_TC_PITCH;
   if (d.M >= (1ll << 31) || d.N >= (1ll << 31) || d.K >= (1ll << 31)) return FRISK_TC_EXTENT;
   // 8-bit operands are taken K-major only (A row-major, B column-major)
-  if (d.a_type == FRISK_DT_E4M3 && (d.transA || !d.transB)) return FRISK_TC_FP8_ORDER;
+  if (is_fp8(d.a_type) && (d.transA || !d.transB)) return FRISK_TC_FP8_ORDER;
   return FRISK_TC_OK;
 }
 bool tcgen05_eligible(const frisk_gemm_desc& d) { return tcgen05_ineligible_reason(d) == FRISK_TC_OK; }
@@ -438,7 +440,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.acc_bufs = (2 * g.mi * g.tile_n <= 512) ? 2 : 1;
   g.tmem_cols = next_pow2_cols(g.acc_bufs * g.mi * g.tile_n);
   g.idesc = make_idesc(d.a_type, a_mn, b_mn, pair ? 256u : 128u, g.tile_n);
-  g.kind_f8 = d.a_type == FRISK_DT_E4M3;
+  g.kind_f8 = is_fp8(d.a_type);
   g.rows = (uint32_t)rows;
   g.cols = (uint32_t)cols;
   const uint32_t tile_rows = pair ? 256u : 128u * g.mi;
@@ -735,6 +737,7 @@ int launch_simt(const frisk_gemm_desc& d, const void* A, const void* B, void* C,
     case FRISK_DT_F16: return launch_simt_in<__half>(d, sp, st);
     case FRISK_DT_BF16: return launch_simt_in<__nv_bfloat16>(d, sp, st);
     case FRISK_DT_E4M3: return launch_simt_in<frisk::e4m3_t>(d, sp, st);
+    case FRISK_DT_E5M2: return launch_simt_in<frisk::e5m2_t>(d, sp, st);
     default: return FRISK_ERR_UNSUPPORTED;
   }
 }
@@ -788,7 +791,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return FRISK_ERR_INVALID_ARGUMENT;
   if (!elem_size(d.a_type) || !elem_size(d.b_type) || !elem_size(d.c_type))
     return FRISK_ERR_INVALID_ARGUMENT;
-  if (d.c_type == FRISK_DT_E4M3) return FRISK_ERR_UNSUPPORTED;
+  if (is_fp8(d.c_type)) return FRISK_ERR_UNSUPPORTED;
   if (d.a_type != d.b_type) return FRISK_ERR_INVALID_ARGUMENT;  // ffi/ir.cpp:357-359
   if (d.scale_mode != FRISK_SCALE_NONE && d.scale_mode != FRISK_SCALE_ROW_COL)
     return FRISK_ERR_INVALID_ARGUMENT;
@@ -1382,7 +1385,7 @@ int frisk_b200_gemm_skinny_static(const frisk_gemm_desc* desc, const void* A, co
   frisk_gemm_desc d = *desc;
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return FRISK_ERR_INVALID_ARGUMENT;
   if (!elem_size(d.a_type) || d.a_type != d.b_type || !elem_size(d.c_type) ||
-      d.c_type == FRISK_DT_E4M3)
+      is_fp8(d.c_type))
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.scale_mode != FRISK_SCALE_NONE && d.scale_mode != FRISK_SCALE_ROW_COL)
     return FRISK_ERR_INVALID_ARGUMENT;
@@ -1516,7 +1519,7 @@ int frisk_b200_measure_mma_peak(int32_t ab_type, int32_t pair, int32_t k_blocks,
     attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const uint32_t kind = ab_type == FRISK_DT_E4M3 ? 1u : ab_type == FRISK_DT_F32 ? 2u : 0u;
+    const uint32_t kind = is_fp8(ab_type) ? 1u : ab_type == FRISK_DT_F32 ? 2u : 0u;
     if (pair)
       return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<1>, (uint32_t)k_blocks, idesc, kind, es, status);
     return cudaLaunchKernelEx(&cfg, frisk::mma_peak_kernel<0>, (uint32_t)k_blocks, idesc, kind, es, status);

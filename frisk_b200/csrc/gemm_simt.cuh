@@ -32,6 +32,14 @@ __device__ __forceinline__ float cast_in<e4m3_t>(e4m3_t v) {
   return __half2float(__half(__nv_cvt_fp8_to_halfraw(v.bits, __NV_E4M3)));
 }
 
+struct e5m2_t {
+  uint8_t bits;
+};
+template <>
+__device__ __forceinline__ float cast_in<e5m2_t>(e5m2_t v) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(v.bits, __NV_E5M2)));
+}
+
 constexpr int kSimtTile = 64;
 constexpr int kSimtBK = 16;
 

@@ -85,7 +85,7 @@ SKIPPED: List[tuple] = []
 
 def _dtype_of(ty) -> int:
     s = str(ty)
-    table = {"f32": W.F32, "f16": W.F16, "bf16": W.BF16, "f8E4M3FN": W.E4M3}
+    table = {"f32": W.F32, "f16": W.F16, "bf16": W.BF16, "f8E4M3FN": W.E4M3, "f8E5M2": W.E5M2}
     if s not in table:
         raise R.FriskError(-2, f"element type {s} has no GEMM kernel")
     return table[s]
@@ -116,7 +116,7 @@ def find_gemms(module, kernel_name: str) -> list:
                                            "only whole-buffer reduces are executed")
             ty = src.get_type()
             dtype = _dtype_of(ty.get_element_ty())
-            if dtype == W.E4M3:
+            if dtype in (W.E4M3, W.E5M2):
                 raise R.FriskError(-2, "frisk.reduce has no kernel for 8-bit floats")
             calls.append(ReduceCall(tuple(ty.get_shape()), r.get_reduce_dim(), dtype, r.get_kind(),
                                     r.get_clear(), args[src.id()], args[dst.id()]))

@@ -15,9 +15,9 @@ from typing import Optional
 
 import numpy as np
 
-F32, F16, BF16, E4M3 = 0, 1, 2, 3  # frisk_dtype of include/frisk_b200.h
-DTYPE_NAMES = {F32: "fp32", F16: "fp16", BF16: "bf16", E4M3: "e4m3fn"}
-ELEM_SIZE = {F32: 4, F16: 2, BF16: 2, E4M3: 1}
+F32, F16, BF16, E4M3, E5M2 = 0, 1, 2, 3, 4  # frisk_dtype of include/frisk_b200.h
+DTYPE_NAMES = {F32: "fp32", F16: "fp16", BF16: "bf16", E4M3: "e4m3fn", E5M2: "e5m2"}
+ELEM_SIZE = {F32: 4, F16: 2, BF16: 2, E4M3: 1, E5M2: 1}
 
 
 # --------------------------------------------------------------------------- codecs
@@ -72,6 +72,28 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     return bits.astype(np.uint8)
 
 
+E5M2_MAX = 57344.0
+
+
+def e5m2_decode(q: np.ndarray) -> np.ndarray:
+    """e5m2 bits are the top byte of an IEEE half."""
+    return (np.ascontiguousarray(q, dtype=np.uint8).astype(np.uint16) << 8).view(np.float16).astype(np.float32)
+
+
+def e5m2_encode(x: np.ndarray) -> np.ndarray:
+    """float32 -> e5m2 bits, round to nearest even, saturating to +-57344 (never NaN/inf), the
+    same convention as e4m3_encode."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    a = np.minimum(np.abs(x.astype(np.float64)), E5M2_MAX)
+    a = np.where(np.isnan(a), E5M2_MAX, a)
+    # spacing of the grid around a: 2^(e-2) for normals (e >= -14), 2^-16 below
+    e = np.floor(np.log2(np.maximum(a, 2.0 ** -14)))
+    step = 2.0 ** (e - 2)
+    r = np.minimum(np.rint(a / step) * step, E5M2_MAX)   # exact in float64; rint rounds half to even
+    bits = (r.astype(np.float16).view(np.uint16) >> 8).astype(np.uint8)   # r is exact in fp16
+    return bits | (np.signbit(x).astype(np.uint8) << 7)
+
+
 def encode(x: np.ndarray, dtype: int) -> np.ndarray:
     if dtype == F32:
         return np.ascontiguousarray(x, dtype=np.float32)
@@ -81,6 +103,8 @@ def encode(x: np.ndarray, dtype: int) -> np.ndarray:
         return bf16_encode(x)
     if dtype == E4M3:
         return e4m3_encode(x)
+    if dtype == E5M2:
+        return e5m2_encode(x)
     raise ValueError(f"unknown dtype {dtype}")
 
 
@@ -93,11 +117,13 @@ def decode(x: np.ndarray, dtype: int) -> np.ndarray:
         return bf16_decode(x)
     if dtype == E4M3:
         return e4m3_decode(x)
+    if dtype == E5M2:
+        return e5m2_decode(x)
     raise ValueError(f"unknown dtype {dtype}")
 
 
 def storage_numpy_dtype(dtype: int):
-    return {F32: np.float32, F16: np.float16, BF16: np.uint16, E4M3: np.uint8}[dtype]
+    return {F32: np.float32, F16: np.float16, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8}[dtype]
 
 
 # --------------------------------------------------------------------------- workloads
@@ -267,6 +293,7 @@ TOLERANCE = {  # (metric, bound) per input type
     F16: ("max_rel", 1e-2),
     BF16: ("max_rel", 1e-2),
     E4M3: ("max_rel", 2e-2),
+    E5M2: ("max_rel", 2e-2),
 }
 
 

@@ -54,7 +54,10 @@ typedef enum {
   FRISK_DT_F32 = 0,
   FRISK_DT_F16 = 1,
   FRISK_DT_BF16 = 2,
-  FRISK_DT_E4M3 = 3 /* "e4m3fn": finite-only fp8, max 448, no inf */
+  FRISK_DT_E4M3 = 3, /* "e4m3fn": finite-only fp8, max 448, no inf */
+  FRISK_DT_E5M2 = 4  /* "e5m2": fp8 with fp16's exponent (the top byte of an fp16), max 57344;
+                        inputs of a gemm only, like e4m3 (the reference names both as buffer
+                        element types: ffi/ir.cpp:411-414, 454-457)                      */
 } frisk_dtype;
 
 typedef enum { FRISK_SCALE_NONE = 0, FRISK_SCALE_ROW_COL = 1 } frisk_scale_mode;

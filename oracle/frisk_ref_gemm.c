@@ -27,7 +27,7 @@
 #include <omp.h>
 #endif
 
-enum { REF_F32 = 0, REF_F16 = 1, REF_BF16 = 2, REF_E4M3 = 3 };
+enum { REF_F32 = 0, REF_F16 = 1, REF_BF16 = 2, REF_E4M3 = 3, REF_E5M2 = 4 };
 
 typedef struct frisk_ref_desc {
   int64_t M, N, K;
@@ -75,6 +75,10 @@ float frisk_ref_decode_e4m3(uint8_t v) {
   return sign ? -r : r;
 }
 
+/* e5m2: 1 sign, 5 exponent (bias 15), 2 mantissa -- the top byte of an IEEE half, infinities and
+ * NaNs included. */
+float frisk_ref_decode_e5m2(uint8_t v) { return frisk_ref_decode_f16((uint16_t)((uint16_t)v << 8)); }
+
 uint16_t frisk_ref_encode_bf16(float f) {
   uint32_t u = f32_as_u32(f);
   if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40u); /* quiet NaN */
@@ -113,7 +117,8 @@ static float decode_in(const void* p, int64_t i, int type) {
     case REF_F32: return ((const float*)p)[i];
     case REF_F16: return frisk_ref_decode_f16(((const uint16_t*)p)[i]);
     case REF_BF16: return frisk_ref_decode_bf16(((const uint16_t*)p)[i]);
-    default: return frisk_ref_decode_e4m3(((const uint8_t*)p)[i]);
+    case REF_E4M3: return frisk_ref_decode_e4m3(((const uint8_t*)p)[i]);
+    default: return frisk_ref_decode_e5m2(((const uint8_t*)p)[i]);
   }
 }
 
@@ -127,7 +132,7 @@ static void store_out(void* p, int64_t i, int type, float v) {
 
 static int valid_desc(const frisk_ref_desc* d) {
   if (!d || d->M <= 0 || d->N <= 0 || d->K <= 0) return 0;
-  if (d->ab_type < 0 || d->ab_type > 3 || d->c_type < 0 || d->c_type > 2) return 0;
+  if (d->ab_type < 0 || d->ab_type > 4 || d->c_type < 0 || d->c_type > 2) return 0;
   if (d->lda < (d->transA ? d->M : d->K)) return 0;
   if (d->ldb < (d->transB ? d->K : d->N)) return 0;
   if (d->ldc < d->N) return 0;

@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
         for name, arg, res in (("frisk_ref_decode_f16", C.c_uint16, C.c_float),
                                ("frisk_ref_decode_bf16", C.c_uint16, C.c_float),
                                ("frisk_ref_decode_e4m3", C.c_uint8, C.c_float),
+                               ("frisk_ref_decode_e5m2", C.c_uint8, C.c_float),
                                ("frisk_ref_encode_bf16", C.c_float, C.c_uint16),
                                ("frisk_ref_encode_f16", C.c_float, C.c_uint16)):
             f = getattr(L, name)

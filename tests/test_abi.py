@@ -121,8 +121,15 @@ def test_plan_create_rejects_bad_descriptions():
     assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -1
     assert L.frisk_b200_gemm_plan_create(None, C.byref(h)) == -1
     d.b_type = W.F16
-    d.c_type = W.E4M3
-    assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -2
+    for fp8 in (W.E4M3, W.E5M2):   # 8-bit floats are input types only
+        d.c_type = fp8
+        assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -2
+    d.a_type = d.b_type = 5        # no such type
+    d.c_type = W.F16
+    assert L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(h)) == -1
+    p5 = R.GemmPlan(512, 512, 512, W.E5M2, W.BF16, transB=True, scales=True)
+    assert p5.info["kernel_name"] == "tcgen05_pair" and p5.info["tile_k"] == 128
+    p5.close()
     with pytest.raises(R.FriskError) as e:
         R.GemmPlan(100, 100, 100, W.BF16, lda=101, force_kernel="tcgen05")
     assert e.value.code == -3
@@ -245,15 +252,15 @@ def test_planner_invariants_over_random_shapes():
     rnd = random.Random(5)
     seen = set()
     for _ in range(400):
-        ab = rnd.choice([W.F32, W.F16, W.BF16, W.E4M3])
-        ct = ab if ab != W.E4M3 else W.BF16
+        ab = rnd.choice([W.F32, W.F16, W.BF16, W.E4M3, W.E5M2])
+        ct = ab if ab not in (W.E4M3, W.E5M2) else W.BF16
         M = rnd.choice([1, 7, 16, 33, 64, 65, 100, 128, 129, 200, 256, 1000, 4096, 8192])
         N = rnd.choice([8, 64, 104, 256, 512, 1000, 2048, 4096, 8192, 28672])
         K = rnd.choice([8, 64, 72, 520, 1024, 4096, 8192])
         ta, tb = rnd.random() < 0.2, rnd.random() < 0.5
-        if ab == W.E4M3 and (ta or not tb):
+        if ab in (W.E4M3, W.E5M2) and (ta or not tb):
             ta, tb = False, True  # 8-bit inputs run on tensor cores only K-inner
-        p = R.GemmPlan(M, N, K, ab, ct, transA=ta, transB=tb, scales=ab == W.E4M3)
+        p = R.GemmPlan(M, N, K, ab, ct, transA=ta, transB=tb, scales=ab in (W.E4M3, W.E5M2))
         i = p.info
         seen.add(i["kernel_name"])
         assert i["kernel_name"] in ("simt", "tcgen05", "tcgen05_pair", "skinny", "tf32x3")

@@ -16,7 +16,7 @@ TORCH_BITS = {4: "float32", 2: "int16", 1: "uint8"}
 
 def make(M, N, K, ab, ct, ta=False, tb=False, clear=True, seed=0):
     rng = np.random.default_rng(seed + M + 7 * N + 13 * K)
-    big = ab == W.E4M3
+    big = ab in (W.E4M3, W.E5M2)
     a = (rng.standard_normal((M, K)) * (4.0 if big else 1.0)).astype(np.float32)
     b = (rng.standard_normal((K, N)) * (4.0 if big else K ** -0.5)).astype(np.float32)
     Aq, Bq = W.encode(a, ab), W.encode(b, ab)
@@ -86,6 +86,7 @@ CASES = [
     (300, 520, 136, W.F16, W.F32, False, True, True, "tcgen05_pair"),     # fp32 C: 32-column pieces
     (260, 1000, 200, W.F16, W.F16, False, False, False, "tcgen05_pair"),  # ragged rows and columns, C +=
     (384, 512, 512, W.E4M3, W.BF16, False, True, True, "tcgen05_pair"),   # scales
+    (300, 328, 272, W.E5M2, W.BF16, False, True, True, "tcgen05_pair"),   # e5m2, scales, ragged
     (128, 256, 192, W.BF16, W.BF16, True, False, True, "tcgen05"),        # one-CTA kernel
     (100, 200, 64, W.F16, W.F16, False, False, True, "tcgen05"),
     (1000, 1000, 1000, W.BF16, W.F16, False, False, True, "tcgen05_pair"),

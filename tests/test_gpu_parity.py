@@ -480,25 +480,29 @@ def test_module_built_with_the_ir_builder_executes():
         F.find_gemms(h2.module, "k")
 
 
-def test_fp8_gemm_with_scale_operands_built_through_the_ir_builder_executes():
-    """cfg4's form written as IR: e4m3 A and B (both K-inner), bf16 C, the two fp32 scale vectors
-    as the additional fourth and fifth operands of frisk.gemm, bound as kernel arguments."""
+@pytest.mark.parametrize("fp8,dt", [("e4m3fn", W.E4M3), ("e5m2", W.E5M2)])
+def test_fp8_gemm_with_scale_operands_built_through_the_ir_builder_executes(fp8, dt):
+    """cfg4's form written as IR: 8-bit float A and B (both K-inner), bf16 C, the two fp32 scale
+    vectors as the additional fourth and fifth operands of frisk.gemm, bound as kernel arguments.
+    Both 8-bit element types the reference's builder names (ffi/ir.cpp:411-414)."""
     import frisk as F
 
     w = W.make_workload("cfg4", 256, 384, 512)
+    if dt == W.E5M2:   # the same values on the other grid
+        w.A, w.B, w.ab_type = (W.encode(W.decode(w.A, W.E4M3), dt), W.encode(W.decode(w.B, W.E4M3), dt), dt)
     h = F.create_session()
     f32 = h.builder.get_f32_ty()
-    tys = [h.memref_type((w.M, w.K), "e4m3fn"), h.memref_type((w.K, w.N), "e4m3fn"),
+    tys = [h.memref_type((w.M, w.K), fp8), h.memref_type((w.K, w.N), fp8),
            h.memref_type((w.M, w.N), "bf16"), h.memref_type((w.M,), f32), h.memref_type((w.N,), f32)]
     _, entry = h.new_kernel("k", tys)
     a = [entry.get_argument(i) for i in range(5)]
     h.builder.create_gemm_op(a[0], a[1], a[2], False, True, True, a[3], a[4])
     (call,) = F.find_gemms(h.module, "k")
-    assert (call.arg_scale_a, call.arg_scale_b, call.ab_type, call.c_type) == (3, 4, W.E4M3, W.BF16)
+    assert (call.arg_scale_a, call.arg_scale_b, call.ab_type, call.c_type) == (3, 4, dt, W.BF16)
     out = np.zeros((w.M, w.N), np.uint16)
     F.run(h.module, "k", [w.A, w.B, out, w.scale_a, w.scale_b])
     assert np.array_equal(out, R.gemm_host(w))
-    ok, err, _ = W.check(W.bf16_decode(out), ref.ref_gemm_f64(w), W.E4M3, absdot=ref.abs_dot(w))
+    ok, err, _ = W.check(W.bf16_decode(out), ref.ref_gemm_f64(w), dt, absdot=ref.abs_dot(w))
     assert ok, err
 
 
@@ -522,17 +526,20 @@ FEW_ROWS = [
     (128, 8192, 512, W.F16, True, False, {}),
     (96, 512, 2048, W.BF16, False, True, {"force_kernel": "skinny"}),  # ... and their stream-K form
     (128, 2048, 1024, W.E4M3, True, True, {}),
+    (32, 4096, 1024, W.E5M2, True, True, {}),     # the other 8-bit float: scales, clusters
+    (16, 512, 4096, W.E5M2, True, False, {}),     # ... stream-K, C +=
 ]
 
 
 @pytest.mark.parametrize("M,N,K,ab,tb,clear,opts", FEW_ROWS)
 def test_few_row_plans_match_oracle(M, N, K, ab, tb, clear, opts):
     rng = np.random.default_rng(M * 131 + N + K)
-    a = (rng.standard_normal((M, K)) * (1.0 if ab != W.E4M3 else 4.0)).astype(np.float32)
-    b = (rng.standard_normal((K, N)) * (0.05 if ab != W.E4M3 else 4.0)).astype(np.float32)
-    ct = W.BF16 if ab == W.E4M3 else ab
+    fp8 = ab in (W.E4M3, W.E5M2)
+    a = (rng.standard_normal((M, K)) * (1.0 if not fp8 else 4.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (0.05 if not fp8 else 4.0)).astype(np.float32)
+    ct = W.BF16 if fp8 else ab
     sa = sb = None
-    if ab == W.E4M3:
+    if fp8:
         sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32)
         sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32)
     Bq = W.encode(b, ab)
@@ -550,12 +557,13 @@ def test_few_row_plans_match_oracle(M, N, K, ab, tb, clear, opts):
     (300, 104, 200, W.BF16, W.BF16, False, False, True),    # 128-column tiles
     (260, 520, 136, W.F16, W.F32, False, True, False),      # fp32 C, C += A x B
     (512, 768, 640, W.E4M3, W.BF16, False, True, True),     # scales
+    (520, 392, 272, W.E5M2, W.F16, False, True, False),     # e5m2 inputs, scales, fp16 C +=
     (384, 1024, 2048, W.BF16, W.F16, True, False, True),    # A stored [K, M]
     (1000, 1000, 1000, W.F16, W.F16, False, False, False),  # ragged everywhere
 ])
 def test_cta_pair_kernel_variants_match_oracle(M, N, K, ab, ct, ta, tb, clear):
     rng = np.random.default_rng(M + 7 * N + 13 * K)
-    big = ab == W.E4M3
+    big = ab in (W.E4M3, W.E5M2)
     a = (rng.standard_normal((M, K)) * (4.0 if big else 1.0)).astype(np.float32)
     b = (rng.standard_normal((K, N)) * (4.0 if big else K ** -0.5)).astype(np.float32)
     sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if big else None
@@ -570,6 +578,9 @@ def test_cta_pair_kernel_variants_match_oracle(M, N, K, ab, ct, ta, tb, clear):
     out1, info1 = run_and_check(w, force_kernel="tcgen05")
     assert info1["kernel_name"] == "tcgen05"
     assert np.array_equal(out, out1)  # same k order, same fp32 accumulation: same bits
+    if ab == W.E5M2:   # ... and the CUDA-core kernel decodes the same 8-bit format
+        _, info2 = run_and_check(w, force_kernel="simt")
+        assert info2["kernel_name"] == "simt"
 
 
 def test_back_to_back_dependent_launches_see_each_others_results():

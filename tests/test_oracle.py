@@ -33,6 +33,28 @@ def test_e4m3_encode_matches_torch_and_saturates():
     assert not np.any(np.isnan(W.e4m3_decode(mine)))
 
 
+def test_e5m2_codecs_match_torch_and_saturate():
+    """e5m2 is the top byte of an IEEE half: all 256 codes decode as torch's float8_e5m2 does (C
+    oracle and numpy alike); the encoder rounds to nearest even and saturates at +-57344."""
+    torch = pytest.importorskip("torch")
+    codes = np.arange(256, dtype=np.uint8)
+    want = torch.from_numpy(codes).view(torch.float8_e5m2).to(torch.float32).numpy()
+    got_c = np.array([ref.lib().frisk_ref_decode_e5m2(int(c)) for c in codes], dtype=np.float32)
+    for got in (got_c, W.e5m2_decode(codes)):
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert np.array_equal(got[~np.isnan(want)], want[~np.isnan(want)])
+    rng = np.random.default_rng(2)
+    x = np.concatenate([
+        (rng.standard_normal(100000) * 10.0 ** rng.integers(-6, 5, 100000)).astype(np.float32),
+        np.array([0.0, -0.0, 57344, 57345, 61439, 61440, 65536, 1e9, -1e9, 2.0 ** -16, 2.0 ** -17,
+                  1.5 * 2.0 ** -16, 2.0 ** -17 * 1.0001, 2.0 ** -14, 1.25, 1.375, 1.125], dtype=np.float32)])
+    mine = W.e5m2_encode(x)
+    want = torch.from_numpy(np.clip(x, -57344, 57344)).to(torch.float8_e5m2).view(torch.uint8).numpy()
+    assert np.array_equal(mine, want)
+    dec = W.e5m2_decode(mine)
+    assert np.all(np.abs(dec) <= 57344.0) and not np.any(np.isnan(dec))
+
+
 def test_bf16_and_f16_codecs_match_torch():
     torch = pytest.importorskip("torch")
     rng = np.random.default_rng(1)
@@ -72,6 +94,18 @@ def test_c_loop_matches_numpy_float64(name, dims):
     got64 = W.decode(ref.ref_gemm(w, acc64=True), w.c_type)
     tol = {W.F32: 1e-6, W.F16: 1e-3, W.BF16: 8e-3}[w.c_type]
     assert np.all(np.abs(got64 - want) <= tol * np.abs(want) + 1e-30)
+
+
+def test_c_loop_takes_e5m2_inputs():
+    """cfg4's form with the other 8-bit float: the C loop against numpy float64 on the decoded bits."""
+    w = W.make_workload("cfg4", 32, 64, 128)
+    w.A, w.B, w.ab_type = W.encode(W.decode(w.A, W.E4M3), W.E5M2), W.encode(W.decode(w.B, W.E4M3), W.E5M2), W.E5M2
+    got = W.decode(ref.ref_gemm(w), w.c_type)
+    want = ref.ref_gemm_f64(w)
+    ok, err, metric = W.check(got, want, W.E5M2, absdot=ref.abs_dot(w))
+    assert ok, f"{metric} = {err}"
+    got64 = W.decode(ref.ref_gemm(w, acc64=True), w.c_type)
+    assert np.all(np.abs(got64 - want) <= 8e-3 * np.abs(want) + 1e-30)
 
 
 def test_transposed_storage_and_accumulate():

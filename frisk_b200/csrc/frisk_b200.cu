@@ -87,6 +87,9 @@ struct frisk_gemm_plan {
   bool tf32 = false;
   bool tf32_pair = false;        // which whole-tile kernel runs the split problem
   size_t tf32_a_bytes = 0, tf32_b_bytes = 0;
+  // Operands whose row pitch is not a multiple of 16 bytes (no tensor map can describe them) are
+  // copied into the front of the workspace at a padded pitch (kd.lda / kd.ldb) before every run.
+  size_t repack_a_bytes = 0, repack_b_bytes = 0;
   int device = -1;
   int sm_count = 148;
   bool have_device = false;
@@ -371,10 +374,12 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     int n_cand = 0;
     for (uint32_t mi = (rows > 128 ? 2u : 1u); mi >= 1; --mi) {
       const uint32_t t = (uint32_t)((rows + 128 * mi - 1) / (128 * mi));
-      // the pushed-partials region and at least four pipeline stages have to fit beside each other
+      // the pushed-partials region and at least four pipeline stages have to fit beside each
+      // other, or the region on top of four stages (red_overlay)
       const size_t stage = (size_t)(128 * mi + g.tile_n) * 128u;
       const size_t red = (size_t)128 * mi * g.tile_n * sizeof(float);
-      if (red + 1024 + 4 * stage > kMaxDynSmem) continue;
+      if (1024 + 4 * stage > kMaxDynSmem) continue;
+      if (red + 1024 + 4 * stage > kMaxDynSmem && red > 4 * stage) continue;
       for (uint32_t s = 8; s >= 2; s >>= 1) {
         if (s > kbs || (uint64_t)t * s > (uint64_t)pl->sm_count) continue;
         if (t * s * 100u >= (uint32_t)pl->sm_count * min_cover) cand[n_cand++] = Cand{t * s, mi, s};
@@ -418,7 +423,31 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.stage_bytes = g.a.stage_bytes + g.b.stage_bytes;
   // split mode 3 keeps one fp32 tile behind the stage buffers: the region the cluster's partials
   // are pushed into
-  const size_t red_bytes = (swap && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
+  size_t red_bytes = (swap && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
+  // The region may instead lie ON the stage buffers (the kernel then holds the pushes back until
+  // every CTA of the cluster has finished its main loop): taken when that buys at least a quarter
+  // more pipeline stages -- measured, bf16 N = K = 8192: the time of a few-row plan follows the
+  // weight bytes it keeps in flight (16 rows: 47 / 30 / 25.5 / 24.5 us at 64 / 96 / 128 / 160 KiB
+  // per CTA), and from 64 rows on the region takes a third of the shared memory or more.
+  bool red_overlay = false;
+  if (red_bytes) {
+    const size_t room = kMaxDynSmem - 1024;
+    size_t st_sep = red_bytes < room ? (room - red_bytes) / g.stage_bytes : 0;
+    size_t st_ovl = room / g.stage_bytes;
+    st_sep = std::min<size_t>(st_sep, frisk::kMaxStages);
+    st_ovl = std::min<size_t>(st_ovl, frisk::kMaxStages);
+    if (d.stages > 0) {
+      st_sep = std::min<size_t>(st_sep, (size_t)d.stages);
+      st_ovl = std::min<size_t>(st_ovl, (size_t)d.stages);
+    }
+    red_overlay = red_bytes <= st_ovl * g.stage_bytes && (st_sep < 2 || 4 * st_ovl >= 5 * st_sep);
+#ifdef FRISK_B200_MEASURE
+    if (const char* e = getenv("FRISK_B200_RED_OVERLAY"))
+      red_overlay = atoi(e) != 0 && red_bytes <= st_ovl * g.stage_bytes;
+#endif
+    if (red_overlay) red_bytes = 0;
+  }
+  g.red_overlay = red_overlay ? 1u : 0u;
   // Whole-tile plans stage the rows of C through 16 KiB of shared memory behind the pipeline
   // stages and store them as 128-byte pieces (measured on bf16 8192^3 and e4m3 8192^3: five, six
   // or seven stages of 32 KiB run within 1 % of each other, so the stage this costs the CTA-pair
@@ -682,6 +711,51 @@ int launch_finalize_t(const frisk_gemm_plan* pl, float* ws, void* C, const float
   return FRISK_OK;
 }
 
+// Copies `rows` rows of `row_bytes` bytes from pitch `src_pitch` to pitch `dst_pitch` (a multiple
+// of 16, like dst itself), zero behind the end of a row.  The source may start anywhere: it is
+// read in 2-byte or 1-byte units (`unit`), the destination written 16 bytes at a time.
+__global__ void __launch_bounds__(256) repack_rows_kernel(const unsigned char* __restrict__ src,
+                                                          unsigned char* __restrict__ dst, int64_t rows,
+                                                          int64_t row_bytes, int64_t src_pitch,
+                                                          int64_t dst_pitch, int unit) {
+  const int64_t chunks = dst_pitch >> 4;
+  const int64_t total = rows * chunks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / chunks, c = (i - r * chunks) << 4;
+    const unsigned char* s = src + r * src_pitch + c;
+    union {
+      uint4 v;
+      unsigned short h[8];
+      unsigned char b[16];
+    } u;
+    u.v = make_uint4(0, 0, 0, 0);
+    const int64_t left = row_bytes - c;
+    if (left >= 16 && (reinterpret_cast<uintptr_t>(s) & 15) == 0) {
+      u.v = *reinterpret_cast<const uint4*>(s);
+    } else if (unit == 2) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (2 * j < left) u.h[j] = *reinterpret_cast<const unsigned short*>(s + 2 * j);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < left) u.b[j] = s[j];
+    }
+    *reinterpret_cast<uint4*>(dst + r * dst_pitch + c) = u.v;
+  }
+}
+
+int launch_repack(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst,
+                  int es, int sm_count, cudaStream_t st) {
+  const int64_t work = rows * (ld_dst * es / 16);
+  const int blocks = (int)std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, 8 * (int64_t)sm_count));
+  repack_rows_kernel<<<blocks, 256, 0, st>>>(static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst),
+                                             rows, cols * es, ld_src * es, ld_dst * es, es);
+  FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
 // One operand of a 3xTF32 plan (`mn` x `k` logically) into its two K segments of `seg` columns
 // (k rounded up to a k-block), K innermost.
 // `k_along_rows`: the source is stored [k, mn] (mn contiguous) and is transposed on the way.
@@ -862,6 +936,23 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     *out = pl;
     return FRISK_OK;
   }
+  // A row pitch of A or B that is not a multiple of 16 bytes rules out tensor maps on the caller's
+  // buffers, not the tensor cores: the plan copies such an operand into the workspace at a padded
+  // pitch before every run (one more launch each; the copy reads and writes the operand once,
+  // against a CUDA-core kernel about 100 x slower on the whole problem).
+  if (tcgen05_ineligible_reason(d) == FRISK_TC_PITCH && d.force_kernel != 1 + FRISK_KERNEL_SIMT) {
+    const int64_t es = elem_size(d.a_type), q = 16 / es;
+    frisk_gemm_desc& k = pl->kd;
+    if ((d.lda * es) % 16) {
+      k.lda = ((d.transA ? d.M : d.K) + q - 1) / q * q;
+      pl->repack_a_bytes = ((size_t)(d.transA ? d.K : d.M) * k.lda * es + 255) / 256 * 256;
+    }
+    if ((d.ldb * es) % 16) {
+      k.ldb = ((d.transB ? d.K : d.N) + q - 1) / q * q;
+      pl->repack_b_bytes = ((size_t)(d.transB ? d.N : d.K) * k.ldb * es + 255) / 256 * 256;
+    }
+    d = k;   // the choices below are made for the repacked problem
+  }
   const bool tc_ok = tcgen05_eligible(d);
   const bool skinny_ok = tc_ok && skinny_shape(d, pl->sm_count);
   const bool pair_ok = tc_ok && d.M > 128 && d.N > 64 && d.tile_n != 64 && pl->sm_count >= 2;
@@ -934,6 +1025,12 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     delete pl;
     return rc;
   }
+  if (pl->info.kernel == FRISK_KERNEL_SIMT) {
+    pl->repack_a_bytes = pl->repack_b_bytes = 0;   // (a forced or otherwise ineligible problem)
+    pl->kd = pl->d;
+  }
+  pl->ws_bytes += pl->repack_a_bytes + pl->repack_b_bytes;
+  pl->info.launches += (pl->repack_a_bytes ? 1 : 0) + (pl->repack_b_bytes ? 1 : 0);
   *out = pl;
   return FRISK_OK;
 }
@@ -1046,6 +1143,30 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
                          : launch_tcgen05_ts<float, false, true>(pl, g, st);
   }
 
+  // operands with an odd row pitch are copied into the front of the workspace first
+  const void *A0 = A, *B0 = B;
+  const size_t repack_bytes = pl->repack_a_bytes + pl->repack_b_bytes;
+  const frisk_gemm_desc& k = pl->kd;
+  if (repack_bytes) {
+    if (!workspace || args->workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
+    if ((uintptr_t)workspace % 16) return FRISK_ERR_MISALIGNED;
+    const int es = elem_size(d.a_type);
+    char* w = static_cast<char*>(workspace);
+    if (pl->repack_a_bytes) {
+      if (int rc = launch_repack(A, w, d.transA ? d.K : d.M, d.transA ? d.M : d.K, d.lda, k.lda, es,
+                                 pl->sm_count, st))
+        return rc;
+      A = w;
+    }
+    if (pl->repack_b_bytes) {
+      char* wb = w + pl->repack_a_bytes;
+      if (int rc = launch_repack(B, wb, d.transB ? d.N : d.K, d.transB ? d.K : d.N, d.ldb, k.ldb, es,
+                                 pl->sm_count, st))
+        return rc;
+      B = wb;
+    }
+    workspace = w + repack_bytes;   // what follows is the kernels' own scratch
+  }
   const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
   if ((args->n_peers > 0 || d.row_reduce) && !(whole_tile_tc && ptr_aligned)) {
     g_last_error = "peer copies of C and the fused row reduce exist only in the whole-tile "
@@ -1059,17 +1180,18 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     g_last_error = "A or B is not 16-byte aligned: this run used the CUDA-core kernel";
   }
   if (pl->info.kernel == FRISK_KERNEL_SIMT || !ptr_aligned)
-    return launch_simt(d, A, B, C, sa, sb, st);  // the CUDA-core kernel has no alignment rule
+    return launch_simt(d, A0, B0, C, sa, sb, st);  // the CUDA-core kernel has no alignment rule
 
   const bool swap = pl->info.kernel == FRISK_KERNEL_SKINNY;
-  if (pl->ws_bytes) {
+  const size_t own_ws_bytes = pl->ws_bytes - repack_bytes;
+  if (own_ws_bytes) {
     if (!workspace || args->workspace_bytes < pl->ws_bytes) return FRISK_ERR_WORKSPACE;
     if ((uintptr_t)workspace % 16) return FRISK_ERR_MISALIGNED;
   }
   frisk::GemmParams g = pl->gp;
   if (A != pl->cached_a || B != pl->cached_b) {
-    OperandView va{A, d.M, d.K, d.lda, d.transA != 0};
-    OperandView vb{B, d.N, d.K, d.ldb, d.transB == 0};
+    OperandView va{A, d.M, d.K, k.lda, d.transA != 0};
+    OperandView vb{B, d.N, d.K, k.ldb, d.transB == 0};
     const OperandView& ra = swap ? vb : va;  // a-role: the 128-row operand
     const OperandView& rb = swap ? va : vb;
     int rc = encode_operand_map(&pl->tmap_a, ra, d.a_type, g.a.box_mn, g.bk_elems, pl->lay_a.swizzle_bytes);
@@ -1110,7 +1232,7 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)
     g.row_scale = sb;
     g.col_scale = sa;
-    if (pl->ws_bytes) {
+    if (own_ws_bytes) {
       g.ws = reinterpret_cast<float*>(workspace);
       g.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->slot_bytes);
     }
@@ -1118,8 +1240,8 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     // but nothing guarantees what the caller hands in: a scratch buffer that was given to other
     // code between two runs, one buffer shared by two plans, a run that gave up on a bounded wait.
     // They are a few bytes per tile, so they are cleared on every run, in stream order.
-    if (pl->ws_bytes)
-      FRISK_CUDA(cudaMemsetAsync(g.counters, 0, pl->ws_bytes - pl->slot_bytes, st));
+    if (own_ws_bytes)
+      FRISK_CUDA(cudaMemsetAsync(g.counters, 0, own_ws_bytes - pl->slot_bytes, st));
   } else {
     g.row_scale = sa;
     g.col_scale = sb;

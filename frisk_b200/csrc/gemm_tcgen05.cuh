@@ -107,6 +107,10 @@ struct GemmParams {
                         //    through distributed shared memory (no workspace)
   uint32_t max_items;   // split mode 2: most tiles one CTA's unit range can touch
   uint32_t cluster_k;   // split mode 3: CTAs per cluster = K slices per tile
+  uint32_t red_overlay; // split mode 3: the region the partials are pushed into lies ON the stage
+                        // buffers instead of behind them (one more cluster barrier, before the
+                        // pushes: every CTA's main loop must be over), which leaves the whole of
+                        // shared memory to the pipeline
   // CTA-pair kernel: work items (whole tiles, then half-width items of the last wave's tiles)
   uint32_t n_items, narrow_from, idesc_narrow;
   uint32_t* counters;   // split mode 2: k-blocks arrived per tile (zero between launches)
@@ -896,6 +900,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
   int32_t* const status = p.status;
   const bool cluster_sync = kSplit && p.split_mode == 3 && p.cluster_k > 1;
+  // with the overlaid reduce region every warp passes the cluster barrier twice
+  const bool cluster_sync2 = cluster_sync && p.red_overlay != 0;
   // (measurement builds only) clock stamps of CTA 0, each relative to the stamping thread's own
   // clock at kernel entry, and the wall-clock entry and exit of every CTA at [1024 + 2 * CTA]
   FRISK_MEASURE_ONLY(
@@ -1020,7 +1026,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     __syncwarp();
-    if (cluster_sync) {  // see the epilogue role
+    if (cluster_sync2) {  // see the epilogue role
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+    }
+    if (cluster_sync) {
       ptx::cluster_arrive();
       ptx::cluster_wait();
     }
@@ -1118,7 +1128,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
     __syncwarp();
-    if (cluster_sync) {  // see the epilogue role
+    if (cluster_sync2) {  // see the epilogue role
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+    }
+    if (cluster_sync) {
       ptx::cluster_arrive();
       ptx::cluster_wait();
     }
@@ -1199,7 +1213,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t cluster_sh = 31u - __clz(cluster_k);
     const uint32_t my_rank = blockIdx.x & (cluster_k - 1u), share = tile_rows >> cluster_sh;
     const uint32_t share_sh = 31u - __clz(share);
-    const uint32_t red_base = tiles_base + stages * stage_bytes;
+    const uint32_t red_base = cluster_sync2 ? tiles_base : tiles_base + stages * stage_bytes;
+    bool passed_first = false;   // overlaid reduce region: this warp has been through the first barrier
     uint32_t epi_phase = 0;
     uint32_t item = 0;
     bool ok = true;
@@ -1234,6 +1249,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) break;
       ptx::tc_fence_after();
       FRISK_STAMP(threadIdx.x == 64 && item < 4, 330 + 8 * item);
+      if (cluster_sync2 && !passed_first) {
+        // The partials land on the owners' stage buffers: nobody may push before every CTA of the
+        // cluster has seen its last MMA complete (this warp just has, for its own CTA).
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+        passed_first = true;
+      }
       for (uint32_t sub = 0; sub < mi; ++sub) {
         const uint32_t r_local = sub * 128u + quarter * 32u + lane;
         const uint32_t row = tr * tile_rows + r_local;
@@ -1309,8 +1331,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ++item;
     }
     __syncwarp();
+    if (cluster_sync2 && !passed_first) {  // a warp that gave up before its item still takes part
+      ptx::cluster_arrive();
+      ptx::cluster_wait();
+    }
     if (cluster_sync) {
-      // Split mode 3.  Every warp of every CTA of the cluster passes this barrier exactly once,
+      // Split mode 3.  Every warp of every CTA of the cluster passes this barrier exactly once
+      // (and the one before the pushes, when the reduce region is overlaid on the stage buffers),
       // whatever happened in its role (all waits above are bounded), so a CTA that gave up cannot
       // strand its peers.  After it every partial has reached its owner, and nobody touches
       // another CTA's shared memory again, so each CTA leaves on its own.

@@ -69,10 +69,27 @@ def test_plan_picks_kernel_family_for_the_benchmark_configs(name, kernel):
     plan.close()
 
 
-def test_plan_falls_back_to_simt_for_unaligned_leading_dimensions():
-    p = R.GemmPlan(100, 100, 100, W.BF16, lda=101, ldb=100)  # 202-byte rows: no TMA
-    assert p.info["kernel_name"] == "simt"
+def test_odd_row_pitches_are_repacked_not_sent_to_the_cuda_cores():
+    """A row pitch that is not a multiple of 16 bytes rules out a tensor map on the caller's buffer:
+    the plan keeps the tensor-core kernel and copies that operand into the workspace at a padded
+    pitch first (one more launch per repacked operand)."""
+    base = R.GemmPlan(100, 104, 104, W.BF16)
+    p = R.GemmPlan(100, 104, 104, W.BF16, lda=107)           # 214-byte rows of A
+    assert (p.info["kernel_name"], p.info["cuda_core_reason"]) == (base.info["kernel_name"], 0)
+    assert p.info["launches"] == base.info["launches"] + 1
+    assert p.workspace_bytes == base.workspace_bytes + (100 * 104 * 2 + 255) // 256 * 256
     p.close()
+    p = R.GemmPlan(100, 100, 100, W.BF16, lda=101, ldb=100)  # both pitches odd; padded to 104 elements
+    assert p.info["kernel_name"] == "tcgen05" and p.info["launches"] == 3
+    assert p.workspace_bytes == 2 * ((100 * 104 * 2 + 255) // 256 * 256)
+    p.close()
+    p = R.GemmPlan(16, 4096, 1000, W.F16, transB=True, ldb=1001)   # a few-row plan on repacked weights
+    assert p.info["kernel_name"] == "skinny" and p.info["launches"] == 2
+    p.close()
+    p = R.GemmPlan(100, 100, 100, W.BF16, lda=101, force_kernel="simt")   # asked for: no repacking
+    assert p.info["kernel_name"] == "simt" and p.workspace_bytes == 0 and p.info["launches"] == 1
+    p.close()
+    base.close()
     p = R.GemmPlan(100, 104, 104, W.BF16)
     assert p.info["kernel_name"] == "tcgen05"
     p.close()
@@ -89,7 +106,6 @@ def test_plan_info_says_why_a_plan_runs_on_cuda_cores():
     rule that kept it off the tensor cores, so a 100x slower run is never a silent one."""
     cases = [
         (dict(ab=W.F32), 1),                                   # FRISK_TC_INPUT_TYPE
-        (dict(ab=W.BF16, lda=101), 2),                         # FRISK_TC_PITCH
         (dict(ab=W.E4M3, ct=W.BF16, transB=False), 4),         # FRISK_TC_FP8_ORDER
         (dict(ab=W.BF16, force_kernel="simt"), 5),             # FRISK_TC_FORCED
     ]
@@ -130,9 +146,9 @@ def test_plan_create_rejects_bad_descriptions():
     p5 = R.GemmPlan(512, 512, 512, W.E5M2, W.BF16, transB=True, scales=True)
     assert p5.info["kernel_name"] == "tcgen05_pair" and p5.info["tile_k"] == 128
     p5.close()
-    with pytest.raises(R.FriskError) as e:
-        R.GemmPlan(100, 100, 100, W.BF16, lda=101, force_kernel="tcgen05")
-    assert e.value.code == -3
+    p = R.GemmPlan(100, 100, 100, W.BF16, lda=101, force_kernel="tcgen05")   # odd pitches (B: 200 bytes): both repacked
+    assert p.info["kernel_name"] == "tcgen05" and p.info["launches"] == 3
+    p.close()
 
 
 def test_run_without_device_reports_no_device_or_runs():
@@ -264,7 +280,16 @@ def test_planner_invariants_over_random_shapes():
         i = p.info
         seen.add(i["kernel_name"])
         assert i["kernel_name"] in ("simt", "tcgen05", "tcgen05_pair", "skinny", "tf32x3")
-        assert i["launches"] == (3 if i["kernel_name"] == "tf32x3" else 1) and i["num_ctas"] >= 1
+        # operands with an odd row pitch are repacked into the workspace: a launch and a padded copy each
+        es = W.ELEM_SIZE[ab]
+        repack = 0
+        if ab != W.F32 and i["kernel_name"] != "simt":
+            for rows, cols in (((K, M) if ta else (M, K)), ((N, K) if tb else (K, N))):
+                if cols * es % 16:
+                    repack += (rows * (-(-cols * es // 16) * 16) + 255) // 256 * 256
+        n_repack = 0 if not repack else sum(1 for c in ((M if ta else K), (K if tb else N)) if c * es % 16)
+        assert i["launches"] == (3 if i["kernel_name"] == "tf32x3" else 1) + n_repack and i["num_ctas"] >= 1
+        own_ws = p.workspace_bytes - repack
         if i["kernel_name"] == "tf32x3":   # fp32 in and out, at least about a GFLOP, TMA-able rows
             assert ab == W.F32 and 2.0 * M * N * K >= 1e9 and p.workspace_bytes >= 2 * 4 * (M * K + K * N)
         if i["kernel_name"] != "simt":
@@ -275,13 +300,13 @@ def test_planner_invariants_over_random_shapes():
         if i["kernel_name"] == "skinny":
             assert M <= 128 and N >= 256 and not ta and i["swap_ab"] == 1
             assert i["tile_m"] == (M + 15) // 16 * 16 and i["tile_n"] in (128, 256)
-            if p.workspace_bytes == 0:   # clusters: tiles x a power-of-two cluster size
+            if own_ws == 0:              # clusters: tiles x a power-of-two cluster size
                 tiles = -(-N // i["tile_n"])
                 assert i["num_ctas"] % tiles == 0 and i["num_ctas"] // tiles in (2, 4, 8)
             else:                        # stream-K: slots + one counter per tile
-                assert p.workspace_bytes % 4 == 0 and i["num_ctas"] <= 14 * -(-N // i["tile_n"])
+                assert own_ws % 4 == 0 and i["num_ctas"] <= 14 * -(-N // i["tile_n"])
         elif i["kernel_name"] != "tf32x3":
-            assert p.workspace_bytes == 0
+            assert own_ws == 0
         p.close()
     assert seen == {"simt", "tcgen05", "tcgen05_pair", "skinny", "tf32x3"}
 

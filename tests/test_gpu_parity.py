@@ -196,6 +196,57 @@ def test_mixed_output_types_and_padded_leading_dimensions():
     assert ok, err
 
 
+@pytest.mark.parametrize("M,N,K,ab,ta,tb,pad_a,pad_b,want", [
+    (300, 5000, 700, W.BF16, False, False, 0, 0, "tcgen05_pair"),   # K = 700: 1400-byte rows of A
+    (260, 333, 264, W.F16, False, True, 3, 5, "tcgen05_pair"),      # both pitches odd, B stored [N, K]
+    (100, 520, 137, W.BF16, True, False, 1, 0, "tcgen05"),          # A stored [K, M], 202-byte rows
+    (16, 4096, 1000, W.F16, False, True, 0, 1, "skinny"),           # few rows on repacked weights
+    (256, 384, 200, W.E4M3, False, True, 0, 0, "tcgen05_pair"),     # 8-bit: 200-byte rows
+])
+def test_odd_row_pitches_run_on_the_tensor_cores_after_a_repack(M, N, K, ab, ta, tb, pad_a, pad_b, want):
+    """Operands whose row pitch is not a multiple of 16 bytes are copied into the workspace at a
+    padded pitch and run on the tensor cores; the bits equal those of the same values handed over
+    in buffers with 16-byte pitches, and the oracle's tolerance holds."""
+    rng = np.random.default_rng(M + N + K)
+    fp8 = ab in (W.E4M3, W.E5M2)
+    ct = W.BF16 if fp8 else ab
+    a = (rng.standard_normal((M, K)) * (4.0 if fp8 else 1.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (4.0 if fp8 else K ** -0.5)).astype(np.float32)
+    Aq, Bq = W.encode(a, ab), W.encode(b, ab)
+    As = np.ascontiguousarray(Aq.T) if ta else Aq
+    Bs = np.ascontiguousarray(Bq.T) if tb else Bq
+    sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if fp8 else None
+    sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32) if fp8 else None
+    es = W.ELEM_SIZE[ab]
+
+    def padded(x, extra):   # the same rows at a pitch `extra` elements longer, canaries in the padding
+        out = np.full((x.shape[0], x.shape[1] + extra), 0x7F if es == 1 else 0x7E01, x.dtype if es == 1 else np.uint16)
+        out[:, :x.shape[1]] = x.view(out.dtype)
+        return out
+
+    def run(A, B):
+        plan = R.GemmPlan(M, N, K, ab, ct, transA=ta, transB=tb, lda=A.shape[1], ldb=B.shape[1], scales=fp8)
+        out = np.zeros((M, N), W.storage_numpy_dtype(ct))
+        plan.run_host(A, B, out, sa, sb)
+        info = plan.info
+        plan.close()
+        return out, info
+
+    odd_a, odd_b = padded(As, pad_a), padded(Bs, pad_b)
+    assert (odd_a.shape[1] * es) % 16 or (odd_b.shape[1] * es) % 16
+    got, info = run(odd_a, odd_b)
+    assert info["kernel_name"] == want and info["cuda_core_reason"] == 0
+    n_odd = int(bool((odd_a.shape[1] * es) % 16)) + int(bool((odd_b.shape[1] * es) % 16))
+    # the same values at 16-byte pitches: no repack, the same kernel, the same bits
+    q = 16 // es
+    even, info0 = run(padded(As, -As.shape[1] % q), padded(Bs, -Bs.shape[1] % q))
+    assert info0["kernel_name"] == want and info["launches"] == info0["launches"] + n_odd
+    assert np.array_equal(got, even)
+    w = W.GemmWorkload("odd", M, N, K, ab, ct, transA=ta, transB=tb, A=As, B=Bs, scale_a=sa, scale_b=sb)
+    ok, err, metric = W.check(W.decode(got, ct), ref.ref_gemm_f64(w), ab, absdot=ref.abs_dot(w))
+    assert ok, f"{metric} = {err}"
+
+
 def test_guard_bands_around_c_and_workspace_stay_untouched():
     torch = pytest.importorskip("torch")
     dev = torch.device("cuda:0")

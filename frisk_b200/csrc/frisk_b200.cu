@@ -327,8 +327,11 @@ bool pair_tail_split(uint64_t tile_n, uint64_t tiles, uint64_t pairs) {
   return tile_n == 256 && rest > 0 && 2 * rest <= pairs;
 }
 
-// cluster_try: which cluster candidate of a skinny plan to take (-1: none, plan stream-K).
-void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0) {
+// cluster_try: which cluster candidate of a K-split plan to take (-1: none, plan stream-K).
+// ksplit: the K-split forms of the few-row plan (a cluster per tile, or stream-K) for a problem
+// that is NOT swapped: few tiles of C against a long K (512 x 512 x 65536 has 8 tiles for 148 SMs).
+void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0, bool ksplit = false) {
+  const bool split = swap || ksplit;
   const frisk_gemm_desc& d = pl->kd;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
@@ -344,7 +347,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     b_mn = d.transB == 0;  // B stored K x N
     rows = d.M;
     cols = d.N;
-    g.mi = 1;
+    g.mi = (ksplit && rows > 128) ? 2 : 1;
     uint32_t tn = d.tile_n ? (uint32_t)d.tile_n : (cols > 128 ? 256u : (cols > 64 ? 128u : 64u));
     if (pair && tn < 128) tn = 128;
     g.tile_n = tn;
@@ -356,6 +359,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     cols = d.M;
     g.mi = rows > 128 ? 2 : 1;
     g.tile_n = (uint32_t)((cols + 15) / 16 * 16);
+  }
+  if (split) {
     // Split mode 3 (a cluster per tile, a K slice per CTA, partials summed through distributed
     // shared memory) needs tiles x cluster size CTAs to cover most of the SMs; otherwise the
     // stream-K plan (mode 2) spreads the work evenly over all of them.
@@ -373,7 +378,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     } cand[8];
     int n_cand = 0;
     for (uint32_t mi = (rows > 128 ? 2u : 1u); mi >= 1; --mi) {
-      const uint32_t t = (uint32_t)((rows + 128 * mi - 1) / (128 * mi));
+      // tiles of the plan (the swapped plan has one tile column: all of M fits its tile width)
+      const uint32_t t = (uint32_t)((rows + 128 * mi - 1) / (128 * mi)) *
+                         (uint32_t)((cols + g.tile_n - 1) / g.tile_n);
       // the pushed-partials region and at least four pipeline stages have to fit beside each
       // other, or the region on top of four stages (red_overlay)
       const size_t stage = (size_t)(128 * mi + g.tile_n) * 128u;
@@ -423,7 +430,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.stage_bytes = g.a.stage_bytes + g.b.stage_bytes;
   // split mode 3 keeps one fp32 tile behind the stage buffers: the region the cluster's partials
   // are pushed into
-  size_t red_bytes = (swap && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
+  size_t red_bytes = (split && use_cluster) ? (size_t)128 * g.mi * g.tile_n * sizeof(float) : 0;
   // The region may instead lie ON the stage buffers (the kernel then holds the pushes back until
   // every CTA of the cluster has finished its main loop): taken when that buys at least a quarter
   // more pipeline stages -- measured, bf16 N = K = 8192: the time of a few-row plan follows the
@@ -457,8 +464,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // desc.epilogue = 4 on a CTA-pair plan: TMA tensor stores out of two staging buffers per warp
   // (needs rows of C that start on 16-byte boundaries, like every tensor map).
   const bool epi_tma = pair && !pl->tf32 && d.epilogue == 4 && (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
-  const size_t epi_bytes = swap ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
-  g.epi_staged = swap ? 0u : epi_tma ? 3u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
+  const size_t epi_bytes = split ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
+  g.epi_staged = split ? 0u : epi_tma ? 3u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
   uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
@@ -482,10 +489,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.group_r = d.band_tiles > 0 ? (uint32_t)d.band_tiles : (pair ? 8u : 16u);
   g.group_c = (pair && d.panel_tiles > 0) ? (uint32_t)d.panel_tiles : 0u;
   g.l2_hints = pair ? (uint32_t)d.l2_hints : 0u;
-  g.split_mode = swap ? 1 : 0;
+  g.split_mode = split ? 1 : 0;
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
-  g.epilogue_backoff_ns = swap ? 0u : frisk::kEpilogueBackoffNs;
+  g.epilogue_backoff_ns = split ? 0u : frisk::kEpilogueBackoffNs;
 #ifdef FRISK_B200_MEASURE
   if (const char* e = getenv("FRISK_B200_EPI_BACKOFF")) g.epilogue_backoff_ns = (uint32_t)atoi(e);
 #endif
@@ -496,7 +503,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.ws_ld = d.N;
 
   const uint64_t tiles = (uint64_t)g.tiles_r * g.tiles_c;
-  const uint64_t units = swap ? tiles * g.num_kb : tiles;
+  const uint64_t units = split ? tiles * g.num_kb : tiles;
   uint32_t ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)pl->sm_count);
   if (d.num_ctas > 0) ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)d.num_ctas);
   g.n_items = g.narrow_from = (uint32_t)tiles;
@@ -518,16 +525,16 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes + epi_bytes;
   pl->ws_bytes = 0;
   pl->rr_partial_bytes = 0;
-  if (!swap && d.row_reduce) {
+  if (!split && d.row_reduce) {
     g.rr_kind = (uint32_t)d.row_reduce;
     pl->rr_partial_bytes = ((size_t)2 * g.tiles_c * (size_t)rows * sizeof(float) + 15) / 16 * 16;
     pl->ws_bytes = pl->rr_partial_bytes;
   }
-  if (swap && use_cluster) {
+  if (split && use_cluster) {
     g.split_mode = 3;
     g.cluster_k = cluster_k;
     ctas = (uint32_t)tiles * cluster_k;
-  } else if (swap) {
+  } else if (split) {
     // Split mode 2: every CTA writes the partial tiles of its unit range into private slots; the
     // workspace is [ctas * max_items slots of tile_rows x tile_n fp32][one arrival counter per tile].
     g.split_mode = 2;
@@ -550,15 +557,15 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   in.stages = (int)g.stages;
   in.num_ctas = (int)ctas;
   in.swap_ab = swap;
-  in.split_k = swap;
+  in.split_k = split;
   in.smem_bytes = (int)pl->dyn_smem;
-  in.launches = (!swap && d.row_reduce) ? 2 : 1;   // the fold's finalize launch
+  in.launches = (!split && d.row_reduce) ? 2 : 1;   // the fold's finalize launch
   in.swizzle_a = pl->lay_a.swizzle_bytes;
   in.swizzle_b = pl->lay_b.swizzle_bytes;
   // the clusters must all be resident at once for the plan to make sense; if this device cannot
   // place them, plan again without
-  if (swap && use_cluster && pl->have_device && !skinny_clusters_fit(pl))
-    plan_tcgen05(pl, swap, pair, cluster_try + 1);
+  if (split && use_cluster && pl->have_device && !skinny_clusters_fit(pl))
+    plan_tcgen05(pl, swap, pair, cluster_try + 1, ksplit);
 }
 
 constexpr int kMaxDevices = 64;
@@ -1015,6 +1022,40 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     // more tiles than SMs) whole tiles are as good or better (128 x 28672 x 4096: 45 against 79 us).
     if (kind == FRISK_KERNEL_SKINNY && d.M > 64 && !d.force_kernel && pl->gp.split_mode != 3)
       plan_tcgen05(pl, /*swap=*/false, /*pair=*/false);
+    // Few tiles of C against a long K: whole tiles would leave most SMs idle (512 x 512 x 65536:
+    // 8 tiles; measured 227 us against 43 us for cuBLAS), so K is split over clusters or, where
+    // no cluster shape fits, over all SMs (stream-K), as in the few-row plan but without the swap.
+    // Considered when the whole-tile plan would use at most a quarter of the SMs and K has at least
+    // 48 k-blocks, or at most half of them and K has at least 192 (8192 x 128 x 8192 on 64 SMs:
+    // 34.1 us whole, 36.9 us split over 128; 1024 x 1024 x 16384 on 64: 62.7 whole, 44.5 split)
+    // (1024^3 with 16 k-blocks: 15.4 us split against 10.1 us whole -- the fold of the partials
+    // costs more than the idle SMs); taken when it puts more CTAs to work.
+    if (!d.force_kernel && !d.row_reduce && !d.num_ctas && !d.tile_n &&
+        (pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) &&
+        2 * pl->info.num_ctas <= pl->sm_count) {
+      const uint64_t kbs = (uint64_t)((d.K + pl->info.tile_k - 1) / pl->info.tile_k);
+      const uint64_t t128 = (uint64_t)((d.M + 127) / 128) * (uint64_t)((d.N + 63) / 64);
+      const bool few = 4 * pl->info.num_ctas <= pl->sm_count;
+      if ((few ? kbs >= 48 : kbs >= 192) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
+        // narrower tiles give a small C more of them: the width with the most CTAs wins, a
+        // cluster plan (the reduction stays on chip) before a stream-K one
+        const frisk_gemm_plan_info whole = pl->info;
+        int best_score = whole.num_ctas, best_tn = -1;
+        for (int tn : {0, 128, 64}) {
+          if (tn && d.N <= tn) continue;
+          pl->kd.tile_n = tn;
+          plan_tcgen05(pl, /*swap=*/false, /*pair=*/false, /*cluster_try=*/0, /*ksplit=*/true);
+          const int score = pl->info.num_ctas + (pl->gp.split_mode == 3 ? 1000 : 0);
+          if (!pl->plan_error && score > best_score) {
+            best_score = score;
+            best_tn = tn;
+          }
+        }
+        pl->kd.tile_n = best_tn > 0 ? best_tn : 0;
+        if (best_tn >= 0) plan_tcgen05(pl, /*swap=*/false, /*pair=*/false, /*cluster_try=*/0, /*ksplit=*/true);
+        else plan_tcgen05(pl, /*swap=*/false, whole.kernel == FRISK_KERNEL_TCGEN05_PAIR);   // nothing gained
+      }
+    }
     if (pl->info.kernel == FRISK_KERNEL_SKINNY && d.row_reduce) {  // a forced few-row plan
       delete pl;
       return FRISK_ERR_UNSUPPORTED;
@@ -1108,8 +1149,8 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
   cudaStream_t st = reinterpret_cast<cudaStream_t>(args->stream);
   const float* sa = d.scale_mode ? args->scale_a : nullptr;
   const float* sb = d.scale_mode ? args->scale_b : nullptr;
-  const bool whole_tile_tc =
-      pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR;
+  const bool whole_tile_tc = pl->gp.split_mode == 0 && (pl->info.kernel == FRISK_KERNEL_TCGEN05 ||
+                                                        pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR);
 
   if (pl->tf32) {
     // fp32 on the tensor cores: split A and B into the workspace, then run the tensor-core
@@ -1228,10 +1269,10 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
       }
     }
   }
-  if (swap) {
-    // D is C transposed: its rows run over N (scale_b), its columns over M (scale_a)
-    g.row_scale = sb;
-    g.col_scale = sa;
+  if (g.split_mode) {
+    // (swapped: D is C transposed, its rows run over N (scale_b), its columns over M (scale_a))
+    g.row_scale = swap ? sb : sa;
+    g.col_scale = swap ? sa : sb;
     if (own_ws_bytes) {
       g.ws = reinterpret_cast<float*>(workspace);
       g.counters = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + pl->slot_bytes);

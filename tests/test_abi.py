@@ -305,8 +305,16 @@ def test_planner_invariants_over_random_shapes():
                 assert i["num_ctas"] % tiles == 0 and i["num_ctas"] // tiles in (2, 4, 8)
             else:                        # stream-K: slots + one counter per tile
                 assert own_ws % 4 == 0 and i["num_ctas"] <= 14 * -(-N // i["tile_n"])
+        elif i["kernel_name"] == "tcgen05" and i["split_k"]:
+            # few tiles against a long K: the K-split forms without the swap
+            assert K >= 48 * i["tile_k"] and i["swap_ab"] == 0 and i["tile_m"] in (128, 256)
+            tiles = -(-M // i["tile_m"]) * -(-N // i["tile_n"])
+            if own_ws == 0:
+                assert i["num_ctas"] % tiles == 0 and i["num_ctas"] // tiles in (2, 4, 8)
+            else:
+                assert own_ws % 4 == 0 and i["num_ctas"] <= 14 * tiles
         elif i["kernel_name"] != "tf32x3":
-            assert own_ws == 0
+            assert own_ws == 0 and not i["split_k"]
         p.close()
     assert seen == {"simt", "tcgen05", "tcgen05_pair", "skinny", "tf32x3"}
 

@@ -634,6 +634,49 @@ def test_cta_pair_kernel_variants_match_oracle(M, N, K, ab, ct, ta, tb, clear):
         assert info2["kernel_name"] == "simt"
 
 
+@pytest.mark.parametrize("M,N,K,ab,ct,ta,tb,clear", [
+    (512, 512, 4096, W.BF16, W.BF16, False, False, True),     # 128 x 128 tiles, clusters of 8
+    (256, 256, 8192, W.F16, W.F32, False, True, False),       # 128 x 64 tiles, fp32 C +=
+    (1024, 1024, 12288, W.BF16, W.F16, True, False, True),    # A stored [K, M]; 128 x 256 tiles
+    (2048, 128, 4096, W.F16, W.F16, False, False, True),      # one tile column, 256-row tiles
+    (300, 200, 4104, W.BF16, W.BF16, False, False, False),    # ragged everywhere, C +=
+    (129, 1000, 8192, W.E4M3, W.BF16, False, True, True),     # scales in the split epilogue
+    (128, 128, 4096, W.BF16, W.BF16, False, False, True),     # two tiles: stream-K, workspace
+])
+def test_k_split_plans_without_the_swap_match_oracle(M, N, K, ab, ct, ta, tb, clear):
+    """Few tiles of C against a long K: the planner splits K over clusters (or stream-K) of the
+    one-CTA kernel instead of leaving most SMs idle.  Same oracle, same tolerances; the summation
+    order is fixed by the plan, so two runs give the same bits."""
+    rng = np.random.default_rng(M + 7 * N + 13 * K)
+    big = ab in (W.E4M3, W.E5M2)
+    a = (rng.standard_normal((M, K)) * (4.0 if big else 1.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (4.0 if big else K ** -0.5)).astype(np.float32)
+    sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if big else None
+    sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32) if big else None
+    Aq, Bq = W.encode(a, ab), W.encode(b, ab)
+    w = W.GemmWorkload("k-split", M, N, K, ab, ct, transA=ta, transB=tb, clear_accum=clear,
+                       A=np.ascontiguousarray(Aq.T) if ta else Aq,
+                       B=np.ascontiguousarray(Bq.T) if tb else Bq, scale_a=sa, scale_b=sb,
+                       C0=None if clear else W.encode(rng.standard_normal((M, N)).astype(np.float32), ct))
+    def run(**kw):
+        plan = R.GemmPlan.for_workload(w, **kw)
+        info = plan.info
+        plan.close()
+        return R.gemm_host(w, **kw), info
+
+    out, info = run()
+    assert info["kernel_name"] == "tcgen05" and info["split_k"] == 1 and info["swap_ab"] == 0, info
+    assert np.array_equal(out, R.gemm_host(w))
+    floor = ref.abs_dot(w)
+    for other in (ref.ref_gemm_f64(w), W.decode(ref.ref_gemm(w), ct), torch_matmul_fp32(w)):
+        ok, err, metric = W.check(W.decode(out, ct), other, ab, absdot=floor)
+        assert ok, (metric, err)
+    whole, info_w = run(force_kernel="tcgen05")   # the same problem as whole tiles
+    assert info_w["split_k"] == 0
+    ok, err, metric = W.check(W.decode(out, ct), W.decode(whole, ct), ab, absdot=floor)
+    assert ok, (metric, err)
+
+
 def test_back_to_back_dependent_launches_see_each_others_results():
     """The tensor-core kernels are launched with programmatic stream serialization (their set-up may
     overlap the previous kernel's tail).  A chain in which every GEMM reads what the one before

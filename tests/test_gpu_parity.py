@@ -677,6 +677,48 @@ def test_k_split_plans_without_the_swap_match_oracle(M, N, K, ab, ct, ta, tb, cl
     assert ok, (metric, err)
 
 
+def test_planner_choices_over_seeded_random_problems_match_the_oracle():
+    """Whatever the planner picks -- whole tiles, CTA pairs, few-row clusters, stream-K, K-split
+    without the swap, repacked operands, CUDA cores -- the result is the oracle's.  48 seeded
+    problems: every input type and storage order, odd sizes and pitches, C += and scales."""
+    import random
+    rnd = random.Random(20)
+    seen = {}
+    for case in range(48):
+        ab = rnd.choice([W.F32, W.F16, W.BF16, W.BF16, W.E4M3, W.E5M2])
+        fp8 = ab in (W.E4M3, W.E5M2)
+        ct = W.BF16 if fp8 else rnd.choice([ab, ab, W.F32]) if ab != W.F32 else W.F32
+        M = rnd.choice([1, 5, 16, 48, 100, 128, 129, 200, 256, 300, 520, 1000])
+        N = rnd.choice([8, 72, 128, 200, 256, 520, 1000, 2048, 4100])
+        K = rnd.choice([8, 72, 136, 520, 1000, 3072, 4104, 8192])
+        ta, tb = rnd.random() < 0.25, rnd.random() < 0.5
+        if fp8 and rnd.random() < 0.8:
+            ta, tb = False, True
+        clear = rnd.random() < 0.7
+        rng = np.random.default_rng(1000 + case)
+        a = (rng.standard_normal((M, K)) * (4.0 if fp8 else 1.0)).astype(np.float32)
+        b = (rng.standard_normal((K, N)) * (4.0 if fp8 else K ** -0.5)).astype(np.float32)
+        Aq, Bq = W.encode(a, ab), W.encode(b, ab)
+        w = W.GemmWorkload(f"fuzz{case}", M, N, K, ab, ct, transA=ta, transB=tb, clear_accum=clear,
+                           A=np.ascontiguousarray(Aq.T) if ta else Aq,
+                           B=np.ascontiguousarray(Bq.T) if tb else Bq,
+                           scale_a=(rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if fp8 else None,
+                           scale_b=(rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32) if fp8 else None,
+                           C0=None if clear else W.encode(rng.standard_normal((M, N)).astype(np.float32), ct))
+        plan = R.GemmPlan.for_workload(w)
+        info = plan.info
+        plan.close()
+        out = R.gemm_host(w)
+        ok, err, metric = W.check(W.decode(out, ct), ref.ref_gemm_f64(w), ab, absdot=ref.abs_dot(w))
+        what = (info["kernel_name"], info["split_k"], info["launches"])
+        assert ok, f"case {case}: {M}x{N}x{K} types {ab}->{ct} trans {ta},{tb} clear {clear} via {what}: {metric} = {err:.3e}"
+        seen[what] = seen.get(what, 0) + 1
+    kinds = {k[0] for k in seen}
+    assert {"simt", "tcgen05", "tcgen05_pair", "skinny"} <= kinds, seen
+    assert any(k[0] == "tcgen05" and k[1] for k in seen), seen          # K-split without the swap
+    assert any(k[2] > 1 and k[0] not in ("tf32x3",) for k in seen), seen   # a repacked operand
+
+
 def test_back_to_back_dependent_launches_see_each_others_results():
     """The tensor-core kernels are launched with programmatic stream serialization (their set-up may
     overlap the previous kernel's tail).  A chain in which every GEMM reads what the one before

@@ -463,7 +463,13 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // through it too.
   // desc.epilogue = 4 on a CTA-pair plan: TMA tensor stores out of two staging buffers per warp
   // (needs rows of C that start on 16-byte boundaries, like every tensor map).
-  const bool epi_tma = pair && !pl->tf32 && d.epilogue == 4 && (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
+  // Taken by default when K is short (at most 32 k-blocks): the epilogue of a tile then takes
+  // longer than its main loop, and the tensor stores need a fraction of the instructions
+  // (measured, bf16 8192 x 8192 x K: K = 256 58.6 -> 41.4 us, K = 512 65.3 -> 54.3 us, equal from
+  // K = 1024 on; cuBLAS: 41.2 and 58.5 us).
+  const bool short_k = (d.K + bk - 1) / bk <= 32;
+  const bool epi_tma = pair && !pl->tf32 && (d.epilogue == 4 || (d.epilogue == 0 && short_k)) &&
+                       (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
   const size_t epi_bytes = split ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
   g.epi_staged = split ? 0u : epi_tma ? 3u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem

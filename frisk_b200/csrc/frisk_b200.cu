@@ -1036,12 +1036,19 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     // 34.1 us whole, 36.9 us split over 128; 1024 x 1024 x 16384 on 64: 62.7 whole, 44.5 split)
     // (1024^3 with 16 k-blocks: 15.4 us split against 10.1 us whole -- the fold of the partials
     // costs more than the idle SMs); taken when it puts more CTAs to work.
+    bool consider_split = 2 * pl->info.num_ctas <= pl->sm_count;
+#ifdef FRISK_B200_MEASURE
+    if (const char* e = getenv("FRISK_B200_KSPLIT")) consider_split = atoi(e) != 0;
+#endif
     if (!d.force_kernel && !d.row_reduce && !d.num_ctas && !d.tile_n &&
         (pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) &&
-        2 * pl->info.num_ctas <= pl->sm_count) {
+        consider_split) {
       const uint64_t kbs = (uint64_t)((d.K + pl->info.tile_k - 1) / pl->info.tile_k);
       const uint64_t t128 = (uint64_t)((d.M + 127) / 128) * (uint64_t)((d.N + 63) / 64);
-      const bool few = 4 * pl->info.num_ctas <= pl->sm_count;
+      bool few = 4 * pl->info.num_ctas <= pl->sm_count;
+#ifdef FRISK_B200_MEASURE
+      if (getenv("FRISK_B200_KSPLIT")) few = true;
+#endif
       if ((few ? kbs >= 48 : kbs >= 192) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
         // narrower tiles give a small C more of them: the width with the most CTAs wins, a
         // cluster plan (the reduction stays on chip) before a stream-K one
@@ -1052,7 +1059,11 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
           pl->kd.tile_n = tn;
           plan_tcgen05(pl, /*swap=*/false, /*pair=*/false, /*cluster_try=*/0, /*ksplit=*/true);
           const int score = pl->info.num_ctas + (pl->gp.split_mode == 3 ? 1000 : 0);
-          if (!pl->plan_error && score > best_score) {
+          bool better = score > best_score;
+#ifdef FRISK_B200_MEASURE
+          if (getenv("FRISK_B200_KSPLIT")) better = best_tn < 0 || score > best_score;
+#endif
+          if (!pl->plan_error && better) {
             best_score = score;
             best_tn = tn;
           }

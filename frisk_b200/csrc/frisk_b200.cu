@@ -894,7 +894,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   if (d.force_kernel < 0 || d.force_kernel > 5 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.epilogue < 0 || d.epilogue > 4 || d.row_reduce < 0 || d.row_reduce > 4 ||
-      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3)
+      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3 || d.k_split < -1 || d.k_split > 1)
     return FRISK_ERR_INVALID_ARGUMENT;
   d.row_reduce_clear = d.row_reduce_clear != 0;
 
@@ -1036,20 +1036,15 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     // 34.1 us whole, 36.9 us split over 128; 1024 x 1024 x 16384 on 64: 62.7 whole, 44.5 split)
     // (1024^3 with 16 k-blocks: 15.4 us split against 10.1 us whole -- the fold of the partials
     // costs more than the idle SMs); taken when it puts more CTAs to work.
-    bool consider_split = 2 * pl->info.num_ctas <= pl->sm_count;
-#ifdef FRISK_B200_MEASURE
-    if (const char* e = getenv("FRISK_B200_KSPLIT")) consider_split = atoi(e) != 0;
-#endif
+    const bool force_split = d.k_split > 0;
+    const bool consider_split = d.k_split >= 0 && (force_split || 2 * pl->info.num_ctas <= pl->sm_count);
     if (!d.force_kernel && !d.row_reduce && !d.num_ctas && !d.tile_n &&
         (pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) &&
         consider_split) {
       const uint64_t kbs = (uint64_t)((d.K + pl->info.tile_k - 1) / pl->info.tile_k);
       const uint64_t t128 = (uint64_t)((d.M + 127) / 128) * (uint64_t)((d.N + 63) / 64);
-      bool few = 4 * pl->info.num_ctas <= pl->sm_count;
-#ifdef FRISK_B200_MEASURE
-      if (getenv("FRISK_B200_KSPLIT")) few = true;
-#endif
-      if ((few ? kbs >= 48 : kbs >= 192) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
+      const bool few = 4 * pl->info.num_ctas <= pl->sm_count;
+      if ((force_split || (few ? kbs >= 48 : kbs >= 192)) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
         // narrower tiles give a small C more of them: the width with the most CTAs wins, a
         // cluster plan (the reduction stays on chip) before a stream-K one
         const frisk_gemm_plan_info whole = pl->info;
@@ -1059,10 +1054,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
           pl->kd.tile_n = tn;
           plan_tcgen05(pl, /*swap=*/false, /*pair=*/false, /*cluster_try=*/0, /*ksplit=*/true);
           const int score = pl->info.num_ctas + (pl->gp.split_mode == 3 ? 1000 : 0);
-          bool better = score > best_score;
-#ifdef FRISK_B200_MEASURE
-          if (getenv("FRISK_B200_KSPLIT")) better = best_tn < 0 || score > best_score;
-#endif
+          const bool better = score > best_score || (force_split && best_tn < 0);
           if (!pl->plan_error && better) {
             best_score = score;
             best_tn = tn;

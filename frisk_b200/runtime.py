@@ -38,7 +38,7 @@ class GemmDesc(C.Structure):
         ("force_kernel", C.c_int32), ("tile_n", C.c_int32), ("stages", C.c_int32),
         ("num_ctas", C.c_int32), ("band_tiles", C.c_int32),
         ("epilogue", C.c_int32), ("row_reduce", C.c_int32), ("row_reduce_clear", C.c_int32),
-        ("panel_tiles", C.c_int32), ("l2_hints", C.c_int32),
+        ("panel_tiles", C.c_int32), ("l2_hints", C.c_int32), ("k_split", C.c_int32),
     ]
 
 
@@ -230,7 +230,7 @@ class GemmPlan:
                  force_kernel: Optional[str] = None, tile_n: int = 0, stages: int = 0,
                  num_ctas: int = 0, band_tiles: int = 0, epilogue: int = 0,
                  row_reduce: Optional[str] = None, row_reduce_clear: bool = True,
-                 panel_tiles: int = 0, l2_hints: int = 0):
+                 panel_tiles: int = 0, l2_hints: int = 0, k_split: int = 0):
         L = lib()
         d = GemmDesc()
         d.M, d.N, d.K = M, N, K
@@ -245,7 +245,7 @@ class GemmPlan:
         d.epilogue = epilogue
         d.row_reduce = 0 if row_reduce is None else 1 + REDUCE_KINDS[row_reduce]
         d.row_reduce_clear = int(row_reduce_clear)
-        d.panel_tiles, d.l2_hints = panel_tiles, l2_hints
+        d.panel_tiles, d.l2_hints, d.k_split = panel_tiles, l2_hints, k_split
         self.desc = d
         self._h = C.c_void_p()
         _check(L.frisk_b200_gemm_plan_create(C.byref(d), C.byref(self._h)), "plan_create")

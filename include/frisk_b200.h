@@ -115,6 +115,9 @@ typedef struct frisk_gemm_desc {
   int32_t panel_tiles;  /* > 0: walk the tiles in panels of this many tile columns (the panel
                            of B stays in L2 while A streams past) instead of bands of rows      */
   int32_t l2_hints;     /* bit 0: loads of A evict-first in L2; bit 1: loads of B evict-last    */
+  int32_t k_split;      /* the K-split form of an unswapped problem (a cluster per tile, or
+                           stream-K): 0 = where the plan expects it to pay, 1 = whenever one
+                           exists, -1 = never                                                   */
 } frisk_gemm_desc;
 
 typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */

@@ -101,6 +101,23 @@ def test_odd_row_pitches_are_repacked_not_sent_to_the_cuda_cores():
     p.close()
 
 
+def test_k_split_override():
+    """desc.k_split: 0 lets the plan decide (few tiles against a long K are split), -1 never splits,
+    1 splits whenever a K-split form exists."""
+    auto = R.GemmPlan(512, 512, 65536, W.BF16)
+    never = R.GemmPlan(512, 512, 65536, W.BF16, k_split=-1)
+    assert (auto.info["split_k"], auto.info["kernel_name"], auto.info["swap_ab"]) == (1, "tcgen05", 0)
+    assert auto.info["num_ctas"] > 4 * never.info["num_ctas"] and never.info["split_k"] == 0
+    big = R.GemmPlan(4096, 4096, 4096, W.BF16)
+    forced = R.GemmPlan(4096, 4096, 4096, W.BF16, k_split=1)
+    assert big.info["split_k"] == 0 and forced.info["split_k"] == 1
+    for p in (auto, never, big, forced):
+        p.close()
+    with pytest.raises(R.FriskError) as e:
+        R.GemmPlan(512, 512, 512, W.BF16, k_split=2)
+    assert e.value.code == -1
+
+
 def test_plan_info_says_why_a_plan_runs_on_cuda_cores():
     """FRISK_TC_* of include/frisk_b200.h: a plan that resolved to the CUDA-core kernel names the
     rule that kept it off the tensor cores, so a 100x slower run is never a silent one."""

@@ -214,7 +214,8 @@ def test_run_ex_argument_errors():
     """Host-side checks of frisk_b200_gemm_run_ex that come before any device work."""
     L = R.lib()
     plan = R.GemmPlan(256, 256, 256, W.BF16, row_reduce="max")
-    assert plan.workspace_bytes == 2 * 256 * 4 and plan.info["launches"] == 2   # a fold per row and half tile
+    tiles_c = 256 // plan.info["tile_n"]
+    assert plan.workspace_bytes == 2 * tiles_c * 256 * 4 and plan.info["launches"] == 2   # a fold per row and half tile
     a = R.GemmRunArgs()
     assert L.frisk_b200_gemm_run_ex(plan._h, None) == -1
     assert L.frisk_b200_gemm_run_ex(None, C.byref(a)) == -1

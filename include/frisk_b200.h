@@ -128,7 +128,8 @@ typedef struct frisk_gemm_plan_info {
   int32_t stages;
   int32_t num_ctas;
   int32_t swap_ab;     /* 1 when the weights feed the 128-row operand (skinny path)          */
-  int32_t split_k;     /* 1 when several CTAs share a tile's K range (skinny path)           */
+  int32_t split_k;     /* 1 when several CTAs share a tile's K range: the few-row plan, and
+                          FRISK_KERNEL_TCGEN05 plans for a few tiles against a long K          */
   int32_t smem_bytes;  /* dynamic shared memory per CTA                                      */
   int32_t launches;    /* kernels launched per run                                           */
   int32_t swizzle_a, swizzle_b; /* TMA/UMMA swizzle width in bytes (0, 32, 64, 128)          */
@@ -154,10 +155,12 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
 void frisk_b200_gemm_plan_destroy(frisk_gemm_plan* plan);
 int frisk_b200_gemm_plan_info(const frisk_gemm_plan* plan, frisk_gemm_plan_info* out);
 
-/* Bytes of device scratch `run` needs.  0 for every plan but the stream-K form of the few-row
- * plan (few-row shapes whose tiles cannot be covered by thread-block clusters), plans with a
- * fused row reduce (one fp32 per row and half tile) and 3xTF32 plans (three times the bytes of A
- * and B; 256-byte aligned); `run` takes a NULL workspace when it is 0. */
+/* Bytes of device scratch `run` needs.  0 for every plan but the stream-K forms of the K-split
+ * plans (shapes whose tiles cannot be covered by thread-block clusters), plans with a fused row
+ * reduce (one fp32 per row and half tile), 3xTF32 plans (twice the bytes of A and B; 256-byte
+ * aligned) and plans for an A or B whose row pitch is not a multiple of 16 bytes (a copy of that
+ * operand at a padded pitch, made by one more launch before every run); `run` takes a NULL
+ * workspace when it is 0. */
 int frisk_b200_gemm_workspace_bytes(const frisk_gemm_plan* plan, size_t* out);
 
 /*

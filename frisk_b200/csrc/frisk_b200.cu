@@ -350,12 +350,13 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     g.mi = (ksplit && rows > 128) ? 2 : 1;
     uint32_t tn = d.tile_n ? (uint32_t)d.tile_n : (cols > 128 ? 256u : (cols > 64 ? 128u : 64u));
     if (pair && tn < 128) tn = 128;
-    // One row of 256-wide tiles that fills at most half of the pairs would run as half-width items
-    // anyway (pair_tail_split); planned as 128-wide tiles the same items get stages of 24 instead
-    // of 32 KiB, eight of them instead of six, and it is bytes in flight that such a weight-streaming
-    // shape waits for (256 x 8192 x 8192: 39.3 -> 35.5 us, 256 x 4096 x 4096: 21.6 -> 18.8 us).
-    if (pair && !d.tile_n && tn == 256 && rows <= 256 &&
-        2 * ((cols + 255) / 256) <= (int64_t)std::max(1, pl->sm_count / 2))
+    // 256-wide tiles that fill at most half of the pairs would run as half-width items anyway
+    // (pair_tail_split); planned as 128-wide tiles the same items get stages of 24 instead of
+    // 32 KiB, eight of them instead of six, and it is bytes in flight that such an operand-streaming
+    // shape waits for (256 x 8192 x 8192: 39.3 -> 35.5 us, 256 x 4096 x 4096: 21.6 -> 18.8 us,
+    // 8192 x 256 x 8192: 40.1 -> 37.1 us).
+    if (pair && !d.tile_n && tn == 256 &&
+        2 * ((rows + 255) / 256) * ((cols + 255) / 256) <= (int64_t)std::max(1, pl->sm_count / 2))
       tn = 128;
     g.tile_n = tn;
   } else {

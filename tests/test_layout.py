@@ -104,7 +104,7 @@ def test_kernel_operand_layouts_are_the_mapped_ones():
     ((8192, 8192, 8192), W.BF16, {}, ((128, 64, True), (64, 128, False))),            # pair: half of B per CTA
     ((4096, 4096, 4096), W.F16, dict(transB=True), ((128, 64, True), (128, 64, True))),
     ((8192, 8192, 8192), W.E4M3, dict(transB=True, c_type=W.BF16, scales=True), ((128, 128, True), (128, 128, True))),
-    ((384, 1024, 2048), W.BF16, dict(transA=True), ((64, 128, False), (64, 128, False))),   # A stored [K, M]
+    ((384, 1024, 2048), W.BF16, dict(transA=True), ((64, 128, False), (64, 64, False))),    # A stored [K, M]; 128-wide tiles
     ((128, 512, 256), W.BF16, dict(force_kernel="tcgen05"), ((128, 64, True), (64, 256, False))),
     ((16, 8192, 8192), W.BF16, {}, ((64, 256, False), (16, 64, True))),               # few rows: weights first
     ((64, 8192, 256), W.F16, dict(transB=True), ((256, 64, True), (64, 64, True))),

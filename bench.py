@@ -37,11 +37,12 @@ FULL_DIMS = {
     "cfg1": (512, 512, 512), "cfg2": (4096, 4096, 4096), "cfg3": (16, 8192, 8192),
     "cfg4": (8192, 8192, 8192), "cfg5": (65536, 8192, 8192), "bf16_8192": (8192, 8192, 8192),
     "fp32_4096": (4096, 4096, 4096),   # cfg1's layout and distribution at a size the 3xTF32 plan takes
+    "bf16_short_k": (8192, 8192, 256),  # cfg5's distributions with a short K: the epilogue is the kernel's time
 }
 AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3, "fp32_4096": W.F32}
 C_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "fp32_4096": W.F32}
 TRANS_B = {"cfg2", "cfg4"}
-BOUND = {"cfg3": "hbm"}  # everything else is measured against the tensor-core peak
+BOUND = {"cfg3": "hbm", "bf16_short_k": "hbm"}  # everything else is measured against the tensor-core peak
 # DRAM bytes per launch of the dominant kernel (ncu: dram__bytes_read.sum + dram__bytes_write.sum
 # of one captured launch, `--clock-control none`); None where no capture exists.
 NCU_TRAFFIC_BYTES = {

@@ -330,8 +330,13 @@ bool pair_tail_split(uint64_t tile_n, uint64_t tiles, uint64_t pairs) {
 // cluster_try: which cluster candidate of a K-split plan to take (-1: none, plan stream-K).
 // ksplit: the K-split forms of the few-row plan (a cluster per tile, or stream-K) for a problem
 // that is NOT swapped: few tiles of C against a long K (512 x 512 x 65536 has 8 tiles for 148 SMs).
-void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0, bool ksplit = false) {
+// kparts > 1 (CTA-pair plans only): K planes -- K cut into that many parts at most, one work item
+// per (tile, part), the partial tiles written as fp32 planes into the workspace and folded into C
+// by a second launch (kplanes_sum_kernel).
+void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0, bool ksplit = false,
+                  int kparts = 0) {
   const bool split = swap || ksplit;
+  const bool planes = pair && !split && kparts > 1 && !pl->kd.row_reduce && !pl->tf32;
   const frisk_gemm_desc& d = pl->kd;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
@@ -355,7 +360,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     // 32 KiB, eight of them instead of six, and it is bytes in flight that such an operand-streaming
     // shape waits for (256 x 8192 x 8192: 39.3 -> 35.5 us, 256 x 4096 x 4096: 21.6 -> 18.8 us,
     // 8192 x 256 x 8192: 40.1 -> 37.1 us).
-    if (pair && !d.tile_n && tn == 256 &&
+    if (pair && !planes && !d.tile_n && tn == 256 &&
         2 * ((rows + 255) / 256) * ((cols + 255) / 256) <= (int64_t)std::max(1, pl->sm_count / 2))
       tn = 128;
     g.tile_n = tn;
@@ -476,10 +481,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // (measured, bf16 8192 x 8192 x K: K = 256 58.6 -> 41.4 us, K = 512 65.3 -> 54.3 us, equal from
   // K = 1024 on; cuBLAS: 41.2 and 58.5 us).
   const bool short_k = (d.K + bk - 1) / bk <= 32;
-  const bool epi_tma = pair && !pl->tf32 && (d.epilogue == 4 || (d.epilogue == 0 && short_k)) &&
+  const bool epi_tma = pair && !planes && !pl->tf32 && (d.epilogue == 4 || (d.epilogue == 0 && short_k)) &&
                        (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
   const size_t epi_bytes = split ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
-  g.epi_staged = split ? 0u : epi_tma ? 3u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
+  g.epi_staged = split ? 0u : epi_tma ? 3u : planes ? 1u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
   uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
   stages = std::min<uint32_t>(stages, frisk::kMaxStages);
@@ -506,7 +511,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.split_mode = split ? 1 : 0;
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
-  g.epilogue_backoff_ns = split ? 0u : frisk::kEpilogueBackoffNs;
+  g.epilogue_backoff_ns = (split || planes) ? 0u : frisk::kEpilogueBackoffNs;
 #ifdef FRISK_B200_MEASURE
   if (const char* e = getenv("FRISK_B200_EPI_BACKOFF")) g.epilogue_backoff_ns = (uint32_t)atoi(e);
 #endif
@@ -515,12 +520,25 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.c_type = d.c_type;
   g.ldc = d.ldc;
   g.ws_ld = d.N;
+  size_t planes_bytes = 0;
+  if (planes) {
+    // the GEMM launch writes fp32 partial tiles, whole, without scales, at a pitch that keeps
+    // every row of every plane on a 16-byte boundary
+    g.kb_per = (g.num_kb + (uint32_t)kparts - 1) / (uint32_t)kparts;
+    g.k_parts = (g.num_kb + g.kb_per - 1) / g.kb_per;   // no empty part
+    const int64_t ldp = (d.N + 3) / 4 * 4;
+    g.plane_elems = (uint64_t)d.M * (uint64_t)ldp;
+    g.c_type = FRISK_DT_F32;
+    g.ldc = ldp;
+    g.clear_accum = 1;
+    planes_bytes = ((size_t)g.k_parts * g.plane_elems * sizeof(float) + 255) / 256 * 256;
+  }
 
   const uint64_t tiles = (uint64_t)g.tiles_r * g.tiles_c;
   const uint64_t units = split ? tiles * g.num_kb : tiles;
   uint32_t ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)pl->sm_count);
   if (d.num_ctas > 0) ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)d.num_ctas);
-  g.n_items = g.narrow_from = (uint32_t)tiles;
+  g.n_items = g.narrow_from = (uint32_t)(planes ? tiles * g.k_parts : tiles);
   if (pair) {  // one cluster of two CTAs per tile in flight
     uint64_t slots = (uint64_t)pl->sm_count / 2;
     if (d.num_ctas > 1) slots = std::min<uint64_t>(slots, (uint64_t)d.num_ctas / 2);
@@ -528,7 +546,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     // Tiles that fill the last wave of pairs at most half are cut into two half-width items each:
     // the wave then takes about 0.56 of a whole-tile wave instead of a full one.
     const uint64_t rest = tiles % slots;
-    if (pair_tail_split(g.tile_n, tiles, slots)) {
+    if (!planes && pair_tail_split(g.tile_n, tiles, slots)) {
       g.narrow_from = (uint32_t)(tiles - rest);
       g.n_items = (uint32_t)(tiles + rest);
       g.idesc_narrow = make_idesc(d.a_type, a_mn, b_mn, 256u, g.tile_n / 2);
@@ -537,7 +555,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     ctas = (uint32_t)(2 * pairs);
   }
   pl->dyn_smem = (size_t)g.stages * g.stage_bytes + 1024 + red_bytes + epi_bytes;
-  pl->ws_bytes = 0;
+  pl->ws_bytes = planes_bytes;
   pl->rr_partial_bytes = 0;
   if (!split && d.row_reduce) {
     g.rr_kind = (uint32_t)d.row_reduce;
@@ -579,9 +597,9 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   in.stages = (int)g.stages;
   in.num_ctas = (int)ctas;
   in.swap_ab = swap;
-  in.split_k = split;
+  in.split_k = split || planes;
   in.smem_bytes = (int)pl->dyn_smem;
-  in.launches = (!split && d.row_reduce) ? 2 : 1;   // the fold's finalize launch
+  in.launches = ((!split && d.row_reduce) || planes) ? 2 : 1;   // the fold's finalize launch / the planes' sum
   in.swizzle_a = pl->lay_a.swizzle_bytes;
   in.swizzle_b = pl->lay_b.swizzle_bytes;
   // the clusters must all be resident at once for the plan to make sense; if this device cannot
@@ -724,6 +742,29 @@ int launch_row_fold_t(const frisk_gemm_plan* pl, const frisk::GemmParams& g, voi
   FRISK_CUDA(cudaLaunchKernelEx(&cfg, frisk::row_fold_finalize_kernel<TC>, (const float*)g.rr_partials,
                                 reinterpret_cast<TC*>(dst), g.rows, 2u * g.tiles_c, g.rr_kind,
                                 (uint32_t)(pl->d.row_reduce_clear ? 1 : 0)));
+  return FRISK_OK;
+}
+
+// The second launch of a K-planes plan: sums the fp32 planes into the caller's C.
+template <typename TC>
+int launch_kplanes_sum_t(const frisk_gemm_plan* pl, const frisk::GemmParams& g, const float* planes,
+                         void* C, const float* sa, const float* sb, cudaStream_t st) {
+  const frisk_gemm_desc& d = pl->d;
+  const int64_t work = d.M * ((d.N + 3) / 4);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, 8 * (int64_t)pl->sm_count)), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = st;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const int vec_ok = ((uintptr_t)C % (4 * sizeof(TC)) == 0) && (d.ldc % 4 == 0);
+  FRISK_CUDA(cudaLaunchKernelEx(&cfg, frisk::kplanes_sum_kernel<TC>, planes, (uint64_t)g.plane_elems,
+                                (uint32_t)g.k_parts, (int64_t)g.ldc, reinterpret_cast<TC*>(C), (int64_t)d.ldc,
+                                (int64_t)d.M, (int64_t)d.N, sa, sb, (int)(d.clear_accum ? 1 : 0), vec_ok));
   return FRISK_OK;
 }
 
@@ -910,7 +951,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   if (d.force_kernel < 0 || d.force_kernel > 5 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.epilogue < 0 || d.epilogue > 4 || d.row_reduce < 0 || d.row_reduce > 4 ||
-      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3 || d.k_split < -1 || d.k_split > 1)
+      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3 || d.k_split < -1 || d.k_split > 2)
     return FRISK_ERR_INVALID_ARGUMENT;
   d.row_reduce_clear = d.row_reduce_clear != 0;
 
@@ -1052,15 +1093,23 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
     // 34.1 us whole, 36.9 us split over 128; 1024 x 1024 x 16384 on 64: 62.7 whole, 44.5 split)
     // (1024^3 with 16 k-blocks: 15.4 us split against 10.1 us whole -- the fold of the partials
     // costs more than the idle SMs); taken when it puts more CTAs to work.
-    const bool force_split = d.k_split > 0;
-    const bool consider_split = d.k_split >= 0 && (force_split || 2 * pl->info.num_ctas <= pl->sm_count);
+    const bool force_split = d.k_split == 1;
+    const bool consider_split = d.k_split >= 0 && (d.k_split > 0 || 2 * pl->info.num_ctas <= pl->sm_count);
     if (!d.force_kernel && !d.row_reduce && !d.num_ctas && !d.tile_n &&
         (pl->info.kernel == FRISK_KERNEL_TCGEN05 || pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) &&
         consider_split) {
       const uint64_t kbs = (uint64_t)((d.K + pl->info.tile_k - 1) / pl->info.tile_k);
       const uint64_t t128 = (uint64_t)((d.M + 127) / 128) * (uint64_t)((d.N + 63) / 64);
       const bool few = 4 * pl->info.num_ctas <= pl->sm_count;
-      if ((force_split || (few ? kbs >= 48 : kbs >= 192)) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
+      // K planes on the CTA-pair kernel: 256-row tiles, as many K parts as there are pairs for
+      // (at least eight k-blocks each)
+      const uint64_t tn256 = d.N > 128 ? 256 : 128;
+      const uint64_t tiles256 = (uint64_t)((d.M + 255) / 256) * (((uint64_t)d.N + tn256 - 1) / tn256);
+      const uint64_t kparts = std::min<uint64_t>((uint64_t)(pl->sm_count / 2) / tiles256, kbs / 8);
+      const bool planes_ok = pair_ok && kparts >= 2;
+      bool planes = planes_ok && d.k_split == 2;
+      if (!planes &&
+          (force_split || (few ? kbs >= 48 : kbs >= 192)) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
         // narrower tiles give a small C more of them: the width with the most CTAs wins, a
         // cluster plan (the reduction stays on chip) before a stream-K one
         const frisk_gemm_plan_info whole = pl->info;
@@ -1079,6 +1128,26 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
         pl->kd.tile_n = best_tn > 0 ? best_tn : 0;
         if (best_tn >= 0) plan_tcgen05(pl, /*swap=*/false, /*pair=*/false, /*cluster_try=*/0, /*ksplit=*/true);
         else plan_tcgen05(pl, /*swap=*/false, whole.kernel == FRISK_KERNEL_TCGEN05_PAIR);   // nothing gained
+        // The split forms above fill the SMs with small tiles, and small tiles pull many bytes from
+        // L2 per FLOP: their time follows tiles x (tile rows + tile columns) x K bytes at 7 - 9 TB/s
+        // (512 x 512 x 65536 as 128 x 64 tiles: 805 MB, 100 us).  K planes keep 256 x 256 tiles and
+        // pay a second launch that cannot start before the first has drained (about 10 us more on a
+        // problem of a few microseconds), so they are taken when they save more L2 traffic than
+        // that costs.  bf16, K split over clusters -> K planes (cuBLAS): 512 x 512 x 65536
+        // 100 -> 40 us (44), 1024 x 1024 x 16384 43 -> 35 us (36), 512 x 1024 x 8192 20.9 -> 19.4 us
+        // (16); 129 x 1000 x 8192 18.2 -> 21.8 us and 512 x 512 x 4096 12.3 -> 17.0 us are what the
+        // rule keeps out.
+        if (best_tn >= 0 && planes_ok && d.k_split == 0) {
+          const frisk::GemmParams& sg = pl->gp;
+          const double es = (double)elem_size(d.a_type), kk = (double)d.K;
+          const double split_bytes = (double)sg.tiles_r * sg.tiles_c * (128.0 * sg.mi + sg.tile_n) * kk * es;
+          const double planes_bytes = (double)tiles256 * (256.0 + (double)tn256) * kk * es;
+          planes = split_bytes - planes_bytes > 80.0e6;
+        }
+      }
+      if (planes) {
+        pl->kd.tile_n = 0;
+        plan_tcgen05(pl, /*swap=*/false, /*pair=*/true, 0, false, (int)kparts);
       }
     }
     if (pl->info.kernel == FRISK_KERNEL_SKINNY && d.row_reduce) {  // a forced few-row plan
@@ -1174,7 +1243,7 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
   cudaStream_t st = reinterpret_cast<cudaStream_t>(args->stream);
   const float* sa = d.scale_mode ? args->scale_a : nullptr;
   const float* sb = d.scale_mode ? args->scale_b : nullptr;
-  const bool whole_tile_tc = pl->gp.split_mode == 0 && (pl->info.kernel == FRISK_KERNEL_TCGEN05 ||
+  const bool whole_tile_tc = pl->gp.split_mode == 0 && pl->gp.k_parts <= 1u && (pl->info.kernel == FRISK_KERNEL_TCGEN05 ||
                                                         pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR);
 
   if (pl->tf32) {
@@ -1313,8 +1382,25 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     g.col_scale = sb;
     if (d.row_reduce) g.rr_partials = reinterpret_cast<float*>(workspace);
   }
+  const bool planes = g.k_parts > 1u;
+  if (planes) {   // the GEMM launch writes raw fp32 planes; scales, += C and the cast follow in the sum
+    g.C = workspace;
+    g.c_vec_ok = 1;
+    g.row_scale = g.col_scale = nullptr;
+  }
   int rc;
-  if (pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) {
+  if (planes) {
+    rc = launch_pair_t<float>(pl, g, st);
+    if (!rc) {
+      const float* w = static_cast<const float*>(workspace);
+      switch (d.c_type) {
+        case FRISK_DT_F32: rc = launch_kplanes_sum_t<float>(pl, g, w, C, sa, sb, st); break;
+        case FRISK_DT_F16: rc = launch_kplanes_sum_t<__half>(pl, g, w, C, sa, sb, st); break;
+        case FRISK_DT_BF16: rc = launch_kplanes_sum_t<__nv_bfloat16>(pl, g, w, C, sa, sb, st); break;
+        default: rc = FRISK_ERR_UNSUPPORTED;
+      }
+    }
+  } else if (pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR) {
     switch (d.c_type) {
       case FRISK_DT_F32: rc = launch_pair_t<float>(pl, g, st); break;
       case FRISK_DT_F16: rc = launch_pair_t<__half>(pl, g, st); break;

@@ -113,6 +113,12 @@ struct GemmParams {
                         // shared memory to the pipeline
   // CTA-pair kernel: work items (whole tiles, then half-width items of the last wave's tiles)
   uint32_t n_items, narrow_from, idesc_narrow;
+  // CTA-pair kernel, K planes: K is cut into k_parts parts of kb_per k-blocks; an item is one part
+  // of one tile, and part z leaves as fp32 into plane z (C + z * plane_elems elements, which the
+  // host points at the workspace); kplanes_sum_kernel then folds the planes into the caller's C.
+  // k_parts <= 1: whole K per item.
+  uint32_t k_parts, kb_per;
+  uint64_t plane_elems;
   uint32_t* counters;   // split mode 2: k-blocks arrived per tile (zero between launches)
   // epilogue
   void* C;
@@ -1426,6 +1432,61 @@ __global__ void splitk_finalize_kernel(float* __restrict__ ws, int64_t ws_ld, TC
         if (!clear_accum) x += cast_in<TC>(*dst);
         *dst = cast_out<TC>(x);
       }
+    }
+  }
+}
+
+// The second launch of a K-planes plan: C = cast(scale_m * scale_n * (plane 0 + plane 1 + ...)
+// (+ C)), the planes summed in their order, four columns per thread.  `ldp` (the planes' pitch) is
+// a multiple of 4; `vec_ok`: four elements of C at a column that is a multiple of 4 may leave as
+// one store.  Launched as a programmatic dependent of the GEMM, like row_fold_finalize_kernel.
+template <typename TC>
+__global__ void __launch_bounds__(256) kplanes_sum_kernel(const float* __restrict__ planes,
+                                                          uint64_t plane_elems, uint32_t parts,
+                                                          int64_t ldp, TC* __restrict__ C, int64_t ldc,
+                                                          int64_t M, int64_t N,
+                                                          const float* __restrict__ scale_m,
+                                                          const float* __restrict__ scale_n,
+                                                          int clear_accum, int vec_ok) {
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
+  const int64_t n4 = (N + 3) / 4;
+  const int64_t total = M * n4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / n4;
+    const int64_t n0 = (i - m * n4) * 4;
+    const float* src = planes + m * ldp + n0;
+    float4 s = __ldcg(reinterpret_cast<const float4*>(src));
+    // (unrolled so that eight loads are in flight per thread; the adds keep the planes' order)
+#pragma unroll 8
+    for (uint32_t z = 1; z < parts; ++z) {
+      const float4 t = __ldcg(reinterpret_cast<const float4*>(src + (size_t)z * plane_elems));
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    float v[4] = {s.x, s.y, s.z, s.w};
+    const float sm = scale_m ? __ldg(scale_m + m) : 1.0f;
+    TC* dst = C + m * ldc + n0;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);   // four elements of C (the first 8 bytes for 16-bit types)
+    TC* e = reinterpret_cast<TC*>(&raw);
+    const bool whole = vec_ok && n0 + 4 <= N;
+    if (whole && !clear_accum) {
+      if (sizeof(TC) == 4) raw = *reinterpret_cast<const uint4*>(dst);
+      else *reinterpret_cast<uint2*>(&raw) = *reinterpret_cast<const uint2*>(dst);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (n0 + j < N) {
+        float x = v[j] * sm;
+        if (scale_n) x *= __ldg(scale_n + n0 + j);
+        if (!clear_accum) x += cast_in<TC>(whole ? e[j] : dst[j]);
+        e[j] = cast_out<TC>(x);
+        if (!whole) dst[j] = e[j];
+      }
+    }
+    if (whole) {
+      if (sizeof(TC) == 4) *reinterpret_cast<uint4*>(dst) = raw;
+      else *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(&raw);
     }
   }
 }

@@ -23,15 +23,28 @@ namespace frisk {
 // tiles do not fill the last wave of pairs at least half, each tile of that wave is cut into two
 // 256 x tile_n/2 items instead, so that the wave takes about half as long: items narrow_from,
 // narrow_from + 1, ... are the left and right halves of tiles narrow_from, narrow_from + 1, ...
+//
+// K planes (k_parts > 1; no narrow items then): item i is part i / tiles of tile i % tiles, covers
+// k-blocks [kb0, kb1) and leaves as fp32 into plane `part` (GemmParams::k_parts).
 struct PairItem {
-  uint32_t tile, narrow, half;
+  uint32_t tile, narrow, half, part, kb0, kb1;
 };
-__device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t narrow_from) {
+__device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t narrow_from, const GemmParams& p) {
   PairItem it;
   const uint32_t j = i - narrow_from;   // meaningful when i >= narrow_from
   it.narrow = i >= narrow_from ? 1u : 0u;
   it.tile = it.narrow ? narrow_from + (j >> 1) : i;
   it.half = it.narrow ? (j & 1u) : 0u;
+  it.part = 0;
+  it.kb0 = 0;
+  it.kb1 = p.num_kb;
+  if (p.k_parts > 1u) {
+    const uint32_t tiles = p.tiles_r * p.tiles_c;
+    it.part = i / tiles;
+    it.tile = i - it.part * tiles;
+    it.kb0 = it.part * p.kb_per;
+    it.kb1 = min(p.num_kb, it.kb0 + p.kb_per);
+  }
   return it;
 }
 
@@ -77,7 +90,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_cols = p.tmem_cols;
   const uint32_t tiles_r = p.tiles_r, tiles_c = p.tiles_c, group_r = p.group_r, group_c = p.group_c;
   const uint32_t n_items = p.n_items, narrow_from = p.narrow_from;
-  const uint32_t num_kb = p.num_kb;
   int32_t* const status = p.status;
   const uint32_t debug_mode = kMeasureBuild ? p.debug_mode : 0u;
 
@@ -124,7 +136,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t stage = 0, phase = 0, turn = 0;
     bool ok = true;
     for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
-      const PairItem it = pair_item(i, narrow_from);
+      const PairItem it = pair_item(i, narrow_from, p);
       uint32_t tr, tc;
       tile_coords(group_r, tiles_r, tiles_c, it.tile, tr, tc, group_c);
       const int32_t r0 = (int32_t)(tr * 256u + rank * 128u);
@@ -133,7 +145,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int32_t c0 = (int32_t)(tc * tile_n + it.half * (tile_n >> 1) + rank * (cols_item >> 1));
       const uint32_t b_boxes_item = it.narrow ? (b_boxes >> 1) : b_boxes;
       const uint32_t bytes_item = it.narrow ? a_stage_bytes + ((stage_bytes - a_stage_bytes) >> 1) : stage_bytes;
-      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+      for (uint32_t kb = it.kb0; kb < it.kb1; ++kb) {
         if (turn != my_turn) {  // the other producer warp loads this k-block
           turn ^= 1u;
           if (++stage == stages) {
@@ -212,6 +224,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
         const uint32_t idesc = i >= narrow_from ? idesc_narrow : idesc_wide;
+        const PairItem it = pair_item(i, narrow_from, p);
         const uint32_t acc = item & 1u;
         const uint32_t acc_phase = (item >> 1) & 1u;
         ok = bounded_wait(acc_empty0 + 8 * acc, acc_phase ^ 1, abort_flag, status,
@@ -224,7 +237,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t prev_stage = 0;
         bool have_prev = false;
         uint32_t ready = __all_sync(0xffffffffu, ptx::mbar_try_wait(full0 + 8 * stage, phase));
-        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        for (uint32_t kb = it.kb0; kb < it.kb1; ++kb) {
           if (!ready) {
             ok = bounded_wait_slow(full0 + 8 * stage, phase, abort_flag, status, kStatusMmaTimeout,
                                    0);
@@ -235,7 +248,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_addr = a_addr + a_stage_bytes;
           const uint64_t adesc0 = a_desc_base | (uint64_t)((a_addr & 0x3FFFFu) >> 4);
           const uint64_t bdesc0 = b_desc_base | (uint64_t)((b_addr & 0x3FFFFu) >> 4);
-          const uint32_t first = kb > 0 ? 1u : 0u;
+          const uint32_t first = kb > it.kb0 ? 1u : 0u;
           uint32_t next_stage = stage + 1, next_phase = phase;
           if (next_stage == stages) {
             next_stage = 0;
@@ -318,7 +331,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
     uint32_t item = 0;
     bool ok = true;
     for (uint32_t i = pair; ok && i < n_items; i += num_pairs) {
-      const PairItem it = pair_item(i, narrow_from);
+      const PairItem it = pair_item(i, narrow_from, p);
       const uint32_t acc = item & 1u;
       const uint32_t acc_phase = (item >> 1) & 1u;
       uint32_t tr, tc;
@@ -326,9 +339,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t cols_item = it.narrow ? (tile_n >> 1) : tile_n;
       const uint32_t col0 = tc * tile_n + it.half * (tile_n >> 1);
       ok = bounded_wait(acc_full0 + 8 * acc, acc_phase, abort_flag, status, kStatusEpilogueTimeout,
-                        kEpilogueBackoffNs);
+                        p.epilogue_backoff_ns);
       if (!ok) break;
       ptx::tc_fence_after();
+      if (p.k_parts > 1u) ep.C = reinterpret_cast<TC*>(p.C) + (size_t)it.part * p.plane_elems;
       const uint32_t warp_row0 = tr * 256u + rank * 128u + quarter * 32u;
       const uint32_t t_row = tmem_base + ((quarter * 32u) << 16) + acc * tile_n;
       float red = fold_identity(rf.kind);

@@ -115,9 +115,13 @@ typedef struct frisk_gemm_desc {
   int32_t panel_tiles;  /* > 0: walk the tiles in panels of this many tile columns (the panel
                            of B stays in L2 while A streams past) instead of bands of rows      */
   int32_t l2_hints;     /* bit 0: loads of A evict-first in L2; bit 1: loads of B evict-last    */
-  int32_t k_split;      /* the K-split form of an unswapped problem (a cluster per tile, or
-                           stream-K): 0 = where the plan expects it to pay, 1 = whenever one
-                           exists, -1 = never                                                   */
+  int32_t k_split;      /* the K-split forms of an unswapped problem with few tiles of C and a
+                           long K: 0 = where the plan expects one to pay, -1 = never,
+                           1 = a cluster per tile (or stream-K) whenever that form exists,
+                           2 = K planes whenever they exist (CTA-pair kernel, one work item per
+                           tile and K part, fp32 partial tiles in the workspace, summed into C
+                           by a second launch; plan_info: kernel tcgen05_pair, split_k = 1,
+                           launches = 2)                                                        */
 } frisk_gemm_desc;
 
 typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */
@@ -129,7 +133,8 @@ typedef struct frisk_gemm_plan_info {
   int32_t num_ctas;
   int32_t swap_ab;     /* 1 when the weights feed the 128-row operand (skinny path)          */
   int32_t split_k;     /* 1 when several CTAs share a tile's K range: the few-row plan, and
-                          FRISK_KERNEL_TCGEN05 plans for a few tiles against a long K          */
+                          FRISK_KERNEL_TCGEN05 / FRISK_KERNEL_TCGEN05_PAIR (K planes) plans for
+                          a few tiles against a long K                                        */
   int32_t smem_bytes;  /* dynamic shared memory per CTA                                      */
   int32_t launches;    /* kernels launched per run                                           */
   int32_t swizzle_a, swizzle_b; /* TMA/UMMA swizzle width in bytes (0, 32, 64, 128)          */
@@ -157,7 +162,8 @@ int frisk_b200_gemm_plan_info(const frisk_gemm_plan* plan, frisk_gemm_plan_info*
 
 /* Bytes of device scratch `run` needs.  0 for every plan but the stream-K forms of the K-split
  * plans (shapes whose tiles cannot be covered by thread-block clusters), plans with a fused row
- * reduce (one fp32 per row and half tile), 3xTF32 plans (twice the bytes of A and B; 256-byte
+ * reduce (one fp32 per row and half tile), K-planes plans (one fp32 copy of C per K part, at
+ * most 20 MB), 3xTF32 plans (twice the bytes of A and B; 256-byte
  * aligned) and plans for an A or B whose row pitch is not a multiple of 16 bytes (a copy of that
  * operand at a padded pitch, made by one more launch before every run); `run` takes a NULL
  * workspace when it is 0. */

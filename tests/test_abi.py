@@ -103,18 +103,32 @@ def test_odd_row_pitches_are_repacked_not_sent_to_the_cuda_cores():
 
 def test_k_split_override():
     """desc.k_split: 0 lets the plan decide (few tiles against a long K are split), -1 never splits,
-    1 splits whenever a K-split form exists."""
+    1 takes the cluster / stream-K form whenever it exists, 2 the K planes of the CTA-pair kernel."""
     auto = R.GemmPlan(512, 512, 65536, W.BF16)
     never = R.GemmPlan(512, 512, 65536, W.BF16, k_split=-1)
-    assert (auto.info["split_k"], auto.info["kernel_name"], auto.info["swap_ab"]) == (1, "tcgen05", 0)
-    assert auto.info["num_ctas"] > 4 * never.info["num_ctas"] and never.info["split_k"] == 0
+    clusters = R.GemmPlan(512, 512, 65536, W.BF16, k_split=1)
+    # a deep K on four 256 x 256 tiles: K planes (the small tiles of the cluster form would pull
+    # three times the bytes from L2)
+    assert (auto.info["split_k"], auto.info["kernel_name"], auto.info["launches"]) == (1, "tcgen05_pair", 2)
+    assert auto.workspace_bytes >= 2 * 512 * 512 * 4 and auto.workspace_bytes <= 20 << 20
+    assert (clusters.info["split_k"], clusters.info["kernel_name"], clusters.info["swap_ab"]) == (1, "tcgen05", 0)
+    assert clusters.info["launches"] == 1 and clusters.workspace_bytes == 0
+    for p in (auto, clusters):
+        assert p.info["num_ctas"] > 4 * never.info["num_ctas"]
+    assert never.info["split_k"] == 0
+    # a shallower problem keeps the cluster form: the second launch would cost more than it saves
+    small = R.GemmPlan(129, 1000, 8192, W.BF16)
+    small_planes = R.GemmPlan(129, 1000, 8192, W.BF16, k_split=2)
+    assert (small.info["split_k"], small.info["kernel_name"], small.info["launches"]) == (1, "tcgen05", 1)
+    assert (small_planes.info["kernel_name"], small_planes.info["launches"]) == ("tcgen05_pair", 2)
     big = R.GemmPlan(4096, 4096, 4096, W.BF16)
     forced = R.GemmPlan(4096, 4096, 4096, W.BF16, k_split=1)
-    assert big.info["split_k"] == 0 and forced.info["split_k"] == 1
-    for p in (auto, never, big, forced):
+    no_room = R.GemmPlan(4096, 4096, 4096, W.BF16, k_split=2)   # more tiles than pairs: no planes
+    assert big.info["split_k"] == 0 and forced.info["split_k"] == 1 and no_room.info["split_k"] == 0
+    for p in (auto, never, clusters, small, small_planes, big, forced, no_room):
         p.close()
     with pytest.raises(R.FriskError) as e:
-        R.GemmPlan(512, 512, 512, W.BF16, k_split=2)
+        R.GemmPlan(512, 512, 512, W.BF16, k_split=3)
     assert e.value.code == -1
 
 

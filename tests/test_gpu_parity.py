@@ -664,15 +664,55 @@ def test_k_split_plans_without_the_swap_match_oracle(M, N, K, ab, ct, ta, tb, cl
         plan.close()
         return R.gemm_host(w, **kw), info
 
-    out, info = run()
+    out, info = run(k_split=1)
     assert info["kernel_name"] == "tcgen05" and info["split_k"] == 1 and info["swap_ab"] == 0, info
-    assert np.array_equal(out, R.gemm_host(w))
+    assert np.array_equal(out, R.gemm_host(w, k_split=1))
     floor = ref.abs_dot(w)
     for other in (ref.ref_gemm_f64(w), W.decode(ref.ref_gemm(w), ct), torch_matmul_fp32(w)):
         ok, err, metric = W.check(W.decode(out, ct), other, ab, absdot=floor)
         assert ok, (metric, err)
     whole, info_w = run(force_kernel="tcgen05")   # the same problem as whole tiles
     assert info_w["split_k"] == 0
+    ok, err, metric = W.check(W.decode(out, ct), W.decode(whole, ct), ab, absdot=floor)
+    assert ok, (metric, err)
+
+
+@pytest.mark.parametrize("M,N,K,ab,ct,ta,tb,clear,auto", [
+    (512, 512, 32768, W.BF16, W.BF16, False, False, True, True),    # 4 tiles x 18 parts: the plan's own choice
+    (1024, 1024, 12288, W.F16, W.F16, True, False, False, True),    # A stored [K, M]; C +=
+    (300, 200, 4104, W.BF16, W.BF16, False, False, False, False),   # ragged tiles, ragged last K part, C +=
+    (129, 1000, 8192, W.E4M3, W.BF16, False, True, True, False),    # scales applied by the sum
+    (256, 130, 2048, W.F16, W.F32, False, True, False, False),      # fp32 C +=, 128-wide tiles, odd N
+    (520, 264, 2320, W.E5M2, W.BF16, False, True, True, False),     # six tiles, two unequal K parts
+])
+def test_k_planes_plans_match_oracle(M, N, K, ab, ct, ta, tb, clear, auto):
+    """K planes: the CTA-pair kernel takes one work item per (tile, K part), writes fp32 partial
+    tiles into the workspace, and a second launch sums the planes, in their order, into C (scales,
+    += C and the cast happen there).  Same oracle, same tolerances, same bits on every run."""
+    rng = np.random.default_rng(M + 7 * N + 13 * K)
+    big = ab in (W.E4M3, W.E5M2)
+    a = (rng.standard_normal((M, K)) * (4.0 if big else 1.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (4.0 if big else K ** -0.5)).astype(np.float32)
+    sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if big else None
+    sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32) if big else None
+    Aq, Bq = W.encode(a, ab), W.encode(b, ab)
+    w = W.GemmWorkload("k-planes", M, N, K, ab, ct, transA=ta, transB=tb, clear_accum=clear,
+                       A=np.ascontiguousarray(Aq.T) if ta else Aq,
+                       B=np.ascontiguousarray(Bq.T) if tb else Bq, scale_a=sa, scale_b=sb,
+                       C0=None if clear else W.encode(rng.standard_normal((M, N)).astype(np.float32), ct))
+    kw = {} if auto else {"k_split": 2}
+    plan = R.GemmPlan.for_workload(w, **kw)
+    info, ws = plan.info, plan.workspace_bytes
+    plan.close()
+    assert (info["kernel_name"], info["split_k"], info["launches"]) == ("tcgen05_pair", 1, 2), info
+    assert ws >= 2 * M * N * 4
+    out = R.gemm_host(w, **kw)
+    assert np.array_equal(out, R.gemm_host(w, **kw))
+    floor = ref.abs_dot(w)
+    for other in (ref.ref_gemm_f64(w), W.decode(ref.ref_gemm(w), ct), torch_matmul_fp32(w)):
+        ok, err, metric = W.check(W.decode(out, ct), other, ab, absdot=floor)
+        assert ok, (metric, err)
+    whole = R.gemm_host(w, k_split=-1)   # the same problem as whole tiles
     ok, err, metric = W.check(W.decode(out, ct), W.decode(whole, ct), ab, absdot=floor)
     assert ok, (metric, err)
 

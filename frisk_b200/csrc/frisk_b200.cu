@@ -480,8 +480,12 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   // longer than its main loop, and the tensor stores need a fraction of the instructions
   // (measured, bf16 8192 x 8192 x K: K = 256 58.6 -> 41.4 us, K = 512 65.3 -> 54.3 us, equal from
   // K = 1024 on; cuBLAS: 41.2 and 58.5 us).
+  // ... and when every pair has a single tile, whose epilogue nothing hides (1024 x 1024 x 4096
+  // 18.5 -> 18.1 us, 2048 x 2048 x 4096 29.5 -> 27.5 us, 2304 x 2048 x 8192 53.2 -> 51.9 us).
   const bool short_k = (d.K + bk - 1) / bk <= 32;
-  const bool epi_tma = pair && !planes && !pl->tf32 && (d.epilogue == 4 || (d.epilogue == 0 && short_k)) &&
+  const bool one_wave = pair && 2 * ((rows + 255) / 256) * ((cols + g.tile_n - 1) / g.tile_n) <=
+                                    (int64_t)(d.num_ctas > 1 ? std::min(d.num_ctas, pl->sm_count) : pl->sm_count);
+  const bool epi_tma = pair && !planes && !pl->tf32 && (d.epilogue == 4 || (d.epilogue == 0 && (short_k || one_wave))) &&
                        (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
   const size_t epi_bytes = split ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
   g.epi_staged = split ? 0u : epi_tma ? 3u : planes ? 1u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;

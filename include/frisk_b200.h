@@ -93,7 +93,7 @@ typedef struct frisk_gemm_desc {
   int32_t num_ctas;     /* persistent grid size                                              */
   int32_t band_tiles;   /* tile rows walked together by the rasterisation (L2 reuse)         */
   int32_t epilogue;     /* whole-tile tensor-core plans (0: staged as in 2, or as in 4 on a CTA-pair
-                           plan whose K has at most 32 k-blocks): 1 = every thread stores its own row
+                           plan whose K has at most 32 k-blocks or whose pairs have one tile each): 1 = every thread stores its own row
                            pieces, 2 = rows staged through shared memory and stored as 128-byte
                            pieces (a C without 16-byte aligned rows is stored element-wise
                            either way), 3 = as 2 with linear instead of swizzled staging rows:

@@ -824,7 +824,8 @@ def test_runs_are_capturable_in_a_cuda_graph_and_replay_with_new_inputs():
     """Every launch of the library is stream-ordered work on the caller's stream, so a chain of GEMMs
     can be captured into a CUDA graph once and replayed: CTA-pair kernel with the row fold in its
     epilogue (two launches) -> few-row cluster plan -> few-row stream-K plan (a memset and a launch)
-    -> 3xTF32 plan (three launches).  The replay must give the bits of the same chain launched
+    -> 3xTF32 plan (three launches) -> K planes (the pair kernel and the sum of the planes).  The
+    replay must give the bits of the same chain launched
     directly, also after the inputs' contents have changed."""
     torch = pytest.importorskip("torch")
     dev = torch.device("cuda:0")
@@ -844,9 +845,14 @@ def test_runs_are_capturable_in_a_cuda_graph_and_replay_with_new_inputs():
     y2 = torch.empty(16, 4096, device=dev, dtype=bf)
     y3 = torch.empty(16, 512, device=dev, dtype=bf)
     y4 = torch.empty(512, 1024, device=dev, dtype=torch.float32)
+    w_deep = rnd(4096, 256, scale=4096 ** -0.5)
+    x5 = torch.empty(512, 4096, device=dev, dtype=bf)   # 32 copies of y2, written inside the chain
+    y5 = torch.empty(512, 256, device=dev, dtype=bf)
     plans = [R.GemmPlan(512, K, K, W.BF16, row_reduce="max"), R.GemmPlan(16, 4096, K, W.BF16),
-             R.GemmPlan(16, 512, 4096, W.BF16), R.GemmPlan(512, 1024, 1024, W.F32, W.F32, force_kernel="tf32x3")]
-    assert [p.info["kernel_name"] for p in plans] == ["tcgen05_pair", "skinny", "skinny", "tf32x3"]
+             R.GemmPlan(16, 512, 4096, W.BF16), R.GemmPlan(512, 1024, 1024, W.F32, W.F32, force_kernel="tf32x3"),
+             R.GemmPlan(512, 256, 4096, W.BF16, k_split=2)]
+    assert [p.info["kernel_name"] for p in plans] == ["tcgen05_pair", "skinny", "skinny", "tf32x3", "tcgen05_pair"]
+    assert plans[4].info["launches"] == 2 and plans[4].workspace_bytes > 0
     assert plans[1].workspace_bytes == 0 and plans[2].workspace_bytes > 0   # clusters, then stream-K
     wss = [torch.zeros(max(p.workspace_bytes, 256), dtype=torch.uint8, device=dev) for p in plans]
 
@@ -855,8 +861,10 @@ def test_runs_are_capturable_in_a_cuda_graph_and_replay_with_new_inputs():
         plans[1].run(y1[:16], w_wide, y2, None, None, wss[1], status, stream)
         plans[2].run(y2, w_narrow, y3, None, None, wss[2], status, stream)
         plans[3].run(a32, b32, y4, None, None, wss[3], status, stream)
+        x5.view(32, 16, 4096).copy_(y2)
+        plans[4].run(x5, w_deep, y5, None, None, wss[4], status, stream)
 
-    outs = (y1, rowmax, y2, y3, y4)
+    outs = (y1, rowmax, y2, y3, y4, y5)
     chain(torch.cuda.current_stream().cuda_stream)          # also loads every kernel before the capture
     torch.cuda.synchronize()
     want = [t.clone() for t in outs]

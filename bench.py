@@ -38,11 +38,12 @@ FULL_DIMS = {
     "cfg4": (8192, 8192, 8192), "cfg5": (65536, 8192, 8192), "bf16_8192": (8192, 8192, 8192),
     "fp32_4096": (4096, 4096, 4096),   # cfg1's layout and distribution at a size the 3xTF32 plan takes
     "bf16_short_k": (8192, 8192, 256),  # cfg5's distributions with a short K: the epilogue is the kernel's time
+    "bf16_deep_k": (512, 512, 65536),   # ... with four tiles of C against a deep K: the K-planes plan
 }
 AB_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "cfg4": W.E4M3, "fp32_4096": W.F32}
 C_TYPE = {"cfg1": W.F32, "cfg2": W.F16, "fp32_4096": W.F32}
 TRANS_B = {"cfg2", "cfg4"}
-BOUND = {"cfg3": "hbm", "bf16_short_k": "hbm"}  # everything else is measured against the tensor-core peak
+BOUND = {"cfg3": "hbm", "bf16_short_k": "hbm", "bf16_deep_k": "hbm"}  # everything else is measured against the tensor-core peak
 # DRAM bytes per launch of the dominant kernel (ncu: dram__bytes_read.sum + dram__bytes_write.sum
 # of one captured launch, `--clock-control none`); None where no capture exists.
 NCU_TRAFFIC_BYTES = {
@@ -556,7 +557,9 @@ def main():
                     help="bit 0: A loads evict-first, bit 1: B loads evict-last (0: the plan's choice)")
     ap.add_argument("--epilogue", type=int, default=0,
                     help="1: per-thread row stores, 2: rows staged through swizzled shared memory, 3: staged through "
-                         "linear rows (0: the plan's choice)")
+                         "linear rows, 4: TMA tensor stores (0: the plan's choice)")
+    ap.add_argument("--k-split", type=int, default=0,
+                    help="-1: never split K, 1: over clusters or stream-K, 2: K planes (0: the plan's choice)")
     ap.add_argument("--rows", type=int, default=0,
                     help="run the workload on this many rows only (a small case for a profiler)")
     args = ap.parse_args()
@@ -606,7 +609,7 @@ def main():
     C = torch.empty((rows, N), device=dev, dtype=out_dtype(torch, name))
     plan = R.GemmPlan(rows, N, K, ab, ct, transB=name in TRANS_B, scales=sa is not None,
                       band_tiles=args.band, epilogue=args.epilogue, panel_tiles=args.panel,
-                      l2_hints=args.l2_hints)
+                      l2_hints=args.l2_hints, k_split=args.k_split)
     ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream

@@ -717,6 +717,49 @@ def test_k_planes_plans_match_oracle(M, N, K, ab, ct, ta, tb, clear, auto):
     assert ok, (metric, err)
 
 
+@pytest.mark.parametrize("ldc_extra,c_off", [(24, 0), (3, 0), (24, 2)])
+def test_k_planes_keep_to_their_columns_and_their_workspace(ldc_extra, c_off):
+    """The sum launch of a K-planes plan writes C's N columns and nothing else -- at a padded pitch
+    that allows vector stores, at an odd one, and from a base off the 16-byte grid -- and the two
+    launches stay inside the workspace the plan asked for."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    M, N, K = 300, 200, 2048
+    rng = np.random.default_rng(77 + ldc_extra + c_off)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * K ** -0.5).astype(np.float32)
+    c0 = rng.standard_normal((M, N)).astype(np.float32)
+    w = W.GemmWorkload("planes-ld", M, N, K, W.BF16, W.BF16, clear_accum=False, A=W.bf16_encode(a),
+                       B=W.bf16_encode(b), C0=W.bf16_encode(c0))
+    ldc = N + ldc_extra
+    plan = R.GemmPlan(M, N, K, W.BF16, ldc=ldc, clear_accum=False, k_split=2)
+    assert (plan.info["kernel_name"], plan.info["launches"]) == ("tcgen05_pair", 2)
+    guard = 4096
+    ws_bytes = plan.workspace_bytes
+    cbuf = torch.full((guard + M * ldc,), 0x7FC0, dtype=torch.int16, device=dev)   # NaN canaries
+    cview = cbuf[guard // 2 + c_off: guard // 2 + c_off + M * ldc].view(M, ldc)
+    cview[:, :N] = torch.from_numpy(w.C0.view(np.int16)).to(dev)
+    wsbuf = torch.full((guard * 2 + ws_bytes,), 0xCD, dtype=torch.uint8, device=dev)
+    A = torch.from_numpy(w.A.view(np.int16)).to(dev)
+    B = torch.from_numpy(w.B.view(np.int16)).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    rc = R.lib().frisk_b200_gemm_run(plan._h, A.data_ptr(), B.data_ptr(), cview.data_ptr(), None, None,
+                                     wsbuf.data_ptr() + guard, ws_bytes, status.data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    R.check_status(status)
+    plan.close()
+    nan16 = np.int16(0x7FC0)
+    flat = cbuf.cpu().numpy()
+    body = flat[guard // 2 + c_off: guard // 2 + c_off + M * ldc].reshape(M, ldc)
+    assert (flat[:guard // 2 + c_off] == nan16).all() and (flat[guard // 2 + c_off + M * ldc:] == nan16).all()
+    assert (body[:, N:] == nan16).all(), "the sum wrote outside C's columns"
+    assert (wsbuf[:guard] == 0xCD).all() and (wsbuf[guard + ws_bytes:] == 0xCD).all()
+    got = W.bf16_decode(np.ascontiguousarray(body[:, :N]).view(np.uint16))
+    ok, err, metric = W.check(got, ref.ref_gemm_f64(w), W.BF16, absdot=ref.abs_dot(w))
+    assert ok, (metric, err)
+
+
 def test_planner_choices_over_seeded_random_problems_match_the_oracle():
     """Whatever the planner picks -- whole tiles, CTA pairs, few-row clusters, stream-K, K-split
     without the swap, repacked operands, CUDA cores -- the result is the oracle's.  48 seeded

@@ -748,11 +748,12 @@ def main():
         others = {}
         tensor_peaks = measure_tensor_peaks(torch, R, dev, {"e4m3": 0.37, "bf16": 0.70, "tf32": 0.45})
         line["tensor_peaks_measured"] = tensor_peaks
-        for other in ("cfg1", "cfg2", "cfg3", "cfg4", "bf16_8192", "fp32_4096"):
+        for other in ("cfg1", "cfg2", "cfg3", "cfg4", "bf16_8192", "fp32_4096", "bf16_short_k", "bf16_deep_k"):
             if other == name:
                 continue
             m, n, k = FULL_DIMS[other]
-            small = other in ("cfg1", "cfg2", "cfg3")  # operands (nearly) fit in L2: rotate copies
+            # operands (nearly) fit in L2: rotate copies
+            small = other in ("cfg1", "cfg2", "cfg3", "bf16_short_k", "bf16_deep_k")
             ms, oinfo, l2_note = time_device(torch, R, other, m, n, k,
                                              max(args.steps, 200 if small else 10), args.warmup, dev,
                                              seed=int(other[-1]) if other.startswith("cfg") else 5,
@@ -767,6 +768,9 @@ def main():
                                                "launches_per_graph": oinfo["cuda_graph_launches"]}
             if other == "cfg2":
                 others[other]["library_same_shape"] = library_matmul(torch, dev, m, n, k, torch.float16)
+            if other in ("bf16_short_k", "bf16_deep_k"):   # planner rules made for shapes like these
+                others[other]["library_same_shape"] = library_matmul(torch, dev, m, n, k, torch.bfloat16,
+                                                                     b_row_major=True)
             if other == "cfg1":   # the same problem forced onto the 3xTF32 plan (three launches)
                 ms3, _, _ = time_device(torch, R, other, m, n, k, 200, args.warmup, dev, seed=1, rotate=True,
                                         force_kernel="tf32x3")
@@ -832,25 +836,30 @@ def time_fused_row_reduce(torch, R, dev, steps, warmup):
     return out
 
 
-def library_matmul(torch, dev, m, n, k, dtype):
+def library_matmul(torch, dev, m, n, k, dtype, b_row_major=False):
     """torch.matmul (cuBLAS) on the same shape with rotating operands, for context beside a
-    configuration whose roofline denominator was measured on another shape."""
+    configuration whose roofline denominator was measured on another shape.  B is stored [N, K]
+    (cfg2's order) unless `b_row_major` ([K, N], the order of the bf16 workloads)."""
     copies = 4
     a = [torch.randn(m, k, device=dev).to(dtype) * k ** -0.5 for _ in range(copies)]
-    b = [torch.randn(n, k, device=dev).to(dtype) * k ** -0.5 for _ in range(copies)]
+    if b_row_major:
+        b = [torch.randn(k, n, device=dev).to(dtype) * k ** -0.5 for _ in range(copies)]
+    else:
+        b = [(torch.randn(n, k, device=dev).to(dtype) * k ** -0.5).t() for _ in range(copies)]
+    c = [torch.empty(m, n, device=dev, dtype=dtype) for _ in range(copies)]
     for i in range(copies):
-        torch.matmul(a[i], b[i].t())
+        torch.matmul(a[i], b[i], out=c[i])
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     steps = 200
     e0.record()
     for i in range(steps):
-        torch.matmul(a[i % copies], b[i % copies].t())
+        torch.matmul(a[i % copies], b[i % copies], out=c[i % copies])
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     return {"ms": round(ms, 5), "tflops": round(2.0 * m * n * k / (ms * 1e-3) / 1e12, 2),
-            "how": "torch.matmul, same rotation of operands, 200 launches"}
+            "how": "torch.matmul, four rotating copies of A, B and C, 200 launches"}
 
 
 def time_allgather(torch, R, S, dist, plan, A, B, C, sa, sb, ws, status, stream, M, N, world, rank, dev,

@@ -862,6 +862,29 @@ int launch_simt_tm(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaSt
   return FRISK_OK;
 }
 
+// fp32 problems the pipelined CUDA-core kernel takes (gemm_simt.cuh): the tile of the generic
+// kernel's 32-row form without edges, rows of A and B that cp.async can read 16 bytes at a time.
+bool simt_f32_pipelined_ok(const frisk_gemm_desc& d, const frisk::SimtParams& sp) {
+  if (d.a_type != FRISK_DT_F32 || d.transA || d.transB) return false;
+  if (d.M % 32 || d.N % frisk::kSimtTile || d.K % frisk::kSimtPipeBK) return false;
+  if (d.lda % 4 || d.ldb % 4 || (uintptr_t)sp.A % 16 || (uintptr_t)sp.B % 16) return false;
+  // where the generic kernel would take 32-row tiles (launch_simt_in; plan_info reports that tile)
+  const int64_t ctas64 = ((d.N + 63) / 64) * ((d.M + 63) / 64);
+  return d.M > 32 && ctas64 < 148;
+}
+
+int launch_simt_f32_pipelined(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaStream_t st) {
+  const dim3 grid((unsigned)(d.N / frisk::kSimtTile), (unsigned)(d.M / 32));
+  switch (d.c_type) {
+    case FRISK_DT_F32: frisk::gemm_simt_f32_pipelined_kernel<float><<<grid, 128, 0, st>>>(sp); break;
+    case FRISK_DT_F16: frisk::gemm_simt_f32_pipelined_kernel<__half><<<grid, 128, 0, st>>>(sp); break;
+    case FRISK_DT_BF16: frisk::gemm_simt_f32_pipelined_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(sp); break;
+    default: return FRISK_ERR_UNSUPPORTED;
+  }
+  FRISK_CUDA(cudaGetLastError());
+  return FRISK_OK;
+}
+
 template <typename TIn>
 int launch_simt_in(const frisk_gemm_desc& d, const frisk::SimtParams& sp, cudaStream_t st) {
   // 32-row tiles when 64-row tiles would leave SMs idle (fp32 512^3: 64 CTAs for 148 SMs)
@@ -880,6 +903,7 @@ int launch_simt(const frisk_gemm_desc& d, const void* A, const void* B, void* C,
   sp.M = d.M; sp.N = d.N; sp.K = d.K;
   sp.lda = d.lda; sp.ldb = d.ldb; sp.ldc = d.ldc;
   sp.transA = d.transA; sp.transB = d.transB; sp.clear_accum = d.clear_accum;
+  if (simt_f32_pipelined_ok(d, sp)) return launch_simt_f32_pipelined(d, sp, st);
   switch (d.a_type) {
     case FRISK_DT_F32: return launch_simt_in<float>(d, sp, st);
     case FRISK_DT_F16: return launch_simt_in<__half>(d, sp, st);

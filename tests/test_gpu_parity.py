@@ -316,6 +316,49 @@ def test_misaligned_pointers_take_the_cuda_core_kernel():
     plan.close()
 
 
+@pytest.mark.parametrize("M,N,K,ct,clear,ldx", [
+    (512, 512, 512, W.F32, True, 0),     # the fp32 configuration
+    (64, 128, 96, W.F32, False, 4),      # three slices, C +=, padded pitches
+    (96, 64, 32, W.BF16, True, 0),       # one slice, bf16 C
+])
+def test_fp32_pipelined_cuda_core_kernel_gives_the_generic_kernels_bits(M, N, K, ct, clear, ldx):
+    """fp32 problems without edges (rows of 32, columns of 64, K of 32, 16-byte aligned row-major
+    A and B) run on the cp.async-pipelined CUDA-core kernel; it adds the same products in the same
+    order as the generic kernel, which the same problem takes when A sits 4 bytes off the 16-byte
+    grid.  Both must give the same bits, and the oracle's."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(M + N + K)
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (M, N)).astype(np.float32)
+    lda, ldb = K + ldx, N + ldx
+    Ah = np.zeros((M, lda), np.float32); Ah[:, :K] = a
+    Bh = np.zeros((K, ldb), np.float32); Bh[:, :N] = b
+    w = W.GemmWorkload("f32-pipe", M, N, K, W.F32, ct, clear_accum=clear, A=a, B=b,
+                       C0=None if clear else W.encode(c0, ct))
+    plan = R.GemmPlan(M, N, K, W.F32, ct, lda=lda, ldb=ldb, clear_accum=clear)
+    assert plan.info["kernel_name"] == "simt" and plan.info["tile_m"] == 32
+    Bd = torch.from_numpy(Bh).to(dev)
+    abuf = torch.zeros(M * lda + 4, dtype=torch.float32, device=dev)
+    outs = []
+    for off in (0, 1):   # aligned: pipelined kernel; one float further: the generic one
+        abuf.zero_()
+        Ad = abuf[off:off + M * lda].view(M, lda)
+        Ad.copy_(torch.from_numpy(Ah))
+        Cd = torch.from_numpy(np.ascontiguousarray(w.C0 if not clear else W.encode(np.zeros((M, N), np.float32), ct))
+                              .view(np.int32 if ct == W.F32 else np.int16)).to(dev)
+        plan.run(Ad, Bd, Cd)
+        torch.cuda.synchronize()
+        outs.append(Cd.cpu().numpy().view(W.storage_numpy_dtype(ct)))
+    plan.close()
+    assert np.array_equal(outs[0], outs[1])
+    got = W.decode(outs[0], ct)
+    # (a 16-bit C is held to the 16-bit bound: its last rounding is what the error is then)
+    ok, err, metric = W.check(got, ref.ref_gemm_f64(w), ct, absdot=ref.abs_dot(w))
+    assert ok, (metric, err)
+
+
 def test_stream_k_workspace_may_be_shared_and_dirty():
     """The workspace is scratch: two stream-K plans with different slot sizes run alternately on
     ONE buffer, and a buffer handed back full of other bytes, give the same bits as private,

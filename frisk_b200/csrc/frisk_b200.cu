@@ -378,7 +378,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     // shared memory) needs tiles x cluster size CTAs to cover most of the SMs; otherwise the
     // stream-K plan (mode 2) spreads the work evenly over all of them.
     // Candidates: 256- or 128-row tiles with the largest power-of-two cluster that keeps the grid
-    // within the SMs, most CTAs first, then the larger tile (fewer, larger TMA boxes).  `cluster_try` skips the candidates the device could not place.
+    // within the SMs, most CTAs first, then the larger tile (fewer, larger TMA boxes).
+    // `cluster_try` skips the candidates the device could not place.
     const uint32_t kbs = (uint32_t)((d.K + bk - 1) / bk);
     // percent of the SMs a cluster plan has to use: measured, 64 CTAs in clusters still beat
     // stream-K over all SMs (16x2048x2048: 10.4 against 15.5 us; 32x2048x8192: 18.7 against 25.7)
@@ -485,7 +486,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   const bool short_k = (d.K + bk - 1) / bk <= 32;
   const bool one_wave = pair && 2 * ((rows + 255) / 256) * ((cols + g.tile_n - 1) / g.tile_n) <=
                                     (int64_t)(d.num_ctas > 1 ? std::min(d.num_ctas, pl->sm_count) : pl->sm_count);
-  const bool epi_tma = pair && !planes && !pl->tf32 && (d.epilogue == 4 || (d.epilogue == 0 && (short_k || one_wave))) &&
+  const bool want_tma = d.epilogue == 4 || (d.epilogue == 0 && (short_k || one_wave));
+  const bool epi_tma = pair && !planes && !pl->tf32 && want_tma &&
                        (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
   const size_t epi_bytes = split ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
   g.epi_staged = split ? 0u : epi_tma ? 3u : planes ? 1u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
@@ -757,7 +759,8 @@ int launch_kplanes_sum_t(const frisk_gemm_plan* pl, const frisk::GemmParams& g, 
   const int64_t work = d.M * ((d.N + 3) / 4);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
-  cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, 8 * (int64_t)pl->sm_count)), 1, 1);
+  const int64_t blocks = std::min<int64_t>((work + 255) / 256, 8 * (int64_t)pl->sm_count);
+  cfg.gridDim = dim3((unsigned)std::max<int64_t>(1, blocks), 1, 1);
   cfg.blockDim = dim3(256, 1, 1);
   cfg.stream = st;
   cudaLaunchAttribute attr;
@@ -1136,8 +1139,8 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       const uint64_t kparts = std::min<uint64_t>((uint64_t)(pl->sm_count / 2) / tiles256, kbs / 8);
       const bool planes_ok = pair_ok && kparts >= 2;
       bool planes = planes_ok && d.k_split == 2;
-      if (!planes &&
-          (force_split || (few ? kbs >= 48 : kbs >= 192)) && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
+      const bool deep = force_split || (few ? kbs >= 48 : kbs >= 192);
+      if (!planes && deep && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
         // narrower tiles give a small C more of them: the width with the most CTAs wins, a
         // cluster plan (the reduction stays on chip) before a stream-K one
         const frisk_gemm_plan_info whole = pl->info;

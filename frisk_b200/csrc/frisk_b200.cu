@@ -16,6 +16,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_pair.cuh"
+#include "gemm_tcgen05_pair_ksplit.cuh"
 #include "mma_peak.cuh"
 #include "tf32_split.cuh"
 
@@ -86,6 +87,7 @@ struct frisk_gemm_plan {
   frisk_gemm_desc kd;
   bool tf32 = false;
   bool tf32_pair = false;        // which whole-tile kernel runs the split problem
+  int pair_cluster = 0;          // > 0: the CTA-pair kernel with K split over this many pairs per cluster
   size_t tf32_a_bytes = 0, tf32_b_bytes = 0;
   // Operands whose row pitch is not a multiple of 16 bytes (no tensor map can describe them) are
   // copied into the front of the workspace at a padded pitch (kd.lda / kd.ldb) before every run.
@@ -334,9 +336,12 @@ bool pair_tail_split(uint64_t tile_n, uint64_t tiles, uint64_t pairs) {
 // per (tile, part), the partial tiles written as fp32 planes into the workspace and folded into C
 // by a second launch (kplanes_sum_kernel).
 void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0, bool ksplit = false,
-                  int kparts = 0) {
+                  int kparts = 0, int pair_cluster = 0) {
   const bool split = swap || ksplit;
   const bool planes = pair && !split && kparts > 1 && !pl->kd.row_reduce && !pl->tf32;
+  // K split over the pairs of a cluster (gemm_tcgen05_pair_ksplit.cuh): 256 x 128 tiles
+  const bool pcl = pair && !split && !planes && pair_cluster > 1 && !pl->kd.row_reduce && !pl->tf32;
+  pl->pair_cluster = pcl ? pair_cluster : 0;
   const frisk_gemm_desc& d = pl->kd;
   frisk::GemmParams& g = pl->gp;
   memset(&g, 0, sizeof g);
@@ -360,7 +365,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
     // 32 KiB, eight of them instead of six, and it is bytes in flight that such an operand-streaming
     // shape waits for (256 x 8192 x 8192: 39.3 -> 35.5 us, 256 x 4096 x 4096: 21.6 -> 18.8 us,
     // 8192 x 256 x 8192: 40.1 -> 37.1 us).
-    if (pair && !planes && !d.tile_n && tn == 256 &&
+    if (pcl) tn = 128;
+    if (pair && !planes && !pcl && !d.tile_n && tn == 256 &&
         2 * ((rows + 255) / 256) * ((cols + 255) / 256) <= (int64_t)std::max(1, pl->sm_count / 2))
       tn = 128;
     g.tile_n = tn;
@@ -487,9 +493,10 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   const bool one_wave = pair && 2 * ((rows + 255) / 256) * ((cols + g.tile_n - 1) / g.tile_n) <=
                                     (int64_t)(d.num_ctas > 1 ? std::min(d.num_ctas, pl->sm_count) : pl->sm_count);
   const bool want_tma = d.epilogue == 4 || (d.epilogue == 0 && (short_k || one_wave));
-  const bool epi_tma = pair && !planes && !pl->tf32 && want_tma &&
+  const bool epi_tma = pair && !planes && !pcl && !pl->tf32 && want_tma &&
                        (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
-  const size_t epi_bytes = split ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
+  const size_t epi_bytes = (split || pcl) ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
+  if (pcl) red_bytes = (size_t)g.tile_n * 128 * sizeof(float);   // [pair][column][row of the share]
   g.epi_staged = split ? 0u : epi_tma ? 3u : planes ? 1u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
   uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
@@ -517,7 +524,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   g.split_mode = split ? 1 : 0;
   // a split plan has one or two work items per CTA, so the wake-up delay of a sleeping epilogue
   // warp is paid at the end of the kernel; a whole-tile plan hides it behind the next tile
-  g.epilogue_backoff_ns = (split || planes) ? 0u : frisk::kEpilogueBackoffNs;
+  g.epilogue_backoff_ns = (split || planes || pcl) ? 0u : frisk::kEpilogueBackoffNs;
 #ifdef FRISK_B200_MEASURE
   if (const char* e = getenv("FRISK_B200_EPI_BACKOFF")) g.epilogue_backoff_ns = (uint32_t)atoi(e);
 #endif
@@ -545,7 +552,12 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   uint32_t ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)pl->sm_count);
   if (d.num_ctas > 0) ctas = (uint32_t)std::min<uint64_t>(units, (uint64_t)d.num_ctas);
   g.n_items = g.narrow_from = (uint32_t)(planes ? tiles * g.k_parts : tiles);
-  if (pair) {  // one cluster of two CTAs per tile in flight
+  if (pcl) {
+    g.cluster_k = (uint32_t)pair_cluster;
+    g.kb_per = (g.num_kb + g.cluster_k - 1) / g.cluster_k;
+    if ((g.cluster_k - 1) * g.kb_per >= g.num_kb) pl->plan_error = FRISK_ERR_UNSUPPORTED;   // an empty part
+    ctas = (uint32_t)tiles * 2u * g.cluster_k;
+  } else if (pair) {  // one cluster of two CTAs per tile in flight
     uint64_t slots = (uint64_t)pl->sm_count / 2;
     if (d.num_ctas > 1) slots = std::min<uint64_t>(slots, (uint64_t)d.num_ctas / 2);
     slots = std::max<uint64_t>(slots, 1);
@@ -603,7 +615,7 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   in.stages = (int)g.stages;
   in.num_ctas = (int)ctas;
   in.swap_ab = swap;
-  in.split_k = split || planes;
+  in.split_k = split || planes || pcl;
   in.smem_bytes = (int)pl->dyn_smem;
   in.launches = ((!split && d.row_reduce) || planes) ? 2 : 1;   // the fold's finalize launch / the planes' sum
   in.swizzle_a = pl->lay_a.swizzle_bytes;
@@ -730,6 +742,57 @@ int launch_pair_tf(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t
 template <typename TC>
 int launch_pair_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st) {
   return launch_pair_tf<TC>(pl, g, st);
+}
+
+// The CTA-pair kernel with K split over the pairs of a cluster: one cluster of 2 x cluster_k CTAs
+// per tile.  `occupancy`: ask how many such clusters the device holds at once instead of launching.
+template <typename TC> struct PairKsplitKernelTag {};
+template <typename TC>
+int launch_pair_ksplit_t(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st,
+                         int* occupancy = nullptr) {
+  auto kern = frisk::gemm_tcgen05_pair_ksplit_kernel<TC>;
+  if (int rc = ensure_dyn_smem<PairKsplitKernelTag<TC>>(kern, pl->device)) return rc;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3((unsigned)pl->info.num_ctas, 1, 1);
+  cfg.blockDim = dim3(frisk::kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = kLaunchDynSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2u * g.cluster_k;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  if (occupancy) {
+    cfg.numAttrs = 1;
+    FRISK_CUDA(cudaOccupancyMaxActiveClusters(occupancy, kern, &cfg));
+    return FRISK_OK;
+  }
+  cfg.numAttrs = 2;
+  FRISK_CUDA(cudaLaunchKernelEx(&cfg, kern, pl->tmap_a, pl->tmap_b, g));
+  return FRISK_OK;
+}
+
+int launch_pair_ksplit(frisk_gemm_plan* pl, const frisk::GemmParams& g, cudaStream_t st, int* occupancy = nullptr) {
+  switch (pl->d.c_type) {
+    case FRISK_DT_F32: return launch_pair_ksplit_t<float>(pl, g, st, occupancy);
+    case FRISK_DT_F16: return launch_pair_ksplit_t<__half>(pl, g, st, occupancy);
+    case FRISK_DT_BF16: return launch_pair_ksplit_t<__nv_bfloat16>(pl, g, st, occupancy);
+    default: return FRISK_ERR_UNSUPPORTED;
+  }
+}
+
+// Whether the device can hold all of the plan's clusters at once (they wait for one another).
+bool pair_clusters_fit(frisk_gemm_plan* pl) {
+  int n = 0;
+  if (launch_pair_ksplit(pl, pl->gp, nullptr, &n) != FRISK_OK) {
+    cudaGetLastError();
+    return false;
+  }
+  return (int64_t)n * 2 * pl->gp.cluster_k >= (int64_t)pl->info.num_ctas;
 }
 
 // The second launch of a plan with a fused row reduce: folds the per-tile results of every row.
@@ -982,7 +1045,7 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
   if (d.force_kernel < 0 || d.force_kernel > 5 || d.stages < 0 || d.num_ctas < 0 || d.band_tiles < 0)
     return FRISK_ERR_INVALID_ARGUMENT;
   if (d.epilogue < 0 || d.epilogue > 4 || d.row_reduce < 0 || d.row_reduce > 4 ||
-      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3 || d.k_split < -1 || d.k_split > 2)
+      d.panel_tiles < 0 || d.l2_hints < 0 || d.l2_hints > 3 || d.k_split < -1 || d.k_split > 3)
     return FRISK_ERR_INVALID_ARGUMENT;
   d.row_reduce_clear = d.row_reduce_clear != 0;
 
@@ -1139,8 +1202,38 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       const uint64_t kparts = std::min<uint64_t>((uint64_t)(pl->sm_count / 2) / tiles256, kbs / 8);
       const bool planes_ok = pair_ok && kparts >= 2;
       bool planes = planes_ok && d.k_split == 2;
+      // K split over the pairs of a cluster (gemm_tcgen05_pair_ksplit.cuh): 256 x 128 tiles, four
+      // pairs per cluster when the SMs allow, else two; at least eight k-blocks per pair.
+      // Taken where measured ahead: six to nine tiles, clusters of four pairs that the device can
+      // place all at once, K up to 192 k-blocks (deeper: K planes).  bf16, clusters of single
+      // CTAs -> clusters of pairs (cuBLAS): 512 x 512 x 2048 11.3 (whole tiles) -> 9.5 us (13.6),
+      // x 4096 12.8 -> 11.5 us (13.7), x 8192 18.8 -> 15.2 us (14.6); 384 x 384 x 8192
+      // 17.1 -> 14.8 us (14.5).  With two pairs per cluster, or four tiles, the fold of the
+      // partials costs what the shorter K saves (1024 x 1024 x 4096 18.3 -> 17.8 us,
+      // 1024 x 512 x 4096 15.6 -> 17.0 us, 256 x 256 x 4096 9.0 -> 10.5 us).
       const bool deep = force_split || (few ? kbs >= 48 : kbs >= 192);
-      if (!planes && deep && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
+      const uint64_t tiles128 = (uint64_t)((d.M + 255) / 256) * (uint64_t)((d.N + 127) / 128);
+      const int whole_kernel = pl->info.kernel;
+      int pcl = 0;
+      for (int sp : {4, 2})
+        if (!pcl && pair_ok && tiles128 * 2 * sp <= (uint64_t)pl->sm_count && kbs >= 8u * sp) pcl = sp;
+      // (and tiles that are not mostly padding: at most a quarter of their rows and columns)
+      const int64_t rows_pad = (d.M + 255) / 256 * 256, cols_pad = (d.N + 127) / 128 * 128;
+      const bool full_tiles = 4 * (rows_pad - d.M) <= rows_pad && 4 * (cols_pad - d.N) <= cols_pad;
+      const bool pcl_auto = d.k_split == 0 && pcl == 4 && tiles128 >= 6 && tiles128 <= 9 && kbs <= 192 &&
+                            full_tiles;
+      bool took_pcl = false;
+      if (pcl && (d.k_split == 3 || pcl_auto)) {
+        plan_tcgen05(pl, /*swap=*/false, /*pair=*/true, 0, false, 0, pcl);
+        took_pcl = !pl->plan_error && (!pl->have_device || pair_clusters_fit(pl));
+        if (!took_pcl && d.k_split == 3 && pcl == 4) {   // forced: two pairs per cluster will do
+          plan_tcgen05(pl, /*swap=*/false, /*pair=*/true, 0, false, 0, 2);
+          took_pcl = !pl->plan_error && (!pl->have_device || pair_clusters_fit(pl));
+        }
+        // no cluster shape the device can place: back to whole tiles, and to the choices below
+        if (!took_pcl) plan_tcgen05(pl, /*swap=*/false, whole_kernel == FRISK_KERNEL_TCGEN05_PAIR);
+      }
+      if (!took_pcl && !planes && deep && t128 * kbs * (uint64_t)(pl->sm_count + 1) < (1ull << 32)) {
         // narrower tiles give a small C more of them: the width with the most CTAs wins, a
         // cluster plan (the reduction stays on chip) before a stream-K one
         const frisk_gemm_plan_info whole = pl->info;
@@ -1274,7 +1367,7 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
   cudaStream_t st = reinterpret_cast<cudaStream_t>(args->stream);
   const float* sa = d.scale_mode ? args->scale_a : nullptr;
   const float* sb = d.scale_mode ? args->scale_b : nullptr;
-  const bool whole_tile_tc = pl->gp.split_mode == 0 && pl->gp.k_parts <= 1u && (pl->info.kernel == FRISK_KERNEL_TCGEN05 ||
+  const bool whole_tile_tc = pl->gp.split_mode == 0 && pl->gp.k_parts <= 1u && !pl->pair_cluster && (pl->info.kernel == FRISK_KERNEL_TCGEN05 ||
                                                         pl->info.kernel == FRISK_KERNEL_TCGEN05_PAIR);
 
   if (pl->tf32) {
@@ -1420,7 +1513,9 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
     g.row_scale = g.col_scale = nullptr;
   }
   int rc;
-  if (planes) {
+  if (pl->pair_cluster) {
+    rc = launch_pair_ksplit(pl, g, st);
+  } else if (planes) {
     rc = launch_pair_t<float>(pl, g, st);
     if (!rc) {
       const float* w = static_cast<const float*>(workspace);

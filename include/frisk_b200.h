@@ -121,7 +121,11 @@ typedef struct frisk_gemm_desc {
                            2 = K planes whenever they exist (CTA-pair kernel, one work item per
                            tile and K part, fp32 partial tiles in the workspace, summed into C
                            by a second launch; plan_info: kernel tcgen05_pair, split_k = 1,
-                           launches = 2)                                                        */
+                           launches = 2),
+                           3 = K split over the CTA pairs of a cluster whenever such a plan exists
+                           (256 x 128 tiles, two or four pairs per tile, partials folded through
+                           distributed shared memory; kernel tcgen05_pair, split_k = 1, one
+                           launch, no workspace)                                                */
 } frisk_gemm_desc;
 
 typedef struct frisk_gemm_plan frisk_gemm_plan; /* opaque */

@@ -127,8 +127,18 @@ def test_k_split_override():
     assert big.info["split_k"] == 0 and forced.info["split_k"] == 1 and no_room.info["split_k"] == 0
     for p in (auto, never, clusters, small, small_planes, big, forced, no_room):
         p.close()
+    # eight tiles of 256 x 128 against 64 k-blocks: clusters of four CTA pairs, one launch, no
+    # workspace (k_split = 3 forces the form, with two pairs per cluster where four do not fit)
+    pairs = R.GemmPlan(512, 512, 4096, W.BF16)
+    pairs2 = R.GemmPlan(1024, 1024, 4096, W.BF16, k_split=3)
+    assert (pairs.info["kernel_name"], pairs.info["split_k"], pairs.info["launches"]) == ("tcgen05_pair", 1, 1)
+    assert (pairs.info["num_ctas"], pairs.info["tile_n"], pairs.workspace_bytes) == (64, 128, 0)
+    assert (pairs2.info["split_k"], pairs2.info["num_ctas"], pairs2.workspace_bytes) == (1, 128, 0)
+    assert R.GemmPlan(1024, 1024, 4096, W.BF16).info["split_k"] == 0   # not the plan's own choice
+    for p in (pairs, pairs2):
+        p.close()
     with pytest.raises(R.FriskError) as e:
-        R.GemmPlan(512, 512, 512, W.BF16, k_split=3)
+        R.GemmPlan(512, 512, 512, W.BF16, k_split=4)
     assert e.value.code == -1
 
 

@@ -760,6 +760,47 @@ def test_k_planes_plans_match_oracle(M, N, K, ab, ct, ta, tb, clear, auto):
     assert ok, (metric, err)
 
 
+@pytest.mark.parametrize("M,N,K,ab,ct,ta,tb,clear,auto,ctas", [
+    (512, 512, 4096, W.BF16, W.BF16, False, False, True, True, 64),     # 8 tiles x 4 pairs: the plan's own choice
+    (384, 384, 8192, W.F16, W.F32, False, True, False, True, 48),       # fp32 C +=, B stored [N, K]
+    (1024, 1024, 4104, W.BF16, W.BF16, True, False, True, False, 128),  # two pairs per cluster, A stored [K, M], ragged K
+    (300, 200, 2056, W.BF16, W.F16, False, False, False, False, 32),    # ragged tiles, C +=
+    (512, 500, 4096, W.E4M3, W.BF16, False, True, True, False, 64),     # scales in the fold
+    (260, 128, 8192, W.E5M2, W.BF16, False, True, True, False, 16),     # one tile column, mostly padding rows
+])
+def test_k_split_over_cta_pairs_of_a_cluster_matches_oracle(M, N, K, ab, ct, ta, tb, clear, auto, ctas):
+    """K split over the CTA pairs of a cluster: every pair multiplies one K part of a 256 x 128 tile
+    with two-SM MMAs, the partial tiles meet through distributed shared memory and each CTA adds
+    the images of the rows it owns in pair order.  One launch, no workspace, the same bits on
+    every run; same oracle and tolerances as every other plan."""
+    rng = np.random.default_rng(M + 7 * N + 13 * K)
+    big = ab in (W.E4M3, W.E5M2)
+    a = (rng.standard_normal((M, K)) * (4.0 if big else 1.0)).astype(np.float32)
+    b = (rng.standard_normal((K, N)) * (4.0 if big else K ** -0.5)).astype(np.float32)
+    sa = (rng.uniform(0.5, 2.0, M) / 448.0).astype(np.float32) if big else None
+    sb = (rng.uniform(0.5, 2.0, N) / 448.0).astype(np.float32) if big else None
+    Aq, Bq = W.encode(a, ab), W.encode(b, ab)
+    w = W.GemmWorkload("pair-clusters", M, N, K, ab, ct, transA=ta, transB=tb, clear_accum=clear,
+                       A=np.ascontiguousarray(Aq.T) if ta else Aq,
+                       B=np.ascontiguousarray(Bq.T) if tb else Bq, scale_a=sa, scale_b=sb,
+                       C0=None if clear else W.encode(rng.standard_normal((M, N)).astype(np.float32), ct))
+    kw = {} if auto else {"k_split": 3}
+    plan = R.GemmPlan.for_workload(w, **kw)
+    info, ws = plan.info, plan.workspace_bytes
+    plan.close()
+    assert (info["kernel_name"], info["split_k"], info["launches"], info["tile_n"]) == ("tcgen05_pair", 1, 1, 128), info
+    assert info["num_ctas"] == ctas and ws == 0, info
+    out = R.gemm_host(w, **kw)
+    assert np.array_equal(out, R.gemm_host(w, **kw))
+    floor = ref.abs_dot(w)
+    for other in (ref.ref_gemm_f64(w), W.decode(ref.ref_gemm(w), ct), torch_matmul_fp32(w)):
+        ok, err, metric = W.check(W.decode(out, ct), other, ab, absdot=floor)
+        assert ok, (metric, err)
+    whole = R.gemm_host(w, k_split=-1)   # the same problem as whole tiles
+    ok, err, metric = W.check(W.decode(out, ct), W.decode(whole, ct), ab, absdot=floor)
+    assert ok, (metric, err)
+
+
 @pytest.mark.parametrize("ldc_extra,c_off", [(24, 0), (3, 0), (24, 2)])
 def test_k_planes_keep_to_their_columns_and_their_workspace(ldc_extra, c_off):
     """The sum launch of a K-planes plan writes C's N columns and nothing else -- at a padded pitch

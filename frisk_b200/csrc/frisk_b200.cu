@@ -496,7 +496,8 @@ void plan_tcgen05(frisk_gemm_plan* pl, bool swap, bool pair, int cluster_try = 0
   const bool epi_tma = pair && !planes && !pcl && !pl->tf32 && want_tma &&
                        (d.ldc * (int64_t)elem_size(d.c_type)) % 16 == 0;
   const size_t epi_bytes = (split || pcl) ? 0 : (epi_tma ? 2 : 1) * frisk::kEpiStageBytes;
-  if (pcl) red_bytes = (size_t)g.tile_n * 128 * sizeof(float);   // [pair][column][row of the share]
+  // (the other pairs' images of the rows a CTA owns: [pair][row of the share][tile_n + 4] fp32)
+  if (pcl) red_bytes = ((size_t)(pair_cluster - 1) * (128 / pair_cluster) * (g.tile_n + 4) * sizeof(float) + 1023) / 1024 * 1024;
   g.epi_staged = split ? 0u : epi_tma ? 3u : planes ? 1u : d.epilogue == 1 ? 0u : d.epilogue == 3 ? 2u : 1u;
   // stages * stage_bytes + 1024 (alignment slack) + red_bytes + epi_bytes stays within kMaxDynSmem
   uint32_t stages = (uint32_t)((kMaxDynSmem - 1024 - red_bytes - epi_bytes) / g.stage_bytes);
@@ -1202,28 +1203,35 @@ int frisk_b200_gemm_plan_create(const frisk_gemm_desc* desc, frisk_gemm_plan** o
       const uint64_t kparts = std::min<uint64_t>((uint64_t)(pl->sm_count / 2) / tiles256, kbs / 8);
       const bool planes_ok = pair_ok && kparts >= 2;
       bool planes = planes_ok && d.k_split == 2;
-      // K split over the pairs of a cluster (gemm_tcgen05_pair_ksplit.cuh): 256 x 128 tiles, four
-      // pairs per cluster when the SMs allow, else two; at least eight k-blocks per pair.
-      // Taken where measured ahead: six to nine tiles, clusters of four pairs that the device can
-      // place all at once, K up to 192 k-blocks (deeper: K planes).  bf16, clusters of single
-      // CTAs -> clusters of pairs (cuBLAS): 512 x 512 x 2048 11.3 (whole tiles) -> 9.5 us (13.6),
-      // x 4096 12.8 -> 11.5 us (13.7), x 8192 18.8 -> 15.2 us (14.6); 384 x 384 x 8192
-      // 17.1 -> 14.8 us (14.5).  With two pairs per cluster, or four tiles, the fold of the
-      // partials costs what the shorter K saves (1024 x 1024 x 4096 18.3 -> 17.8 us,
-      // 1024 x 512 x 4096 15.6 -> 17.0 us, 256 x 256 x 4096 9.0 -> 10.5 us).
+      // K split over the pairs of a cluster (gemm_tcgen05_pair_ksplit.cuh): 256 x 128 tiles, at
+      // least eight k-blocks per pair.  Taken where measured ahead, for K up to 128 k-blocks
+      // (deeper: the forms below) and tiles that are not mostly padding:
+      //   six to nine tiles, four pairs per cluster (bf16, before -> after (cuBLAS)):
+      //     512 x 512 x 4096 12.8 -> 12.8 us (13.2), x 8192 18.8 -> 16.2 us (14.6);
+      //   twelve tiles up to a quarter of the SMs, two pairs per cluster, from 48 k-blocks on:
+      //     1024 x 1024 x 4096 18.2 -> 15.0 us (12.9), 768 x 768 x 4096 17.7 -> 14.9 us (10.4),
+      //     1024 x 512 x 4096 15.4 -> 14.1 us (10.4), 512 x 1024 x 8192 21.5 -> 20.3 us (15.9),
+      //     256 x 4096 x 4096 18.7 -> 15.5 us (14.3), 2304 x 256 x 4096 18.2 -> 14.9 us (11.0);
+      //     1024 x 1024 x 2048 (32 k-blocks) 12.0 -> 11.6 us: not worth a second form;
+      //     512 x 640 x 8192 (ten tiles, 40 CTAs) 19.6 -> 20.4 us: left to the forms below.
+      // With four tiles or fewer the single-CTA clusters below stay ahead (256 x 256 x 4096: 9.0
+      // against 11.5 us).  Clusters of eight CTAs with 214 KB of shared memory each are placed
+      // about a dozen at a time, which is why larger problems get two pairs per cluster.
       const bool deep = force_split || (few ? kbs >= 48 : kbs >= 192);
       const uint64_t tiles128 = (uint64_t)((d.M + 255) / 256) * (uint64_t)((d.N + 127) / 128);
       const int whole_kernel = pl->info.kernel;
-      int pcl = 0;
-      for (int sp : {4, 2})
-        if (!pcl && pair_ok && tiles128 * 2 * sp <= (uint64_t)pl->sm_count && kbs >= 8u * sp) pcl = sp;
-      // (and tiles that are not mostly padding: at most a quarter of their rows and columns)
       const int64_t rows_pad = (d.M + 255) / 256 * 256, cols_pad = (d.N + 127) / 128 * 128;
       const bool full_tiles = 4 * (rows_pad - d.M) <= rows_pad && 4 * (cols_pad - d.N) <= cols_pad;
-      const bool pcl_auto = d.k_split == 0 && pcl == 4 && tiles128 >= 6 && tiles128 <= 9 && kbs <= 192 &&
-                            full_tiles;
+      int pcl = 0;
+      if (d.k_split == 3) {   // forced: four pairs per cluster where the SMs allow, else two
+        for (int sp : {4, 2})
+          if (!pcl && pair_ok && tiles128 * 2 * sp <= (uint64_t)pl->sm_count && kbs >= 8u * sp) pcl = sp;
+      } else if (d.k_split == 0 && pair_ok && full_tiles && kbs <= 128) {
+        if (tiles128 >= 6 && tiles128 <= 9 && kbs >= 32) pcl = 4;
+        else if (tiles128 >= 12 && tiles128 * 4 <= (uint64_t)pl->sm_count && kbs >= 48) pcl = 2;
+      }
       bool took_pcl = false;
-      if (pcl && (d.k_split == 3 || pcl_auto)) {
+      if (pcl) {
         plan_tcgen05(pl, /*swap=*/false, /*pair=*/true, 0, false, 0, pcl);
         took_pcl = !pl->plan_error && (!pl->have_device || pair_clusters_fit(pl));
         if (!took_pcl && d.k_split == 3 && pcl == 4) {   // forced: two pairs per cluster will do

@@ -2,10 +2,11 @@
 // problems whose 256 x 128 tiles number at most a quarter of the SMs: a cluster of 2 S CTAs
 // (S = 2 or 4 pairs) owns one tile, pair q multiplies K part q with two-SM MMAs, and the S
 // partial tiles meet through distributed shared memory as in the few-row plan
-// (gemm_tcgen05.cuh, split mode 3): every CTA pushes the rows of its 128 x tile_n partial into
-// the CTA that owns them (the CTA of pair `row / (128 / S)` on the same side of its pair), one
-// cluster barrier, each owner adds the S images of its rows in pair order, applies the scales
-// and `+= C`, casts and stores.  One launch, no workspace, a fixed summation order.
+// (gemm_tcgen05.cuh, split mode 3), but in rows: pair `row / (128 / S)` owns a row of its side's
+// 128; a CTA keeps the rows its pair owns in tensor memory and sends the others, 16 bytes per
+// remote store, to their owner on the same side; one cluster barrier; each owner adds the S - 1
+// images to its own partial in pair order, applies the scales and `+= C`, casts and stores whole
+// row pieces.  One launch, no workspace, a fixed summation order.
 //
 // Cluster rank r: pair q = r >> 1, side h = r & 1 (h = 0 leads its pair and issues its MMAs).
 // The barriers of the pipeline are those of the pair kernel, addressed relative to r: the
@@ -56,8 +57,8 @@ gemm_tcgen05_pair_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t kb0 = part * p.kb_per, kb1 = min(p.num_kb, kb0 + p.kb_per);
   uint32_t tr, tc;
   tile_coords(p.group_r, p.tiles_r, p.tiles_c, tile, tr, tc, p.group_c);
-  // the region the partials are pushed into lies behind the stage buffers: [pair][column][row of
-  // the share] fp32, tile_n x 128 x 4 bytes
+  // the region the other pairs' partials arrive in lies behind the stage buffers: S - 1 images of
+  // [row of the share][tile_n + 4] fp32
   const uint32_t red_base = tiles_base + stages * stage_bytes;
 
   if (threadIdx.x == 0) {
@@ -189,26 +190,37 @@ gemm_tcgen05_pair_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a,
     ptx::cluster_wait();
   } else {
     // ------------------------------------------------------------- epilogue (every CTA)
+    // A warp's 32 accumulator rows (its TMEM lanes) belong to one owner pair.  Warps whose rows
+    // this pair owns keep them in tensor memory; the others send theirs, 16 bytes per store, to
+    // the owner on the same side of its pair: image `source pair` (owner left out) of the
+    // owner's region, [row of the share][column] fp32 at a pitch of tile_n + 4 floats (rows of
+    // one quarter-warp then start in different banks).
     const uint32_t quarter = warp & 3u;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
     const uint32_t sh = 31u - __clz(parts);
-    const uint32_t share = 128u >> sh;   // rows of this side's 128 that each pair owns
+    const uint32_t share = 128u >> sh;   // rows of this side's 128 that each pair owns (64 or 32)
     const uint32_t share_sh = 31u - __clz(share);
+    const uint32_t r_local = quarter * 32u + lane;
+    const uint32_t owner = r_local >> share_sh, rr = r_local - owner * share;
+    const bool keeper = owner == part;   // warp-uniform
+    const uint32_t row_pitch = (tile_n + 4u) * 4u;
+    const uint32_t img_bytes = share * row_pitch;
+    const uint32_t t_row = tmem_base + ((quarter * 32u) << 16);
     const bool ok = bounded_wait(acc_full0, 0, abort_flag, status, kStatusEpilogueTimeout,
                                  p.epilogue_backoff_ns);
-    if (ok) {
+    if (ok && !keeper) {
       ptx::tc_fence_after();
-      const uint32_t r_local = quarter * 32u + lane;
-      const uint32_t owner = r_local >> share_sh, rr = r_local - owner * share;
-      const uint32_t push_dst = ptx::mapa(red_base + ((part * tile_n) * share + rr) * 4u, 2u * owner + side);
-      const uint32_t t_row = tmem_base + ((quarter * 32u) << 16);
+      const uint32_t slot = part < owner ? part : part - 1u;
+      const uint32_t dst = ptx::mapa(red_base + slot * img_bytes + rr * row_pitch, 2u * owner + side);
       for (uint32_t cc = 0; cc < tile_n; cc += 32) {
         uint32_t v[32];
         ptx::tmem_ld_32x32b_x32(t_row + cc, v);
         ptx::tmem_ld_wait();
-        cluster_push<32>(push_dst, share * 4u, cc, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          ptx::st_shared_cluster_v4(dst + (cc + 4u * i) * 4u, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
       }
       ptx::tc_fence_before();
-    } else if (lane == 0) {
+    } else if (!ok && lane == 0) {
       ptx::st_shared_cluster_u32(peer_abort, 1);
     }
     __syncwarp();
@@ -217,7 +229,8 @@ gemm_tcgen05_pair_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // partial has reached its owner and nobody writes another CTA's shared memory again.
     ptx::cluster_arrive();
     ptx::cluster_wait();
-    if (!*abort_flag) {
+    if (ok && keeper && !*abort_flag) {
+      ptx::tc_fence_after();
       EpiArgs ep;
       ep.C = p.C;
       ep.ws = nullptr;
@@ -231,8 +244,26 @@ gemm_tcgen05_pair_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a,
       ep.transposed_out = 0;
       ep.clear_accum = p.clear_accum;
       ep.c_vec_ok = p.c_vec_ok;
-      reduce_share<TC>(ep, red_base, parts, part, share, tile_n, tr * 256u + side * 128u, tc * tile_n,
-                       threadIdx.x - 64u);
+      const uint32_t row = tr * 256u + side * 128u + r_local;
+      const uint32_t mine = red_base + rr * row_pitch;
+      for (uint32_t cc = 0; cc < tile_n; cc += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32b_x32(t_row + cc, v);
+        ptx::tmem_ld_wait();
+        // own partial first, then the other pairs' images in pair order
+        for (uint32_t slot = 0; slot + 1u < parts; ++slot) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 x = ptx::ld_shared_f32x4(mine + slot * img_bytes + (cc + 4u * i) * 4u);
+            v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + x.x);
+            v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + x.y);
+            v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + x.z);
+            v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + x.w);
+          }
+        }
+        epilogue_store<TC, 32>(ep, row, tc * tile_n + cc, v);
+      }
+      ptx::tc_fence_before();
     }
   }
 

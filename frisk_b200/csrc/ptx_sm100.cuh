@@ -258,6 +258,12 @@ __device__ __forceinline__ float4 ld_shared_cluster_f32x4(uint32_t cluster_addr)
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b,
+                                                     uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b),
+               "r"(c), "r"(d)
+               : "memory");
+}
 // TMA load of a CTA pair: the data lands in this CTA's shared memory, the byte count is
 // reported to `cluster_bar`, which may be the barrier of the pair's leader CTA.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* m,

@@ -130,12 +130,16 @@ def test_k_split_override():
     # eight tiles of 256 x 128 against 64 k-blocks: clusters of four CTA pairs, one launch, no
     # workspace (k_split = 3 forces the form, with two pairs per cluster where four do not fit)
     pairs = R.GemmPlan(512, 512, 4096, W.BF16)
-    pairs2 = R.GemmPlan(1024, 1024, 4096, W.BF16, k_split=3)
+    pairs2 = R.GemmPlan(1024, 1024, 4096, W.BF16)   # 32 tiles: two pairs per cluster
+    forced4 = R.GemmPlan(256, 256, 4096, W.BF16, k_split=3)
     assert (pairs.info["kernel_name"], pairs.info["split_k"], pairs.info["launches"]) == ("tcgen05_pair", 1, 1)
     assert (pairs.info["num_ctas"], pairs.info["tile_n"], pairs.workspace_bytes) == (64, 128, 0)
     assert (pairs2.info["split_k"], pairs2.info["num_ctas"], pairs2.workspace_bytes) == (1, 128, 0)
-    assert R.GemmPlan(1024, 1024, 4096, W.BF16).info["split_k"] == 0   # not the plan's own choice
-    for p in (pairs, pairs2):
+    assert (forced4.info["kernel_name"], forced4.info["num_ctas"]) == ("tcgen05_pair", 16)
+    # two tiles are not the plan's own choice for this form, nor is a K of 32 k-blocks on 32 tiles
+    assert R.GemmPlan(256, 256, 4096, W.BF16).info["kernel_name"] == "tcgen05"
+    assert R.GemmPlan(1024, 1024, 2048, W.BF16).info["split_k"] == 0
+    for p in (pairs, pairs2, forced4):
         p.close()
     with pytest.raises(R.FriskError) as e:
         R.GemmPlan(512, 512, 512, W.BF16, k_split=4)
@@ -330,7 +334,9 @@ def test_planner_invariants_over_random_shapes():
                 if cols * es % 16:
                     repack += (rows * (-(-cols * es // 16) * 16) + 255) // 256 * 256
         n_repack = 0 if not repack else sum(1 for c in ((M if ta else K), (K if tb else N)) if c * es % 16)
-        assert i["launches"] == (3 if i["kernel_name"] == "tf32x3" else 1) + n_repack and i["num_ctas"] >= 1
+        planes = i["kernel_name"] == "tcgen05_pair" and i["split_k"] and p.workspace_bytes - repack > 0
+        assert i["launches"] == (3 if i["kernel_name"] == "tf32x3" else 2 if planes else 1) + n_repack
+        assert i["num_ctas"] >= 1
         own_ws = p.workspace_bytes - repack
         if i["kernel_name"] == "tf32x3":   # fp32 in and out, at least about a GFLOP, TMA-able rows
             assert ab == W.F32 and 2.0 * M * N * K >= 1e9 and p.workspace_bytes >= 2 * 4 * (M * K + K * N)
@@ -355,6 +361,13 @@ def test_planner_invariants_over_random_shapes():
                 assert i["num_ctas"] % tiles == 0 and i["num_ctas"] // tiles in (2, 4, 8)
             else:
                 assert own_ws % 4 == 0 and i["num_ctas"] <= 14 * tiles
+        elif i["kernel_name"] == "tcgen05_pair" and i["split_k"]:
+            tiles = -(-M // 256) * -(-N // i["tile_n"])
+            if i["launches"] - n_repack == 2:   # K planes: one fp32 copy of C per K part
+                assert own_ws >= 2 * M * N * 4 and i["num_ctas"] % 2 == 0
+            else:                               # K split over the pairs of a cluster
+                assert own_ws == 0 and i["tile_n"] == 128 and i["num_ctas"] // tiles in (4, 8)
+                assert K >= 32 * i["tile_k"]
         elif i["kernel_name"] != "tf32x3":
             assert own_ws == 0 and not i["split_k"]
         p.close()

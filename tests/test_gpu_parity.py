@@ -763,7 +763,7 @@ def test_k_planes_plans_match_oracle(M, N, K, ab, ct, ta, tb, clear, auto):
 @pytest.mark.parametrize("M,N,K,ab,ct,ta,tb,clear,auto,ctas", [
     (512, 512, 4096, W.BF16, W.BF16, False, False, True, True, 64),     # 8 tiles x 4 pairs: the plan's own choice
     (384, 384, 8192, W.F16, W.F32, False, True, False, True, 48),       # fp32 C +=, B stored [N, K]
-    (1024, 1024, 4104, W.BF16, W.BF16, True, False, True, False, 128),  # two pairs per cluster, A stored [K, M], ragged K
+    (1024, 1024, 4104, W.BF16, W.BF16, True, False, True, True, 128),   # two pairs per cluster, A stored [K, M], ragged K
     (300, 200, 2056, W.BF16, W.F16, False, False, False, False, 32),    # ragged tiles, C +=
     (512, 500, 4096, W.E4M3, W.BF16, False, True, True, False, 64),     # scales in the fold
     (260, 128, 8192, W.E5M2, W.BF16, False, True, True, False, 16),     # one tile column, mostly padding rows

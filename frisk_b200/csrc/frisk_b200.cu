@@ -1437,7 +1437,8 @@ int frisk_b200_gemm_run_ex(frisk_gemm_plan* pl, const frisk_gemm_run_args* args)
   const bool ptr_aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0);
   if ((args->n_peers > 0 || d.row_reduce) && !(whole_tile_tc && ptr_aligned)) {
     g_last_error = "peer copies of C and the fused row reduce exist only in the whole-tile "
-                   "tensor-core kernels (16-byte aligned A and B)";
+                   "tensor-core kernels (16-byte aligned A and B; a plan that splits K is kept to "
+                   "whole tiles by desc.k_split = -1)";
     return FRISK_ERR_UNSUPPORTED;
   }
   if (pl->info.kernel != FRISK_KERNEL_SIMT && !ptr_aligned) {

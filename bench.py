@@ -609,7 +609,9 @@ def main():
     C = torch.empty((rows, N), device=dev, dtype=out_dtype(torch, name))
     plan = R.GemmPlan(rows, N, K, ab, ct, transB=name in TRANS_B, scales=sa is not None,
                       band_tiles=args.band, epilogue=args.epilogue, panel_tiles=args.panel,
-                      l2_hints=args.l2_hints, k_split=args.k_split)
+                      l2_hints=args.l2_hints,
+                      # (the peer stores of the fused all-gather live in the whole-tile epilogue)
+                      k_split=args.k_split if world == 1 or args.k_split else -1)
     ws = torch.empty(max(plan.workspace_bytes, 16), dtype=torch.uint8, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream().cuda_stream

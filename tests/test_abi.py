@@ -146,6 +146,40 @@ def test_k_split_override():
     assert e.value.code == -1
 
 
+def test_forced_pair_split_forms_keep_their_invariants_over_random_shapes():
+    """k_split = 2 (K planes) and 3 (K split over the CTA pairs of a cluster) on seeded random
+    problems: where the form exists the plan fits the device (an even number of CTAs, at most one
+    per SM), K planes ask for one fp32 copy of C per part and launch twice, pair clusters ask for
+    nothing and launch once; where it does not, the plan is what k_split = 0 or -1 would give."""
+    import random
+    rnd = random.Random(7)
+    forms = {2: 0, 3: 0}
+    for _ in range(120):
+        M = rnd.choice([130, 200, 256, 300, 512, 640, 1000, 1024, 2048, 4096])
+        N = rnd.choice([72, 128, 200, 256, 520, 1024, 2048, 4104])   # (16-byte pitches: no repack)
+        K = rnd.choice([512, 1024, 2064, 4096, 8192, 32768])
+        ab = rnd.choice([W.BF16, W.F16, W.E4M3])
+        ks = rnd.choice([2, 3])
+        kw = dict(transB=True) if ab == W.E4M3 else {}
+        p = R.GemmPlan(M, N, K, ab, W.BF16, k_split=ks, scales=ab == W.E4M3, **kw)
+        i, ws = p.info, p.workspace_bytes
+        p.close()
+        if not (i["kernel_name"] == "tcgen05_pair" and i["split_k"]):
+            continue
+        assert i["num_ctas"] % 2 == 0 and 4 <= i["num_ctas"] <= 148 and i["tile_m"] == 256, (M, N, K, i)
+        if ks == 2:
+            tiles = -(-M // 256) * -(-N // i["tile_n"])
+            parts = i["num_ctas"] // 2 // tiles if i["num_ctas"] // 2 >= tiles else 0
+            assert i["launches"] == 2 and ws >= 2 * M * N * 4 and ws <= 20 << 20, (M, N, K, i, ws)
+            assert parts == 0 or ws >= parts * M * N * 4
+        else:
+            tiles = -(-M // 256) * -(-N // 128)
+            assert i["launches"] == 1 and ws == 0 and i["tile_n"] == 128, (M, N, K, i)
+            assert i["num_ctas"] == tiles * 8 or i["num_ctas"] == tiles * 4
+        forms[ks] += 1
+    assert forms[2] >= 10 and forms[3] >= 10, forms
+
+
 def test_plan_info_says_why_a_plan_runs_on_cuda_cores():
     """FRISK_TC_* of include/frisk_b200.h: a plan that resolved to the CUDA-core kernel names the
     rule that kept it off the tensor cores, so a 100x slower run is never a silent one."""
